@@ -1,0 +1,175 @@
+/* sphmap.h -- C ABI of the B200 (sm_100a) mapped-operator library, libsphmap.so.
+ *
+ * These entry points are what the host side of the Spherical-Package extension
+ * modules (package `_spherical_distortion_ext`) binds for the mapped-operator
+ * path: mapped convolution / transposed convolution forward and backward,
+ * mapped max pooling with its argmax backward, and resample_from_map /
+ * resample_to_map.  Every pointer is a DEVICE pointer unless said otherwise;
+ * tensors are dense, row major ("contiguous NCHW"), float32 or float64.
+ * Nothing here allocates, synchronises or throws: every function enqueues its
+ * kernels on `stream` (a cudaStream_t passed as void*) and returns a status
+ * (0 = SPH_OK).  Scratch memory is supplied by the caller; the sizes come
+ * from the *_bytes queries.
+ *
+ * Conventions shared by all entry points
+ *   map     sample map, (OH,OW,K,2) or, with interpolation weights,
+ *           (OH,OW,K,P,2); last axis is (x, y) in pixel units of the sampled
+ *           image; same dtype as the data.
+ *   iw      interpolation weights (OH,OW,K,P), or NULL with P = 0.
+ *   interp  0 nearest, 1 bilinear (zero outside), 2 bispherical (x wraps).
+ *   dtype   0 float32, 1 float64.
+ *   precision  0: arithmetic in the tensor's own type (SIMT path, the one
+ *           compared bit-for-bit / to 1e-5 with the reference CPU code);
+ *           1: bf16 operands with fp32 accumulation on the tcgen05 tensor
+ *           cores (float32 tensors only).
+ *
+ * Reference interfaces are cited as file:line inside the reference project.
+ */
+#ifndef SPHMAP_H_
+#define SPHMAP_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum sph_status {
+  SPH_OK = 0,
+  SPH_ERR_INVALID_ARGUMENT = 1,
+  SPH_ERR_UNSUPPORTED = 2,
+  SPH_ERR_WORKSPACE_TOO_SMALL = 3,
+  SPH_ERR_CUDA = 4,
+  SPH_ERR_TOO_LARGE = 5
+};
+enum sph_dtype { SPH_F32 = 0, SPH_F64 = 1 };
+enum sph_interp { SPH_NEAREST = 0, SPH_BILINEAR = 1, SPH_BISPHERICAL = 2 };
+enum sph_precision { SPH_PRECISION_EXACT = 0, SPH_PRECISION_BF16 = 1 };
+
+/* Human-readable text for a status code (host pointer, static storage). */
+const char *sph_status_string(int status);
+/* Library version, major*10000 + minor*100 + patch. */
+int sph_version(void);
+
+/* ------------------------------------------------------------------------
+ * resample_from_map ("Unresample"): y[b,c,i] = interp(x[b,c], map[i]).
+ * Replaces spherical::ResampleFromMap, ext_modules/include/layers/
+ * resample_layer.h:70-88 (weighted twin: weighted_resample_layer.h:80-103).
+ * x (B,C,H,W); map (MH,MW[,P],2); iw (MH,MW,P) or NULL; y (B,C,MH,MW).
+ * ---------------------------------------------------------------------- */
+int sph_resample_from_map(const void *x, const void *map, const void *iw, void *y, int64_t B, int64_t C,
+                          int64_t H, int64_t W, int64_t MH, int64_t MW, int64_t P, int dtype, int interp,
+                          void *stream);
+
+/* ------------------------------------------------------------------------
+ * Scatter plan.  Every adjoint ("scatter") operator of the reference adds
+ * through float atomics.  This library instead inverts the sample map once
+ * into a CSR table keyed by (destination pixel, kernel slot) and every
+ * scatter becomes a gather that sums its segment in a fixed order, so the
+ * results are deterministic.  A plan depends only on the map, the weights,
+ * the interpolation type and the destination size; build it once per map.
+ *
+ *   n_src   number of map positions (MH*MW, or OH*OW for convolution maps)
+ *   K       kernel slots per position (1 for resample maps)
+ *   dstH/W  size of the image the map points into
+ * The plan blob is opaque; sph_plan_bytes() gives its size (a host function,
+ * no device work).  No counterpart in the reference (its scatter kernels are
+ * ext_modules/include/cuda/resample.cuh:14-47, mapped_im2col.cuh:52-91).
+ * ---------------------------------------------------------------------- */
+size_t sph_plan_bytes(int64_t n_src, int64_t K, int64_t P, int interp, int64_t dstH, int64_t dstW, int dtype);
+int sph_plan_build(const void *map, const void *iw, int64_t n_src, int64_t K, int64_t P, int interp,
+                   int64_t dstH, int64_t dstW, int dtype, void *plan, size_t plan_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
+ * resample_to_map ("Resample"): out[b,c] = sum_i scatter(x[b,c,i], map[i]).
+ * Replaces spherical::ResampleToMap, resample_layer.h:45-68 (weighted twin:
+ * weighted_resample_layer.h:54-78).  `plan` was built from the (MH,MW[,P],2)
+ * map with K = 1 and dst = (OH,OW).  x (B,C,MH,MW); out (B,C,OH,OW), fully
+ * written (no pre-zeroing needed).
+ * ---------------------------------------------------------------------- */
+int sph_resample_to_map(const void *x, const void *plan, void *out, int64_t B, int64_t C, int64_t MH,
+                        int64_t MW, int64_t OH, int64_t OW, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Mapped max pooling.  out[b,c,o] = max_k interp(x[b,c], map[o,k]); idx is
+ * the int64 offset of the winning entry's x coordinate in the flattened map
+ * (first strict maximum; running maximum starts at -FLT_MAX as in the
+ * reference's CUDA build).  Replaces spherical::MappedMaxPoolForward /
+ * MappedMaxPoolBackward, ext_modules/include/layers/
+ * mapped_max_pooling_layer.h:42-97 (weighted: weighted_mapped_max_pooling_
+ * layer.h).  x (B,C,IH,IW); out, idx, g (B,C,OH,OW); grad_in (B,C,IH,IW),
+ * fully written by the unpool call.
+ * ---------------------------------------------------------------------- */
+int sph_mapped_max_pool(const void *x, const void *map, const void *iw, void *out, int64_t *idx, int64_t B,
+                        int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
+                        int dtype, int interp, void *stream);
+int sph_mapped_max_unpool(const void *g, const int64_t *idx, const void *map, const void *iw, void *grad_in,
+                          int64_t B, int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
+                          int64_t P, int dtype, int interp, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Mapped convolution.  weight (Cout,Cin,K), bias (Cout), x (B,Cin,IH,IW),
+ * out / gout (B,Cout,OH,OW), map (OH,OW,K[,P],2).
+ *   forward          out = W * im2col(x) + bias     (no column buffer)
+ *   backward_input   gx  = col2im(W^T * gout), through a plan built from the
+ *                    map with n_src = OH*OW, K, dst = (IH,IW)
+ *   backward_weight  gw  = sum_b gout[b] * im2col(x[b])^T, gb = sum gout
+ * Replaces spherical::MappedConvForward / MappedConvBackward,
+ * ext_modules/include/layers/mapped_convolution_layer.h:62-134 (weighted:
+ * weighted_mapped_convolution_layer.h:69-162).
+ * ws/ws_bytes: scratch of at least sph_conv_workspace_bytes(op, ...) bytes.
+ * ---------------------------------------------------------------------- */
+enum sph_conv_op {
+  SPH_CONV_FORWARD = 0,
+  SPH_CONV_BACKWARD_INPUT = 1,
+  SPH_CONV_BACKWARD_WEIGHT = 2,
+  SPH_TCONV_FORWARD = 3,
+  SPH_TCONV_BACKWARD_INPUT = 4,
+  SPH_TCONV_BACKWARD_WEIGHT = 5
+};
+size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                                int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                int precision);
+int sph_mapped_conv_forward(const void *x, const void *map, const void *iw, const void *weight,
+                            const void *bias, void *out, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                            int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                            int precision, void *ws, size_t ws_bytes, void *stream);
+int sph_mapped_conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx,
+                                   int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
+                                   int64_t OW, int64_t K, int dtype, int precision, void *ws, size_t ws_bytes,
+                                   void *stream);
+int sph_mapped_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw,
+                                    void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                                    int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
+                                    int interp, int precision, void *ws, size_t ws_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Mapped transposed convolution.  weight (Cin,Cout,K), bias (Cout),
+ * x (B,Cin,IH,IW), out / gout (B,Cout,OH,OW); the map has the INPUT's size,
+ * (IH,IW,K[,P],2), and points into the (OH,OW) output grid.
+ *   forward          out = col2im(W^T * x) + bias, through a plan built from
+ *                    the map with n_src = IH*IW, K, dst = (OH,OW)
+ *   backward_input   gx  = W * im2col(gout)
+ *   backward_weight  gw  = sum_b x[b] * im2col(gout[b])^T, gb = sum gout
+ * Replaces spherical::MappedTransposedConvForward / ...Backward,
+ * ext_modules/include/layers/mapped_transposed_convolution_layer.h:62-149
+ * (weighted: weighted_mapped_transposed_convolution_layer.h).
+ * ---------------------------------------------------------------------- */
+int sph_mapped_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out,
+                             int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
+                             int64_t OW, int64_t K, int dtype, int precision, void *ws, size_t ws_bytes,
+                             void *stream);
+int sph_mapped_tconv_backward_input(const void *gout, const void *map, const void *iw, const void *weight,
+                                    void *gx, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                                    int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                    int precision, void *ws, size_t ws_bytes, void *stream);
+int sph_mapped_tconv_backward_weight(const void *gout, const void *x, const void *map, const void *iw,
+                                     void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                                     int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
+                                     int interp, int precision, void *ws, size_t ws_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPHMAP_H_ */

@@ -1,0 +1,162 @@
+// C entry points of the mapped (transposed) convolution family: argument
+// checks and dispatch to the exact SIMT kernels or the bf16 tensor-core path.
+#include "common.cuh"
+#include "conv_internal.h"
+
+using namespace sph;
+
+namespace {
+
+struct Dims {
+  int64_t B, Cin, Cout, IH, IW, OH, OW, K, P;
+};
+
+int check_dims(const Dims &d, int dtype, int interp, int precision) {
+  if (d.B < 0 || d.Cin <= 0 || d.Cout <= 0 || d.IH <= 0 || d.IW <= 0 || d.OH <= 0 || d.OW <= 0 || d.K <= 0 || d.P < 0)
+    return SPH_ERR_INVALID_ARGUMENT;
+  if (interp < 0 || interp > 2) return SPH_ERR_INVALID_ARGUMENT;
+  if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
+  if (precision != SPH_PRECISION_EXACT && precision != SPH_PRECISION_BF16) return SPH_ERR_INVALID_ARGUMENT;
+  if (precision == SPH_PRECISION_BF16 && dtype != SPH_F32) return SPH_ERR_UNSUPPORTED;
+  const int64_t lim = (int64_t)1 << 31, PP = d.P > 0 ? d.P : 1;
+  if (d.IH * d.IW >= lim || d.OH * d.OW >= lim || d.B >= 65535) return SPH_ERR_TOO_LARGE;
+  if (d.IH * d.IW * d.K * PP * 4 >= lim || d.OH * d.OW * d.K * PP * 4 >= lim) return SPH_ERR_TOO_LARGE;
+  if (d.Cin * d.K >= lim || d.Cout * d.K >= lim || d.Cin * d.Cout * d.K >= lim) return SPH_ERR_TOO_LARGE;
+  return SPH_OK;
+}
+
+}  // namespace
+
+extern "C" const char *sph_status_string(int status) {
+  switch (status) {
+    case SPH_OK: return "ok";
+    case SPH_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, negative size or unknown enum value)";
+    case SPH_ERR_UNSUPPORTED: return "unsupported dtype / precision combination";
+    case SPH_ERR_WORKSPACE_TOO_SMALL: return "workspace or plan buffer too small";
+    case SPH_ERR_CUDA: return "CUDA runtime reported an error at launch";
+    case SPH_ERR_TOO_LARGE: return "tensor too large for 32-bit plane indexing";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int sph_version(void) { return 100; }
+
+extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                                           int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                           int precision) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
+  if (check_dims(d, dtype, interp, precision) != SPH_OK) return 0;
+  const size_t ts = dtype == SPH_F64 ? 8 : 4;
+  if (precision == SPH_PRECISION_BF16) return tc_workspace_bytes(op, B, Cin, Cout, IH, IW, OH, OW, K, P, interp);
+  switch (op) {
+    case SPH_CONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts);
+    case SPH_TCONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, ts);
+    default: return 0;
+  }
+}
+
+#define SPH_BY_DTYPE(fn, ...) (dtype == SPH_F32 ? fn<float>(__VA_ARGS__) : fn<double>(__VA_ARGS__))
+
+extern "C" int sph_mapped_conv_forward(const void *x, const void *map, const void *iw, const void *weight,
+                                       const void *bias, void *out, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                                       int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                       int precision, void *ws, size_t ws_bytes, void *stream) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
+  const int rc = check_dims(d, dtype, interp, precision);
+  if (rc != SPH_OK) return rc;
+  if (!x || !map || !weight || !bias || !out || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
+  if (B == 0) return SPH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (precision == SPH_PRECISION_BF16)
+    return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
+  return SPH_BY_DTYPE(simt_gemm, false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1,
+                      bias, out, Cout, B, st);
+}
+
+extern "C" int sph_mapped_conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx,
+                                              int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
+                                              int64_t OW, int64_t K, int dtype, int precision, void *ws,
+                                              size_t ws_bytes, void *stream) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, 0};
+  const int rc = check_dims(d, dtype, 0, precision);
+  if (rc != SPH_OK) return rc;
+  if (!gout || !plan || !weight || !gx) return SPH_ERR_INVALID_ARGUMENT;
+  if (B == 0) return SPH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (precision == SPH_PRECISION_BF16)
+    return tc_conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st);
+  return SPH_BY_DTYPE(simt_gemm, true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH * IW, 0, weight, K, Cin * K, 1,
+                      nullptr, gx, Cin, B, st);
+}
+
+extern "C" int sph_mapped_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw,
+                                               void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                                               int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
+                                               int interp, int precision, void *ws, size_t ws_bytes, void *stream) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
+  const int rc = check_dims(d, dtype, interp, precision);
+  if (rc != SPH_OK) return rc;
+  if (!gout || !x || !map || !gw || !gb || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t ts = dtype == SPH_F64 ? 8 : 4;
+  if (B == 0) {
+    if (cudaMemsetAsync(gw, 0, ts * (size_t)(Cout * Cin * K), st) != cudaSuccess) return SPH_ERR_CUDA;
+    return cudaMemsetAsync(gb, 0, ts * (size_t)Cout, st) == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
+  }
+  if (precision == SPH_PRECISION_BF16)
+    return tc_conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
+  return SPH_BY_DTYPE(simt_dw, gout, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout,
+                      OH * OW, gb, ws, ws_bytes, st);
+}
+
+extern "C" int sph_mapped_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias,
+                                        void *out, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                                        int64_t OH, int64_t OW, int64_t K, int dtype, int precision, void *ws,
+                                        size_t ws_bytes, void *stream) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, 0};
+  const int rc = check_dims(d, dtype, 0, precision);
+  if (rc != SPH_OK) return rc;
+  if (!x || !plan || !weight || !bias || !out) return SPH_ERR_INVALID_ARGUMENT;
+  if (B == 0) return SPH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (precision == SPH_PRECISION_BF16)
+    return tc_tconv_forward(x, plan, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st);
+  return SPH_BY_DTYPE(simt_gemm, true, x, nullptr, nullptr, plan, Cin, IH, IW, K, 0, OH * OW, 0, weight, K, Cout * K, 1,
+                      bias, out, Cout, B, st);
+}
+
+extern "C" int sph_mapped_tconv_backward_input(const void *gout, const void *map, const void *iw, const void *weight,
+                                               void *gx, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                                               int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                               int precision, void *ws, size_t ws_bytes, void *stream) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
+  const int rc = check_dims(d, dtype, interp, precision);
+  if (rc != SPH_OK) return rc;
+  if (!gout || !map || !weight || !gx || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
+  if (B == 0) return SPH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (precision == SPH_PRECISION_BF16)
+    return tc_tconv_backward_input(gout, map, iw, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
+  return SPH_BY_DTYPE(simt_gemm, false, gout, map, iw, nullptr, Cout, OH, OW, K, P, IH * IW, interp, weight, Cout * K, K, 1,
+                      nullptr, gx, Cin, B, st);
+}
+
+extern "C" int sph_mapped_tconv_backward_weight(const void *gout, const void *x, const void *map, const void *iw,
+                                                void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                                                int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
+                                                int interp, int precision, void *ws, size_t ws_bytes, void *stream) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
+  const int rc = check_dims(d, dtype, interp, precision);
+  if (rc != SPH_OK) return rc;
+  if (!gout || !x || !map || !gw || !gb || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t ts = dtype == SPH_F64 ? 8 : 4;
+  if (B == 0) {
+    if (cudaMemsetAsync(gw, 0, ts * (size_t)(Cout * Cin * K), st) != cudaSuccess) return SPH_ERR_CUDA;
+    return cudaMemsetAsync(gb, 0, ts * (size_t)Cout, st) == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
+  }
+  if (precision == SPH_PRECISION_BF16)
+    return tc_tconv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
+  return SPH_BY_DTYPE(simt_dw, x, gout, map, iw, Cout, OH, OW, K, P, IH * IW, interp, Cin, B, gw, Cout * K, K, 1, gout, Cout,
+                      OH * OW, gb, ws, ws_bytes, st);
+}

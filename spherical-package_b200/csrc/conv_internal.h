@@ -1,0 +1,43 @@
+// Internal (non-exported) interfaces between conv.cu, conv_simt.cu and conv_tc.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sph {
+
+// ---- exact SIMT kernels (conv_simt.cu) -----------------------------------
+template <typename T>
+int simt_gemm(bool use_plan, const void *src, const void *map, const void *iw, const void *plan, int64_t CH, int64_t SH,
+              int64_t SW, int64_t K, int64_t P, int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc,
+              int64_t sk, const void *bias, void *out, int64_t M, int64_t B, cudaStream_t st);
+template <typename T>
+int simt_dw(const void *A, const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K,
+            int64_t P, int64_t npix, int interp, int64_t M, int64_t B, void *gw, int64_t sm, int64_t sc, int64_t sk,
+            const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st);
+size_t simt_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts);
+
+// ---- bf16 tcgen05 path (conv_tc.cu); float32 tensors only ----------------
+size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
+                          int64_t K, int64_t P, int interp);
+int tc_conv_forward(const void *x, const void *map, const void *iw, const void *weight, const void *bias, void *out,
+                    int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
+                    int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st);
+int tc_conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx, int64_t B, int64_t Cin,
+                           int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
+                           size_t ws_bytes, cudaStream_t st);
+int tc_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb,
+                            int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
+                            int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st);
+int tc_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out, int64_t B,
+                     int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
+                     size_t ws_bytes, cudaStream_t st);
+int tc_tconv_backward_input(const void *gout, const void *map, const void *iw, const void *weight, void *gx, int64_t B,
+                            int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
+                            int interp, void *ws, size_t ws_bytes, cudaStream_t st);
+int tc_tconv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb,
+                             int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
+                             int64_t K, int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st);
+
+}  // namespace sph

@@ -1,0 +1,290 @@
+// Exact-arithmetic (float32 / float64, SIMT) mapped convolution family.
+//
+// Every operator of the family is one of two fused kernels, neither of which
+// materialises the column buffer the reference builds per image
+// (src/cpp/mapped_convolution_layer.cpp:24-45):
+//
+//   conv_gemm_kernel   Out[b,m,pix] = sum_{ch,k} Wgt[m,ch,k] * Col[b,ch,k,pix] (+ bias[m])
+//   conv_dw_kernel     dW[m,ch,k]   = sum_{b,pix} A[b,m,pix] * Col[b,ch,k,pix]
+//
+// where Col is produced on the fly, either straight from the sample map
+// (mapped_im2col, common/mapped_im2col.h:11-41, 80-116) or, for the adjoint
+// direction (mapped_col2im, :44-77, 119-158), from a scatter plan:
+//
+//   forward            Col = im2col(x),      Wgt = W  (Cout,Cin,K)      m = co, ch = c
+//   backward_input     Col = plan(gout),     Wgt = W  read transposed   m = c,  ch = co
+//   tconv forward      Col = plan(x),        Wgt = Wt (Cin,Cout,K) tr.  m = co, ch = ci
+//   tconv backward_in  Col = im2col(gout),   Wgt = Wt                   m = ci, ch = co
+//   (t)conv backward_weight: A = gout (conv) or x (tconv), Col = im2col(x) or im2col(gout)
+#include "common.cuh"
+#include "conv_internal.h"
+
+namespace sph {
+
+constexpr int COL_PLAN = 3;  // column source: scatter plan (modes 0..2 are the interpolation types)
+
+template <typename T> struct ColSrc {
+  const T *src;      // (B, CH, SH*SW) tensor the columns are gathered from
+  const T *map;      // direct modes
+  const T *iw;
+  const void *plan;  // plan mode
+  int CH, SH, SW, K, P, npix;
+};
+
+template <typename T, int MODE, bool WEIGHTED>
+__device__ __forceinline__ T col_value(const ColSrc<T> &s, const PlanView<T> &pv, const T *__restrict__ plane, int k,
+                                       int pix) {
+  if (MODE == COL_PLAN) {
+    const int key = pix * s.K + k;
+    const int e0 = __ldg(pv.offsets + key), e1 = __ldg(pv.offsets + key + 1);
+    T acc = T(0);
+    for (int e = e0; e < e1; e++) acc += __ldg(pv.w + e) * __ldg(plane + __ldg(pv.src + e));
+    return acc;
+  } else {
+    const int PP = WEIGHTED ? s.P : 1;
+    const size_t e = ((size_t)pix * s.K + k) * PP;
+    return gather_slot<T, MODE == COL_PLAN ? 0 : MODE, WEIGHTED>(plane, s.map + 2 * e, s.iw + e, s.P, s.SH, s.SW);
+  }
+}
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+template <typename T, int MODE, bool WEIGHTED>
+__global__ void __launch_bounds__(256)
+conv_gemm_kernel(ColSrc<T> cs, const T *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk,
+                 const T *__restrict__ bias, T *__restrict__ out, int M) {
+  __shared__ T Ws[TK][TM + 1];
+  __shared__ T Cs[TK][TN];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int b = blockIdx.z, m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  const int CHK = cs.CH * cs.K;
+  const size_t shw = (size_t)cs.SH * cs.SW;
+  PlanView<T> pv{};
+  bool ok = true;
+  if (MODE == COL_PLAN) pv = plan_view<T>(cs.plan, cs.npix * cs.K, ok);
+  T acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = T(0);
+
+  for (int kk0 = 0; kk0 < CHK; kk0 += TK) {
+    for (int e = tid; e < TK * TM; e += 256) {
+      const int kl = e % TK, ml = e / TK, kk = kk0 + kl, m = m0 + ml;
+      Ws[kl][ml] = (kk < CHK && m < M) ? __ldg(wgt + m * sm + (kk / cs.K) * sc + (kk % cs.K) * sk) : T(0);
+    }
+    for (int e = tid; e < TK * TN; e += 256) {
+      const int nl = e % TN, kl = e / TN, kk = kk0 + kl, pix = n0 + nl;
+      T v = T(0);
+      if (ok && kk < CHK && pix < cs.npix)
+        v = col_value<T, MODE, WEIGHTED>(cs, pv, cs.src + ((size_t)b * cs.CH + kk / cs.K) * shw, kk % cs.K, pix);
+      Cs[kl][nl] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kl = 0; kl < TK; kl++) {
+      T a[4], c[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = Ws[kl][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) c[j] = Cs[kl][tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] += a[i] * c[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+    const T bv = bias ? __ldg(bias + m) : T(0);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int pix = n0 + tx + 16 * j;
+      if (pix < cs.npix) out[((size_t)b * M + m) * cs.npix + pix] = acc[i][j] + bv;
+    }
+  }
+}
+
+constexpr int kDwChunk = 256;  // pixels per split-K work unit
+
+template <typename T, int MODE, bool WEIGHTED>
+__global__ void __launch_bounds__(256)
+conv_dw_kernel(ColSrc<T> cs, const T *__restrict__ A, int M, int B, T *__restrict__ partial) {
+  __shared__ T As[16][TM + 1];
+  __shared__ T Cs[16][TN + 1];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int kk0 = blockIdx.x * TN, m0 = blockIdx.y * TM, splits = gridDim.z;
+  const int CHK = cs.CH * cs.K;
+  const size_t shw = (size_t)cs.SH * cs.SW;
+  const int chunks = (cs.npix + kDwChunk - 1) / kDwChunk;
+  PlanView<T> pv{};
+  T acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = T(0);
+
+  for (int unit = blockIdx.z; unit < B * chunks; unit += splits) {
+    const int b = unit / chunks, pbase = (unit % chunks) * kDwChunk, pend = min(cs.npix, pbase + kDwChunk);
+    for (int p0 = pbase; p0 < pend; p0 += 16) {
+      for (int e = tid; e < 16 * TM; e += 256) {
+        const int pl = e & 15, ml = e >> 4, pix = p0 + pl, m = m0 + ml;
+        As[pl][ml] = (pix < pend && m < M) ? __ldg(A + ((size_t)b * M + m) * cs.npix + pix) : T(0);
+      }
+      for (int e = tid; e < 16 * TN; e += 256) {
+        const int pl = e & 15, kl = e >> 4, pix = p0 + pl, kk = kk0 + kl;
+        T v = T(0);
+        if (pix < pend && kk < CHK)
+          v = col_value<T, MODE, WEIGHTED>(cs, pv, cs.src + ((size_t)b * cs.CH + kk / cs.K) * shw, kk % cs.K, pix);
+        Cs[pl][kl] = v;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int pl = 0; pl < 16; pl++) {
+        T a[4], c[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) a[i] = As[pl][ty * 4 + i];
+#pragma unroll
+        for (int j = 0; j < 4; j++) c[j] = Cs[pl][tx + 16 * j];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[i][j] += a[i] * c[j];
+      }
+      __syncthreads();
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int kk = kk0 + tx + 16 * j;
+      if (kk < CHK) partial[((size_t)blockIdx.z * M + m) * CHK + kk] = acc[i][j];
+    }
+  }
+}
+
+// gw[m,ch,k] = sum over splits, in split order (deterministic).
+template <typename T>
+__global__ void dw_reduce_kernel(const T *__restrict__ partial, int splits, int M, int CHK, int K, int64_t sm, int64_t sc,
+                                 int64_t sk, T *__restrict__ gw) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * CHK) return;
+  const int m = i / CHK, kk = i % CHK;
+  T s = T(0);
+  for (int z = 0; z < splits; z++) s += partial[(size_t)z * M * CHK + i];
+  gw[m * sm + (kk / K) * sc + (kk % K) * sk] = s;
+}
+
+// Bias gradient: sum of g over batch and pixels per channel, two fixed-order stages.
+constexpr int kBiasSplits = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256) bias_partial_kernel(const T *__restrict__ g, int B, int C, int n, T *__restrict__ part) {
+  __shared__ T red[256];
+  const int c = blockIdx.x, s = blockIdx.y;
+  const int64_t total = (int64_t)B * n, per = (total + kBiasSplits - 1) / kBiasSplits;
+  const int64_t i0 = s * per, i1 = min(total, i0 + per);
+  T acc = T(0);
+  for (int64_t i = i0 + threadIdx.x; i < i1; i += 256) {
+    const int64_t b = i / n, p = i % n;
+    acc += __ldg(g + ((size_t)b * C + c) * n + p);
+  }
+  red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int d = 128; d > 0; d >>= 1) {
+    if (threadIdx.x < d) red[threadIdx.x] += red[threadIdx.x + d];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) part[c * kBiasSplits + s] = red[0];
+}
+
+template <typename T>
+__global__ void bias_final_kernel(const T *__restrict__ part, int C, T *__restrict__ gb) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  T s = T(0);
+  for (int i = 0; i < kBiasSplits; i++) s += part[c * kBiasSplits + i];
+  gb[c] = s;
+}
+
+static int dw_splits(int64_t B, int64_t npix, int64_t M, int64_t CHK) {
+  const int64_t units = B * ((npix + kDwChunk - 1) / kDwChunk);
+  const int64_t tiles = ((CHK + TN - 1) / TN) * ((M + TM - 1) / TM);
+  int64_t s = (4 * 148 + tiles - 1) / tiles;
+  if (s > 64) s = 64;
+  if (s > units) s = units;
+  if (s < 1) s = 1;
+  return (int)s;
+}
+
+size_t simt_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts) {
+  const int64_t CHK = CH * K;
+  return align_up(ts * (size_t)(dw_splits(B, npix, M, CHK) * M * CHK), 256) + align_up(ts * (size_t)(Cbias * kBiasSplits), 256);
+}
+
+template <typename T, int MODE, bool WEIGHTED>
+static void launch_gemm(const ColSrc<T> &cs, const T *wgt, int64_t sm, int64_t sc, int64_t sk, const T *bias, T *out, int M,
+                        int B, cudaStream_t st) {
+  dim3 grid(cdiv(cs.npix, TN), cdiv(M, TM), B);
+  conv_gemm_kernel<T, MODE, WEIGHTED><<<grid, 256, 0, st>>>(cs, wgt, sm, sc, sk, bias, out, M);
+}
+
+// Out[b,m,pix] (+bias) with columns gathered through the map (mode = interp) or through a plan.
+template <typename T>
+int simt_gemm(bool use_plan, const void *src, const void *map, const void *iw, const void *plan, int64_t CH, int64_t SH,
+              int64_t SW, int64_t K, int64_t P, int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc,
+              int64_t sk, const void *bias, void *out, int64_t M, int64_t B, cudaStream_t st) {
+  ColSrc<T> cs{(const T *)src, (const T *)map, (const T *)iw, plan, (int)CH, (int)SH, (int)SW, (int)K, (int)P, (int)npix};
+  if (use_plan) {
+    launch_gemm<T, COL_PLAN, false>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st);
+  } else {
+    SPH_DISPATCH_INTERP(interp, {
+      if (P > 0) launch_gemm<T, INTERP, true>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st);
+      else launch_gemm<T, INTERP, false>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st);
+    });
+  }
+  return launch_status();
+}
+
+// gw[m,ch,k] = sum_{b,pix} A[b,m,pix] * im2col(src)[b,ch,k,pix];  gb[c] = sum gbias_src[b,c,:]
+template <typename T>
+int simt_dw(const void *A, const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K,
+            int64_t P, int64_t npix, int interp, int64_t M, int64_t B, void *gw, int64_t sm, int64_t sc, int64_t sk,
+            const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st) {
+  const int64_t CHK = CH * K;
+  const int splits = dw_splits(B, npix, M, CHK);
+  if (ws_bytes < simt_dw_workspace(B, npix, M, CH, K, Cbias, sizeof(T)) || !ws) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  T *partial = (T *)ws;
+  T *bpart = (T *)((char *)ws + align_up(sizeof(T) * (size_t)(splits * M * CHK), 256));
+  ColSrc<T> cs{(const T *)src, (const T *)map, (const T *)iw, nullptr, (int)CH, (int)SH, (int)SW, (int)K, (int)P, (int)npix};
+  dim3 grid(cdiv(CHK, TN), cdiv(M, TM), splits);
+  SPH_DISPATCH_INTERP(interp, {
+    if (P > 0) conv_dw_kernel<T, INTERP, true><<<grid, 256, 0, st>>>(cs, (const T *)A, (int)M, (int)B, partial);
+    else conv_dw_kernel<T, INTERP, false><<<grid, 256, 0, st>>>(cs, (const T *)A, (int)M, (int)B, partial);
+  });
+  dw_reduce_kernel<T><<<cdiv(M * CHK, 256), 256, 0, st>>>(partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw);
+  bias_partial_kernel<T><<<dim3((unsigned)Cbias, kBiasSplits), 256, 0, st>>>((const T *)gbias_src, (int)B, (int)Cbias, (int)nbias, bpart);
+  bias_final_kernel<T><<<cdiv(Cbias, 128), 128, 0, st>>>(bpart, (int)Cbias, (T *)gb);
+  return launch_status();
+}
+
+template int simt_gemm<float>(bool, const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t,
+                              int64_t, int64_t, int, const void *, int64_t, int64_t, int64_t, const void *, void *, int64_t,
+                              int64_t, cudaStream_t);
+template int simt_gemm<double>(bool, const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t,
+                               int64_t, int64_t, int, const void *, int64_t, int64_t, int64_t, const void *, void *, int64_t,
+                               int64_t, cudaStream_t);
+template int simt_dw<float>(const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t, int64_t,
+                            int64_t, int, int64_t, int64_t, void *, int64_t, int64_t, int64_t, const void *, int64_t, int64_t,
+                            void *, void *, size_t, cudaStream_t);
+template int simt_dw<double>(const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t, int64_t,
+                             int64_t, int, int64_t, int64_t, void *, int64_t, int64_t, int64_t, const void *, int64_t, int64_t,
+                             void *, void *, size_t, cudaStream_t);
+
+}  // namespace sph

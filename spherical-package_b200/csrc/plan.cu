@@ -1,0 +1,206 @@
+// Scatter plan: the sample map inverted into a CSR table keyed by
+// (destination pixel, kernel slot), entries ordered by their position in the
+// map so that every adjoint operator sums in one fixed order.
+#include "common.cuh"
+
+namespace sph {
+
+// Visit every valid tap of map slot s (= position * K + k): f(key, id, weight).
+template <typename T, int INTERP, bool WEIGHTED, typename F>
+__device__ __forceinline__ void for_each_tap(const T *__restrict__ map, const T *__restrict__ iw, int s, int K, int PP,
+                                             int H, int W, F f) {
+  const int k = s % K;
+  Taps<T> t;
+  for (int q = 0; q < PP; q++) {
+    const size_t e = (size_t)s * PP + q;
+    decode<T, INTERP>(__ldg(map + 2 * e), __ldg(map + 2 * e + 1), H, W, t);
+    const T wq = WEIGHTED ? __ldg(iw + e) : T(1);
+#pragma unroll
+    for (int i = 0; i < TapCount<INTERP>::value; i++)
+      if (t.off[i] >= 0) f(t.off[i] * K + k, (int)(e * 4 + i), WEIGHTED ? wq * t.w[i] : t.w[i]);
+  }
+}
+
+template <typename T, int INTERP, bool WEIGHTED>
+__global__ void plan_count_kernel(const T *map, const T *iw, int n_slots, int K, int PP, int H, int W, int *cnt) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n_slots) return;
+  for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, [&](int key, int, T) { atomicAdd(cnt + key, 1); });
+}
+
+template <typename T, int INTERP, bool WEIGHTED>
+__global__ void plan_fill_kernel(const T *map, const T *iw, int n_slots, int K, int PP, int H, int W,
+                                 const int *offsets, int *cursor, int *ids, T *w) {
+  const int s = blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n_slots) return;
+  for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, [&](int key, int id, T wt) {
+    const int pos = offsets[key] + atomicAdd(cursor + key, 1);
+    ids[pos] = id;
+    w[pos] = wt;
+  });
+}
+
+// One thread per key: order the segment by entry id (the fill order above is
+// not reproducible), then turn ids into source positions.
+template <typename T>
+__global__ void plan_sort_kernel(const int *offsets, int *ids, T *w, int n_keys, int id_div) {
+  const int key = blockIdx.x * blockDim.x + threadIdx.x;
+  if (key >= n_keys) return;
+  const int e0 = offsets[key], e1 = offsets[key + 1];
+  for (int i = e0 + 1; i < e1; i++) {
+    const int id = ids[i];
+    const T wi = w[i];
+    int j = i - 1;
+    while (j >= e0 && ids[j] > id) {
+      ids[j + 1] = ids[j];
+      w[j + 1] = w[j];
+      j--;
+    }
+    ids[j + 1] = id;
+    w[j + 1] = wi;
+  }
+  for (int i = e0; i < e1; i++) ids[i] = ids[i] / id_div;
+}
+
+// ---- exclusive scan of n ints (three passes, kScanItems per block) -------
+constexpr int kScanThreads = 256;
+constexpr int kScanPer = kScanItems / kScanThreads;
+
+__device__ __forceinline__ int block_exclusive_scan(int v, int *total) {
+  __shared__ int warp_sums[kScanThreads / 32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int u = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += u;
+  }
+  if (lane == 31) warp_sums[wid] = incl;
+  __syncthreads();
+  if (wid == 0) {
+    int s = lane < kScanThreads / 32 ? warp_sums[lane] : 0;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, s, d);
+      if (lane >= d) s += u;
+    }
+    if (lane < kScanThreads / 32) warp_sums[lane] = s;
+  }
+  __syncthreads();
+  const int base = wid ? warp_sums[wid - 1] : 0;
+  if (total) *total = warp_sums[kScanThreads / 32 - 1];
+  __syncthreads();
+  return base + incl - v;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_sums_kernel(const int *in, int n, int *sums) {
+  const int base = blockIdx.x * kScanItems + threadIdx.x * kScanPer;
+  int s = 0;
+#pragma unroll
+  for (int i = 0; i < kScanPer; i++)
+    if (base + i < n) s += in[base + i];
+  int total;
+  block_exclusive_scan(s, &total);
+  if (threadIdx.x == 0) sums[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_top_kernel(int *sums, int nb) {
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < nb; b0 += kScanThreads) {
+    const int i = b0 + threadIdx.x;
+    const int v = i < nb ? sums[i] : 0;
+    int total;
+    const int ex = block_exclusive_scan(v, &total);
+    const int c = carry;
+    if (i < nb) sums[i] = c + ex;
+    __syncthreads();
+    if (threadIdx.x == 0) carry = c + total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) sums[nb] = carry;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_final_kernel(const int *in, int n, const int *sums, int *out) {
+  const int base = blockIdx.x * kScanItems + threadIdx.x * kScanPer;
+  int v[kScanPer], s = 0;
+#pragma unroll
+  for (int i = 0; i < kScanPer; i++) {
+    v[i] = base + i < n ? in[base + i] : 0;
+    s += v[i];
+  }
+  int run = block_exclusive_scan(s, nullptr) + sums[blockIdx.x];
+#pragma unroll
+  for (int i = 0; i < kScanPer; i++) {
+    if (base + i < n) out[base + i] = run;
+    run += v[i];
+  }
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) out[n] = sums[gridDim.x];
+}
+
+__global__ void plan_header_kernel(PlanHeader *dst, PlanHeader h) { *dst = h; }
+
+template <typename T>
+static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int64_t P, int interp, int64_t H,
+                 int64_t W, int dtype, void *plan, const PlanLayout &L, cudaStream_t st) {
+  char *base = (char *)plan;
+  int *offsets = (int *)(base + L.off_offsets), *src = (int *)(base + L.off_src);
+  int *cursor = (int *)(base + L.off_cursor), *sums = (int *)(base + L.off_sums);
+  T *w = (T *)(base + L.off_w);
+  const int n_slots = (int)(n_src * K), PP = (int)(P > 0 ? P : 1), nk = (int)L.n_keys;
+  if (cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)nk, st) != cudaSuccess) return SPH_ERR_CUDA;
+  const int gb = cdiv(n_slots, 256);
+  SPH_DISPATCH_INTERP(interp, {
+    if (P > 0)
+      plan_count_kernel<T, INTERP, true><<<gb, 256, 0, st>>>((const T *)map, (const T *)iw, n_slots, (int)K, PP, (int)H, (int)W, cursor);
+    else
+      plan_count_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, cursor);
+  });
+  scan_sums_kernel<<<L.n_scan_blocks, kScanThreads, 0, st>>>(cursor, nk, sums);
+  scan_top_kernel<<<1, kScanThreads, 0, st>>>(sums, L.n_scan_blocks);
+  scan_final_kernel<<<L.n_scan_blocks, kScanThreads, 0, st>>>(cursor, nk, sums, offsets);
+  if (cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)nk, st) != cudaSuccess) return SPH_ERR_CUDA;
+  SPH_DISPATCH_INTERP(interp, {
+    if (P > 0)
+      plan_fill_kernel<T, INTERP, true><<<gb, 256, 0, st>>>((const T *)map, (const T *)iw, n_slots, (int)K, PP, (int)H, (int)W, offsets, cursor, src, w);
+    else
+      plan_fill_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, offsets, cursor, src, w);
+  });
+  plan_sort_kernel<T><<<cdiv(nk, 256), 256, 0, st>>>(offsets, src, w, nk, (int)(4 * PP * K));
+  PlanHeader h;
+  h.magic = kPlanMagic;
+  h.n_keys = nk;
+  h.K = (int)K;
+  h.dtype = dtype;
+  h.e_max = (int)L.e_max;
+  h.off_offsets = L.off_offsets;
+  h.off_src = L.off_src;
+  h.off_w = L.off_w;
+  plan_header_kernel<<<1, 1, 0, st>>>((PlanHeader *)plan, h);
+  return launch_status();
+}
+
+}  // namespace sph
+
+using namespace sph;
+
+extern "C" size_t sph_plan_bytes(int64_t n_src, int64_t K, int64_t P, int interp, int64_t dstH, int64_t dstW,
+                                 int dtype) {
+  PlanLayout L;
+  if (P < 0 || !plan_layout(n_src, K, P, interp, dstH, dstW, dtype, L)) return 0;
+  return L.total;
+}
+
+extern "C" int sph_plan_build(const void *map, const void *iw, int64_t n_src, int64_t K, int64_t P, int interp,
+                              int64_t dstH, int64_t dstW, int dtype, void *plan, size_t plan_bytes, void *stream) {
+  if (!map || !plan || P < 0 || (P > 0 && !iw) || interp < 0 || interp > 2) return SPH_ERR_INVALID_ARGUMENT;
+  if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
+  PlanLayout L;
+  if (!plan_layout(n_src, K, P, interp, dstH, dstW, dtype, L)) return SPH_ERR_TOO_LARGE;
+  if (plan_bytes < L.total) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  if (((uintptr_t)plan & 255) != 0) return SPH_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == SPH_F32 ? build<float>(map, iw, n_src, K, P, interp, dstH, dstW, dtype, plan, L, st)
+                          : build<double>(map, iw, n_src, K, P, interp, dstH, dstW, dtype, plan, L, st);
+}

@@ -1,0 +1,161 @@
+// Mapped max pooling: forward (value + argmax index) and argmax backward.
+#include <float.h>
+
+#include "common.cuh"
+
+namespace sph {
+
+// out[p,o] = max over the K map slots of output position o, first strict
+// maximum, starting from -FLT_MAX as the reference's CUDA build does
+// (ext_modules/include/common/mapped_max_pool.h:27-51).  idx is the offset of
+// the winning slot's x coordinate in the flattened map (line 49).  One thread
+// per output position walks kPlanesPerThread planes; the whole batch is one
+// launch (the reference launches once per image:
+// src/cuda/mapped_max_pooling_layer.cu:11-36).
+template <typename T, int INTERP, bool WEIGHTED>
+__global__ void __launch_bounds__(256)
+max_pool_kernel(const T *__restrict__ x, const T *__restrict__ map, const T *__restrict__ iw, T *__restrict__ out,
+                int64_t *__restrict__ idx, int n, int planes, int H, int W, int K, int P) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= n) return;
+  const int p0 = blockIdx.y * kPlanesPerThread;
+  const int np = min(kPlanesPerThread, planes - p0);
+  const size_t hw = (size_t)H * W;
+  const T *xp = x + (size_t)p0 * hw;
+  const int PP = WEIGHTED ? P : 1;
+  T best[kPlanesPerThread];
+  int bk[kPlanesPerThread];
+#pragma unroll
+  for (int j = 0; j < kPlanesPerThread; j++) { best[j] = (T)(-FLT_MAX); bk[j] = -1; }
+  for (int k = 0; k < K; k++) {
+    const size_t e = ((size_t)o * K + k) * PP;
+    if (!WEIGHTED) {
+      Taps<T> t;
+      decode<T, INTERP>(__ldg(map + 2 * e), __ldg(map + 2 * e + 1), H, W, t);
+#pragma unroll
+      for (int j = 0; j < kPlanesPerThread; j++)
+        if (j < np) {
+          const T v = gather<T, INTERP>(xp + j * hw, t);
+          if (v > best[j]) { best[j] = v; bk[j] = k; }
+        }
+    } else {
+#pragma unroll
+      for (int j = 0; j < kPlanesPerThread; j++)
+        if (j < np) {
+          const T v = gather_slot<T, INTERP, true>(xp + j * hw, map + 2 * e, iw + e, P, H, W);
+          if (v > best[j]) { best[j] = v; bk[j] = k; }
+        }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kPlanesPerThread; j++)
+    if (j < np) {
+      out[(size_t)(p0 + j) * n + o] = best[j];
+      idx[(size_t)(p0 + j) * n + o] = bk[j] < 0 ? (int64_t)-1 : ((int64_t)o * K + bk[j]) * PP * 2;
+    }
+}
+
+// Argmax backward: the gradient of output (p,o) goes back through the one
+// map slot idx names (common/mapped_max_pool.h:60-78, 136-171).  grad_in is
+// zeroed first; contributions are added with red.global.add as in the
+// reference's CUDA kernel (cuda/mapped_max_pool.cuh:57-95).
+template <typename T, int INTERP, bool WEIGHTED>
+__global__ void __launch_bounds__(256)
+max_unpool_kernel(const T *__restrict__ g, const int64_t *__restrict__ idx, const T *__restrict__ map,
+                  const T *__restrict__ iw, T *__restrict__ gin, int n, int planes, int H, int W, int P,
+                  int64_t map_elems) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= n) return;
+  const int p0 = blockIdx.y * kPlanesPerThread;
+  const int np = min(kPlanesPerThread, planes - p0);
+  const size_t hw = (size_t)H * W;
+  const int PP = WEIGHTED ? P : 1;
+  for (int j = 0; j < np; j++) {
+    const size_t at = (size_t)(p0 + j) * n + o;
+    const int64_t s = idx[at];
+    if (s < 0 || s + 2 * PP > map_elems) continue;
+    const T v = g[at];
+    T *plane = gin + (size_t)(p0 + j) * hw;
+    Taps<T> t;
+    for (int q = 0; q < PP; q++) {
+      decode<T, INTERP>(__ldg(map + s + 2 * q), __ldg(map + s + 2 * q + 1), H, W, t);
+      const T vq = WEIGHTED ? __ldg(iw + s / 2 + q) * v : v;
+#pragma unroll
+      for (int i = 0; i < TapCount<INTERP>::value; i++)
+        if (t.off[i] >= 0) atomicAdd(plane + t.off[i], INTERP == SPH_NEAREST ? vq : t.w[i] * vq);
+    }
+  }
+}
+
+template <typename T>
+static int pool(const void *x, const void *map, const void *iw, void *out, int64_t *idx, int64_t planes, int64_t H,
+                int64_t W, int64_t n, int64_t K, int64_t P, int interp, cudaStream_t st) {
+  dim3 grid(cdiv(n, 256), cdiv(planes, kPlanesPerThread));
+  SPH_DISPATCH_INTERP(interp, {
+    if (P > 0)
+      max_pool_kernel<T, INTERP, true><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, (const T *)iw, (T *)out, idx,
+                                                             (int)n, (int)planes, (int)H, (int)W, (int)K, (int)P);
+    else
+      max_pool_kernel<T, INTERP, false><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, nullptr, (T *)out, idx, (int)n,
+                                                              (int)planes, (int)H, (int)W, (int)K, 0);
+  });
+  return launch_status();
+}
+
+template <typename T>
+static int unpool(const void *g, const int64_t *idx, const void *map, const void *iw, void *gin, int64_t planes,
+                  int64_t H, int64_t W, int64_t n, int64_t K, int64_t P, int interp, cudaStream_t st) {
+  if (cudaMemsetAsync(gin, 0, sizeof(T) * (size_t)(planes * H * W), st) != cudaSuccess) return SPH_ERR_CUDA;
+  dim3 grid(cdiv(n, 256), cdiv(planes, kPlanesPerThread));
+  const int64_t map_elems = n * K * (P > 0 ? P : 1) * 2;
+  SPH_DISPATCH_INTERP(interp, {
+    if (P > 0)
+      max_unpool_kernel<T, INTERP, true><<<grid, 256, 0, st>>>((const T *)g, idx, (const T *)map, (const T *)iw, (T *)gin,
+                                                               (int)n, (int)planes, (int)H, (int)W, (int)P, map_elems);
+    else
+      max_unpool_kernel<T, INTERP, false><<<grid, 256, 0, st>>>((const T *)g, idx, (const T *)map, nullptr, (T *)gin, (int)n,
+                                                                (int)planes, (int)H, (int)W, 0, map_elems);
+  });
+  return launch_status();
+}
+
+static int check(const void *a, const void *b, const void *c, const void *d, const void *iw, int64_t B, int64_t C,
+                 int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp) {
+  if (!a || !b || !c || !d || B < 0 || C < 0 || IH <= 0 || IW <= 0 || OH < 0 || OW < 0 || K <= 0 || P < 0 ||
+      (P > 0 && !iw) || interp < 0 || interp > 2)
+    return SPH_ERR_INVALID_ARGUMENT;
+  if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
+  const int64_t lim = (int64_t)1 << 31;
+  if (IH * IW >= lim || OH * OW * K * (P > 0 ? P : 1) * 2 >= lim || B * C / kPlanesPerThread >= 65535)
+    return SPH_ERR_TOO_LARGE;
+  return SPH_OK;
+}
+
+}  // namespace sph
+
+using namespace sph;
+
+extern "C" int sph_mapped_max_pool(const void *x, const void *map, const void *iw, void *out, int64_t *idx, int64_t B,
+                                   int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
+                                   int dtype, int interp, void *stream) {
+  const int rc = check(x, map, out, idx, iw, B, C, IH, IW, OH, OW, K, P, dtype, interp);
+  if (rc != SPH_OK) return rc;
+  if (B * C == 0 || OH * OW == 0) return SPH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == SPH_F32 ? pool<float>(x, map, iw, out, idx, B * C, IH, IW, OH * OW, K, P, interp, st)
+                          : pool<double>(x, map, iw, out, idx, B * C, IH, IW, OH * OW, K, P, interp, st);
+}
+
+extern "C" int sph_mapped_max_unpool(const void *g, const int64_t *idx, const void *map, const void *iw, void *grad_in,
+                                     int64_t B, int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
+                                     int64_t P, int dtype, int interp, void *stream) {
+  const int rc = check(g, map, grad_in, idx, iw, B, C, IH, IW, OH, OW, K, P, dtype, interp);
+  if (rc != SPH_OK) return rc;
+  if (B * C == 0) return SPH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (OH * OW == 0)
+    return cudaMemsetAsync(grad_in, 0, (dtype == SPH_F64 ? 8 : 4) * (size_t)(B * C * IH * IW), st) == cudaSuccess
+               ? SPH_OK : SPH_ERR_CUDA;
+  return dtype == SPH_F32 ? unpool<float>(g, idx, map, iw, grad_in, B * C, IH, IW, OH * OW, K, P, interp, st)
+                          : unpool<double>(g, idx, map, iw, grad_in, B * C, IH, IW, OH * OW, K, P, interp, st);
+}

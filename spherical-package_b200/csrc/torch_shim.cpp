@@ -1,0 +1,462 @@
+// Host side of the drop-in `_spherical_distortion_ext` package: a thin
+// PyTorch extension that checks arguments, allocates outputs with torch's
+// caching allocator and calls the C ABI of libsphmap.so (include/sphmap.h) on
+// the current CUDA stream.  Function names and positional argument order are
+// those of the reference's pybind modules (ext_modules/include/layers/*.h);
+// the Python files next to this extension re-export them under the reference's
+// module names.  There is no CPU path: CPU tensors raise.
+#include <torch/extension.h>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <cstdlib>
+#include <list>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "sphmap.h"
+
+namespace {
+
+enum class InterpolationType { NEAREST = 0, BILINEAR = 1, BISPHERICAL = 2 };   // include/enums.h:12-16
+enum class DistortionType { SIMPLE_RADIAL = 0, BROWN = 1, FISHEYE = 2 };       // include/enums.h:6-10
+
+int g_precision = -1;
+
+int precision() {
+  if (g_precision < 0) {
+    const char *e = std::getenv("SPHERICAL_MAPPED_PRECISION");
+    const std::string s = e ? e : "fp32";
+    TORCH_CHECK(s == "fp32" || s == "bf16", "SPHERICAL_MAPPED_PRECISION must be fp32 or bf16, got ", s);
+    g_precision = s == "bf16" ? SPH_PRECISION_BF16 : SPH_PRECISION_EXACT;
+  }
+  return g_precision;
+}
+
+void set_precision(const std::string &s) {
+  TORCH_CHECK(s == "fp32" || s == "bf16", "precision must be 'fp32' or 'bf16', got ", s);
+  g_precision = s == "bf16" ? SPH_PRECISION_BF16 : SPH_PRECISION_EXACT;
+}
+
+std::string get_precision() { return precision() == SPH_PRECISION_BF16 ? "bf16" : "fp32"; }
+
+void ok(int status, const char *what) {
+  TORCH_CHECK(status == SPH_OK, what, ": ", sph_status_string(status));
+}
+
+int dtype_of(const torch::Tensor &t) {
+  TORCH_CHECK(t.scalar_type() == torch::kFloat || t.scalar_type() == torch::kDouble,
+              "mapped operators support float32 and float64 tensors only");
+  return t.scalar_type() == torch::kDouble ? SPH_F64 : SPH_F32;
+}
+
+// Same preconditions as CHECK_CUDA / CHECK_CONTIGUOUS of include/cuda_helper.h:12-18.
+void check(const torch::Tensor &t, const char *name, const torch::Tensor &like) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor (this build has no CPU path)");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  TORCH_CHECK(t.device() == like.device(), name, " must be on the same device as the input");
+}
+
+void check_float(const torch::Tensor &t, const char *name, const torch::Tensor &like) {
+  check(t, name, like);
+  TORCH_CHECK(t.scalar_type() == like.scalar_type(), name, " must have the input's dtype");
+}
+
+struct MapInfo {
+  int64_t H, W, K, P;  // map spatial size, kernel slots (1 if absent), interpolation points (0 if unweighted)
+};
+
+// map: (H,W,[K,][P,]2); weights: (H,W,[K,]P)
+MapInfo map_info(const torch::Tensor &map, const torch::Tensor *iw, bool has_k, int64_t kernel_size) {
+  const int64_t want = 3 + (has_k ? 1 : 0) + (iw ? 1 : 0);
+  TORCH_CHECK(map.dim() == want, "sample map must have ", want, " dimensions, got ", map.dim());
+  TORCH_CHECK(map.size(-1) == 2, "last dimension of the sample map must be 2");
+  MapInfo m{map.size(0), map.size(1), has_k ? map.size(2) : 1, 0};
+  if (has_k) TORCH_CHECK(m.K == kernel_size, "kernel size of the sample map (", m.K, ") != kernel_size (", kernel_size, ")");
+  if (iw) {
+    m.P = map.size(-2);
+    TORCH_CHECK(iw->dim() == want - 1 && iw->size(-1) == m.P && iw->size(0) == m.H && iw->size(1) == m.W &&
+                    (!has_k || iw->size(2) == m.K),
+                "interpolation weights do not match the sample map");
+    TORCH_CHECK(m.P > 0, "need at least one interpolation point");
+  }
+  return m;
+}
+
+// ---- scatter-plan cache ---------------------------------------------------
+// A plan depends only on the map (and weights); training loops call the same
+// layer with the same map every step, so plans are kept, keyed by the
+// identity and version of the tensors' storage.
+struct PlanKey {
+  c10::weak_intrusive_ptr<c10::StorageImpl> map_s, iw_s;
+  const void *map_p, *iw_p;
+  int64_t map_off, iw_off;
+  uint32_t map_v, iw_v;
+  int64_t n_src, K, P, dstH, dstW;
+  int interp, dtype, device;
+  torch::Tensor blob;
+};
+std::list<PlanKey> g_plans;
+std::mutex g_plan_mu;
+constexpr size_t kMaxPlans = 64;
+
+torch::Tensor get_plan(const torch::Tensor &map, const torch::Tensor *iw, int64_t n_src, int64_t K, int64_t P, int interp,
+                       int64_t dstH, int64_t dstW) {
+  const int dtype = dtype_of(map), device = map.get_device();
+  std::lock_guard<std::mutex> lock(g_plan_mu);
+  for (auto it = g_plans.begin(); it != g_plans.end();) {
+    if (it->map_s.expired() || (it->iw_p && it->iw_s.expired())) {
+      it = g_plans.erase(it);
+      continue;
+    }
+    const bool hit = it->map_p == map.data_ptr() && it->map_off == map.storage_offset() && it->map_v == map._version() &&
+                     it->map_s.lock().get() == map.storage().unsafeGetStorageImpl() &&
+                     (iw ? (it->iw_p == iw->data_ptr() && it->iw_v == iw->_version() &&
+                            it->iw_s.lock().get() == iw->storage().unsafeGetStorageImpl())
+                         : it->iw_p == nullptr) &&
+                     it->n_src == n_src && it->K == K && it->P == P && it->dstH == dstH && it->dstW == dstW &&
+                     it->interp == interp && it->dtype == dtype && it->device == device;
+    if (hit) {
+      g_plans.splice(g_plans.begin(), g_plans, it);
+      return g_plans.front().blob;
+    }
+    ++it;
+  }
+  const size_t bytes = sph_plan_bytes(n_src, K, P, interp, dstH, dstW, dtype);
+  TORCH_CHECK(bytes > 0, "sample map too large for a scatter plan");
+  torch::Tensor blob = torch::empty({(int64_t)bytes}, map.options().dtype(torch::kUInt8));
+  ok(sph_plan_build(map.data_ptr(), iw ? iw->data_ptr() : nullptr, n_src, K, P, interp, dstH, dstW, dtype, blob.data_ptr(),
+                    bytes, at::cuda::getCurrentCUDAStream().stream()),
+     "sph_plan_build");
+  PlanKey k{c10::weak_intrusive_ptr<c10::StorageImpl>(map.storage().getWeakStorageImpl()),
+            iw ? c10::weak_intrusive_ptr<c10::StorageImpl>(iw->storage().getWeakStorageImpl())
+               : c10::weak_intrusive_ptr<c10::StorageImpl>(map.storage().getWeakStorageImpl()),
+            map.data_ptr(), iw ? iw->data_ptr() : nullptr, map.storage_offset(), iw ? iw->storage_offset() : 0,
+            map._version(), iw ? iw->_version() : 0u, n_src, K, P, dstH, dstW, interp, dtype, device, blob};
+  g_plans.push_front(std::move(k));
+  if (g_plans.size() > kMaxPlans) g_plans.pop_back();
+  return blob;
+}
+
+void clear_plan_cache() {
+  std::lock_guard<std::mutex> lock(g_plan_mu);
+  g_plans.clear();
+}
+
+int64_t plan_cache_size() {
+  std::lock_guard<std::mutex> lock(g_plan_mu);
+  return (int64_t)g_plans.size();
+}
+
+torch::Tensor workspace(size_t bytes, const torch::Tensor &like) {
+  return torch::empty({(int64_t)(bytes ? bytes : 1)}, like.options().dtype(torch::kUInt8));
+}
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+// ---- resample (include/layers/resample_layer.h:40-82, weighted_resample_layer.h:49-105) ----
+torch::Tensor resample_from_map_impl(torch::Tensor x, torch::Tensor map, const torch::Tensor *iw, InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4, "input must have 4 dimensions");
+  check(x, "input", x);
+  check_float(map, "sample_map", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw, false, 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor y = torch::empty({x.size(0), x.size(1), m.H, m.W}, x.options());
+  ok(sph_resample_from_map(x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr, y.data_ptr(), x.size(0), x.size(1),
+                           x.size(2), x.size(3), m.H, m.W, m.P, dtype_of(x), (int)it, stream()),
+     "sph_resample_from_map");
+  return y;
+}
+
+torch::Tensor resample_to_map_impl(torch::Tensor x, torch::Tensor map, const torch::Tensor *iw, int64_t oh, int64_t ow,
+                                   InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4, "input must have 4 dimensions");
+  check(x, "input", x);
+  check_float(map, "sample_map", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw, false, 1);
+  TORCH_CHECK(x.size(2) == m.H && x.size(3) == m.W, "input spatial size must match the sample map");
+  TORCH_CHECK(oh > 0 && ow > 0, "output size must be positive");
+  c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor plan = get_plan(map, iw, m.H * m.W, 1, m.P, (int)it, oh, ow);
+  torch::Tensor out = torch::empty({x.size(0), x.size(1), oh, ow}, x.options());
+  ok(sph_resample_to_map(x.data_ptr(), plan.data_ptr(), out.data_ptr(), x.size(0), x.size(1), m.H, m.W, oh, ow, dtype_of(x),
+                         stream()),
+     "sph_resample_to_map");
+  return out;
+}
+
+torch::Tensor resample_to_map(torch::Tensor x, torch::Tensor map, int64_t oh, int64_t ow, InterpolationType it) {
+  return resample_to_map_impl(x, map, nullptr, oh, ow, it);
+}
+torch::Tensor resample_from_map(torch::Tensor x, torch::Tensor map, InterpolationType it) {
+  return resample_from_map_impl(x, map, nullptr, it);
+}
+torch::Tensor weighted_resample_to_map(torch::Tensor x, torch::Tensor map, torch::Tensor iw, int64_t oh, int64_t ow,
+                                       InterpolationType it) {
+  return resample_to_map_impl(x, map, &iw, oh, ow, it);
+}
+torch::Tensor weighted_resample_from_map(torch::Tensor x, torch::Tensor map, torch::Tensor iw, InterpolationType it) {
+  return resample_from_map_impl(x, map, &iw, it);
+}
+
+// ---- max pooling (include/layers/mapped_max_pooling_layer.h:42-97) ---------
+std::vector<torch::Tensor> max_pool_impl(torch::Tensor x, torch::Tensor map, const torch::Tensor *iw, int64_t K,
+                                         InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4, "input must have 4 dimensions");
+  check(x, "input", x);
+  check_float(map, "sample_map", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw, true, K);
+  c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor out = torch::empty({x.size(0), x.size(1), m.H, m.W}, x.options());
+  torch::Tensor idx = torch::empty({x.size(0), x.size(1), m.H, m.W}, x.options().dtype(torch::kLong));
+  ok(sph_mapped_max_pool(x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr, out.data_ptr(),
+                         idx.data_ptr<int64_t>(), x.size(0), x.size(1), x.size(2), x.size(3), m.H, m.W, m.K, m.P,
+                         dtype_of(x), (int)it, stream()),
+     "sph_mapped_max_pool");
+  return {out, idx};
+}
+
+torch::Tensor max_unpool_impl(torch::Tensor g, torch::Tensor idx, torch::Tensor map, const torch::Tensor *iw, int64_t ih,
+                              int64_t iwidth, int64_t K, InterpolationType it) {
+  TORCH_CHECK(g.dim() == 4, "grad_output must have 4 dimensions");
+  g = g.contiguous();
+  check(g, "grad_output", g);
+  check(idx, "idx_mask", g);
+  TORCH_CHECK(idx.scalar_type() == torch::kLong && idx.sizes() == g.sizes(), "idx_mask must be int64 with grad_output's shape");
+  check_float(map, "sample_map", g);
+  if (iw) check_float(*iw, "interp_weights", g);
+  const MapInfo m = map_info(map, iw, true, K);
+  TORCH_CHECK(g.size(2) == m.H && g.size(3) == m.W, "grad_output spatial size must match the sample map");
+  TORCH_CHECK(ih > 0 && iwidth > 0, "input size must be positive");
+  c10::cuda::CUDAGuard guard(g.device());
+  torch::Tensor gin = torch::empty({g.size(0), g.size(1), ih, iwidth}, g.options());
+  ok(sph_mapped_max_unpool(g.data_ptr(), idx.data_ptr<int64_t>(), map.data_ptr(), iw ? iw->data_ptr() : nullptr,
+                           gin.data_ptr(), g.size(0), g.size(1), ih, iwidth, m.H, m.W, m.K, m.P, dtype_of(g), (int)it,
+                           stream()),
+     "sph_mapped_max_unpool");
+  return gin;
+}
+
+std::vector<torch::Tensor> mapped_max_pool(torch::Tensor x, torch::Tensor map, int64_t K, InterpolationType it) {
+  return max_pool_impl(x, map, nullptr, K, it);
+}
+torch::Tensor mapped_max_unpool(torch::Tensor g, torch::Tensor idx, torch::Tensor map, int64_t ih, int64_t iw, int64_t K,
+                                InterpolationType it) {
+  return max_unpool_impl(g, idx, map, nullptr, ih, iw, K, it);
+}
+std::vector<torch::Tensor> weighted_mapped_max_pool(torch::Tensor x, torch::Tensor map, torch::Tensor w, int64_t K,
+                                                    InterpolationType it) {
+  return max_pool_impl(x, map, &w, K, it);
+}
+torch::Tensor weighted_mapped_max_unpool(torch::Tensor g, torch::Tensor idx, torch::Tensor map, torch::Tensor w, int64_t ih,
+                                         int64_t iw, int64_t K, InterpolationType it) {
+  return max_unpool_impl(g, idx, map, &w, ih, iw, K, it);
+}
+
+// ---- mapped convolution (include/layers/mapped_convolution_layer.h:62-134) --
+struct ConvArgs {
+  int64_t B, Cin, Cout, IH, IW, OH, OW, K, P;
+  int dtype, interp, prec;
+};
+
+torch::Tensor conv_forward_impl(torch::Tensor x, torch::Tensor map, const torch::Tensor *iw, torch::Tensor weight,
+                                torch::Tensor bias, int64_t K, InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4 && weight.dim() == 3 && bias.dim() == 1, "input (B,C,H,W), weight (Cout,Cin,K), bias (Cout)");
+  check(x, "input", x);
+  check_float(map, "sample_map", x);
+  check_float(weight, "weight", x);
+  check_float(bias, "bias", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw, true, K);
+  TORCH_CHECK(weight.size(1) == x.size(1) && weight.size(2) == K && bias.size(0) == weight.size(0),
+              "weight / bias shapes do not match the input");
+  c10::cuda::CUDAGuard guard(x.device());
+  const ConvArgs a{x.size(0), x.size(1), weight.size(0), x.size(2), x.size(3), m.H, m.W, K, m.P, dtype_of(x), (int)it,
+                   dtype_of(x) == SPH_F32 ? precision() : SPH_PRECISION_EXACT};
+  torch::Tensor out = torch::empty({a.B, a.Cout, a.OH, a.OW}, x.options());
+  const size_t wb = sph_conv_workspace_bytes(SPH_CONV_FORWARD, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
+                                             a.interp, a.prec);
+  torch::Tensor ws = workspace(wb, x);
+  ok(sph_mapped_conv_forward(x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr, weight.data_ptr(), bias.data_ptr(),
+                             out.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp, a.prec,
+                             ws.data_ptr(), wb, stream()),
+     "sph_mapped_conv_forward");
+  return out;
+}
+
+std::vector<torch::Tensor> conv_backward_impl(torch::Tensor go, torch::Tensor map, const torch::Tensor *iw, torch::Tensor x,
+                                              torch::Tensor weight, torch::Tensor bias, int64_t K, InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4 && go.dim() == 4 && weight.dim() == 3, "input/grad_output (B,C,H,W), weight (Cout,Cin,K)");
+  go = go.contiguous();  // the reference never checks grad_output; make it dense here
+  check(x, "input", x);
+  check_float(go, "grad_output", x);
+  check_float(map, "sample_map", x);
+  check_float(weight, "weight", x);
+  check_float(bias, "bias", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw, true, K);
+  TORCH_CHECK(weight.size(1) == x.size(1) && weight.size(2) == K, "weight shape does not match the input");
+  TORCH_CHECK(go.size(0) == x.size(0) && go.size(1) == weight.size(0) && go.size(2) == m.H && go.size(3) == m.W,
+              "grad_output shape does not match the sample map / weight");
+  c10::cuda::CUDAGuard guard(x.device());
+  const ConvArgs a{x.size(0), x.size(1), weight.size(0), x.size(2), x.size(3), m.H, m.W, K, m.P, dtype_of(x), (int)it,
+                   dtype_of(x) == SPH_F32 ? precision() : SPH_PRECISION_EXACT};
+  torch::Tensor gx = torch::empty_like(x), gw = torch::empty_like(weight), gb = torch::empty({a.Cout}, x.options());
+  torch::Tensor plan = get_plan(map, iw, a.OH * a.OW, a.K, a.P, a.interp, a.IH, a.IW);
+  size_t wb = sph_conv_workspace_bytes(SPH_CONV_BACKWARD_INPUT, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
+                                       a.dtype, a.interp, a.prec);
+  torch::Tensor ws = workspace(wb, x);
+  ok(sph_mapped_conv_backward_input(go.data_ptr(), plan.data_ptr(), weight.data_ptr(), gx.data_ptr(), a.B, a.Cin, a.Cout,
+                                    a.IH, a.IW, a.OH, a.OW, a.K, a.dtype, a.prec, ws.data_ptr(), wb, stream()),
+     "sph_mapped_conv_backward_input");
+  wb = sph_conv_workspace_bytes(SPH_CONV_BACKWARD_WEIGHT, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
+                                a.interp, a.prec);
+  torch::Tensor ws2 = workspace(wb, x);
+  ok(sph_mapped_conv_backward_weight(go.data_ptr(), x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr,
+                                     gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
+                                     a.dtype, a.interp, a.prec, ws2.data_ptr(), wb, stream()),
+     "sph_mapped_conv_backward_weight");
+  return {gx, gw, gb};
+}
+
+torch::Tensor mapped_conv_forward(torch::Tensor x, torch::Tensor map, torch::Tensor w, torch::Tensor b, int64_t K,
+                                  InterpolationType it) {
+  return conv_forward_impl(x, map, nullptr, w, b, K, it);
+}
+std::vector<torch::Tensor> mapped_conv_backward(torch::Tensor go, torch::Tensor map, torch::Tensor x, torch::Tensor w,
+                                                torch::Tensor b, int64_t K, InterpolationType it) {
+  return conv_backward_impl(go, map, nullptr, x, w, b, K, it);
+}
+torch::Tensor weighted_mapped_conv_forward(torch::Tensor x, torch::Tensor map, torch::Tensor iw, torch::Tensor w,
+                                           torch::Tensor b, int64_t K, InterpolationType it) {
+  return conv_forward_impl(x, map, &iw, w, b, K, it);
+}
+std::vector<torch::Tensor> weighted_mapped_conv_backward(torch::Tensor go, torch::Tensor map, torch::Tensor iw,
+                                                         torch::Tensor x, torch::Tensor w, torch::Tensor b, int64_t K,
+                                                         InterpolationType it) {
+  return conv_backward_impl(go, map, &iw, x, w, b, K, it);
+}
+
+// ---- transposed (include/layers/mapped_transposed_convolution_layer.h:62-149) --
+torch::Tensor tconv_forward_impl(torch::Tensor x, torch::Tensor map, const torch::Tensor *iw, torch::Tensor weight,
+                                 torch::Tensor bias, int64_t oh, int64_t ow, int64_t K, InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4 && weight.dim() == 3 && bias.dim() == 1, "input (B,C,H,W), weight (Cin,Cout,K), bias (Cout)");
+  check(x, "input", x);
+  check_float(map, "sample_map", x);
+  check_float(weight, "weight", x);
+  check_float(bias, "bias", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw, true, K);
+  TORCH_CHECK(x.size(2) == m.H && x.size(3) == m.W, "input spatial size must match the sample map");
+  TORCH_CHECK(weight.size(0) == x.size(1) && weight.size(2) == K && bias.size(0) == weight.size(1),
+              "weight / bias shapes do not match the input");
+  TORCH_CHECK(oh > 0 && ow > 0, "output size must be positive");
+  c10::cuda::CUDAGuard guard(x.device());
+  const ConvArgs a{x.size(0), x.size(1), weight.size(1), x.size(2), x.size(3), oh, ow, K, m.P, dtype_of(x), (int)it,
+                   dtype_of(x) == SPH_F32 ? precision() : SPH_PRECISION_EXACT};
+  torch::Tensor plan = get_plan(map, iw, a.IH * a.IW, a.K, a.P, a.interp, a.OH, a.OW);
+  torch::Tensor out = torch::empty({a.B, a.Cout, a.OH, a.OW}, x.options());
+  const size_t wb = sph_conv_workspace_bytes(SPH_TCONV_FORWARD, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
+                                             a.interp, a.prec);
+  torch::Tensor ws = workspace(wb, x);
+  ok(sph_mapped_tconv_forward(x.data_ptr(), plan.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(), a.B, a.Cin,
+                              a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.dtype, a.prec, ws.data_ptr(), wb, stream()),
+     "sph_mapped_tconv_forward");
+  return out;
+}
+
+std::vector<torch::Tensor> tconv_backward_impl(torch::Tensor go, torch::Tensor map, const torch::Tensor *iw, torch::Tensor x,
+                                               torch::Tensor weight, torch::Tensor bias, int64_t K, InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4 && go.dim() == 4 && weight.dim() == 3, "input/grad_output (B,C,H,W), weight (Cin,Cout,K)");
+  go = go.contiguous();
+  check(x, "input", x);
+  check_float(go, "grad_output", x);
+  check_float(map, "sample_map", x);
+  check_float(weight, "weight", x);
+  check_float(bias, "bias", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw, true, K);
+  TORCH_CHECK(x.size(2) == m.H && x.size(3) == m.W, "input spatial size must match the sample map");
+  TORCH_CHECK(weight.size(0) == x.size(1) && weight.size(2) == K, "weight shape does not match the input");
+  TORCH_CHECK(go.size(0) == x.size(0) && go.size(1) == weight.size(1), "grad_output shape does not match the weight");
+  c10::cuda::CUDAGuard guard(x.device());
+  const ConvArgs a{x.size(0), x.size(1), weight.size(1), x.size(2), x.size(3), go.size(2), go.size(3), K, m.P, dtype_of(x),
+                   (int)it, dtype_of(x) == SPH_F32 ? precision() : SPH_PRECISION_EXACT};
+  torch::Tensor gx = torch::empty_like(x), gw = torch::empty_like(weight), gb = torch::empty({a.Cout}, x.options());
+  size_t wb = sph_conv_workspace_bytes(SPH_TCONV_BACKWARD_INPUT, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
+                                       a.dtype, a.interp, a.prec);
+  torch::Tensor ws = workspace(wb, x);
+  ok(sph_mapped_tconv_backward_input(go.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr, weight.data_ptr(),
+                                     gx.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp,
+                                     a.prec, ws.data_ptr(), wb, stream()),
+     "sph_mapped_tconv_backward_input");
+  wb = sph_conv_workspace_bytes(SPH_TCONV_BACKWARD_WEIGHT, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
+                                a.interp, a.prec);
+  torch::Tensor ws2 = workspace(wb, x);
+  ok(sph_mapped_tconv_backward_weight(go.data_ptr(), x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr,
+                                      gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
+                                      a.dtype, a.interp, a.prec, ws2.data_ptr(), wb, stream()),
+     "sph_mapped_tconv_backward_weight");
+  return {gx, gw, gb};
+}
+
+torch::Tensor mapped_transposed_conv_forward(torch::Tensor x, torch::Tensor map, torch::Tensor w, torch::Tensor b, int64_t oh,
+                                             int64_t ow, int64_t K, InterpolationType it) {
+  return tconv_forward_impl(x, map, nullptr, w, b, oh, ow, K, it);
+}
+std::vector<torch::Tensor> mapped_transposed_conv_backward(torch::Tensor go, torch::Tensor map, torch::Tensor x,
+                                                           torch::Tensor w, torch::Tensor b, int64_t K, InterpolationType it) {
+  return tconv_backward_impl(go, map, nullptr, x, w, b, K, it);
+}
+torch::Tensor weighted_mapped_transposed_conv_forward(torch::Tensor x, torch::Tensor map, torch::Tensor iw, torch::Tensor w,
+                                                      torch::Tensor b, int64_t oh, int64_t ow, int64_t K,
+                                                      InterpolationType it) {
+  return tconv_forward_impl(x, map, &iw, w, b, oh, ow, K, it);
+}
+std::vector<torch::Tensor> weighted_mapped_transposed_conv_backward(torch::Tensor go, torch::Tensor map, torch::Tensor iw,
+                                                                    torch::Tensor x, torch::Tensor w, torch::Tensor b,
+                                                                    int64_t K, InterpolationType it) {
+  return tconv_backward_impl(go, map, &iw, x, w, b, K, it);
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  // include/layers/enum_export.h:8-29
+  py::enum_<InterpolationType>(m, "InterpolationType", py::arithmetic(), "How a fractional map coordinate is sampled")
+      .value("NEAREST", InterpolationType::NEAREST)
+      .value("BILINEAR", InterpolationType::BILINEAR)
+      .value("BISPHERICAL", InterpolationType::BISPHERICAL);
+  py::enum_<DistortionType>(m, "DistortionType", py::arithmetic(), "Lens distortion model")
+      .value("SIMPLE_RADIAL", DistortionType::SIMPLE_RADIAL)
+      .value("BROWN", DistortionType::BROWN)
+      .value("FISHEYE", DistortionType::FISHEYE);
+
+  m.def("resample_to_map", &resample_to_map);
+  m.def("resample_from_map", &resample_from_map);
+  m.def("weighted_resample_to_map", &weighted_resample_to_map);
+  m.def("weighted_resample_from_map", &weighted_resample_from_map);
+  m.def("mapped_max_pool", &mapped_max_pool);
+  m.def("mapped_max_unpool", &mapped_max_unpool);
+  m.def("weighted_mapped_max_pool", &weighted_mapped_max_pool);
+  m.def("weighted_mapped_max_unpool", &weighted_mapped_max_unpool);
+  m.def("mapped_conv_forward", &mapped_conv_forward);
+  m.def("mapped_conv_backward", &mapped_conv_backward);
+  m.def("weighted_mapped_conv_forward", &weighted_mapped_conv_forward);
+  m.def("weighted_mapped_conv_backward", &weighted_mapped_conv_backward);
+  m.def("mapped_transposed_conv_forward", &mapped_transposed_conv_forward);
+  m.def("mapped_transposed_conv_backward", &mapped_transposed_conv_backward);
+  m.def("weighted_mapped_transposed_conv_forward", &weighted_mapped_transposed_conv_forward);
+  m.def("weighted_mapped_transposed_conv_backward", &weighted_mapped_transposed_conv_backward);
+
+  m.def("set_precision", &set_precision, "'fp32' (exact SIMT path) or 'bf16' (tcgen05 tensor cores) for float32 convolutions");
+  m.def("get_precision", &get_precision);
+  m.def("clear_plan_cache", &clear_plan_cache);
+  m.def("plan_cache_size", &plan_cache_size);
+  m.def("abi_version", []() { return sph_version(); });
+}

@@ -1,0 +1,209 @@
+"""ctypes binding of the C ABI declared in include/sphmap.h.
+
+Each wrapper takes CUDA torch tensors, allocates the outputs (and the scratch
+the ABI asks for) with torch, and passes raw device pointers, sizes and the
+current stream to libsphmap.so.  Nothing here computes anything; if the
+library is missing the import fails.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "_spherical_distortion_ext", "libsphmap.so")
+
+F32, F64 = 0, 1
+NEAREST, BILINEAR, BISPHERICAL = 0, 1, 2
+EXACT, BF16 = 0, 1
+CONV_FORWARD, CONV_BACKWARD_INPUT, CONV_BACKWARD_WEIGHT = 0, 1, 2
+TCONV_FORWARD, TCONV_BACKWARD_INPUT, TCONV_BACKWARD_WEIGHT = 3, 4, 5
+
+SYMBOLS = [
+    "sph_status_string", "sph_version", "sph_resample_from_map", "sph_plan_bytes", "sph_plan_build",
+    "sph_resample_to_map", "sph_mapped_max_pool", "sph_mapped_max_unpool", "sph_conv_workspace_bytes",
+    "sph_mapped_conv_forward", "sph_mapped_conv_backward_input", "sph_mapped_conv_backward_weight",
+    "sph_mapped_tconv_forward", "sph_mapped_tconv_backward_input", "sph_mapped_tconv_backward_weight",
+]
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError("libsphmap.so not built (run spherical-package_b200/build.py): " + LIB_PATH)
+lib = ctypes.CDLL(LIB_PATH)
+lib.sph_status_string.restype = ctypes.c_char_p
+lib.sph_status_string.argtypes = [ctypes.c_int]
+lib.sph_plan_bytes.restype = ctypes.c_size_t
+lib.sph_conv_workspace_bytes.restype = ctypes.c_size_t
+
+_vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+
+
+class SphError(RuntimeError):
+    pass
+
+
+def _ok(rc, what):
+    if rc != 0:
+        raise SphError("%s failed: %s" % (what, lib.sph_status_string(rc).decode()))
+
+
+def _ptr(t):
+    return _vp(0 if t is None else t.data_ptr())
+
+
+def _dt(t):
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.float64:
+        return F64
+    raise TypeError("float32/float64 only")
+
+
+def _stream():
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def _ints(*v):
+    return [_i64(int(x)) for x in v]
+
+
+def _P(iw):
+    return 0 if iw is None else iw.shape[-1]
+
+
+def _bytes(n, like):
+    return torch.empty(max(int(n), 1), dtype=torch.uint8, device=like.device)
+
+
+def resample_from_map(x, smap, interp, iw=None):
+    B, C, H, W = x.shape
+    MH, MW = smap.shape[:2]
+    y = torch.empty(B, C, MH, MW, dtype=x.dtype, device=x.device)
+    _ok(lib.sph_resample_from_map(_ptr(x), _ptr(smap), _ptr(iw), _ptr(y), *_ints(B, C, H, W, MH, MW, _P(iw)),
+                                  _int(_dt(x)), _int(int(interp)), _stream()), "sph_resample_from_map")
+    return y
+
+
+def plan_build(smap, iw, n_src, K, interp, dstH, dstW):
+    """Scatter plan for `smap` ((..., K, [P,] 2) flattened to n_src positions) pointing into a dstH x dstW image."""
+    P = _P(iw)
+    n = lib.sph_plan_bytes(*_ints(n_src, K, P), _int(int(interp)), *_ints(dstH, dstW), _int(_dt(smap)))
+    if n == 0:
+        raise SphError("sph_plan_bytes: map too large")
+    plan = _bytes(n, smap)
+    _ok(lib.sph_plan_build(_ptr(smap), _ptr(iw), *_ints(n_src, K, P), _int(int(interp)), *_ints(dstH, dstW),
+                           _int(_dt(smap)), _ptr(plan), _sz(n), _stream()), "sph_plan_build")
+    return plan
+
+
+def resample_to_map(x, plan, oh, ow):
+    B, C, MH, MW = x.shape
+    out = torch.empty(B, C, int(oh), int(ow), dtype=x.dtype, device=x.device)
+    _ok(lib.sph_resample_to_map(_ptr(x), _ptr(plan), _ptr(out), *_ints(B, C, MH, MW, oh, ow), _int(_dt(x)), _stream()),
+        "sph_resample_to_map")
+    return out
+
+
+def mapped_max_pool(x, smap, K, interp, iw=None, out=None, idx=None):
+    B, C, IH, IW = x.shape
+    OH, OW = smap.shape[:2]
+    if out is None:
+        out = torch.empty(B, C, OH, OW, dtype=x.dtype, device=x.device)
+        idx = torch.empty(B, C, OH, OW, dtype=torch.int64, device=x.device)
+    _ok(lib.sph_mapped_max_pool(_ptr(x), _ptr(smap), _ptr(iw), _ptr(out), _ptr(idx),
+                                *_ints(B, C, IH, IW, OH, OW, K, _P(iw)), _int(_dt(x)), _int(int(interp)), _stream()),
+        "sph_mapped_max_pool")
+    return out, idx
+
+
+def mapped_max_unpool(g, idx, smap, ih, iw_, K, interp, iw=None, out=None):
+    B, C, OH, OW = g.shape
+    if out is None:
+        out = torch.empty(B, C, int(ih), int(iw_), dtype=g.dtype, device=g.device)
+    _ok(lib.sph_mapped_max_unpool(_ptr(g), _ptr(idx), _ptr(smap), _ptr(iw), _ptr(out),
+                                  *_ints(B, C, ih, iw_, OH, OW, K, _P(iw)), _int(_dt(g)), _int(int(interp)), _stream()),
+        "sph_mapped_max_unpool")
+    return out
+
+
+def conv_workspace(op, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, like):
+    n = lib.sph_conv_workspace_bytes(_int(op), *_ints(B, Cin, Cout, IH, IW, OH, OW, K, P), _int(dtype),
+                                     _int(int(interp)), _int(precision))
+    return _bytes(n, like), n
+
+
+def conv_forward(x, smap, weight, bias, K, interp, iw=None, precision=EXACT, out=None, ws=None):
+    B, Cin, IH, IW = x.shape
+    OH, OW = smap.shape[:2]
+    Cout = weight.shape[0]
+    if out is None:
+        out = torch.empty(B, Cout, OH, OW, dtype=x.dtype, device=x.device)
+    if ws is None:
+        ws = conv_workspace(CONV_FORWARD, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
+    _ok(lib.sph_mapped_conv_forward(_ptr(x), _ptr(smap), _ptr(iw), _ptr(weight), _ptr(bias), _ptr(out),
+                                    *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)), _int(_dt(x)), _int(int(interp)),
+                                    _int(precision), _ptr(ws[0]), _sz(ws[1]), _stream()), "sph_mapped_conv_forward")
+    return out
+
+
+def conv_backward_input(go, plan, weight, IH, IW, K, precision=EXACT, out=None, ws=None):
+    B, Cout, OH, OW = go.shape
+    Cin = weight.shape[1]
+    if out is None:
+        out = torch.empty(B, Cin, int(IH), int(IW), dtype=go.dtype, device=go.device)
+    if ws is None:
+        ws = conv_workspace(CONV_BACKWARD_INPUT, B, Cin, Cout, IH, IW, OH, OW, K, 0, _dt(go), 0, precision, go)
+    _ok(lib.sph_mapped_conv_backward_input(_ptr(go), _ptr(plan), _ptr(weight), _ptr(out),
+                                           *_ints(B, Cin, Cout, IH, IW, OH, OW, K), _int(_dt(go)), _int(precision),
+                                           _ptr(ws[0]), _sz(ws[1]), _stream()), "sph_mapped_conv_backward_input")
+    return out
+
+
+def conv_backward_weight(go, x, smap, K, interp, iw=None, precision=EXACT, ws=None):
+    B, Cin, IH, IW = x.shape
+    _, Cout, OH, OW = go.shape
+    gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
+    gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
+    if ws is None:
+        ws = conv_workspace(CONV_BACKWARD_WEIGHT, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
+    _ok(lib.sph_mapped_conv_backward_weight(_ptr(go), _ptr(x), _ptr(smap), _ptr(iw), _ptr(gw), _ptr(gb),
+                                            *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)), _int(_dt(x)),
+                                            _int(int(interp)), _int(precision), _ptr(ws[0]), _sz(ws[1]), _stream()),
+        "sph_mapped_conv_backward_weight")
+    return gw, gb
+
+
+def tconv_forward(x, plan, weight, bias, oh, ow, K, precision=EXACT):
+    B, Cin, IH, IW = x.shape
+    Cout = weight.shape[1]
+    out = torch.empty(B, Cout, int(oh), int(ow), dtype=x.dtype, device=x.device)
+    ws = conv_workspace(TCONV_FORWARD, B, Cin, Cout, IH, IW, oh, ow, K, 0, _dt(x), 0, precision, x)
+    _ok(lib.sph_mapped_tconv_forward(_ptr(x), _ptr(plan), _ptr(weight), _ptr(bias), _ptr(out),
+                                     *_ints(B, Cin, Cout, IH, IW, oh, ow, K), _int(_dt(x)), _int(precision),
+                                     _ptr(ws[0]), _sz(ws[1]), _stream()), "sph_mapped_tconv_forward")
+    return out
+
+
+def tconv_backward_input(go, smap, weight, K, interp, iw=None, precision=EXACT):
+    B, Cout, OH, OW = go.shape
+    IH, IW = smap.shape[:2]
+    Cin = weight.shape[0]
+    gx = torch.empty(B, Cin, IH, IW, dtype=go.dtype, device=go.device)
+    ws = conv_workspace(TCONV_BACKWARD_INPUT, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(go), interp, precision, go)
+    _ok(lib.sph_mapped_tconv_backward_input(_ptr(go), _ptr(smap), _ptr(iw), _ptr(weight), _ptr(gx),
+                                            *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)), _int(_dt(go)),
+                                            _int(int(interp)), _int(precision), _ptr(ws[0]), _sz(ws[1]), _stream()),
+        "sph_mapped_tconv_backward_input")
+    return gx
+
+
+def tconv_backward_weight(go, x, smap, K, interp, iw=None, precision=EXACT):
+    B, Cin, IH, IW = x.shape
+    _, Cout, OH, OW = go.shape
+    gw = torch.empty(Cin, Cout, K, dtype=x.dtype, device=x.device)
+    gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
+    ws = conv_workspace(TCONV_BACKWARD_WEIGHT, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
+    _ok(lib.sph_mapped_tconv_backward_weight(_ptr(go), _ptr(x), _ptr(smap), _ptr(iw), _ptr(gw), _ptr(gb),
+                                             *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)), _int(_dt(x)),
+                                             _int(int(interp)), _int(precision), _ptr(ws[0]), _sz(ws[1]), _stream()),
+        "sph_mapped_tconv_backward_weight")
+    return gw, gb
