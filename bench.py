@@ -1,0 +1,448 @@
+#!/usr/bin/env python
+"""Benchmark of the mapped-operator path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload encoder|pool|resample] [--precision bf16|fp32] [--batch B]
+
+Default workload: the batch-sharded spherical encoder stack (four bilinear
+mapped convolutions + ReLU on 3x3 gnomonic maps, channels 3->64->128->256->256,
+512x1024 -> 128x256, global batch 64 split evenly over the GPUs), one step =
+forward + backward (dInput, dW, dBias of every layer) + sum-allreduce of the
+weight gradients.  Metric: algorithmic TFLOP/s (2*M*N*K of the three
+contractions per layer) of the whole job.
+
+One JSON line is printed by rank 0.  `value` is measured with the inputs
+resident in HBM; `e2e` goes through the public nn.Module API with the input
+batch copied from pinned host memory and the loss read back every step.
+`--impl reference` times the reference's own CPU implementation (the compiled
+reference modules when present, else the plain-C oracle port) on a bounded
+sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "spherical-package_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], bf16_tflops_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
+        if not sm:
+            return None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v.lower().startswith("active")})
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        return dict(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx) if mx else None, reasons=reasons, samples=len(sm))
+
+
+def dist_setup(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, local, world
+
+
+def barrier_sync(world):
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms, world, dev):
+    if world == 1:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed_loop(step, steps, warmup, world, dev, sampler=None):
+    for _ in range(warmup):
+        step()
+    barrier_sync(world)
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier_sync(world)
+    clocks = sampler.stop() if sampler else None
+    return max_over_ranks(e0.elapsed_time(e1), world, dev), clocks
+
+
+# ---------------------------------------------------------------------------
+# encoder stack (flagship)
+# ---------------------------------------------------------------------------
+def cpu_encoder_seconds(cfg, impl, images):
+    """Reference CPU path (forward + backward of the four layers) on `images` images; returns seconds."""
+    x = cfg["x"][:images]
+    go = cfg["grad_output"][:images]
+    K, it = cfg["K"], cfg["interp"]
+    t0 = time.perf_counter()
+    acts, ins, h = [], [], x
+    for li in range(4):
+        ins.append(h)
+        h = impl.mapped_conv_forward(h, cfg["maps"][li], cfg["weights"][li], cfg["biases"][li], K, it).relu_()
+        acts.append(h)
+    g = go
+    for li in reversed(range(4)):
+        g = g * (acts[li] > 0)
+        g, _, _ = impl.mapped_conv_backward(g, cfg["maps"][li], ins[li], cfg["weights"][li], cfg["biases"][li], K, it)
+    return time.perf_counter() - t0
+
+
+def pick_cpu_impl():
+    from oracle import port, ref
+    if ref.available():
+        return ref, "reference"
+    return port, "port"
+
+
+def run_encoder(args, rank, local, world):
+    from sphmap import capi, workloads as wl
+    from sphmap.parallel import EncoderStack, GradReducer, shard_batch
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    prec = capi.BF16 if args.precision == "bf16" else capi.EXACT
+    B = args.batch
+    lo, hi = shard_batch(B, rank, world)
+    cfg = wl.config4(B=B, H=args.height, W=2 * args.height)
+    x_host = cfg["x"][lo:hi].contiguous().pin_memory()
+    go = cfg["grad_output"][lo:hi].contiguous().to(dev)
+    x_dev = x_host.to(dev)
+    flops_step = 3 * wl.encoder_flops(B, args.height, 2 * args.height)
+
+    # --- device-resident arm: straight through the C ABI, every conv launch bracketed by CUDA events ---
+    phases = [(li, ph) for li in range(4) for ph in ("fwd", "dw", "dx")]
+
+    def new_timers():
+        return {k: [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)] for k in phases}
+
+    stack = EncoderStack(cfg, dev, prec, hi - lo, GradReducer(), None)
+    per_step_timers = []
+
+    def step():
+        stack.step(x_dev, go)
+
+    def step_timed():
+        stack.timers = new_timers()
+        per_step_timers.append(stack.timers)
+        stack.step(x_dev, go)
+
+    l0 = capi.lib.sph_launch_count()
+    for _ in range(args.warmup):
+        step()
+    launches_per_step = (capi.lib.sph_launch_count() - l0) // max(args.warmup, 1)
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, clocks = timed_loop(step_timed, args.steps, 0, world, dev, sampler)
+    # per-launch durations of the timed region itself (events were recorded on the launching stream)
+    per_launch = {k: sum(t[k][0].elapsed_time(t[k][1]) for t in per_step_timers) / len(per_step_timers) for k in phases}
+    value = flops_step * args.steps / (ms * 1e-3) / 1e12
+
+    # --- end-to-end arm: public nn.Module API, pinned host input copied in and loss read back per step ---
+    import _spherical_distortion_ext as ext
+    from spherical_distortion.nn import InterpolationType, MappedConvolution
+    ext.set_precision(args.precision)
+    mods = []
+    for li, (ci, co, _, _, _) in enumerate(cfg["layers"]):
+        m = MappedConvolution(ci, co, 9, InterpolationType.BILINEAR).to(dev)
+        with torch.no_grad():
+            m.weight.copy_(cfg["weights"][li])
+            m.bias.copy_(cfg["biases"][li])
+        mods.append(m)
+    maps = [t.to(dev) for t in cfg["maps"]]
+    params = [p for m in mods for p in (m.weight, m.bias)]
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        xb = x_host.to(dev, non_blocking=True)
+        h = xb
+        for m, sm in zip(mods, maps):
+            h = torch.relu(m(h, sm))
+        loss = (h * go).sum()
+        for p in params:
+            p.grad = None
+        loss.backward()
+        if world > 1:
+            flat = torch.cat([p.grad.reshape(-1) for p in params])
+            dist.all_reduce(flat)
+        loss_host.copy_(loss.detach(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    del stack
+    torch.cuda.empty_cache()
+    e2e_ms, _ = timed_loop(e2e_step, args.steps, args.warmup, world, dev)
+    e2e_value = flops_step * args.steps / (e2e_ms * 1e-3) / 1e12
+
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    dom = max(per_launch, key=per_launch.get)
+    li, ph = dom
+    ci, co, _, (oh, ow), _ = cfg["layers"][li]
+    dom_flops = 2 * (hi - lo) * co * ci * 9 * oh * ow
+    tensor_peak = peaks["bf16_tflops_sustained"]
+    achieved = dom_flops / (per_launch[dom] * 1e-3) / 1e12
+    out = {
+        "metric": "mapped-conv fwd+bwd TFLOP/s", "value": round(value, 3), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16" if args.precision == "bf16" else "f32", "data": "synthetic",
+        "config": {"workload": "spherical encoder stack (BASELINE config 4): 4x bilinear mapped conv + ReLU on 3x3 "
+                               "gnomonic maps, 3->64->128->256->256, %dx%d -> %dx%d, fwd+bwd+dW allreduce"
+                               % (args.height, 2 * args.height, args.height // 4, args.height // 2),
+                   "global_batch": B, "parallelism": "batch-sharded dp%d" % world, "precision": args.precision,
+                   "l2": "activations (GBs per layer) exceed the 126 MB L2; no flush needed",
+                   "mpix_per_s": round(B * sum(oh * ow for _, _, _, (oh, ow), _ in cfg["layers"]) * args.steps
+                                       / (ms * 1e-3) / 1e6, 1)},
+        "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 4 * world,
+                "d2h_bytes_per_step": 4 * world, "ms_per_step": round(e2e_ms / args.steps, 3),
+                "api": "spherical_distortion.nn.MappedConvolution + autograd"},
+        "gpu_launches": int(launches_per_step * args.steps),
+        "roofline": {"bound": "tensor", "kernel": "layer %d %s (Cin=%d, Cout=%d, %dx%d, local batch %d)"
+                                                  % (li + 1, ph, ci, co, oh, ow, hi - lo),
+                     "achieved": round(achieved, 2), "peak": tensor_peak, "unit": "TFLOP/s",
+                     "frac": round(achieved / tensor_peak, 4), "traffic": None,
+                     "peak_source": peaks["source"] + " bf16 sustained (kernel timed inside a long step)",
+                     "per_launch_ms": {"L%d.%s" % (k[0] + 1, k[1]): round(v, 3) for k, v in per_launch.items()}},
+        "clocks": clocks,
+    }
+    if world == 1:
+        impl, kind = pick_cpu_impl()
+        cores = os.cpu_count()
+        torch.set_num_threads(cores)
+        os.environ["OMP_NUM_THREADS"] = str(cores)
+        images = 4
+        secs = cpu_encoder_seconds(cfg, impl, images)
+        out["cpu_baseline"] = {"value": round(3 * wl.encoder_flops(images, args.height, 2 * args.height) / secs / 1e12, 5),
+                               "unit": "TFLOP/s", "cores": cores, "kind": kind,
+                               "sample": "%d image(s) of the same stack, fwd+bwd, %.1f s wall" % (images, secs)}
+    return out
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's own CPU implementation of the same stack on the host cores."""
+    if rank != 0:
+        return None
+    from sphmap import workloads as wl
+    impl, kind = pick_cpu_impl()
+    cores = os.cpu_count()
+    torch.set_num_threads(cores)
+    images = 4
+    cfg = wl.config4(B=images, H=args.height, W=2 * args.height)
+    for _ in range(min(args.warmup, 1)):
+        cpu_encoder_seconds(cfg, impl, images)
+    steps = min(args.steps, 3)
+    t = sum(cpu_encoder_seconds(cfg, impl, images) for _ in range(steps))
+    flops = 3 * wl.encoder_flops(images, args.height, 2 * args.height) * steps
+    v = round(flops / t / 1e12, 5)
+    sample = "%d image(s) per step (global batch of the GPU arm: %d), %d steps, %.1f s" % (images, args.batch, steps, t)
+    return {"impl": "reference", "metric": "mapped-conv fwd+bwd TFLOP/s", "value": v, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": round(t / steps * 1e3, 1),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "spherical encoder stack (BASELINE config 4) on the reference CPU path", "sample": sample},
+            "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+# ---------------------------------------------------------------------------
+# HBM-bound workloads: max pooling (config 2) and tangent-image resampling (config 1)
+# ---------------------------------------------------------------------------
+def run_pool(args, rank, local, world):
+    from sphmap import capi, workloads as wl
+    from sphmap.parallel import shard_batch
+    dev = torch.device("cuda", local)
+    cfg = wl.config2(B=args.batch if args.batch != 64 else 8)
+    B = cfg["x"].shape[0]
+    lo, hi = shard_batch(B, rank, world)
+    x, go, m = cfg["x"][lo:hi].to(dev), cfg["grad_output"][lo:hi].to(dev), cfg["map"].to(dev)
+    out, idx = capi.mapped_max_pool(x, m, 9, 0)
+    gin = torch.empty_like(x)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ef = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    tf, tb = [], []
+
+    def step():
+        flush.zero_()
+        ef[0].record()
+        capi.mapped_max_pool(x, m, 9, 0, None, out, idx)
+        ef[1].record()
+        flush.zero_()
+        ef[2].record()
+        capi.mapped_max_unpool(go, idx, m, x.shape[2], x.shape[3], 9, 0, None, gin)
+        ef[3].record()
+        torch.cuda.synchronize()
+        tf.append(ef[0].elapsed_time(ef[1]))
+        tb.append(ef[2].elapsed_time(ef[3]))
+
+    for _ in range(args.warmup):
+        step()
+    tf.clear(), tb.clear()
+    sampler = ClockSampler(local) if rank == 0 else None
+    barrier_sync(world)
+    if sampler:
+        sampler.start()
+    for _ in range(args.steps):
+        step()
+    clocks = sampler.stop() if sampler else None
+    n = hi - lo
+    fwd_bytes = x.numel() * 4 + out.numel() * 4 + idx.numel() * 8 + m.numel() * 4
+    f_ms, b_ms = sum(tf) / len(tf), sum(tb) / len(tb)
+    f_ms, b_ms = max_over_ranks(f_ms, world, dev), max_over_ranks(b_ms, world, dev)
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    gbs = 2 * fwd_bytes * world / ((f_ms + b_ms) * 1e-3) / 1e9
+    return {"metric": "mapped max pool fwd+bwd HBM GB/s", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(f_ms + b_ms, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "mapped max pool (BASELINE config 2): B=%d C=64 256x512 -> 128x256, K=9, nearest, "
+                                   "uniform-random map" % B, "l2": "256 MB flush before every launch", "local_batch": n},
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "max_pool_kernel (forward)", "achieved": round(fwd_bytes / (f_ms * 1e-3) / 1e9, 1),
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(fwd_bytes / (f_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                         "traffic": None, "fwd_ms": round(f_ms, 4), "bwd_ms": round(b_ms, 4),
+                         "bwd_achieved": round(fwd_bytes / (b_ms * 1e-3) / 1e9, 1)},
+            "clocks": clocks}
+
+
+def run_resample(args, rank, local, world):
+    from sphmap import capi, workloads as wl
+    from sphmap.parallel import shard_batch
+    dev = torch.device("cuda", local)
+    B = args.batch if args.batch != 64 else 8
+    cfg = wl.config1(B=B)
+    lo, hi = shard_batch(B, rank, world)
+    x, m = cfg["x"][lo:hi].to(dev), cfg["map"].to(dev)
+    H, W = cfg["out_hw"]
+    plan = capi.plan_build(m, None, m.shape[0] * m.shape[1], 1, 1, H, W)
+    y = capi.resample_from_map(x, m, 1)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    tg, ts = [], []
+
+    def step():
+        flush.zero_()
+        ev[0].record()
+        capi.resample_from_map(x, m, 1)
+        ev[1].record()
+        flush.zero_()
+        ev[2].record()
+        capi.resample_to_map(y, plan, H, W)
+        ev[3].record()
+        torch.cuda.synchronize()
+        tg.append(ev[0].elapsed_time(ev[1]))
+        ts.append(ev[2].elapsed_time(ev[3]))
+
+    for _ in range(args.warmup):
+        step()
+    tg.clear(), ts.clear()
+    barrier_sync(world)
+    for _ in range(args.steps):
+        step()
+    n = hi - lo
+    C, ns = x.shape[1], m.shape[0] * m.shape[1]
+    g_bytes = n * C * ns * 4 + m.numel() * 4 + n * C * min(4 * ns, H * W) * 4
+    s_bytes = n * C * ns * 4 + m.numel() * 4 + n * C * H * W * 4
+    g_ms, s_ms = max_over_ranks(sum(tg) / len(tg), world, dev), max_over_ranks(sum(ts) / len(ts), world, dev)
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    return {"metric": "tangent-image resample HBM GB/s", "value": round((g_bytes + s_bytes) * world / ((g_ms + s_ms) * 1e-3) / 1e9, 1),
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(g_ms + s_ms, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "tangent-image resampling (BASELINE config 1): B=%d C=3 512x1024 <-> 20x64x64, bilinear" % B,
+                       "l2": "256 MB flush before every launch"},
+            "gpu_launches": 2 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "resample_from_map_kernel", "achieved": round(g_bytes / (g_ms * 1e-3) / 1e9, 1),
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(g_bytes / (g_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                         "traffic": None, "gather_ms": round(g_ms, 4), "scatter_ms": round(s_ms, 4),
+                         "scatter_achieved": round(s_bytes / (s_ms * 1e-3) / 1e9, 1)}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="encoder", choices=["encoder", "pool", "resample"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--batch", type=int, default=64, help="global batch")
+    ap.add_argument("--height", type=int, default=512, help="input height of the encoder stack (width = 2x)")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        out = run_reference(args, rank, world)
+        if out is not None:
+            print(json.dumps(out), flush=True)
+        return 0
+    rank, local, world = dist_setup(args.gpus)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+    fn = {"encoder": run_encoder, "pool": run_pool, "resample": run_resample}[args.workload]
+    out = fn(args, rank, local, world)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -51,11 +51,14 @@ enum sph_precision { SPH_PRECISION_EXACT = 0, SPH_PRECISION_BF16 = 1 };
 const char *sph_status_string(int status);
 /* Library version, major*10000 + minor*100 + patch. */
 int sph_version(void);
+/* Number of kernels this library has launched in this process so far (a
+ * tracing aid for benchmarks; no counterpart in the reference). */
+unsigned long long sph_launch_count(void);
 
 /* ------------------------------------------------------------------------
  * resample_from_map ("Unresample"): y[b,c,i] = interp(x[b,c], map[i]).
  * Replaces spherical::ResampleFromMap, ext_modules/include/layers/
- * resample_layer.h:70-88 (weighted twin: weighted_resample_layer.h:80-103).
+ * resample_layer.h:62-82 (weighted twin: weighted_resample_layer.h:77-105).
  * x (B,C,H,W); map (MH,MW[,P],2); iw (MH,MW,P) or NULL; y (B,C,MH,MW).
  * ---------------------------------------------------------------------- */
 int sph_resample_from_map(const void *x, const void *map, const void *iw, void *y, int64_t B, int64_t C,
@@ -83,8 +86,8 @@ int sph_plan_build(const void *map, const void *iw, int64_t n_src, int64_t K, in
 
 /* ------------------------------------------------------------------------
  * resample_to_map ("Resample"): out[b,c] = sum_i scatter(x[b,c,i], map[i]).
- * Replaces spherical::ResampleToMap, resample_layer.h:45-68 (weighted twin:
- * weighted_resample_layer.h:54-78).  `plan` was built from the (MH,MW[,P],2)
+ * Replaces spherical::ResampleToMap, resample_layer.h:40-60 (weighted twin:
+ * weighted_resample_layer.h:49-75).  `plan` was built from the (MH,MW[,P],2)
  * map with K = 1 and dst = (OH,OW).  x (B,C,MH,MW); out (B,C,OH,OW), fully
  * written (no pre-zeroing needed).
  * ---------------------------------------------------------------------- */

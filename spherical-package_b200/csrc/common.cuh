@@ -172,7 +172,15 @@ __device__ __forceinline__ PlanView<T> plan_view(const void *plan, int n_keys, b
   return PlanView<T>{(const int *)(p + h->off_offsets), (const int *)(p + h->off_src), (const T *)(p + h->off_w)};
 }
 
-inline int launch_status() { return cudaGetLastError() == cudaSuccess ? SPH_OK : SPH_ERR_CUDA; }
+// Kernel launches issued by this library in this process (tracing aid, see sph_launch_count()).
+extern unsigned long long g_launch_count;
+inline void note_launches(int n) { __atomic_fetch_add(&g_launch_count, (unsigned long long)n, __ATOMIC_RELAXED); }
+
+// Status of the launches just issued; n = how many kernels the caller enqueued.
+inline int launch_status(int n = 1) {
+  note_launches(n);
+  return cudaGetLastError() == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
+}
 
 inline int cdiv(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 

@@ -41,6 +41,9 @@ extern "C" const char *sph_status_string(int status) {
 
 extern "C" int sph_version(void) { return 100; }
 
+namespace sph { unsigned long long g_launch_count = 0; }
+extern "C" unsigned long long sph_launch_count(void) { return __atomic_load_n(&sph::g_launch_count, __ATOMIC_RELAXED); }
+
 extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
                                            int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
                                            int precision) {

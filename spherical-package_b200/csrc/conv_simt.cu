@@ -271,7 +271,7 @@ int simt_dw(const void *A, const void *src, const void *map, const void *iw, int
   dw_reduce_kernel<T><<<cdiv(M * CHK, 256), 256, 0, st>>>(partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw);
   bias_partial_kernel<T><<<dim3((unsigned)Cbias, kBiasSplits), 256, 0, st>>>((const T *)gbias_src, (int)B, (int)Cbias, (int)nbias, bpart);
   bias_final_kernel<T><<<cdiv(Cbias, 128), 128, 0, st>>>(bpart, (int)Cbias, (T *)gb);
-  return launch_status();
+  return launch_status(4);
 }
 
 template int simt_gemm<float>(bool, const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t,

@@ -178,7 +178,7 @@ static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int6
   h.off_src = L.off_src;
   h.off_w = L.off_w;
   plan_header_kernel<<<1, 1, 0, st>>>((PlanHeader *)plan, h);
-  return launch_status();
+  return launch_status(7);
 }
 
 }  // namespace sph

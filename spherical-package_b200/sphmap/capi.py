@@ -20,7 +20,7 @@ CONV_FORWARD, CONV_BACKWARD_INPUT, CONV_BACKWARD_WEIGHT = 0, 1, 2
 TCONV_FORWARD, TCONV_BACKWARD_INPUT, TCONV_BACKWARD_WEIGHT = 3, 4, 5
 
 SYMBOLS = [
-    "sph_status_string", "sph_version", "sph_resample_from_map", "sph_plan_bytes", "sph_plan_build",
+    "sph_status_string", "sph_version", "sph_launch_count", "sph_resample_from_map", "sph_plan_bytes", "sph_plan_build",
     "sph_resample_to_map", "sph_mapped_max_pool", "sph_mapped_max_unpool", "sph_conv_workspace_bytes",
     "sph_mapped_conv_forward", "sph_mapped_conv_backward_input", "sph_mapped_conv_backward_weight",
     "sph_mapped_tconv_forward", "sph_mapped_tconv_backward_input", "sph_mapped_tconv_backward_weight",
@@ -32,6 +32,7 @@ lib = ctypes.CDLL(LIB_PATH)
 lib.sph_status_string.restype = ctypes.c_char_p
 lib.sph_status_string.argtypes = [ctypes.c_int]
 lib.sph_plan_bytes.restype = ctypes.c_size_t
+lib.sph_launch_count.restype = ctypes.c_ulonglong
 lib.sph_conv_workspace_bytes.restype = ctypes.c_size_t
 
 _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t

@@ -1,0 +1,118 @@
+"""Batch-sharded execution of mapped-operator stacks.
+
+Every operator of the path is independent per image and the maps, weights and
+biases are small, so the only sharded axis is the batch: each rank (one process
+per GPU) takes a contiguous slice of the batch, runs forward / backward with no
+exchange, and the single collective is the sum-allreduce of the weight and
+bias gradients (NCCL on GPUs, gloo in the CPU tests), issued per layer as soon
+as that layer's gradients are final so that it overlaps the rest of backward.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_batch(B, rank, world):
+    """Contiguous slice [lo, hi) of a batch of B images owned by `rank`; sizes differ by at most one."""
+    base, rem = divmod(B, world)
+    lo = rank * base + min(rank, rem)
+    return lo, lo + base + (1 if rank < rem else 0)
+
+
+class GradReducer:
+    """Sum-allreduce of per-layer (dW, dBias), flattened into one message per layer, asynchronously."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.pending = []
+        self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+
+    def submit(self, gw, gb):
+        if not self.enabled:
+            return
+        flat = torch.cat([gw.reshape(-1), gb.reshape(-1)])
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self.pending.append((work, flat, gw, gb))
+
+    def finish(self):
+        for work, flat, gw, gb in self.pending:
+            work.wait()
+            gw.copy_(flat[:gw.numel()].view_as(gw))
+            gb.copy_(flat[gw.numel():].view_as(gb))
+        self.pending = []
+
+
+class EncoderStack:
+    """The four-layer spherical encoder of the benchmark (mapped conv + ReLU per layer), driven straight
+    through the C ABI: forward, backward (dInput, dW, dBias per layer) and gradient allreduce.  Buffers
+    are allocated once; `step` enqueues one forward+backward pass and returns the loss tensor
+    sum(out * grad_output) (device scalar)."""
+
+    def __init__(self, cfg, device, precision, local_batch, reducer=None, timers=None):
+        from . import capi
+        self.c = capi
+        self.prec = precision
+        self.K, self.interp = cfg["K"], cfg["interp"]
+        self.layers = cfg["layers"]
+        self.dev = device
+        self.B = local_batch
+        self.w = [t.to(device) for t in cfg["weights"]]
+        self.b = [t.to(device) for t in cfg["biases"]]
+        self.maps = [t.to(device) for t in cfg["maps"]]
+        self.reducer = reducer
+        self.timers = timers          # optional {(layer, phase): [start_event, end_event]} to time single launches
+        self.plans, self.acts, self.ws = [], [], {}
+        f32 = dict(dtype=torch.float32, device=device)
+        for li, (ci, co, (ih, iw), (oh, ow), s) in enumerate(self.layers):
+            self.plans.append(capi.plan_build(self.maps[li], None, oh * ow, self.K, self.interp, ih, iw))
+            self.acts.append(torch.empty(local_batch, co, oh, ow, **f32))
+            for op in (capi.CONV_FORWARD, capi.CONV_BACKWARD_INPUT, capi.CONV_BACKWARD_WEIGHT):
+                self.ws[(li, op)] = capi.conv_workspace(op, local_batch, ci, co, ih, iw, oh, ow, self.K, 0, capi.F32,
+                                                        self.interp, precision, self.w[li])
+        self.gx = [torch.empty(local_batch, ci, ih, iw, **f32) for ci, co, (ih, iw), _, _ in self.layers]
+        self.gw, self.gb = [None] * 4, [None] * 4
+
+    def _timed(self, key, fn):
+        if self.timers is not None and key in self.timers:
+            s, e = self.timers[key]
+            s.record()
+            r = fn()
+            e.record()
+            return r
+        return fn()
+
+    def forward(self, x):
+        c = self.c
+        self.inputs = []
+        h = x
+        for li in range(4):
+            self.inputs.append(h)
+            out = self._timed((li, "fwd"), lambda: c.conv_forward(h, self.maps[li], self.w[li], self.b[li], self.K,
+                                                                  self.interp, None, self.prec, out=self.acts[li],
+                                                                  ws=self.ws[(li, c.CONV_FORWARD)]))
+            h = out.relu_()
+        return h
+
+    def backward(self, go):
+        c = self.c
+        g = go
+        for li in reversed(range(4)):
+            ci, co, (ih, iw), (oh, ow), s = self.layers[li]
+            g = g * (self.acts[li] > 0)                         # ReLU backward (activations were rectified in place)
+            gw, gb = self._timed((li, "dw"), lambda: c.conv_backward_weight(
+                g, self.inputs[li], self.maps[li], self.K, self.interp, None, self.prec,
+                ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)]))
+            self.gw[li], self.gb[li] = gw, gb
+            if self.reducer is not None:
+                self.reducer.submit(gw, gb)
+            g = self._timed((li, "dx"), lambda: c.conv_backward_input(
+                g, self.plans[li], self.w[li], ih, iw, self.K, self.prec, out=self.gx[li],
+                ws=self.ws[(li, c.CONV_BACKWARD_INPUT)]))
+        if self.reducer is not None:
+            self.reducer.finish()
+        return g
+
+    def step(self, x, go):
+        out = self.forward(x)
+        loss = (out * go).sum()
+        self.backward(go)
+        return loss
