@@ -17,6 +17,9 @@ int simt_dw(const void *A, const void *src, const void *map, const void *iw, int
             int64_t P, int64_t npix, int interp, int64_t M, int64_t B, void *gw, int64_t sm, int64_t sc, int64_t sk,
             const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st);
 size_t simt_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts);
+size_t simt_bias_workspace(int64_t C, size_t ts);
+template <typename T>
+int simt_bias_grad(const void *g, int64_t B, int64_t C, int64_t n, void *gb, void *ws, cudaStream_t st);
 
 // ---- bf16 tcgen05 path (conv_tc.cu); float32 tensors only ----------------
 size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,

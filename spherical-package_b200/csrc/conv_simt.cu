@@ -213,6 +213,18 @@ __global__ void bias_final_kernel(const T *__restrict__ part, int C, T *__restri
   gb[c] = s;
 }
 
+size_t simt_bias_workspace(int64_t C, size_t ts) { return align_up(ts * (size_t)(C * kBiasSplits), 256); }
+
+// gb[c] = sum over batch and pixels of g[b,c,:] (two fixed-order stages); ws holds C * kBiasSplits partials.
+template <typename T>
+int simt_bias_grad(const void *g, int64_t B, int64_t C, int64_t n, void *gb, void *ws, cudaStream_t st) {
+  bias_partial_kernel<T><<<dim3((unsigned)C, kBiasSplits), 256, 0, st>>>((const T *)g, (int)B, (int)C, (int)n, (T *)ws);
+  bias_final_kernel<T><<<cdiv(C, 128), 128, 0, st>>>((const T *)ws, (int)C, (T *)gb);
+  return launch_status(2);
+}
+template int simt_bias_grad<float>(const void *, int64_t, int64_t, int64_t, void *, void *, cudaStream_t);
+template int simt_bias_grad<double>(const void *, int64_t, int64_t, int64_t, void *, void *, cudaStream_t);
+
 static int dw_splits(int64_t B, int64_t npix, int64_t M, int64_t CHK) {
   const int64_t units = B * ((npix + kDwChunk - 1) / kDwChunk);
   const int64_t tiles = ((CHK + TN - 1) / TN) * ((M + TM - 1) / TM);

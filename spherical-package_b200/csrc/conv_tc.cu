@@ -1,18 +1,24 @@
 // bf16 tensor-core path of the mapped convolution family (float32 tensors,
 // bf16 operands, fp32 accumulation in tensor memory).
 //
-// One persistent, warp-specialised kernel computes
-//     Out[b, n, pix] = sum_{slot, ch} Col[b, pix, (slot, ch)] * Wt[n, (slot, ch)]  (+ bias[n])
-// for a tile of 128 pixels at a time.  Col is never written to HBM: eight
-// producer warps gather it (through the sample map's taps, or through a scatter
-// plan for the adjoint direction) from a channels-last bf16 copy of the source
-// image straight into the 128-byte-swizzled shared-memory layout tcgen05.mma
-// reads; the matching weight tile arrives by one bulk async copy per stage from a
-// pre-swizzled bf16 image of the weights; one thread issues the MMAs into a
-// double-buffered TMEM accumulator; four epilogue warps read TMEM, add the bias
-// and store coalesced NCHW rows.  The reference does the same work per image as
-// im2col kernel + cuBLAS SGEMM + bias kernel with a (Cin*K, OH*OW) column buffer
-// in HBM (src/cuda/mapped_convolution_layer.cu:16-74).
+// Two persistent, warp-specialised kernels cover the six operators:
+//
+//   tc_gemm_kernel   Out[b, n, pix] = sum_j Col[b, pix, j] * Wt[n, j]  (+ bias[n])
+//                    conv forward, conv dInput (through a scatter plan), transposed conv forward (plan) and
+//                    transposed conv dInput.  128 pixels (an 8x16 block of the output grid) per tile.
+//   tc_dw_kernel     dW[n, j] = sum_{b, pix} G[b, n, pix] * Col[b, pix, j]
+//                    weight gradients; split over pixel ranges, partial sums reduced in a fixed order.
+//
+// j runs over (slot, channel) pairs of the sample map.  Col is never written
+// to HBM: eight producer warps gather it (through the sample map's taps, or
+// through a scatter plan for the adjoint direction) from a channels-last bf16
+// copy of the source image straight into the 128-byte-swizzled shared-memory
+// layout tcgen05.mma reads; the other operand (weights, or the gradient tile
+// image) arrives by bulk async copies from a pre-swizzled bf16 image; one
+// thread issues the MMAs into TMEM; four epilogue warps drain TMEM.  The
+// reference does the same work per image as im2col kernel + cuBLAS SGEMM + bias
+// kernel with a (Cin*K, OH*OW) column buffer in HBM
+// (src/cuda/mapped_convolution_layer.cu:16-193).
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -24,68 +30,43 @@ namespace {
 
 using namespace tc;
 
-constexpr int kTileM = 128;          // pixels per tile = TMEM lanes
-constexpr int kChunk = 64;           // GEMM-K columns per pipeline stage (one 128-byte swizzle row)
-constexpr int kAStageBytes = kTileM * 128;
+constexpr int kChunk = 64;  // GEMM columns per 128-byte swizzle row
+constexpr int kTW = 16;     // pixel tiles are kTW wide; 8 rows (forward-type) or 4 rows (weight gradient)
 constexpr int kEpilogueWarps = 4, kProducerWarps = 8;
 constexpr int kProducerThreads = 32 * kProducerWarps;
 constexpr int kThreads = 32 * (kEpilogueWarps + 1 + kProducerWarps);
 constexpr int kFirstProducerThread = 32 * (kEpilogueWarps + 1);
-constexpr int kMaxTapBytes = 40 * 1024;
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kTmemCols = 512;
 
 enum { MODE_DIRECT = 0, MODE_PLAN = 1 };
 
-struct TcParams {
+// ---- column <-> (slot, channel) mapping -------------------------------------------------------
+// Channels are padded to Cp (a multiple of 8 that divides 64, or a multiple of 64).  With Cp >= 64 a chunk
+// is 64 channels of one slot and chunks are ordered channel-block major, slot minor, so that consecutive
+// chunks re-read the same input neighbourhood; with Cp < 64 a chunk holds 64 / Cp whole slots.
+__host__ __device__ inline int num_chunks(int Cp, int K) { return Cp >= 64 ? (Cp / 64) * K : (K * Cp + 63) / 64; }
+__host__ __device__ inline void chunk_vec(int Cp, int K, int chunk, int v, int &slot, int &c0) {
+  if (Cp >= 64) {
+    const int cc = chunk / K;
+    slot = chunk - cc * K;
+    c0 = cc * 64 + v * 8;
+  } else {
+    const int q = chunk * 64 + v * 8;
+    slot = q / Cp;  // >= K for padding columns
+    c0 = q - slot * Cp;
+  }
+}
+
+struct Gather {
   const __nv_bfloat16 *xh;  // (B, SH*SW, Cp) channels-last bf16 source
-  const __nv_bfloat16 *wp;  // weight tile images: [nblk][nchunks][Npb rows][64] bf16, 128B-swizzled
-  const float *bias;        // (Nout) or null
-  float *out;               // (B, Nout, npix)
-  const float *map, *iw;    // direct mode: sample map (+ interpolation weights)
-  const void *plan;         // plan mode
-  int *status;              // set to 1 if a bounded wait gave up
-  int B, Cp, SH, SW, K, P, npix, Nout, Npb, nblk, nchunks, KC, tiles_per_image, interp, nt, stages;
+  const float *map, *iw;    // direct mode: sample map (+ interpolation weights) over the (GH, GW) pixel grid
+  const void *plan;         // plan mode: keyed by (pixel of the (GH, GW) grid) * K + slot
+  int Cp, SH, SW, K, P, GH, GW, interp, nt;
 };
-
-struct Smem {
-  uint8_t *A, *Bw;
-  int *tap_off;
-  float *tap_w;
-  uint64_t *full, *empty, *tfull, *tempty;
-  uint32_t *tmem_ptr;
-  volatile int *abort_flag;
-};
-
-__host__ __device__ inline size_t smem_bytes(int stages, int Npb, int K, int nt, bool direct) {
-  size_t s = 1024;  // alignment slack
-  s += (size_t)stages * (kAStageBytes + Npb * 128);
-  if (direct) s += (size_t)K * kTileM * nt * 8;
-  s += 8 * (2 * stages + 4) + 16;
-  return s;
-}
-
-__device__ inline Smem carve(uint8_t *raw, const TcParams &p, bool direct) {
-  Smem s;
-  uint8_t *b = (uint8_t *)(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
-  s.A = b;
-  s.Bw = b + (size_t)p.stages * kAStageBytes;
-  uint8_t *q = s.Bw + (size_t)p.stages * p.Npb * 128;
-  s.tap_off = (int *)q;
-  s.tap_w = (float *)(q + (direct ? (size_t)p.K * kTileM * p.nt * 4 : 0));
-  q += direct ? (size_t)p.K * kTileM * p.nt * 8 : 0;
-  s.full = (uint64_t *)q;
-  s.empty = s.full + p.stages;
-  s.tfull = s.empty + p.stages;
-  s.tempty = s.tfull + 2;
-  s.tmem_ptr = (uint32_t *)(s.tempty + 2);
-  s.abort_flag = (volatile int *)(s.tmem_ptr + 1);
-  return s;
-}
 
 __device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); }
 
-// acc[0..7] += w * (8 bf16 channels in q)
 __device__ __forceinline__ void fma8(float (&acc)[8], float w, const uint4 &q) {
   acc[0] = fmaf(w, bf16_lo(q.x), acc[0]);
   acc[1] = fmaf(w, bf16_hi(q.x), acc[1]);
@@ -96,32 +77,153 @@ __device__ __forceinline__ void fma8(float (&acc)[8], float w, const uint4 &q) {
   acc[6] = fmaf(w, bf16_lo(q.w), acc[6]);
   acc[7] = fmaf(w, bf16_hi(q.w), acc[7]);
 }
+__device__ __forceinline__ uint4 pack8(const float (&a)[8]) {
+  uint4 o;
+  o.x = pack_bf16(a[0], a[1]);
+  o.y = pack_bf16(a[2], a[3]);
+  o.z = pack_bf16(a[4], a[5]);
+  o.w = pack_bf16(a[6], a[7]);
+  return o;
+}
 
-// Taps of map slot (pix, slot) into the shared tap table (nt entries; unused ones get weight 0).
+// One tap-table entry: element offset of the source pixel and its weight (0 = unused).
+struct __align__(8) Tap {
+  int off;
+  float w;
+};
+
+// Taps of map slot (pix, slot) into nt table entries.
 template <int INTERP>
-__device__ __forceinline__ void fill_taps(const TcParams &p, int pix, int slot, int *off, float *w) {
-  const int PP = p.P > 0 ? p.P : 1;
-  const size_t e0 = ((size_t)pix * p.K + slot) * PP;
+__device__ __forceinline__ void fill_taps(const Gather &g, int pix, int slot, Tap *dst) {
+  const int PP = g.P > 0 ? g.P : 1;
+  const size_t e0 = ((size_t)pix * g.K + slot) * PP;
   Taps<float> t;
   int n = 0;
   for (int q = 0; q < PP; q++) {
-    decode<float, INTERP>(__ldg(p.map + 2 * (e0 + q)), __ldg(p.map + 2 * (e0 + q) + 1), p.SH, p.SW, t);
-    const float wq = p.P > 0 ? __ldg(p.iw + e0 + q) : 1.0f;
+    decode<float, INTERP>(__ldg(g.map + 2 * (e0 + q)), __ldg(g.map + 2 * (e0 + q) + 1), g.SH, g.SW, t);
+    const float wq = g.P > 0 ? __ldg(g.iw + e0 + q) : 1.0f;
 #pragma unroll
     for (int i = 0; i < TapCount<INTERP>::value; i++, n++) {
       const bool ok = t.off[i] >= 0;
-      off[n] = ok ? t.off[i] : 0;
-      w[n] = ok ? wq * t.w[i] : 0.0f;
+      dst[n].off = ok ? t.off[i] : 0;
+      dst[n].w = ok ? wq * t.w[i] : 0.0f;
     }
   }
 }
 
-template <int MODE>
+__device__ __forceinline__ void fill_taps_any(const Gather &g, int pix, int slot, Tap *dst) {
+  SPH_DISPATCH_INTERP(g.interp, fill_taps<INTERP>(g, pix, slot, dst));
+}
+
+// Weighted sum of 8 channels over the taps of one (pixel, slot): all loads are issued before any is used.
+template <int NT>
+__device__ __forceinline__ uint4 gather_taps(const __nv_bfloat16 *__restrict__ img, const Tap *__restrict__ taps, int nt,
+                                             int Cp, int c0) {
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+  if (NT > 0) {
+    uint4 q[NT > 0 ? NT : 1];
+    float w[NT > 0 ? NT : 1];
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+      const Tap tp = taps[t];
+      w[t] = tp.w;
+      q[t] = make_uint4(0, 0, 0, 0);
+      if (tp.w != 0.0f) q[t] = __ldg((const uint4 *)(img + (size_t)tp.off * Cp + c0));
+    }
+#pragma unroll
+    for (int t = 0; t < NT; t++) fma8(acc, w[t], q[t]);
+  } else {
+    for (int t = 0; t < nt; t++) {
+      const Tap tp = taps[t];
+      if (tp.w != 0.0f) fma8(acc, tp.w, __ldg((const uint4 *)(img + (size_t)tp.off * Cp + c0)));
+    }
+  }
+  return pack8(acc);
+}
+
+__device__ __forceinline__ uint4 gather_plan(const __nv_bfloat16 *__restrict__ img, const PlanView<float> &pv, int key, int Cp,
+                                             int c0) {
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+  const int e0 = __ldg(pv.offsets + key), e1 = __ldg(pv.offsets + key + 1);
+  int e = e0;
+  for (; e + 1 < e1; e += 2) {
+    const int s0 = __ldg(pv.src + e), s1 = __ldg(pv.src + e + 1);
+    const float w0 = __ldg(pv.w + e), w1 = __ldg(pv.w + e + 1);
+    const uint4 q0 = __ldg((const uint4 *)(img + (size_t)s0 * Cp + c0));
+    const uint4 q1 = __ldg((const uint4 *)(img + (size_t)s1 * Cp + c0));
+    fma8(acc, w0, q0);
+    fma8(acc, w1, q1);
+  }
+  if (e < e1) fma8(acc, __ldg(pv.w + e), __ldg((const uint4 *)(img + (size_t)__ldg(pv.src + e) * Cp + c0)));
+  return pack8(acc);
+}
+
+// Pixel of local index l inside tile (ty, tx) of a (GH, GW) grid tiled TH x kTW; -1 if outside.
+__device__ __forceinline__ int tile_pixel(int l, int ty, int tx, int TH, int GH, int GW) {
+  const int y = ty * TH + (l >> 4), x = tx * kTW + (l & 15);
+  return (y < GH && x < GW) ? y * GW + x : -1;
+}
+
+// =================================================================================================
+// forward-type kernel
+// =================================================================================================
+constexpr int kTileM = 128, kTH = 8;
+constexpr int kAStageBytes = kTileM * 128;
+constexpr int kMaxTapBytes = 40 * 1024;
+
+struct TcParams {
+  Gather g;
+  const __nv_bfloat16 *wp;  // weight tile images: [nblk][nchunks][Npb rows][64] bf16, 128B-swizzled
+  const float *bias;        // (Nout) or null
+  float *out;               // (B, Nout, GH*GW)
+  int *status;              // set to 1 if a bounded wait gave up
+  int B, Nout, Npb, nblk, nchunks, tiles_x, tiles_y, stages;
+};
+
+struct Smem {
+  uint8_t *A, *Bw;
+  Tap *taps;
+  uint64_t *full, *empty, *tfull, *tempty;
+  uint32_t *tmem_ptr;
+  volatile int *abort_flag;
+};
+
+inline size_t gemm_smem_bytes(int stages, int Npb, int K, int nt, bool direct) {
+  size_t s = 1024;  // alignment slack
+  s += (size_t)stages * (kAStageBytes + Npb * 128);
+  if (direct) s += (size_t)K * kTileM * nt * sizeof(Tap);
+  s += 8 * (2 * stages + 4) + 16;
+  return s;
+}
+
+__device__ inline Smem carve(uint8_t *raw, const TcParams &p, bool direct) {
+  Smem s;
+  uint8_t *b = (uint8_t *)(((uintptr_t)raw + 1023) & ~(uintptr_t)1023);
+  s.A = b;
+  s.Bw = b + (size_t)p.stages * kAStageBytes;
+  uint8_t *q = s.Bw + (size_t)p.stages * p.Npb * 128;
+  s.taps = (Tap *)q;
+  q += direct ? (size_t)p.g.K * kTileM * p.g.nt * sizeof(Tap) : 0;
+  s.full = (uint64_t *)q;
+  s.empty = s.full + p.stages;
+  s.tfull = s.empty + p.stages;
+  s.tempty = s.tfull + 2;
+  s.tmem_ptr = (uint32_t *)(s.tempty + 2);
+  s.abort_flag = (volatile int *)(s.tmem_ptr + 1);
+  return s;
+}
+
+template <int MODE, int NT>
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = carve(smem_raw, p, MODE == MODE_DIRECT);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int S = p.stages;
+  const Gather &g = p.g;
 
   if (tid == 0) {
     for (int s = 0; s < S; s++) {
@@ -143,20 +245,23 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *sm.tmem_ptr;
-  const int total_tiles = p.B * p.tiles_per_image * p.nblk;
-  const size_t shw = (size_t)p.SH * p.SW;
+  const int tiles_per_image = p.tiles_x * p.tiles_y;
+  const int total_tiles = p.B * tiles_per_image * p.nblk;
+  const int npix = g.GH * g.GW;
+  const size_t shw = (size_t)g.SH * g.SW;
 
   if (warp < kEpilogueWarps) {
     // ---------------- epilogue: TMEM -> registers -> (+bias) -> global ----------------
     int tl = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tl++) {
       const int nb = tile % p.nblk, rest = tile / p.nblk;
-      const int b = rest / p.tiles_per_image, pix = (rest % p.tiles_per_image) * kTileM + warp * 32 + lane;
+      const int b = rest / tiles_per_image, t2 = rest % tiles_per_image;
+      const int pix = tile_pixel(warp * 32 + lane, t2 / p.tiles_x, t2 % p.tiles_x, kTH, g.GH, g.GW);
       const int buf = tl & 1;
       if (!mbar_wait(sm.tfull + buf, (tl >> 1) & 1, sm.abort_flag)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * 256;
-      float *orow = p.out + ((size_t)b * p.Nout) * p.npix + pix;
+      float *orow = p.out + ((size_t)b * p.Nout) * npix + (pix >= 0 ? pix : 0);
       for (int n0 = 0; n0 < p.Npb; n0 += 32) {
         uint32_t r[32];
         if (p.Npb - n0 >= 32) {
@@ -168,12 +273,12 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
           for (int j = 0; j < 16; j++) { r[j] = h[j]; r[j + 16] = 0; }
         }
         tmem_ld_wait();
-        if (pix < p.npix) {
+        if (pix >= 0) {
 #pragma unroll
           for (int j = 0; j < 32; j++) {
             const int n = nb * p.Npb + n0 + j;
             if (n < p.Nout && n0 + j < p.Npb)
-              orow[(size_t)n * p.npix] = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + n) : 0.0f);
+              orow[(size_t)n * npix] = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + n) : 0.0f);
           }
         }
       }
@@ -213,21 +318,22 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
     bool alive = true;
     PlanView<float> pv{};
     bool plan_ok = true;
-    if (MODE == MODE_PLAN) pv = plan_view<float>(p.plan, p.npix * p.K, plan_ok);
+    if (MODE == MODE_PLAN) pv = plan_view<float>(g.plan, npix * g.K, plan_ok);
     for (int tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
       const int nb = tile % p.nblk, rest = tile / p.nblk;
-      const int b = rest / p.tiles_per_image, pix0 = (rest % p.tiles_per_image) * kTileM;
-      const __nv_bfloat16 *img = p.xh + (size_t)b * shw * p.Cp;
+      const int b = rest / tiles_per_image, t2 = rest % tiles_per_image;
+      const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
+      const __nv_bfloat16 *img = g.xh + (size_t)b * shw * g.Cp;
       if (MODE == MODE_DIRECT) {
         producer_bar();  // every producer is done reading the previous tile's taps
-        for (int idx = pt; idx < p.K * kTileM; idx += kProducerThreads) {
-          const int slot = idx / kTileM, pl = idx % kTileM, pix = pix0 + pl;
-          int *off = sm.tap_off + (size_t)idx * p.nt;
-          float *w = sm.tap_w + (size_t)idx * p.nt;
-          if (pix < p.npix) {
-            SPH_DISPATCH_INTERP(p.interp, fill_taps<INTERP>(p, pix, slot, off, w));
+        for (int idx = pt; idx < g.K * kTileM; idx += kProducerThreads) {
+          const int slot = idx / kTileM, pl = idx % kTileM;
+          const int pix = tile_pixel(pl, ty, tx, kTH, g.GH, g.GW);
+          Tap *dst = sm.taps + (size_t)idx * g.nt;
+          if (pix >= 0) {
+            fill_taps_any(g, pix, slot, dst);
           } else {
-            for (int i = 0; i < p.nt; i++) { off[i] = 0; w[i] = 0.0f; }
+            for (int i = 0; i < g.nt; i++) { dst[i].off = 0; dst[i].w = 0.0f; }
           }
         }
         producer_bar();
@@ -241,34 +347,20 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
           bulk_copy_g2s(sm.Bw + (size_t)s * bytes, p.wp + ((size_t)nb * p.nchunks + chunk) * p.Npb * kChunk, bytes, sm.full + s);
         }
         uint8_t *As = sm.A + (size_t)s * kAStageBytes;
-#pragma unroll 2
+#pragma unroll
         for (int r = 0; r < kTileM * 8 / kProducerThreads; r++) {
           const int idx = pt + r * kProducerThreads, pl = idx >> 3, v = idx & 7;
-          const int j = chunk * kChunk + v * 8;
-          float acc[8];
-#pragma unroll
-          for (int i = 0; i < 8; i++) acc[i] = 0.0f;
-          if (j < p.KC) {
-            const int slot = j / p.Cp, c0 = j - slot * p.Cp;
+          int slot, c0;
+          chunk_vec(g.Cp, g.K, chunk, v, slot, c0);
+          uint4 o = make_uint4(0, 0, 0, 0);
+          if (slot < g.K) {
             if (MODE == MODE_DIRECT) {
-              const int *off = sm.tap_off + (size_t)(slot * kTileM + pl) * p.nt;
-              const float *w = sm.tap_w + (size_t)(slot * kTileM + pl) * p.nt;
-              for (int t = 0; t < p.nt; t++) {
-                const float wt = w[t];
-                if (wt != 0.0f) fma8(acc, wt, __ldg((const uint4 *)(img + (size_t)off[t] * p.Cp + c0)));
-              }
-            } else if (plan_ok && pix0 + pl < p.npix) {
-              const int key = (pix0 + pl) * p.K + slot;
-              const int e0 = __ldg(pv.offsets + key), e1 = __ldg(pv.offsets + key + 1);
-              for (int e = e0; e < e1; e++)
-                fma8(acc, __ldg(pv.w + e), __ldg((const uint4 *)(img + (size_t)__ldg(pv.src + e) * p.Cp + c0)));
+              o = gather_taps<NT>(img, sm.taps + (size_t)(slot * kTileM + pl) * g.nt, g.nt, g.Cp, c0);
+            } else {
+              const int pix = tile_pixel(pl, ty, tx, kTH, g.GH, g.GW);
+              if (plan_ok && pix >= 0) o = gather_plan(img, pv, pix * g.K + slot, g.Cp, c0);
             }
           }
-          uint4 o;
-          o.x = pack_bf16(acc[0], acc[1]);
-          o.y = pack_bf16(acc[2], acc[3]);
-          o.z = pack_bf16(acc[4], acc[5]);
-          o.w = pack_bf16(acc[6], acc[7]);
           *(uint4 *)(As + pl * 128 + ((v ^ (pl & 7)) << 4)) = o;
         }
         fence_proxy_async();
@@ -283,6 +375,193 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
   if (warp == kEpilogueWarps) tmem_dealloc(tmem_base, kTmemCols);
   if (tid == 0 && *sm.abort_flag) *p.status = 1;
 }
+
+// =================================================================================================
+// weight-gradient kernel
+// =================================================================================================
+constexpr int kDwPix = 64, kDwTH = 4;      // pixels per reduction step (a 4x16 block)
+constexpr int kDwGroup = 4;                // chunks (of 64 columns) per CTA: N <= 256
+constexpr int kDwColBytes = kDwGroup * kDwPix * 128;   // 32 KB of gathered columns per stage
+constexpr int kDwGtBytes = 128 * 128;                  // one 128-row x 64-pixel gradient tile image
+constexpr int kDwMaxTapBytes = 20 * 1024;
+
+struct DwParams {
+  Gather g;
+  const __nv_bfloat16 *gt;  // gradient tile images [b][ptile][mb][128 rows][64 px], 128B-swizzled
+  float *partial;           // [splits][mbs_total*128][nchunks*64]
+  int *status;
+  int B, mbs_total, nchunks, tiles_x, tiles_y, splits, stages, tap_rows;
+};
+
+struct DwSmem {
+  uint8_t *stage;  // per stage: columns (32 KB) then gradient tiles (mbs * 16 KB)
+  Tap *taps;
+  uint64_t *full, *empty, *tfull;
+  uint32_t *tmem_ptr;
+  volatile int *abort_flag;
+};
+
+inline size_t dw_stage_bytes(int mbs) { return kDwColBytes + (size_t)mbs * kDwGtBytes; }
+inline size_t dw_smem_bytes(int stages, int mbs, int tap_rows, int nt) {
+  return 1024 + stages * dw_stage_bytes(mbs) + (size_t)tap_rows * kDwPix * nt * sizeof(Tap) + 8 * (2 * stages + 1) + 16;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const Gather &g = p.g;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int S = p.stages;
+  const int grp = blockIdx.x, split = blockIdx.y, mb0 = blockIdx.z * 2;
+  const int mbs = min(2, p.mbs_total - mb0);
+  const int chunk0 = grp * kDwGroup, ncg = min(kDwGroup, p.nchunks - chunk0);
+  const size_t stage_bytes = kDwColBytes + (size_t)mbs * kDwGtBytes;
+
+  DwSmem sm;
+  {
+    uint8_t *b = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    sm.stage = b;
+    uint8_t *q = b + (size_t)S * stage_bytes;
+    sm.taps = (Tap *)q;
+    q += (size_t)p.tap_rows * kDwPix * g.nt * sizeof(Tap);
+    sm.full = (uint64_t *)q;
+    sm.empty = sm.full + S;
+    sm.tfull = sm.empty + S;
+    sm.tmem_ptr = (uint32_t *)(sm.tfull + 1);
+    sm.abort_flag = (volatile int *)(sm.tmem_ptr + 1);
+  }
+  if (tid == 0) {
+    for (int s = 0; s < S; s++) {
+      mbar_init(sm.full + s, kProducerWarps + 1);
+      mbar_init(sm.empty + s, 1);
+    }
+    mbar_init(sm.tfull, 1);
+    *sm.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == kEpilogueWarps) {
+    tmem_alloc(sm.tmem_ptr, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *sm.tmem_ptr;
+
+  const int tiles_per_image = p.tiles_x * p.tiles_y;
+  const int64_t total_steps = (int64_t)p.B * tiles_per_image;
+  const int step_lo = (int)(total_steps * split / p.splits), step_hi = (int)(total_steps * (split + 1) / p.splits);
+  const size_t shw = (size_t)g.SH * g.SW;
+  const int ncols_total = p.nchunks * kChunk;
+
+  if (warp < kEpilogueWarps) {
+    // ---------------- epilogue: TMEM -> partial sums ----------------
+    bool have = step_hi > step_lo;
+    if (have) have = mbar_wait(sm.tfull, 0, sm.abort_flag);
+    tc_fence_after();
+    for (int mb = 0; mb < mbs; mb++) {
+      const int row = (mb0 + mb) * 128 + warp * 32 + lane;
+      float *prow = p.partial + ((size_t)split * p.mbs_total * 128 + row) * ncols_total + (size_t)chunk0 * kChunk;
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + mb * 256;
+      for (int n0 = 0; n0 < ncg * kChunk; n0 += 32) {
+        uint32_t r[32];
+        if (have) {
+          tmem_ld_32x32(taddr + n0, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = 0;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *(float4 *)(prow + n0 + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                                   __uint_as_float(r[j + 3]));
+      }
+    }
+    tc_fence_before();
+  } else if (warp == kEpilogueWarps) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && step_hi > step_lo) {
+      const uint32_t idesc = idesc_bf16(128, ncg * kChunk, 0, 1);  // A (gradient) K-major, B (columns) MN-major
+      bool alive = true;
+      int it = 0;
+      for (int step = step_lo; alive && step < step_hi; step++, it++) {
+        const int s = it % S;
+        if (!mbar_wait(sm.full + s, (it / S) & 1, sm.abort_flag)) { alive = false; break; }
+        tc_fence_after();
+        uint8_t *st = sm.stage + (size_t)s * stage_bytes;
+        const uint64_t b0 = smem_desc_sw128(smem_u32(st), kDwPix * 128, 1024);
+        for (int mb = 0; mb < mbs; mb++) {
+          const uint64_t a0 = smem_desc_sw128(smem_u32(st + kDwColBytes + (size_t)mb * kDwGtBytes), 16, 1024);
+#pragma unroll
+          for (int ks = 0; ks < kDwPix / 16; ks++)
+            umma_bf16(tmem_base + mb * 256, a0 + 2 * ks, b0 + (uint64_t)(ks * 16 * 128 >> 4), idesc, (it | ks) != 0);
+        }
+        umma_commit(sm.empty + s);
+      }
+      if (alive) umma_commit(sm.tfull);
+    }
+  } else {
+    // ---------------- producers ----------------
+    const int pt = tid - kFirstProducerThread;
+    bool alive = true;
+    int it = 0;
+    // table row r holds the taps of slot `slot_base + r`
+    int slot_base, dummy;
+    chunk_vec(g.Cp, g.K, chunk0, 0, slot_base, dummy);
+    for (int step = step_lo; alive && step < step_hi; step++, it++) {
+      const int b = step / tiles_per_image, t2 = step % tiles_per_image;
+      const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
+      const __nv_bfloat16 *img = g.xh + (size_t)b * shw * g.Cp;
+      producer_bar();
+      for (int idx = pt; idx < p.tap_rows * kDwPix; idx += kProducerThreads) {
+        const int row = idx / kDwPix, pl = idx % kDwPix;
+        int slot;
+        if (g.Cp >= 64) { int c0; chunk_vec(g.Cp, g.K, chunk0 + row, 0, slot, c0); }   // one slot per chunk
+        else slot = slot_base + row;
+        const int pix = tile_pixel(pl, ty, tx, kDwTH, g.GH, g.GW);
+        Tap *dst = sm.taps + (size_t)idx * g.nt;
+        if (pix >= 0 && slot < g.K && (g.Cp < 64 || row < ncg)) {
+          fill_taps_any(g, pix, slot, dst);
+        } else {
+          for (int i = 0; i < g.nt; i++) { dst[i].off = 0; dst[i].w = 0.0f; }
+        }
+      }
+      producer_bar();
+      const int s = it % S;
+      if (!mbar_wait(sm.empty + s, ((it / S) & 1) ^ 1, sm.abort_flag)) { alive = false; break; }
+      uint8_t *st = sm.stage + (size_t)s * stage_bytes;
+      if (pt == 0) {
+        const uint32_t bytes = (uint32_t)mbs * kDwGtBytes;
+        mbar_arrive_expect_tx(sm.full + s, bytes);
+        bulk_copy_g2s(st + kDwColBytes, p.gt + ((size_t)step * p.mbs_total + mb0) * (kDwGtBytes / 2), bytes, sm.full + s);
+      }
+      for (int idx = pt; idx < ncg * kDwPix * 8; idx += kProducerThreads) {
+        const int gi = idx / (kDwPix * 8), rem = idx % (kDwPix * 8), pl = rem >> 3, v = rem & 7;
+        int slot, c0;
+        chunk_vec(g.Cp, g.K, chunk0 + gi, v, slot, c0);
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (slot < g.K) {
+          const int row = g.Cp >= 64 ? gi : slot - slot_base;
+          o = gather_taps<NT>(img, sm.taps + (size_t)(row * kDwPix + pl) * g.nt, g.nt, g.Cp, c0);
+        }
+        *(uint4 *)(st + gi * (kDwPix * 128) + pl * 128 + ((v ^ (pl & 7)) << 4)) = o;
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.full + s);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kEpilogueWarps) tmem_dealloc(tmem_base, kTmemCols);
+  if (tid == 0 && *sm.abort_flag) *p.status = 1;
+}
+
+// =================================================================================================
+// layout pre-passes
+// =================================================================================================
 
 // (B, C, HW) float32 -> (B, HW, Cp) bf16, channels beyond C zero.  32 pixels x 64 channels per block.
 __global__ void __launch_bounds__(256) nchw_to_nhwc_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ y,
@@ -306,8 +585,8 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_bf16_kernel(const float *__r
   }
 }
 
-// Weights -> bf16 tile images.  Element (n, j = slot*Cp + ch) of block nb, chunk j/64 sits at row n, 16-byte
-// chunk ((j%64)/8) ^ (n&7) of a 128-byte row.  The source is addressed W[n*sn + ch*sc + slot*sk].
+// Weights -> bf16 tile images.  Row n of block nb, chunk `chunk`: 64 columns, 16-byte vector v stored at
+// position v ^ (n & 7) of the 128-byte row.  The source is addressed W[n*sn + ch*sc + slot*sk].
 __global__ void weight_image_kernel(const float *__restrict__ w, __nv_bfloat16 *__restrict__ wp, int Nout, int CH, int Cp,
                                     int K, int Npb, int nblk, int nchunks, int64_t sn, int64_t sc, int64_t sk) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -315,37 +594,61 @@ __global__ void weight_image_kernel(const float *__restrict__ w, __nv_bfloat16 *
   if (i >= total) return;
   const int col = (int)(i % kChunk), n = (int)((i / kChunk) % Npb), chunk = (int)((i / ((int64_t)kChunk * Npb)) % nchunks);
   const int nb = (int)(i / ((int64_t)kChunk * Npb * nchunks));
-  const int j = chunk * kChunk + col, slot = j / Cp, ch = j % Cp, ng = nb * Npb + n;
+  int slot, c0;
+  chunk_vec(Cp, K, chunk, col >> 3, slot, c0);
+  const int ch = c0 + (col & 7), ng = nb * Npb + n;
   const float v = (ng < Nout && slot < K && ch < CH) ? __ldg(w + ng * sn + ch * sc + slot * sk) : 0.0f;
-  const int v16 = col >> 3, e = col & 7;
-  wp[(((int64_t)nb * nchunks + chunk) * Npb + n) * kChunk + ((v16 ^ (n & 7)) << 3) + e] = __float2bfloat16(v);
+  wp[(((int64_t)nb * nchunks + chunk) * Npb + n) * kChunk + (((col >> 3) ^ (n & 7)) << 3) + (col & 7)] = __float2bfloat16(v);
 }
 
-struct Geometry {
-  int Cp, KC, nchunks, Npb, nblk, nt, stages;
-  size_t xh_bytes, wp_bytes, smem;
-  bool ok;
-};
+// Gradient (B, N, GH*GW) float32 -> bf16 tile images [b][ptile][mb][128 rows][64 px]; the 64 pixels of a tile
+// are a 4x16 block of the (GH, GW) grid; 16-byte vector v (8 pixels) of row r sits at position v ^ (r & 7).
+__global__ void __launch_bounds__(256) grad_image_kernel(const float *__restrict__ gsrc, __nv_bfloat16 *__restrict__ gt, int N,
+                                                          int GH, int GW, int tiles_x, int tiles_y, int mbs_total) {
+  const int t2 = blockIdx.x, mb = blockIdx.y, b = blockIdx.z;
+  const int ty = t2 / tiles_x, tx = t2 % tiles_x;
+  const size_t npix = (size_t)GH * GW;
+  __nv_bfloat16 *dst = gt + (((size_t)b * tiles_x * tiles_y + t2) * mbs_total + mb) * (128 * 64);
+  for (int i = threadIdx.x; i < 128 * 8; i += 256) {
+    const int r = i >> 3, v = i & 7, n = mb * 128 + r;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      const int l = v * 8 + e;
+      const int y = ty * kDwTH + (l >> 4), x = tx * kTW + (l & 15);
+      f[e] = (n < N && y < GH && x < GW) ? __ldg(gsrc + ((size_t)b * N + n) * npix + (size_t)y * GW + x) : 0.0f;
+    }
+    uint4 o;
+    o.x = pack_bf16(f[0], f[1]);
+    o.y = pack_bf16(f[2], f[3]);
+    o.z = pack_bf16(f[4], f[5]);
+    o.w = pack_bf16(f[6], f[7]);
+    *(uint4 *)(dst + r * 64 + ((v ^ (r & 7)) << 3)) = o;
+  }
+}
 
-Geometry geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int interp, int64_t Nout, bool direct) {
-  Geometry g{};
-  g.Cp = (int)align_up((size_t)CH, 8);
-  if (g.Cp > 64) g.Cp = (int)align_up((size_t)CH, 64);
-  else while (64 % g.Cp) g.Cp += 8;            // a 16-byte vector never straddles two slots and slots tile a chunk
-  g.KC = (int)(K * g.Cp);
-  g.nchunks = (g.KC + kChunk - 1) / kChunk;
-  const int np = (int)align_up((size_t)Nout, 16);
-  g.Npb = np > 256 ? 256 : np;
-  g.nblk = (np + g.Npb - 1) / g.Npb;
-  g.nt = (int)((P > 0 ? P : 1) * (interp == SPH_NEAREST ? 1 : 4));
-  g.xh_bytes = align_up((size_t)(B * SHW) * g.Cp * 2, 256);
-  g.wp_bytes = align_up((size_t)g.nblk * g.nchunks * g.Npb * kChunk * 2, 256);
-  g.ok = !direct || (size_t)K * kTileM * g.nt * 8 <= (size_t)kMaxTapBytes;
-  g.stages = 4;
-  while (g.stages > 2 && smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct) > (size_t)kSmemLimit) g.stages--;
-  g.smem = smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct);
-  if (g.smem > (size_t)kSmemLimit) g.ok = false;
-  return g;
+// gw[n*sn + ch*sc + slot*sk] = sum over splits (in order) of partial[split][n][column of (slot, ch)].
+__global__ void tc_dw_reduce_kernel(const float *__restrict__ partial, int splits, int rows_total, int ncols_total, int Nout,
+                                    int CH, int Cp, int K, int64_t sn, int64_t sc, int64_t sk, float *__restrict__ gw) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= Nout * CH * K) return;
+  const int slot = i % K, ch = (i / K) % CH, n = i / (K * CH);
+  int col;
+  if (Cp >= 64) col = ((ch / 64) * K + slot) * 64 + (ch % 64);
+  else col = slot * Cp + ch;
+  float s = 0.0f;
+  for (int z = 0; z < splits; z++) s += partial[((size_t)z * rows_total + n) * ncols_total + col];
+  gw[n * sn + ch * sc + slot * sk] = s;
+}
+
+// =================================================================================================
+// host side
+// =================================================================================================
+int padded_channels(int64_t CH) {
+  int cp = (int)align_up((size_t)CH, 8);
+  if (cp > 64) return (int)align_up((size_t)CH, 64);
+  while (64 % cp) cp += 8;  // a 16-byte vector never straddles two slots and whole slots tile a chunk
+  return cp;
 }
 
 int sm_count() {
@@ -358,44 +661,156 @@ int sm_count() {
   return n;
 }
 
-// Out[b,n,pix] (+bias) on the tensor cores.  src is (B,CH,SH,SW) float32.
+struct Geometry {
+  int Cp, nchunks, Npb, nblk, nt, stages;
+  size_t xh_bytes, wp_bytes, smem;
+  bool ok;
+};
+
+Geometry geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int interp, int64_t Nout, bool direct) {
+  Geometry g{};
+  g.Cp = padded_channels(CH);
+  g.nchunks = num_chunks(g.Cp, (int)K);
+  const int np = (int)align_up((size_t)Nout, 16);
+  g.Npb = np > 256 ? 256 : np;
+  g.nblk = (np + g.Npb - 1) / g.Npb;
+  g.nt = (int)((P > 0 ? P : 1) * (interp == SPH_NEAREST ? 1 : 4));
+  g.xh_bytes = align_up((size_t)(B * SHW) * g.Cp * 2, 256);
+  g.wp_bytes = align_up((size_t)g.nblk * g.nchunks * g.Npb * kChunk * 2, 256);
+  g.ok = !direct || (size_t)K * kTileM * g.nt * sizeof(Tap) <= (size_t)kMaxTapBytes;
+  g.stages = 4;
+  while (g.stages > 2 && gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct) > (size_t)kSmemLimit) g.stages--;
+  g.smem = gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct);
+  if (g.smem > (size_t)kSmemLimit) g.ok = false;
+  return g;
+}
+
+void to_nhwc(const void *src, __nv_bfloat16 *xh, int64_t B, int64_t CH, int Cp, int64_t HW, cudaStream_t st) {
+  nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW, 32), cdiv(Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, Cp, (int)HW);
+}
+
+template <int MODE, int NT>
+void launch_gemm(const TcParams &p, int grid, size_t smem, cudaStream_t st) {
+  cudaFuncSetAttribute(tc_gemm_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  tc_gemm_kernel<MODE, NT><<<grid, kThreads, smem, st>>>(p);
+}
+
+// Out[b,n,pix] (+bias) on the tensor cores.  src is (B,CH,SH,SW) float32; the GEMM pixels are the (GH,GW) grid.
 int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, const void *plan, int64_t CH, int64_t SH,
-            int64_t SW, int64_t K, int64_t P, int64_t npix, int interp, const void *wgt, int64_t sn, int64_t sc, int64_t sk,
-            const void *bias, void *out, int64_t Nout, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st) {
+            int64_t SW, int64_t K, int64_t P, int64_t GH, int64_t GW, int interp, const void *wgt, int64_t sn, int64_t sc,
+            int64_t sk, const void *bias, void *out, int64_t Nout, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st) {
   const Geometry g = geometry(B, CH, SH * SW, K, P, interp, Nout, !use_plan);
   if (!g.ok)  // shapes the tile kernel does not cover run on the exact SIMT kernels instead
-    return simt_gemm<float>(use_plan, src, map, iw, plan, CH, SH, SW, K, P, npix, interp, wgt, sn, sc, sk, bias, out, Nout, B, st);
+    return simt_gemm<float>(use_plan, src, map, iw, plan, CH, SH, SW, K, P, GH * GW, interp, wgt, sn, sc, sk, bias, out, Nout, B, st);
   if (!ws || ws_bytes < 256 + g.xh_bytes + g.wp_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
   int *status = (int *)ws;
   __nv_bfloat16 *xh = (__nv_bfloat16 *)((char *)ws + 256);
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
-  const int HW = (int)(SH * SW);
-  nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW, 32), cdiv(g.Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, g.Cp, HW);
+  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st);
   const int64_t wtotal = (int64_t)g.nblk * g.nchunks * g.Npb * kChunk;
   weight_image_kernel<<<cdiv(wtotal, 256), 256, 0, st>>>((const float *)wgt, wp, (int)Nout, (int)CH, g.Cp, (int)K, g.Npb, g.nblk,
                                                          g.nchunks, sn, sc, sk);
   TcParams p{};
-  p.xh = xh; p.wp = wp; p.bias = (const float *)bias; p.out = (float *)out;
-  p.map = (const float *)map; p.iw = (const float *)iw; p.plan = plan; p.status = status;
-  p.B = (int)B; p.Cp = g.Cp; p.SH = (int)SH; p.SW = (int)SW; p.K = (int)K; p.P = (int)P; p.npix = (int)npix;
-  p.Nout = (int)Nout; p.Npb = g.Npb; p.nblk = g.nblk; p.nchunks = g.nchunks; p.KC = g.KC;
-  p.tiles_per_image = cdiv(npix, kTileM); p.interp = interp; p.nt = g.nt; p.stages = g.stages;
-  const int64_t tiles = (int64_t)B * p.tiles_per_image * g.nblk;
+  p.g = Gather{xh, (const float *)map, (const float *)iw, plan, g.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, g.nt};
+  p.wp = wp; p.bias = (const float *)bias; p.out = (float *)out; p.status = status;
+  p.B = (int)B; p.Nout = (int)Nout; p.Npb = g.Npb; p.nblk = g.nblk; p.nchunks = g.nchunks;
+  p.tiles_x = cdiv(GW, kTW); p.tiles_y = cdiv(GH, kTH); p.stages = g.stages;
+  const int64_t tiles = (int64_t)B * p.tiles_x * p.tiles_y * g.nblk;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  if (use_plan) {
-    cudaFuncSetAttribute(tc_gemm_kernel<MODE_PLAN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
-    tc_gemm_kernel<MODE_PLAN><<<grid, kThreads, g.smem, st>>>(p);
-  } else {
-    cudaFuncSetAttribute(tc_gemm_kernel<MODE_DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
-    tc_gemm_kernel<MODE_DIRECT><<<grid, kThreads, g.smem, st>>>(p);
-  }
+  if (use_plan) launch_gemm<MODE_PLAN, 0>(p, grid, g.smem, st);
+  else if (g.nt == 4) launch_gemm<MODE_DIRECT, 4>(p, grid, g.smem, st);
+  else if (g.nt == 1) launch_gemm<MODE_DIRECT, 1>(p, grid, g.smem, st);
+  else launch_gemm<MODE_DIRECT, 0>(p, grid, g.smem, st);
   return launch_status(3);
 }
 
 size_t gemm_ws(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int interp, int64_t Nout, bool direct) {
   const Geometry g = geometry(B, CH, SHW, K, P, interp, Nout, direct);
   return g.ok ? 256 + g.xh_bytes + g.wp_bytes : 0;
+}
+
+struct DwGeometry {
+  int Cp, nchunks, ngroups, mbs_total, nt, stages, splits, tap_rows, tiles_x, tiles_y;
+  size_t xh_bytes, gt_bytes, partial_bytes, bias_bytes, smem;
+  bool ok;
+};
+
+DwGeometry dw_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int interp, int64_t Nout, int64_t GH,
+                       int64_t GW, int64_t Cbias) {
+  DwGeometry d{};
+  d.Cp = padded_channels(CH);
+  d.nchunks = num_chunks(d.Cp, (int)K);
+  d.ngroups = (d.nchunks + kDwGroup - 1) / kDwGroup;
+  d.mbs_total = (int)((Nout + 127) / 128);
+  d.nt = (int)((P > 0 ? P : 1) * (interp == SPH_NEAREST ? 1 : 4));
+  d.tap_rows = d.Cp >= 64 ? kDwGroup : (int)std::min<int64_t>(K, (int64_t)kDwGroup * (64 / d.Cp));
+  d.tiles_x = cdiv(GW, kTW);
+  d.tiles_y = cdiv(GH, kDwTH);
+  const int mbs = d.mbs_total >= 2 ? 2 : 1;
+  d.ok = (size_t)d.tap_rows * kDwPix * d.nt * sizeof(Tap) <= (size_t)kDwMaxTapBytes;
+  d.stages = 4;
+  while (d.stages > 2 && dw_smem_bytes(d.stages, mbs, d.tap_rows, d.nt) > (size_t)kSmemLimit) d.stages--;
+  d.smem = dw_smem_bytes(d.stages, mbs, d.tap_rows, d.nt);
+  if (d.smem > (size_t)kSmemLimit) d.ok = false;
+  const int64_t steps = B * d.tiles_x * d.tiles_y;
+  const int zdim = (d.mbs_total + 1) / 2;
+  int64_t s = sm_count() / (d.ngroups * zdim);
+  if (s < 1) s = 1;
+  if (s > steps) s = steps;
+  d.splits = (int)s;
+  d.xh_bytes = align_up((size_t)(B * SHW) * d.Cp * 2, 256);
+  d.gt_bytes = align_up((size_t)steps * d.mbs_total * kDwGtBytes, 256);
+  d.partial_bytes = align_up((size_t)d.splits * d.mbs_total * 128 * d.nchunks * kChunk * 4, 256);
+  d.bias_bytes = simt_bias_workspace(Cbias, 4);
+  return d;
+}
+
+template <int NT>
+void launch_dw(const DwParams &p, dim3 grid, size_t smem, cudaStream_t st) {
+  cudaFuncSetAttribute(tc_dw_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  tc_dw_kernel<NT><<<grid, kThreads, smem, st>>>(p);
+}
+
+// gw[n,ch,slot] = sum_{b,pix} A[b,n,pix] * im2col(src)[b,pix,(slot,ch)]; gb = sum of gbias_src over batch and pixels.
+int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K,
+          int64_t P, int64_t GH, int64_t GW, int interp, int64_t Nout, int64_t B, void *gw, int64_t sn, int64_t sc, int64_t sk,
+          const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st) {
+  const DwGeometry d = dw_geometry(B, CH, SH * SW, K, P, interp, Nout, GH, GW, Cbias);
+  if (!d.ok)
+    return simt_dw<float>(A, src, map, iw, CH, SH, SW, K, P, GH * GW, interp, Nout, B, gw, sn, sc, sk, gbias_src, Cbias, nbias, gb,
+                          ws, ws_bytes, st);
+  if (!ws || ws_bytes < 256 + d.xh_bytes + d.gt_bytes + d.partial_bytes + d.bias_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  char *w8 = (char *)ws;
+  int *status = (int *)w8;
+  __nv_bfloat16 *xh = (__nv_bfloat16 *)(w8 + 256);
+  __nv_bfloat16 *gt = (__nv_bfloat16 *)(w8 + 256 + d.xh_bytes);
+  float *partial = (float *)(w8 + 256 + d.xh_bytes + d.gt_bytes);
+  void *bias_ws = w8 + 256 + d.xh_bytes + d.gt_bytes + d.partial_bytes;
+  if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
+  to_nhwc(src, xh, B, CH, d.Cp, SH * SW, st);
+  grad_image_kernel<<<dim3(d.tiles_x * d.tiles_y, d.mbs_total, (unsigned)B), 256, 0, st>>>((const float *)A, gt, (int)Nout, (int)GH,
+                                                                                           (int)GW, d.tiles_x, d.tiles_y, d.mbs_total);
+  DwParams p{};
+  p.g = Gather{xh, (const float *)map, (const float *)iw, nullptr, d.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, d.nt};
+  p.gt = gt; p.partial = partial; p.status = status;
+  p.B = (int)B; p.mbs_total = d.mbs_total; p.nchunks = d.nchunks; p.tiles_x = d.tiles_x; p.tiles_y = d.tiles_y;
+  p.splits = d.splits; p.stages = d.stages; p.tap_rows = d.tap_rows;
+  dim3 grid(d.ngroups, d.splits, (d.mbs_total + 1) / 2);
+  if (d.nt == 4) launch_dw<4>(p, grid, d.smem, st);
+  else if (d.nt == 1) launch_dw<1>(p, grid, d.smem, st);
+  else launch_dw<0>(p, grid, d.smem, st);
+  tc_dw_reduce_kernel<<<cdiv(Nout * CH * K, 256), 256, 0, st>>>(partial, d.splits, d.mbs_total * 128, d.nchunks * kChunk, (int)Nout,
+                                                               (int)CH, d.Cp, (int)K, sn, sc, sk, (float *)gw);
+  note_launches(4);
+  return simt_bias_grad<float>(gbias_src, B, Cbias, nbias, gb, bias_ws, st);
+}
+
+size_t dw_ws(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int interp, int64_t Nout, int64_t GH, int64_t GW,
+             int64_t Cbias) {
+  const DwGeometry d = dw_geometry(B, CH, SHW, K, P, interp, Nout, GH, GW, Cbias);
+  if (!d.ok) return simt_dw_workspace(B, GH * GW, Nout, CH, K, Cbias, 4);
+  return 256 + d.xh_bytes + d.gt_bytes + d.partial_bytes + d.bias_bytes;
 }
 
 }  // namespace
@@ -405,10 +820,10 @@ size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t 
   switch (op) {
     case SPH_CONV_FORWARD: return gemm_ws(B, Cin, IH * IW, K, P, interp, Cout, true);
     case SPH_CONV_BACKWARD_INPUT: return gemm_ws(B, Cout, OH * OW, K, 0, 0, Cin, false);
-    case SPH_CONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, 4);
+    case SPH_CONV_BACKWARD_WEIGHT: return dw_ws(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
     case SPH_TCONV_FORWARD: return gemm_ws(B, Cin, IH * IW, K, 0, 0, Cout, false);
     case SPH_TCONV_BACKWARD_INPUT: return gemm_ws(B, Cout, OH * OW, K, P, interp, Cin, true);
-    case SPH_TCONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, 4);
+    case SPH_TCONV_BACKWARD_WEIGHT: return dw_ws(B, Cout, OH * OW, K, P, interp, Cin, IH, IW, Cout);
     default: return 0;
   }
 }
@@ -416,43 +831,43 @@ size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t 
 int tc_conv_forward(const void *x, const void *map, const void *iw, const void *weight, const void *bias, void *out,
                     int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
                     int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st) {
-  return tc_gemm(false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, ws,
+  return tc_gemm(false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH, OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, ws,
                  ws_bytes, st);
 }
 
 int tc_conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx, int64_t B, int64_t Cin,
                            int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
                            size_t ws_bytes, cudaStream_t st) {
-  return tc_gemm(true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH * IW, 0, weight, K, Cin * K, 1, nullptr, gx, Cin, B,
-                 ws, ws_bytes, st);
+  return tc_gemm(true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH, IW, 0, weight, K, Cin * K, 1, nullptr, gx, Cin, B, ws,
+                 ws_bytes, st);
 }
 
 int tc_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb,
                             int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
                             int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st) {
-  return simt_dw<float>(gout, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout, OH * OW, gb,
-                        ws, ws_bytes, st);
+  return tc_dw(gout, x, map, iw, Cin, IH, IW, K, P, OH, OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout, OH * OW, gb, ws,
+               ws_bytes, st);
 }
 
 int tc_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out, int64_t B,
                      int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
                      size_t ws_bytes, cudaStream_t st) {
-  return tc_gemm(true, x, nullptr, nullptr, plan, Cin, IH, IW, K, 0, OH * OW, 0, weight, K, Cout * K, 1, bias, out, Cout, B, ws,
+  return tc_gemm(true, x, nullptr, nullptr, plan, Cin, IH, IW, K, 0, OH, OW, 0, weight, K, Cout * K, 1, bias, out, Cout, B, ws,
                  ws_bytes, st);
 }
 
 int tc_tconv_backward_input(const void *gout, const void *map, const void *iw, const void *weight, void *gx, int64_t B,
                             int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
                             int interp, void *ws, size_t ws_bytes, cudaStream_t st) {
-  return tc_gemm(false, gout, map, iw, nullptr, Cout, OH, OW, K, P, IH * IW, interp, weight, Cout * K, K, 1, nullptr, gx, Cin, B,
+  return tc_gemm(false, gout, map, iw, nullptr, Cout, OH, OW, K, P, IH, IW, interp, weight, Cout * K, K, 1, nullptr, gx, Cin, B,
                  ws, ws_bytes, st);
 }
 
 int tc_tconv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb,
                              int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
                              int64_t K, int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st) {
-  return simt_dw<float>(x, gout, map, iw, Cout, OH, OW, K, P, IH * IW, interp, Cin, B, gw, Cout * K, K, 1, gout, Cout, OH * OW, gb,
-                        ws, ws_bytes, st);
+  return tc_dw(x, gout, map, iw, Cout, OH, OW, K, P, IH, IW, interp, Cin, B, gw, Cout * K, K, 1, gout, Cout, OH * OW, gb, ws,
+               ws_bytes, st);
 }
 
 }  // namespace sph
