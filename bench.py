@@ -224,8 +224,11 @@ def run_encoder(args, rank, local, world):
 
     del stack
     torch.cuda.empty_cache()
-    e2e_ms, _ = timed_loop(e2e_step, args.steps, args.warmup, world, dev)
-    e2e_value = flops_step * args.steps / (e2e_ms * 1e-3) / 1e12
+    if args.skip_e2e:
+        e2e_ms, e2e_value = float("nan"), float("nan")
+    else:
+        e2e_ms, _ = timed_loop(e2e_step, args.steps, args.warmup, world, dev)
+        e2e_value = flops_step * args.steps / (e2e_ms * 1e-3) / 1e12
 
     if rank != 0:
         return None
@@ -260,7 +263,7 @@ def run_encoder(args, rank, local, world):
                      "per_launch_ms": {"L%d.%s" % (k[0] + 1, k[1]): round(v, 3) for k, v in per_launch.items()}},
         "clocks": clocks,
     }
-    if world == 1:
+    if world == 1 and not args.skip_cpu:
         impl, kind = pick_cpu_impl()
         cores = os.cpu_count()
         torch.set_num_threads(cores)
@@ -413,16 +416,78 @@ def run_resample(args, rank, local, world):
                          "scatter_achieved": round(s_bytes / (s_ms * 1e-3) / 1e9, 1)}}
 
 
+def run_conv(args, rank, local, world):
+    """BASELINE config 3: weighted (4-point, nearest) mapped conv forward + backward and the transposed conv,
+    every operator timed alone with CUDA events (L2 flushed in between)."""
+    from sphmap import capi, workloads as wl
+    from sphmap.parallel import shard_batch
+    dev = torch.device("cuda", local)
+    prec = capi.BF16 if args.precision == "bf16" else capi.EXACT
+    B = args.batch if args.batch != 64 else 16
+    cfg = wl.config3(B=B)
+    lo, hi = shard_batch(B, rank, world)
+    d = lambda t: t[lo:hi].contiguous().to(dev)  # noqa: E731
+    x, go, w, b, m, iw = d(cfg["x"]), d(cfg["grad_output"]), cfg["weight"].to(dev), cfg["bias"].to(dev), cfg["map"].to(dev), cfg["iw"].to(dev)
+    t = cfg["t"]
+    tx, tgo, tw, tb, tm, tiw = d(t["x"]), d(t["grad_output"]), t["weight"].to(dev), t["bias"].to(dev), t["map"].to(dev), t["iw"].to(dev)
+    K, H, W = 9, x.shape[2], x.shape[3]
+    plan = capi.plan_build(m, iw, H * W, K, 0, H, W)
+    tplan = capi.plan_build(tm, tiw, tm.shape[0] * tm.shape[1], K, 0, t["oh"], t["ow"])
+    ops = {
+        "conv.fwd": lambda: capi.conv_forward(x, m, w, b, K, 0, iw, prec),
+        "conv.dx": lambda: capi.conv_backward_input(go, plan, w, H, W, K, prec),
+        "conv.dw": lambda: capi.conv_backward_weight(go, x, m, K, 0, iw, prec),
+        "tconv.fwd": lambda: capi.tconv_forward(tx, tplan, tw, tb, t["oh"], t["ow"], K, prec),
+        "tconv.dx": lambda: capi.tconv_backward_input(tgo, tm, tw, K, 0, tiw, prec),
+        "tconv.dw": lambda: capi.tconv_backward_weight(tgo, tx, tm, K, 0, tiw, prec),
+    }
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    times = {k: [] for k in ops}
+    l0 = capi.lib.sph_launch_count()
+    for i in range(args.warmup + args.steps):
+        for k, fn in ops.items():
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= args.warmup:
+                times[k].append(e0.elapsed_time(e1))
+    launches = (capi.lib.sph_launch_count() - l0) * args.steps // (args.warmup + args.steps)
+    ms = {k: max_over_ranks(sum(v) / len(v), world, dev) for k, v in times.items()}
+    if rank != 0:
+        return None
+    gflop_conv = 2 * B * 128 * 64 * 9 * H * W / 1e9
+    gflop_t = 2 * B * 128 * 64 * 9 * (H // 2) * (W // 2) / 1e9
+    conv_ms = ms["conv.fwd"] + ms["conv.dx"] + ms["conv.dw"]
+    peaks = measured_peaks()
+    return {"metric": "mapped-conv fwd+bwd TFLOP/s", "value": round(3 * gflop_conv / conv_ms, 2), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(conv_ms, 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "f32", "data": "synthetic",
+            "config": {"workload": "BASELINE config 3: weighted (P=4, nearest) mapped conv B=%d 64->128 256x512 K=9, uniform-random map; "
+                                   "transposed conv 128->64 128x256->256x512" % B, "precision": args.precision,
+                       "l2": "256 MB flush before every launch",
+                       "mpix_per_s": round(B * H * W / (conv_ms * 1e-3) / 1e6, 1)},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "kernel": "conv forward", "achieved": round(gflop_conv / ms["conv.fwd"], 2),
+                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(gflop_conv / ms["conv.fwd"] / peaks["bf16_tflops"], 4),
+                         "traffic": None, "per_op_ms": {k: round(v, 3) for k, v in ms.items()},
+                         "tconv_fwd_bwd_tflops": round(3 * gflop_t / (ms["tconv.fwd"] + ms["tconv.dx"] + ms["tconv.dw"]), 2)}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="encoder", choices=["encoder", "pool", "resample"])
+    ap.add_argument("--workload", default="encoder", choices=["encoder", "pool", "resample", "conv"])
     ap.add_argument("--precision", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--batch", type=int, default=64, help="global batch")
     ap.add_argument("--height", type=int, default=512, help="input height of the encoder stack (width = 2x)")
+    ap.add_argument("--skip-e2e", action="store_true", help="encoder: only the device-resident arm (for profiling runs)")
+    ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -434,7 +499,7 @@ def main():
     rank, local, world = dist_setup(args.gpus)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
-    fn = {"encoder": run_encoder, "pool": run_pool, "resample": run_resample}[args.workload]
+    fn = {"encoder": run_encoder, "pool": run_pool, "resample": run_resample, "conv": run_conv}[args.workload]
     out = fn(args, rank, local, world)
     if out is not None:
         print(json.dumps(out), flush=True)

@@ -128,6 +128,7 @@ struct PlanHeader {
   unsigned magic;
   int n_keys, K, dtype, e_max;
   unsigned long long off_offsets, off_src, off_w;
+  int max_seg;  // longest segment (entries of one key), written by the sort pass
 };
 constexpr unsigned kPlanMagic = 0x53504c4eu;  // "SPLN"
 

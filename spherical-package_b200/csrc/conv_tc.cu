@@ -59,44 +59,39 @@ __host__ __device__ inline void chunk_vec(int Cp, int K, int chunk, int v, int &
 }
 
 struct Gather {
-  const __nv_bfloat16 *xh;  // (B, SH*SW, Cp) channels-last bf16 source
+  const __nv_bfloat16 *xh;  // (B, SH*SW + 1, Cp) channels-last bf16 source; the extra last pixel of every image is zero
   const float *map, *iw;    // direct mode: sample map (+ interpolation weights) over the (GH, GW) pixel grid
   const void *plan;         // plan mode: keyed by (pixel of the (GH, GW) grid) * K + slot
   int Cp, SH, SW, K, P, GH, GW, interp, nt;
 };
 
+// Gathered columns are accumulated over the taps with packed bf16x2 FMAs (one rounding per tap) by default;
+// building with -DSPH_TC_GATHER_FP32 accumulates in fp32 and rounds once.
+#ifdef SPH_TC_GATHER_FP32
+constexpr bool kAcc32 = true;
+#else
+constexpr bool kAcc32 = false;
+#endif
+
 __device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); }
 
-__device__ __forceinline__ void fma8(float (&acc)[8], float w, const uint4 &q) {
-  acc[0] = fmaf(w, bf16_lo(q.x), acc[0]);
-  acc[1] = fmaf(w, bf16_hi(q.x), acc[1]);
-  acc[2] = fmaf(w, bf16_lo(q.y), acc[2]);
-  acc[3] = fmaf(w, bf16_hi(q.y), acc[3]);
-  acc[4] = fmaf(w, bf16_lo(q.z), acc[4]);
-  acc[5] = fmaf(w, bf16_hi(q.z), acc[5]);
-  acc[6] = fmaf(w, bf16_lo(q.w), acc[6]);
-  acc[7] = fmaf(w, bf16_hi(q.w), acc[7]);
-}
-__device__ __forceinline__ uint4 pack8(const float (&a)[8]) {
-  uint4 o;
-  o.x = pack_bf16(a[0], a[1]);
-  o.y = pack_bf16(a[2], a[3]);
-  o.z = pack_bf16(a[4], a[5]);
-  o.w = pack_bf16(a[6], a[7]);
-  return o;
-}
-
-// One tap-table entry: element offset of the source pixel and its weight (0 = unused).
+// One tap-table entry: byte offset of the source pixel inside its image and the tap weight (fp32 bits, or the
+// weight twice as bf16x2).  Unused entries point at the image's zero pixel with weight 0.
 struct __align__(8) Tap {
   int off;
-  float w;
+  uint32_t w;
 };
+
+__device__ __forceinline__ uint32_t tap_weight(float w) {
+  return kAcc32 ? __float_as_uint(w) : pack_bf16(w, w);
+}
 
 // Taps of map slot (pix, slot) into nt table entries.
 template <int INTERP>
 __device__ __forceinline__ void fill_taps(const Gather &g, int pix, int slot, Tap *dst) {
   const int PP = g.P > 0 ? g.P : 1;
   const size_t e0 = ((size_t)pix * g.K + slot) * PP;
+  const int zero_off = g.SH * g.SW * g.Cp * 2, pitch = g.Cp * 2;
   Taps<float> t;
   int n = 0;
   for (int q = 0; q < PP; q++) {
@@ -105,8 +100,8 @@ __device__ __forceinline__ void fill_taps(const Gather &g, int pix, int slot, Ta
 #pragma unroll
     for (int i = 0; i < TapCount<INTERP>::value; i++, n++) {
       const bool ok = t.off[i] >= 0;
-      dst[n].off = ok ? t.off[i] : 0;
-      dst[n].w = ok ? wq * t.w[i] : 0.0f;
+      dst[n].off = ok ? t.off[i] * pitch : zero_off;
+      dst[n].w = tap_weight(ok ? wq * t.w[i] : 0.0f);
     }
   }
 }
@@ -115,52 +110,97 @@ __device__ __forceinline__ void fill_taps_any(const Gather &g, int pix, int slot
   SPH_DISPATCH_INTERP(g.interp, fill_taps<INTERP>(g, pix, slot, dst));
 }
 
-// Weighted sum of 8 channels over the taps of one (pixel, slot): all loads are issued before any is used.
-template <int NT>
-__device__ __forceinline__ uint4 gather_taps(const __nv_bfloat16 *__restrict__ img, const Tap *__restrict__ taps, int nt,
-                                             int Cp, int c0) {
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; i++) acc[i] = 0.0f;
-  if (NT > 0) {
-    uint4 q[NT > 0 ? NT : 1];
-    float w[NT > 0 ? NT : 1];
-#pragma unroll
-    for (int t = 0; t < NT; t++) {
-      const Tap tp = taps[t];
-      w[t] = tp.w;
-      q[t] = make_uint4(0, 0, 0, 0);
-      if (tp.w != 0.0f) q[t] = __ldg((const uint4 *)(img + (size_t)tp.off * Cp + c0));
-    }
-#pragma unroll
-    for (int t = 0; t < NT; t++) fma8(acc, w[t], q[t]);
-  } else {
-    for (int t = 0; t < nt; t++) {
-      const Tap tp = taps[t];
-      if (tp.w != 0.0f) fma8(acc, tp.w, __ldg((const uint4 *)(img + (size_t)tp.off * Cp + c0)));
-    }
-  }
-  return pack8(acc);
+__device__ __forceinline__ void fill_taps_zero(const Gather &g, Tap *dst) {
+  const int zero_off = g.SH * g.SW * g.Cp * 2;
+  for (int i = 0; i < g.nt; i++) { dst[i].off = zero_off; dst[i].w = 0u; }
 }
 
-__device__ __forceinline__ uint4 gather_plan(const __nv_bfloat16 *__restrict__ img, const PlanView<float> &pv, int key, int Cp,
-                                             int c0) {
-  float acc[8];
+// Accumulator of 8 channels: four bf16x2 registers, or eight floats.
+struct Acc8 {
+  uint32_t h[4];
+  float f[8];
+};
+__device__ __forceinline__ void acc_zero(Acc8 &a) {
+  if (kAcc32) {
 #pragma unroll
-  for (int i = 0; i < 8; i++) acc[i] = 0.0f;
-  const int e0 = __ldg(pv.offsets + key), e1 = __ldg(pv.offsets + key + 1);
-  int e = e0;
-  for (; e + 1 < e1; e += 2) {
-    const int s0 = __ldg(pv.src + e), s1 = __ldg(pv.src + e + 1);
-    const float w0 = __ldg(pv.w + e), w1 = __ldg(pv.w + e + 1);
-    const uint4 q0 = __ldg((const uint4 *)(img + (size_t)s0 * Cp + c0));
-    const uint4 q1 = __ldg((const uint4 *)(img + (size_t)s1 * Cp + c0));
-    fma8(acc, w0, q0);
-    fma8(acc, w1, q1);
+    for (int i = 0; i < 8; i++) a.f[i] = 0.0f;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; i++) a.h[i] = 0u;
   }
-  if (e < e1) fma8(acc, __ldg(pv.w + e), __ldg((const uint4 *)(img + (size_t)__ldg(pv.src + e) * Cp + c0)));
-  return pack8(acc);
 }
+__device__ __forceinline__ uint32_t hfma2_bf16(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ void acc_fma(Acc8 &a, uint32_t w, const uint4 &q) {
+  if (kAcc32) {
+    const float wf = __uint_as_float(w);
+    a.f[0] = fmaf(wf, bf16_lo(q.x), a.f[0]);
+    a.f[1] = fmaf(wf, bf16_hi(q.x), a.f[1]);
+    a.f[2] = fmaf(wf, bf16_lo(q.y), a.f[2]);
+    a.f[3] = fmaf(wf, bf16_hi(q.y), a.f[3]);
+    a.f[4] = fmaf(wf, bf16_lo(q.z), a.f[4]);
+    a.f[5] = fmaf(wf, bf16_hi(q.z), a.f[5]);
+    a.f[6] = fmaf(wf, bf16_lo(q.w), a.f[6]);
+    a.f[7] = fmaf(wf, bf16_hi(q.w), a.f[7]);
+  } else {
+    a.h[0] = hfma2_bf16(w, q.x, a.h[0]);
+    a.h[1] = hfma2_bf16(w, q.y, a.h[1]);
+    a.h[2] = hfma2_bf16(w, q.z, a.h[2]);
+    a.h[3] = hfma2_bf16(w, q.w, a.h[3]);
+  }
+}
+__device__ __forceinline__ uint4 acc_pack(const Acc8 &a) {
+  if (kAcc32)
+    return make_uint4(pack_bf16(a.f[0], a.f[1]), pack_bf16(a.f[2], a.f[3]), pack_bf16(a.f[4], a.f[5]), pack_bf16(a.f[6], a.f[7]));
+  return make_uint4(a.h[0], a.h[1], a.h[2], a.h[3]);
+}
+
+__device__ __forceinline__ uint4 ldg16(const char *p) { return __ldg((const uint4 *)p); }
+
+// Two (pixel, slot) items at once: the 2*NT 16-byte loads are issued before any is consumed.  `imgc` is the
+// image base advanced to the item's first channel; t0/t1 point at the items' table rows.
+template <int NT>
+__device__ __forceinline__ void gather_pair(const char *__restrict__ imgc, const Tap *__restrict__ t0,
+                                            const Tap *__restrict__ t1, int nt, Acc8 &a0, Acc8 &a1) {
+  if (NT > 0) {
+    uint4 q0[NT > 0 ? NT : 1], q1[NT > 0 ? NT : 1];
+    uint32_t w0[NT > 0 ? NT : 1], w1[NT > 0 ? NT : 1];
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+      const Tap a = t0[t];
+      w0[t] = a.w;
+      q0[t] = ldg16(imgc + a.off);
+    }
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+      const Tap a = t1[t];
+      w1[t] = a.w;
+      q1[t] = ldg16(imgc + a.off);
+    }
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc_fma(a0, w0[t], q0[t]);
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc_fma(a1, w1[t], q1[t]);
+  } else {
+    for (int t = 0; t < nt; t++) {
+      const Tap a = t0[t], b = t1[t];
+      const uint4 qa = ldg16(imgc + a.off), qb = ldg16(imgc + b.off);
+      acc_fma(a0, a.w, qa);
+      acc_fma(a1, b.w, qb);
+    }
+  }
+}
+
+// Plan entries [e0, e1) that did not fit the tap table, straight from the plan.
+__device__ __forceinline__ void gather_plan_rest(Acc8 &acc, const char *__restrict__ imgc, const PlanView<float> &pv, int e0,
+                                                 int e1, int pitch) {
+  for (int e = e0; e < e1; e++) acc_fma(acc, tap_weight(__ldg(pv.w + e)), ldg16(imgc + (size_t)__ldg(pv.src + e) * pitch));
+}
+
+constexpr int kPlanTaps = 4;  // plan entries per (pixel, slot) kept in the shared tap table; the rest is read from the plan
 
 // Pixel of local index l inside tile (ty, tx) of a (GH, GW) grid tiled TH x kTW; -1 if outside.
 __device__ __forceinline__ int tile_pixel(int l, int ty, int tx, int TH, int GH, int GW) {
@@ -187,6 +227,7 @@ struct TcParams {
 struct Smem {
   uint8_t *A, *Bw;
   Tap *taps;
+  int2 *rest;  // plan mode: [slot][pixel] range of plan entries beyond the table capacity
   uint64_t *full, *empty, *tfull, *tempty;
   uint32_t *tmem_ptr;
   volatile int *abort_flag;
@@ -195,7 +236,8 @@ struct Smem {
 inline size_t gemm_smem_bytes(int stages, int Npb, int K, int nt, bool direct) {
   size_t s = 1024;  // alignment slack
   s += (size_t)stages * (kAStageBytes + Npb * 128);
-  if (direct) s += (size_t)K * kTileM * nt * sizeof(Tap);
+  s += (size_t)K * kTileM * nt * sizeof(Tap);
+  if (!direct) s += (size_t)K * kTileM * sizeof(int2);
   s += 8 * (2 * stages + 4) + 16;
   return s;
 }
@@ -207,7 +249,9 @@ __device__ inline Smem carve(uint8_t *raw, const TcParams &p, bool direct) {
   s.Bw = b + (size_t)p.stages * kAStageBytes;
   uint8_t *q = s.Bw + (size_t)p.stages * p.Npb * 128;
   s.taps = (Tap *)q;
-  q += direct ? (size_t)p.g.K * kTileM * p.g.nt * sizeof(Tap) : 0;
+  q += (size_t)p.g.K * kTileM * p.g.nt * sizeof(Tap);
+  s.rest = (int2 *)q;
+  q += direct ? 0 : (size_t)p.g.K * kTileM * sizeof(int2);
   s.full = (uint64_t *)q;
   s.empty = s.full + p.stages;
   s.tfull = s.empty + p.stages;
@@ -215,6 +259,39 @@ __device__ inline Smem carve(uint8_t *raw, const TcParams &p, bool direct) {
   s.tmem_ptr = (uint32_t *)(s.tempty + 2);
   s.abort_flag = (volatile int *)(s.tmem_ptr + 1);
   return s;
+}
+
+// One producer thread's share of a 128-pixel x 64-column tile: 16-byte vector v = pt & 7 of pixels
+// (pt >> 3) + 32 r, r = 0..3, two pixels at a time.  STRIDE = table entries per (pixel, slot) (0: g.nt),
+// NTI = entries actually used (0: g.nt).
+template <int STRIDE, int NTI, bool PLAN>
+__device__ __forceinline__ void produce_chunk(const Gather &g, const Tap *taps, const int2 *rest, const PlanView<float> &pv,
+                                              const char *img, int chunk, int pt, uint8_t *As) {
+  const int v = pt & 7, plb = pt >> 3;
+  const int stride = STRIDE > 0 ? STRIDE : g.nt;
+  int slot, c0;
+  chunk_vec(g.Cp, g.K, chunk, v, slot, c0);
+  const bool valid = slot < g.K;
+  const char *imgc = img + c0 * 2;
+  const int row0 = (valid ? slot : 0) * kTileM + plb;
+  const Tap *trow = taps + (size_t)row0 * stride;
+  uint8_t *dst = As + plb * 128 + ((v ^ (plb & 7)) << 4);
+#pragma unroll
+  for (int r = 0; r < kTileM * 8 / kProducerThreads; r += 2) {
+    Acc8 a0, a1;
+    acc_zero(a0);
+    acc_zero(a1);
+    if (valid) {
+      gather_pair<NTI>(imgc, trow + (size_t)(r * 32) * stride, trow + (size_t)((r + 1) * 32) * stride, g.nt, a0, a1);
+      if (PLAN) {
+        const int2 r0 = rest[row0 + r * 32], r1 = rest[row0 + (r + 1) * 32];
+        if (r0.x < r0.y) gather_plan_rest(a0, imgc, pv, r0.x, r0.y, g.Cp * 2);
+        if (r1.x < r1.y) gather_plan_rest(a1, imgc, pv, r1.x, r1.y, g.Cp * 2);
+      }
+    }
+    *(uint4 *)(dst + r * 32 * 128) = acc_pack(a0);
+    *(uint4 *)(dst + (r + 1) * 32 * 128) = acc_pack(a1);
+  }
 }
 
 template <int MODE, int NT>
@@ -318,26 +395,41 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
     bool alive = true;
     PlanView<float> pv{};
     bool plan_ok = true;
-    if (MODE == MODE_PLAN) pv = plan_view<float>(g.plan, npix * g.K, plan_ok);
+    int plan_nti = kPlanTaps;
+    if (MODE == MODE_PLAN) {
+      pv = plan_view<float>(g.plan, npix * g.K, plan_ok);
+      if (plan_ok) plan_nti = min(kPlanTaps, ((const PlanHeader *)g.plan)->max_seg);
+    }
+    const int pitch = g.Cp * 2, zero_off = (int)shw * pitch;
     for (int tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
       const int nb = tile % p.nblk, rest = tile / p.nblk;
       const int b = rest / tiles_per_image, t2 = rest % tiles_per_image;
       const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
-      const __nv_bfloat16 *img = g.xh + (size_t)b * shw * g.Cp;
-      if (MODE == MODE_DIRECT) {
-        producer_bar();  // every producer is done reading the previous tile's taps
-        for (int idx = pt; idx < g.K * kTileM; idx += kProducerThreads) {
-          const int slot = idx / kTileM, pl = idx % kTileM;
-          const int pix = tile_pixel(pl, ty, tx, kTH, g.GH, g.GW);
-          Tap *dst = sm.taps + (size_t)idx * g.nt;
-          if (pix >= 0) {
-            fill_taps_any(g, pix, slot, dst);
-          } else {
-            for (int i = 0; i < g.nt; i++) { dst[i].off = 0; dst[i].w = 0.0f; }
+      const char *img = (const char *)g.xh + (size_t)b * (shw + 1) * pitch;
+      producer_bar();  // every producer is done reading the previous tile's taps
+      for (int idx = pt; idx < g.K * kTileM; idx += kProducerThreads) {
+        const int slot = idx / kTileM, pl = idx % kTileM;
+        const int pix = tile_pixel(pl, ty, tx, kTH, g.GH, g.GW);
+        Tap *dst = sm.taps + (size_t)idx * g.nt;
+        if (MODE == MODE_DIRECT) {
+          if (pix >= 0) fill_taps_any(g, pix, slot, dst);
+          else fill_taps_zero(g, dst);
+        } else {
+          int e0 = 0, e1 = 0;
+          if (plan_ok && pix >= 0) {
+            e0 = __ldg(pv.offsets + pix * g.K + slot);
+            e1 = __ldg(pv.offsets + pix * g.K + slot + 1);
           }
+#pragma unroll
+          for (int i = 0; i < kPlanTaps; i++) {
+            const bool in = e0 + i < e1;
+            dst[i].off = in ? __ldg(pv.src + e0 + i) * pitch : zero_off;
+            dst[i].w = tap_weight(in ? __ldg(pv.w + e0 + i) : 0.0f);
+          }
+          sm.rest[idx] = make_int2(min(e0 + kPlanTaps, e1), e1);
         }
-        producer_bar();
       }
+      producer_bar();
       for (int chunk = 0; chunk < p.nchunks; chunk++, it++) {
         const int s = it % S;
         if (!mbar_wait(sm.empty + s, ((it / S) & 1) ^ 1, sm.abort_flag)) { alive = false; break; }
@@ -347,21 +439,14 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
           bulk_copy_g2s(sm.Bw + (size_t)s * bytes, p.wp + ((size_t)nb * p.nchunks + chunk) * p.Npb * kChunk, bytes, sm.full + s);
         }
         uint8_t *As = sm.A + (size_t)s * kAStageBytes;
-#pragma unroll
-        for (int r = 0; r < kTileM * 8 / kProducerThreads; r++) {
-          const int idx = pt + r * kProducerThreads, pl = idx >> 3, v = idx & 7;
-          int slot, c0;
-          chunk_vec(g.Cp, g.K, chunk, v, slot, c0);
-          uint4 o = make_uint4(0, 0, 0, 0);
-          if (slot < g.K) {
-            if (MODE == MODE_DIRECT) {
-              o = gather_taps<NT>(img, sm.taps + (size_t)(slot * kTileM + pl) * g.nt, g.nt, g.Cp, c0);
-            } else {
-              const int pix = tile_pixel(pl, ty, tx, kTH, g.GH, g.GW);
-              if (plan_ok && pix >= 0) o = gather_plan(img, pv, pix * g.K + slot, g.Cp, c0);
-            }
-          }
-          *(uint4 *)(As + pl * 128 + ((v ^ (pl & 7)) << 4)) = o;
+        if (MODE == MODE_DIRECT) {
+          produce_chunk<NT, NT, false>(g, sm.taps, nullptr, pv, img, chunk, pt, As);
+        } else if (plan_nti >= 3) {
+          produce_chunk<kPlanTaps, 4, true>(g, sm.taps, sm.rest, pv, img, chunk, pt, As);
+        } else if (plan_nti == 2) {
+          produce_chunk<kPlanTaps, 2, true>(g, sm.taps, sm.rest, pv, img, chunk, pt, As);
+        } else {
+          produce_chunk<kPlanTaps, 1, true>(g, sm.taps, sm.rest, pv, img, chunk, pt, As);
         }
         fence_proxy_async();
         __syncwarp();
@@ -512,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
     for (int step = step_lo; alive && step < step_hi; step++, it++) {
       const int b = step / tiles_per_image, t2 = step % tiles_per_image;
       const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
-      const __nv_bfloat16 *img = g.xh + (size_t)b * shw * g.Cp;
+      const char *img = (const char *)g.xh + (size_t)b * (shw + 1) * g.Cp * 2;
       producer_bar();
       for (int idx = pt; idx < p.tap_rows * kDwPix; idx += kProducerThreads) {
         const int row = idx / kDwPix, pl = idx % kDwPix;
@@ -521,11 +606,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         else slot = slot_base + row;
         const int pix = tile_pixel(pl, ty, tx, kDwTH, g.GH, g.GW);
         Tap *dst = sm.taps + (size_t)idx * g.nt;
-        if (pix >= 0 && slot < g.K && (g.Cp < 64 || row < ncg)) {
-          fill_taps_any(g, pix, slot, dst);
-        } else {
-          for (int i = 0; i < g.nt; i++) { dst[i].off = 0; dst[i].w = 0.0f; }
-        }
+        if (pix >= 0 && slot < g.K && (g.Cp < 64 || row < ncg)) fill_taps_any(g, pix, slot, dst);
+        else fill_taps_zero(g, dst);
       }
       producer_bar();
       const int s = it % S;
@@ -536,16 +618,25 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         mbar_arrive_expect_tx(sm.full + s, bytes);
         bulk_copy_g2s(st + kDwColBytes, p.gt + ((size_t)step * p.mbs_total + mb0) * (kDwGtBytes / 2), bytes, sm.full + s);
       }
-      for (int idx = pt; idx < ncg * kDwPix * 8; idx += kProducerThreads) {
-        const int gi = idx / (kDwPix * 8), rem = idx % (kDwPix * 8), pl = rem >> 3, v = rem & 7;
-        int slot, c0;
-        chunk_vec(g.Cp, g.K, chunk0 + gi, v, slot, c0);
-        uint4 o = make_uint4(0, 0, 0, 0);
-        if (slot < g.K) {
-          const int row = g.Cp >= 64 ? gi : slot - slot_base;
-          o = gather_taps<NT>(img, sm.taps + (size_t)(row * kDwPix + pl) * g.nt, g.nt, g.Cp, c0);
+      // thread pt: 16-byte vector v = pt & 7 of pixels (pt >> 3) and (pt >> 3) + 32, for each chunk of the group
+      {
+        const int v = pt & 7, plb = pt >> 3;
+        const int stride = NT > 0 ? NT : g.nt;
+        uint8_t *dst0 = st + plb * 128 + ((v ^ (plb & 7)) << 4);
+        for (int gi = 0; gi < ncg; gi++) {
+          int slot, c0;
+          chunk_vec(g.Cp, g.K, chunk0 + gi, v, slot, c0);
+          Acc8 a0, a1;
+          acc_zero(a0);
+          acc_zero(a1);
+          if (slot < g.K) {
+            const int row = g.Cp >= 64 ? gi : slot - slot_base;
+            const Tap *trow = sm.taps + (size_t)(row * kDwPix + plb) * stride;
+            gather_pair<NT>(img + c0 * 2, trow, trow + (size_t)32 * stride, g.nt, a0, a1);
+          }
+          *(uint4 *)(dst0 + gi * (kDwPix * 128)) = acc_pack(a0);
+          *(uint4 *)(dst0 + gi * (kDwPix * 128) + 32 * 128) = acc_pack(a1);
         }
-        *(uint4 *)(st + gi * (kDwPix * 128) + pl * 128 + ((v ^ (pl & 7)) << 4)) = o;
       }
       fence_proxy_async();
       __syncwarp();
@@ -563,7 +654,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
 // layout pre-passes
 // =================================================================================================
 
-// (B, C, HW) float32 -> (B, HW, Cp) bf16, channels beyond C zero.  32 pixels x 64 channels per block.
+// (B, C, HW) float32 -> (B, HW + 1, Cp) bf16; channels beyond C and the extra pixel HW of every image are
+// zero (unused taps point there).  32 pixels x 64 channels per block.
 __global__ void __launch_bounds__(256) nchw_to_nhwc_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ y,
                                                                  int C, int Cp, int HW) {
   __shared__ float tile[64][33];
@@ -575,13 +667,13 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_bf16_kernel(const float *__r
   }
   __syncthreads();
   const int pp = tid >> 3, v = tid & 7;
-  if (p0 + pp < HW && c0 + v * 8 < Cp) {
+  if (p0 + pp <= HW && c0 + v * 8 < Cp) {
     uint4 o;
     o.x = pack_bf16(tile[v * 8 + 0][pp], tile[v * 8 + 1][pp]);
     o.y = pack_bf16(tile[v * 8 + 2][pp], tile[v * 8 + 3][pp]);
     o.z = pack_bf16(tile[v * 8 + 4][pp], tile[v * 8 + 5][pp]);
     o.w = pack_bf16(tile[v * 8 + 6][pp], tile[v * 8 + 7][pp]);
-    *(uint4 *)(y + ((size_t)b * HW + p0 + pp) * Cp + c0 + v * 8) = o;
+    *(uint4 *)(y + ((size_t)b * (HW + 1) + p0 + pp) * Cp + c0 + v * 8) = o;
   }
 }
 
@@ -669,15 +761,17 @@ struct Geometry {
 
 Geometry geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int interp, int64_t Nout, bool direct) {
   Geometry g{};
+  g.ok = true;
   g.Cp = padded_channels(CH);
   g.nchunks = num_chunks(g.Cp, (int)K);
   const int np = (int)align_up((size_t)Nout, 16);
   g.Npb = np > 256 ? 256 : np;
   g.nblk = (np + g.Npb - 1) / g.Npb;
-  g.nt = (int)((P > 0 ? P : 1) * (interp == SPH_NEAREST ? 1 : 4));
-  g.xh_bytes = align_up((size_t)(B * SHW) * g.Cp * 2, 256);
+  g.nt = direct ? (int)((P > 0 ? P : 1) * (interp == SPH_NEAREST ? 1 : 4)) : kPlanTaps;
+  g.xh_bytes = align_up((size_t)(B * (SHW + 1)) * g.Cp * 2, 256);
+  if ((SHW + 1) * g.Cp * 2 >= ((int64_t)1 << 31)) g.ok = false;
   g.wp_bytes = align_up((size_t)g.nblk * g.nchunks * g.Npb * kChunk * 2, 256);
-  g.ok = !direct || (size_t)K * kTileM * g.nt * sizeof(Tap) <= (size_t)kMaxTapBytes;
+  g.ok = g.ok && (size_t)K * kTileM * g.nt * sizeof(Tap) <= (size_t)kMaxTapBytes;
   g.stages = 4;
   while (g.stages > 2 && gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct) > (size_t)kSmemLimit) g.stages--;
   g.smem = gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct);
@@ -686,7 +780,7 @@ Geometry geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int 
 }
 
 void to_nhwc(const void *src, __nv_bfloat16 *xh, int64_t B, int64_t CH, int Cp, int64_t HW, cudaStream_t st) {
-  nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW, 32), cdiv(Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, Cp, (int)HW);
+  nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW + 1, 32), cdiv(Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, Cp, (int)HW);
 }
 
 template <int MODE, int NT>
@@ -718,7 +812,7 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
   p.tiles_x = cdiv(GW, kTW); p.tiles_y = cdiv(GH, kTH); p.stages = g.stages;
   const int64_t tiles = (int64_t)B * p.tiles_x * p.tiles_y * g.nblk;
   const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  if (use_plan) launch_gemm<MODE_PLAN, 0>(p, grid, g.smem, st);
+  if (use_plan) launch_gemm<MODE_PLAN, kPlanTaps>(p, grid, g.smem, st);
   else if (g.nt == 4) launch_gemm<MODE_DIRECT, 4>(p, grid, g.smem, st);
   else if (g.nt == 1) launch_gemm<MODE_DIRECT, 1>(p, grid, g.smem, st);
   else launch_gemm<MODE_DIRECT, 0>(p, grid, g.smem, st);
@@ -759,7 +853,8 @@ DwGeometry dw_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P,
   if (s < 1) s = 1;
   if (s > steps) s = steps;
   d.splits = (int)s;
-  d.xh_bytes = align_up((size_t)(B * SHW) * d.Cp * 2, 256);
+  d.xh_bytes = align_up((size_t)(B * (SHW + 1)) * d.Cp * 2, 256);
+  if ((SHW + 1) * d.Cp * 2 >= ((int64_t)1 << 31)) d.ok = false;
   d.gt_bytes = align_up((size_t)steps * d.mbs_total * kDwGtBytes, 256);
   d.partial_bytes = align_up((size_t)d.splits * d.mbs_total * 128 * d.nchunks * kChunk * 4, 256);
   d.bias_bytes = simt_bias_workspace(Cbias, 4);

@@ -43,10 +43,11 @@ __global__ void plan_fill_kernel(const T *map, const T *iw, int n_slots, int K, 
 // One thread per key: order the segment by entry id (the fill order above is
 // not reproducible), then turn ids into source positions.
 template <typename T>
-__global__ void plan_sort_kernel(const int *offsets, int *ids, T *w, int n_keys, int id_div) {
+__global__ void plan_sort_kernel(const int *offsets, int *ids, T *w, int n_keys, int id_div, int *max_seg) {
   const int key = blockIdx.x * blockDim.x + threadIdx.x;
   if (key >= n_keys) return;
   const int e0 = offsets[key], e1 = offsets[key + 1];
+  if (e1 - e0 > 1) atomicMax(max_seg, e1 - e0);
   for (int i = e0 + 1; i < e1; i++) {
     const int id = ids[i];
     const T wi = w[i];
@@ -167,7 +168,6 @@ static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int6
     else
       plan_fill_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, offsets, cursor, src, w);
   });
-  plan_sort_kernel<T><<<cdiv(nk, 256), 256, 0, st>>>(offsets, src, w, nk, (int)(4 * PP * K));
   PlanHeader h;
   h.magic = kPlanMagic;
   h.n_keys = nk;
@@ -177,7 +177,9 @@ static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int6
   h.off_offsets = L.off_offsets;
   h.off_src = L.off_src;
   h.off_w = L.off_w;
+  h.max_seg = 1;
   plan_header_kernel<<<1, 1, 0, st>>>((PlanHeader *)plan, h);
+  plan_sort_kernel<T><<<cdiv(nk, 256), 256, 0, st>>>(offsets, src, w, nk, (int)(4 * PP * K), &((PlanHeader *)plan)->max_seg);
   return launch_status(7);
 }
 
