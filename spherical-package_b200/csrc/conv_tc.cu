@@ -32,7 +32,7 @@ using namespace tc;
 
 constexpr int kChunk = 64;  // GEMM columns per 128-byte swizzle row
 constexpr int kTW = 16;     // pixel tiles are kTW wide; 8 rows (forward-type) or 4 rows (weight gradient)
-constexpr int kEpilogueWarps = 4, kProducerWarps = 8;
+constexpr int kEpilogueWarps = 4, kProducerWarps = 16;
 constexpr int kProducerThreads = 32 * kProducerWarps;
 constexpr int kThreads = 32 * (kEpilogueWarps + 1 + kProducerWarps);
 constexpr int kFirstProducerThread = 32 * (kEpilogueWarps + 1);
@@ -163,8 +163,9 @@ __device__ __forceinline__ uint4 ldg16(const char *p) { return __ldg((const uint
 // Two (pixel, slot) items at once: the 2*NT 16-byte loads are issued before any is consumed.  `imgc` is the
 // image base advanced to the item's first channel; t0/t1 point at the items' table rows.
 template <int NT>
-__device__ __forceinline__ void gather_pair(const char *__restrict__ imgc, const Tap *__restrict__ t0,
-                                            const Tap *__restrict__ t1, int nt, Acc8 &a0, Acc8 &a1) {
+__device__ __forceinline__ void gather_pair(const char *__restrict__ imgc, const char *__restrict__ imgd,
+                                            const Tap *__restrict__ t0, const Tap *__restrict__ t1, int nt, Acc8 &a0,
+                                            Acc8 &a1) {
   if (NT > 0) {
     uint4 q0[NT > 0 ? NT : 1], q1[NT > 0 ? NT : 1];
     uint32_t w0[NT > 0 ? NT : 1], w1[NT > 0 ? NT : 1];
@@ -178,7 +179,7 @@ __device__ __forceinline__ void gather_pair(const char *__restrict__ imgc, const
     for (int t = 0; t < NT; t++) {
       const Tap a = t1[t];
       w1[t] = a.w;
-      q1[t] = ldg16(imgc + a.off);
+      q1[t] = ldg16(imgd + a.off);
     }
 #pragma unroll
     for (int t = 0; t < NT; t++) acc_fma(a0, w0[t], q0[t]);
@@ -187,7 +188,7 @@ __device__ __forceinline__ void gather_pair(const char *__restrict__ imgc, const
   } else {
     for (int t = 0; t < nt; t++) {
       const Tap a = t0[t], b = t1[t];
-      const uint4 qa = ldg16(imgc + a.off), qb = ldg16(imgc + b.off);
+      const uint4 qa = ldg16(imgc + a.off), qb = ldg16(imgd + b.off);
       acc_fma(a0, a.w, qa);
       acc_fma(a1, b.w, qb);
     }
@@ -261,8 +262,10 @@ __device__ inline Smem carve(uint8_t *raw, const TcParams &p, bool direct) {
   return s;
 }
 
+constexpr int kRowStep = kProducerThreads / 8;  // pixel rows covered by one pass of all producer threads
+
 // One producer thread's share of a 128-pixel x 64-column tile: 16-byte vector v = pt & 7 of pixels
-// (pt >> 3) + 32 r, r = 0..3, two pixels at a time.  STRIDE = table entries per (pixel, slot) (0: g.nt),
+// (pt >> 3) + kRowStep * r, two pixels at a time.  STRIDE = table entries per (pixel, slot) (0: g.nt),
 // NTI = entries actually used (0: g.nt).
 template <int STRIDE, int NTI, bool PLAN>
 __device__ __forceinline__ void produce_chunk(const Gather &g, const Tap *taps, const int2 *rest, const PlanView<float> &pv,
@@ -277,20 +280,21 @@ __device__ __forceinline__ void produce_chunk(const Gather &g, const Tap *taps, 
   const Tap *trow = taps + (size_t)row0 * stride;
   uint8_t *dst = As + plb * 128 + ((v ^ (plb & 7)) << 4);
 #pragma unroll
-  for (int r = 0; r < kTileM * 8 / kProducerThreads; r += 2) {
+  static_assert(128 * 8 / kProducerThreads >= 2 && (128 * 8 / kProducerThreads) % 2 == 0, "items per thread must be even");
+  for (int r = 0; r < 128 * 8 / kProducerThreads; r += 2) {
     Acc8 a0, a1;
     acc_zero(a0);
     acc_zero(a1);
     if (valid) {
-      gather_pair<NTI>(imgc, trow + (size_t)(r * 32) * stride, trow + (size_t)((r + 1) * 32) * stride, g.nt, a0, a1);
+      gather_pair<NTI>(imgc, imgc, trow + (size_t)(r * kRowStep) * stride, trow + (size_t)((r + 1) * kRowStep) * stride, g.nt, a0, a1);
       if (PLAN) {
-        const int2 r0 = rest[row0 + r * 32], r1 = rest[row0 + (r + 1) * 32];
+        const int2 r0 = rest[row0 + r * kRowStep], r1 = rest[row0 + (r + 1) * kRowStep];
         if (r0.x < r0.y) gather_plan_rest(a0, imgc, pv, r0.x, r0.y, g.Cp * 2);
         if (r1.x < r1.y) gather_plan_rest(a1, imgc, pv, r1.x, r1.y, g.Cp * 2);
       }
     }
-    *(uint4 *)(dst + r * 32 * 128) = acc_pack(a0);
-    *(uint4 *)(dst + (r + 1) * 32 * 128) = acc_pack(a1);
+    *(uint4 *)(dst + r * kRowStep * 128) = acc_pack(a0);
+    *(uint4 *)(dst + (r + 1) * kRowStep * 128) = acc_pack(a1);
   }
 }
 
@@ -618,24 +622,30 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         mbar_arrive_expect_tx(sm.full + s, bytes);
         bulk_copy_g2s(st + kDwColBytes, p.gt + ((size_t)step * p.mbs_total + mb0) * (kDwGtBytes / 2), bytes, sm.full + s);
       }
-      // thread pt: 16-byte vector v = pt & 7 of pixels (pt >> 3) and (pt >> 3) + 32, for each chunk of the group
+      // thread pt: 16-byte vector v = pt & 7 of pixel pt >> 3, two chunks of the group at a time
       {
-        const int v = pt & 7, plb = pt >> 3;
+        static_assert(kProducerThreads == kDwPix * 8, "one (pixel, vector) per producer thread");
+        const int v = pt & 7, pl = pt >> 3;
         const int stride = NT > 0 ? NT : g.nt;
-        uint8_t *dst0 = st + plb * 128 + ((v ^ (plb & 7)) << 4);
-        for (int gi = 0; gi < ncg; gi++) {
-          int slot, c0;
-          chunk_vec(g.Cp, g.K, chunk0 + gi, v, slot, c0);
+        uint8_t *dst0 = st + pl * 128 + ((v ^ (pl & 7)) << 4);
+        for (int gi = 0; gi < ncg; gi += 2) {
+          int slot0, c00, slot1 = g.K, c01 = 0;
+          chunk_vec(g.Cp, g.K, chunk0 + gi, v, slot0, c00);
+          if (gi + 1 < ncg) chunk_vec(g.Cp, g.K, chunk0 + gi + 1, v, slot1, c01);
+          const bool ok0 = slot0 < g.K, ok1 = slot1 < g.K;
+          const int row0 = ok0 ? (g.Cp >= 64 ? gi : slot0 - slot_base) : 0;
+          const int row1 = ok1 ? (g.Cp >= 64 ? gi + 1 : slot1 - slot_base) : 0;
           Acc8 a0, a1;
           acc_zero(a0);
           acc_zero(a1);
-          if (slot < g.K) {
-            const int row = g.Cp >= 64 ? gi : slot - slot_base;
-            const Tap *trow = sm.taps + (size_t)(row * kDwPix + plb) * stride;
-            gather_pair<NT>(img + c0 * 2, trow, trow + (size_t)32 * stride, g.nt, a0, a1);
+          if (ok0 || ok1) {
+            gather_pair<NT>(img + c00 * 2, img + c01 * 2, sm.taps + (size_t)(row0 * kDwPix + pl) * stride,
+                            sm.taps + (size_t)(row1 * kDwPix + pl) * stride, g.nt, a0, a1);
+            if (!ok0) acc_zero(a0);
+            if (!ok1) acc_zero(a1);
           }
           *(uint4 *)(dst0 + gi * (kDwPix * 128)) = acc_pack(a0);
-          *(uint4 *)(dst0 + gi * (kDwPix * 128) + 32 * 128) = acc_pack(a1);
+          if (gi + 1 < ncg) *(uint4 *)(dst0 + (gi + 1) * (kDwPix * 128)) = acc_pack(a1);
         }
       }
       fence_proxy_async();

@@ -22,29 +22,42 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+// try_wait suspends the thread in hardware until the phase completes or `hint_ns` elapses, so waiting
+// warps do not burn issue slots.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
 
-// Bounded wait: gives up after kSpinLimit polls (a few seconds), or as soon as
-// another thread of the CTA has given up, so a protocol error can never hang
-// the GPU.  Returns false on give-up; the caller then leaves its loop.
-constexpr uint32_t kSpinLimit = 1u << 24;
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Bounded wait: gives up after kWaitLimitNs of wall time, or as soon as another thread of the CTA has
+// given up, so a protocol error can never hang the GPU.  Returns false on give-up; the caller then
+// leaves its loop and the kernel reports status 1.
+constexpr uint64_t kWaitLimitNs = 4000000000ull;
+constexpr uint32_t kSuspendHintNs = 100000u;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; i++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  if (mbar_try_wait(bar, parity, kSuspendHintNs)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    if (mbar_try_wait(bar, parity, kSuspendHintNs)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      return false;
+    }
   }
-  *abort_flag = 1;
-  return false;
 }
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
