@@ -1,0 +1,63 @@
+"""Batch sharding and the gradient allreduce on CPU ranks (gloo, world size 2): host-side logic only."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from sphmap.parallel import GradReducer, shard_batch
+
+
+def test_shard_batch_covers_the_batch_evenly():
+    for B in (1, 7, 64):
+        for world in (1, 2, 3, 8):
+            parts = [shard_batch(B, r, world) for r in range(world)]
+            assert parts[0][0] == 0 and parts[-1][1] == B
+            assert all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+            sizes = [hi - lo for lo, hi in parts]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # each rank owns a slice of the batch and produces its partial dW / dBias = sum over its images
+    B = 6
+    per_image_gw = torch.arange(B * 12, dtype=torch.float32).view(B, 3, 2, 2)
+    per_image_gb = torch.arange(B * 3, dtype=torch.float32).view(B, 3)
+    lo, hi = shard_batch(B, rank, world)
+    red = GradReducer()
+    layers = []
+    for scale in (1.0, 2.0):       # two "layers", submitted one after the other, finished together
+        gw, gb = per_image_gw[lo:hi].sum(0) * scale, per_image_gb[lo:hi].sum(0) * scale
+        red.submit(gw, gb)
+        layers.append((gw, gb, scale))
+    red.finish()
+    ok = all(torch.equal(gw, per_image_gw.sum(0) * s) and torch.equal(gb, per_image_gb.sum(0) * s) for gw, gb, s in layers)
+    out[rank] = bool(ok)
+    dist.destroy_process_group()
+
+
+def test_grad_reducer_sums_across_two_gloo_ranks():
+    world, port = 2, _free_port()
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
+        assert dict(out) == {0: True, 1: True}
+
+
+def test_grad_reducer_is_a_no_op_without_a_process_group():
+    red = GradReducer()
+    gw, gb = torch.ones(2, 2), torch.ones(2)
+    red.submit(gw, gb)
+    red.finish()
+    assert not red.enabled and torch.equal(gw, torch.ones(2, 2))
