@@ -50,6 +50,16 @@ extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64
   const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
   if (check_dims(d, dtype, interp, precision) != SPH_OK) return 0;
   const size_t ts = dtype == SPH_F64 ? 8 : 4;
+  // thin contractions (few channels on the gathered / produced side) have their own kernels in both precisions
+  switch (op) {
+    case SPH_CONV_FORWARD: if (small_ok(Cin, K, Cout, ts)) return 0; break;
+    case SPH_CONV_BACKWARD_INPUT: if (small_ok(Cin, K, Cout, ts)) return small_premul_workspace(B, Cin, K, OH * OW, ts); break;
+    case SPH_CONV_BACKWARD_WEIGHT: if (small_ok(Cin, K, Cout, ts)) return small_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts); break;
+    case SPH_TCONV_FORWARD: if (small_ok(Cout, K, Cin, ts)) return small_premul_workspace(B, Cout, K, IH * IW, ts); break;
+    case SPH_TCONV_BACKWARD_INPUT: if (small_ok(Cout, K, Cin, ts)) return 0; break;
+    case SPH_TCONV_BACKWARD_WEIGHT: if (small_ok(Cout, K, Cin, ts)) return small_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, ts); break;
+    default: break;
+  }
   if (precision == SPH_PRECISION_BF16) return tc_workspace_bytes(op, B, Cin, Cout, IH, IW, OH, OW, K, P, interp);
   switch (op) {
     case SPH_CONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts);
@@ -70,6 +80,8 @@ extern "C" int sph_mapped_conv_forward(const void *x, const void *map, const voi
   if (!x || !map || !weight || !bias || !out || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
+    return SPH_BY_DTYPE(small_fwd, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, st);
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
   return SPH_BY_DTYPE(simt_gemm, false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1,
@@ -86,6 +98,9 @@ extern "C" int sph_mapped_conv_backward_input(const void *gout, const void *plan
   if (!gout || !plan || !weight || !gx) return SPH_ERR_INVALID_ARGUMENT;
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
+    return SPH_BY_DTYPE(small_adjoint, gout, plan, Cout, OH * OW, K, IH * IW, weight, K, Cin * K, 1, nullptr, gx, Cin, B, ws,
+                        ws_bytes, st);
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st);
   return SPH_BY_DTYPE(simt_gemm, true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH * IW, 0, weight, K, Cin * K, 1,
@@ -106,6 +121,9 @@ extern "C" int sph_mapped_conv_backward_weight(const void *gout, const void *x, 
     if (cudaMemsetAsync(gw, 0, ts * (size_t)(Cout * Cin * K), st) != cudaSuccess) return SPH_ERR_CUDA;
     return cudaMemsetAsync(gb, 0, ts * (size_t)Cout, st) == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
   }
+  if (small_ok(Cin, K, Cout, ts))
+    return SPH_BY_DTYPE(small_dw, gout, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout,
+                        OH * OW, gb, ws, ws_bytes, st);
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
   return SPH_BY_DTYPE(simt_dw, gout, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout,
@@ -122,6 +140,9 @@ extern "C" int sph_mapped_tconv_forward(const void *x, const void *plan, const v
   if (!x || !plan || !weight || !bias || !out) return SPH_ERR_INVALID_ARGUMENT;
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (small_ok(Cout, K, Cin, dtype == SPH_F64 ? 8 : 4))
+    return SPH_BY_DTYPE(small_adjoint, x, plan, Cin, IH * IW, K, OH * OW, weight, K, Cout * K, 1, bias, out, Cout, B, ws, ws_bytes,
+                        st);
   if (precision == SPH_PRECISION_BF16)
     return tc_tconv_forward(x, plan, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st);
   return SPH_BY_DTYPE(simt_gemm, true, x, nullptr, nullptr, plan, Cin, IH, IW, K, 0, OH * OW, 0, weight, K, Cout * K, 1,
@@ -138,6 +159,9 @@ extern "C" int sph_mapped_tconv_backward_input(const void *gout, const void *map
   if (!gout || !map || !weight || !gx || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (small_ok(Cout, K, Cin, dtype == SPH_F64 ? 8 : 4))
+    return SPH_BY_DTYPE(small_fwd, gout, map, iw, Cout, OH, OW, K, P, IH * IW, interp, weight, Cout * K, K, 1, nullptr, gx, Cin, B,
+                        st);
   if (precision == SPH_PRECISION_BF16)
     return tc_tconv_backward_input(gout, map, iw, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
   return SPH_BY_DTYPE(simt_gemm, false, gout, map, iw, nullptr, Cout, OH, OW, K, P, IH * IW, interp, weight, Cout * K, K, 1,
@@ -158,6 +182,9 @@ extern "C" int sph_mapped_tconv_backward_weight(const void *gout, const void *x,
     if (cudaMemsetAsync(gw, 0, ts * (size_t)(Cout * Cin * K), st) != cudaSuccess) return SPH_ERR_CUDA;
     return cudaMemsetAsync(gb, 0, ts * (size_t)Cout, st) == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
   }
+  if (small_ok(Cout, K, Cin, ts))
+    return SPH_BY_DTYPE(small_dw, x, gout, map, iw, Cout, OH, OW, K, P, IH * IW, interp, Cin, B, gw, Cout * K, K, 1, gout, Cout,
+                        OH * OW, gb, ws, ws_bytes, st);
   if (precision == SPH_PRECISION_BF16)
     return tc_tconv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
   return SPH_BY_DTYPE(simt_dw, x, gout, map, iw, Cout, OH, OW, K, P, IH * IW, interp, Cin, B, gw, Cout * K, K, 1, gout, Cout,

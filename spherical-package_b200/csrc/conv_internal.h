@@ -21,6 +21,27 @@ size_t simt_bias_workspace(int64_t C, size_t ts);
 template <typename T>
 int simt_bias_grad(const void *g, int64_t B, int64_t C, int64_t n, void *gb, void *ws, cudaStream_t st);
 
+template <typename T>
+int simt_dw_reduce(const void *partial, int splits, int64_t M, int64_t CHK, int64_t K, int64_t sm, int64_t sc, int64_t sk,
+                   void *gw, cudaStream_t st);
+
+// ---- thin-contraction kernels (conv_small.cu): side_channels * K <= 32 ----
+bool small_ok(int64_t side_channels, int64_t K, int64_t wide_channels, size_t ts);
+size_t small_premul_workspace(int64_t B, int64_t M, int64_t K, int64_t n_src, size_t ts);
+size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts);
+template <typename T>
+int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K, int64_t P,
+              int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out,
+              int64_t M, int64_t B, cudaStream_t st);
+template <typename T>
+int small_adjoint(const void *src, const void *plan, int64_t CH, int64_t n_src, int64_t K, int64_t n_dst, const void *wgt,
+                  int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out, int64_t M, int64_t B, void *ws,
+                  size_t ws_bytes, cudaStream_t st);
+template <typename T>
+int small_dw(const void *A, const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K,
+             int64_t P, int64_t npix, int interp, int64_t M, int64_t B, void *gw, int64_t sm, int64_t sc, int64_t sk,
+             const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st);
+
 // ---- bf16 tcgen05 path (conv_tc.cu); float32 tensors only ----------------
 size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
                           int64_t K, int64_t P, int interp);

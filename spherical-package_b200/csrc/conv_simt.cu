@@ -213,6 +213,15 @@ __global__ void bias_final_kernel(const T *__restrict__ part, int C, T *__restri
   gb[c] = s;
 }
 
+template <typename T>
+int simt_dw_reduce(const void *partial, int splits, int64_t M, int64_t CHK, int64_t K, int64_t sm, int64_t sc, int64_t sk,
+                   void *gw, cudaStream_t st) {
+  dw_reduce_kernel<T><<<cdiv(M * CHK, 256), 256, 0, st>>>((const T *)partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw);
+  return launch_status();
+}
+template int simt_dw_reduce<float>(const void *, int, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, void *, cudaStream_t);
+template int simt_dw_reduce<double>(const void *, int, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, void *, cudaStream_t);
+
 size_t simt_bias_workspace(int64_t C, size_t ts) { return align_up(ts * (size_t)(C * kBiasSplits), 256); }
 
 // gb[c] = sum over batch and pixels of g[b,c,:] (two fixed-order stages); ws holds C * kBiasSplits partials.

@@ -65,3 +65,39 @@ def test_max_pool_sentinel_is_the_cuda_build_one(impl, golden_dir):
     assert torch.equal(out[keep], c["ref_output"][keep]) and torch.equal(idx[keep], c["ref_idx"][keep])
     o2, i2 = port.mapped_max_pool(c["input"], c["sample_map"], c["kernel_size"], c["interp"], cuda_sentinel=True)
     assert torch.equal(out, o2) and torch.equal(idx, i2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+@pytest.mark.parametrize("interp,P", [(0, 0), (1, 0), (2, 3), (1, 2)])
+def test_exact_path_with_wide_channels(impl, dtype, interp, P):
+    """Channel counts beyond the thin-contraction kernels (Cin*K > 32): the tiled exact SIMT kernels, conv and
+    transposed conv, against the CPU oracle on seeded inputs (ragged sizes, out-of-range coordinates)."""
+    from oracle import port
+    g = torch.Generator().manual_seed(4000 + 10 * interp + P)
+    B, Cin, Cout, IH, IW, OH, OW, K = 2, 12, 70, 9, 13, 7, 11, 5
+    x = torch.randn(B, Cin, IH, IW, generator=g, dtype=dtype)
+    shape = (OH, OW, K, P, 2) if P else (OH, OW, K, 2)
+    m = (torch.rand(*shape, generator=g, dtype=torch.float64) * torch.tensor([IW + 3.0, IH + 3.0]) - 1.5).to(dtype)
+    iw = torch.rand(OH, OW, K, P, generator=g, dtype=dtype) if P else None
+    w = torch.randn(Cout, Cin, K, generator=g, dtype=dtype) / 8
+    b = torch.randn(Cout, generator=g, dtype=dtype)
+    go = torch.randn(B, Cout, OH, OW, generator=g, dtype=dtype)
+    def close(a, r):
+        # 1e-5 (fp32) / 1e-12 (fp64) relative to the tensor's scale: sums of 60 to ~10^4 terms differ from the
+        # oracle only by summation order
+        rt = 1e-5 if dtype == torch.float32 else 1e-12
+        torch.testing.assert_close(a, r, rtol=rt, atol=rt * float(r.abs().max()))
+
+    close(impl.mapped_conv_forward(x, m, w, b, K, interp, iw), port.mapped_conv_forward(x, m, w, b, K, interp, iw))
+    for a, r in zip(impl.mapped_conv_backward(go, m, x, w, b, K, interp, iw),
+                    port.mapped_conv_backward(go, m, x, w, b, K, interp, iw)):
+        close(a, r)
+    # transposed: input on the map grid with Cout channels, output on (IH, IW) with Cin channels
+    xt = torch.randn(B, Cout, OH, OW, generator=g, dtype=dtype)
+    bt = torch.randn(Cin, generator=g, dtype=dtype)
+    got = torch.randn(B, Cin, IH, IW, generator=g, dtype=dtype)
+    close(impl.mapped_transposed_conv_forward(xt, m, w, bt, IH, IW, K, interp, iw),
+          port.mapped_transposed_conv_forward(xt, m, w, bt, IH, IW, K, interp, iw))
+    for a, r in zip(impl.mapped_transposed_conv_backward(got, m, xt, w, bt, K, interp, iw),
+                    port.mapped_transposed_conv_backward(got, m, xt, w, bt, K, interp, iw)):
+        close(a, r)
