@@ -41,7 +41,8 @@ enum sph_status {
   SPH_ERR_UNSUPPORTED = 2,
   SPH_ERR_WORKSPACE_TOO_SMALL = 3,
   SPH_ERR_CUDA = 4,
-  SPH_ERR_TOO_LARGE = 5
+  SPH_ERR_TOO_LARGE = 5,
+  SPH_ERR_STATIC_SCRATCH_EXCEEDED = 6
 };
 enum sph_dtype { SPH_F32 = 0, SPH_F64 = 1 };
 enum sph_interp { SPH_NEAREST = 0, SPH_BILINEAR = 1, SPH_BISPHERICAL = 2 };
@@ -93,6 +94,39 @@ int sph_plan_build(const void *map, const void *iw, int64_t n_src, int64_t K, in
  * ---------------------------------------------------------------------- */
 int sph_resample_to_map(const void *x, const void *plan, void *out, int64_t B, int64_t C, int64_t MH,
                         int64_t MW, int64_t OH, int64_t OW, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------
+ * resample_to_map for callers that cannot allocate device memory.
+ * Has no counterpart in the reference.  It is for hosts that must not call
+ * cudaMalloc (or any allocating routine) around this library: code running
+ * inside a fixed memory budget handed out at start-up, real-time loops where
+ * an allocation could stall or fail, or plug-in sandboxes that only receive
+ * pre-allocated buffers.  sph_resample_to_map needs a scatter plan in caller
+ * scratch; this variant builds the plan from `map` (and `iw`) into a scratch
+ * array that is part of the library image itself (a file-scope __device__
+ * array of SPH_STATIC_SCRATCH_BYTES, resident on every GPU that loads the
+ * library until the process exits) and then runs the same scatter kernel.
+ * The caller still passes the input and the output; nothing is allocated or
+ * freed by this call, by the CUDA runtime on its behalf, or by torch.
+ *
+ *  - Limit: the plan for (MH*MW positions, P points, interp, OHxOW) must fit
+ *    SPH_STATIC_SCRATCH_BYTES (sph_plan_bytes tells); larger problems return
+ *    SPH_ERR_STATIC_SCRATCH_EXCEEDED and launch nothing.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current) before launching; make
+ *    that first call outside any stream capture.
+ *  - Every call on a device shares the one array and overwrites the plan the
+ *    previous call left there (the parts that must start at zero are cleared
+ *    by the call itself).  Two calls whose GPU work can overlap - different
+ *    streams, or host threads on the same device - race on it; serialise
+ *    them.
+ * Arguments as sph_resample_from_map / sph_resample_to_map: x (B,C,MH,MW),
+ * map (MH,MW[,P],2), iw (MH,MW,P) or NULL with P = 0, out (B,C,OH,OW).
+ * ---------------------------------------------------------------------- */
+#define SPH_STATIC_SCRATCH_BYTES (8u << 20)
+int sph_resample_to_map_static(const void *x, const void *map, const void *iw, void *out, int64_t B, int64_t C,
+                               int64_t MH, int64_t MW, int64_t OH, int64_t OW, int64_t P, int dtype, int interp,
+                               void *stream);
 
 /* ------------------------------------------------------------------------
  * Mapped max pooling.  out[b,c,o] = max_k interp(x[b,c], map[o,k]); idx is

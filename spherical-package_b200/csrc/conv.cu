@@ -35,6 +35,7 @@ extern "C" const char *sph_status_string(int status) {
     case SPH_ERR_WORKSPACE_TOO_SMALL: return "workspace or plan buffer too small";
     case SPH_ERR_CUDA: return "CUDA runtime reported an error at launch";
     case SPH_ERR_TOO_LARGE: return "tensor too large for 32-bit plane indexing";
+    case SPH_ERR_STATIC_SCRATCH_EXCEEDED: return "problem needs more scratch than the library's built-in static array holds";
     default: return "unknown status";
   }
 }

@@ -206,3 +206,34 @@ extern "C" int sph_plan_build(const void *map, const void *iw, int64_t n_src, in
   return dtype == SPH_F32 ? build<float>(map, iw, n_src, K, P, interp, dstH, dstW, dtype, plan, L, st)
                           : build<double>(map, iw, n_src, K, P, interp, dstH, dstW, dtype, plan, L, st);
 }
+
+// ---- resample_to_map without any allocation ---------------------------------------------------
+// Scratch for callers that cannot allocate: the plan lives in this array, which is part of the library image
+// on every device.  In host code the name `g_static_scratch` is only a handle for the runtime, not a device
+// address, so the address is looked up once per device and that pointer is what the kernels get.
+static __device__ __align__(256) unsigned char g_static_scratch[SPH_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_ptr[kMaxDevices];  // per device, filled by the first call made with that device current
+}  // namespace
+
+extern "C" int sph_resample_to_map_static(const void *x, const void *map, const void *iw, void *out, int64_t B, int64_t C,
+                                          int64_t MH, int64_t MW, int64_t OH, int64_t OW, int64_t P, int dtype, int interp,
+                                          void *stream) {
+  if (!x || !map || !out || P < 0 || (P > 0 && !iw) || interp < 0 || interp > 2) return SPH_ERR_INVALID_ARGUMENT;
+  if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
+  PlanLayout L;
+  if (!plan_layout(MH * MW, 1, P, interp, OH, OW, dtype, L)) return SPH_ERR_TOO_LARGE;
+  if (L.total > (size_t)SPH_STATIC_SCRATCH_BYTES) return SPH_ERR_STATIC_SCRATCH_EXCEEDED;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SPH_ERR_CUDA;
+  void *scratch = __atomic_load_n(&g_static_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+  if (!scratch) {
+    if (cudaGetSymbolAddress(&scratch, g_static_scratch) != cudaSuccess || !scratch) return SPH_ERR_CUDA;
+    __atomic_store_n(&g_static_scratch_ptr[dev], scratch, __ATOMIC_RELEASE);
+  }
+  const int rc = sph_plan_build(map, iw, MH * MW, 1, P, interp, OH, OW, dtype, scratch, SPH_STATIC_SCRATCH_BYTES, stream);
+  if (rc != SPH_OK) return rc;
+  return sph_resample_to_map(x, scratch, out, B, C, MH, MW, OH, OW, dtype, stream);
+}

@@ -21,7 +21,7 @@ TCONV_FORWARD, TCONV_BACKWARD_INPUT, TCONV_BACKWARD_WEIGHT = 3, 4, 5
 
 SYMBOLS = [
     "sph_status_string", "sph_version", "sph_launch_count", "sph_resample_from_map", "sph_plan_bytes", "sph_plan_build",
-    "sph_resample_to_map", "sph_mapped_max_pool", "sph_mapped_max_unpool", "sph_conv_workspace_bytes",
+    "sph_resample_to_map", "sph_resample_to_map_static", "sph_mapped_max_pool", "sph_mapped_max_unpool", "sph_conv_workspace_bytes",
     "sph_mapped_conv_forward", "sph_mapped_conv_backward_input", "sph_mapped_conv_backward_weight",
     "sph_mapped_tconv_forward", "sph_mapped_tconv_backward_input", "sph_mapped_tconv_backward_weight",
 ]
@@ -101,6 +101,20 @@ def resample_to_map(x, plan, oh, ow):
     out = torch.empty(B, C, int(oh), int(ow), dtype=x.dtype, device=x.device)
     _ok(lib.sph_resample_to_map(_ptr(x), _ptr(plan), _ptr(out), *_ints(B, C, MH, MW, oh, ow), _int(_dt(x)), _stream()),
         "sph_resample_to_map")
+    return out
+
+
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def resample_to_map_static(x, smap, oh, ow, interp, iw=None, out=None):
+    """resample_to_map through the entry point that keeps its scratch inside the library (no allocation by the
+    call itself: pass `out` to keep this wrapper from allocating the result either)."""
+    B, C, MH, MW = x.shape
+    if out is None:
+        out = torch.empty(B, C, int(oh), int(ow), dtype=x.dtype, device=x.device)
+    _ok(lib.sph_resample_to_map_static(_ptr(x), _ptr(smap), _ptr(iw), _ptr(out), *_ints(B, C, MH, MW, oh, ow, _P(iw)),
+                                       _int(_dt(x)), _int(int(interp)), _stream()), "sph_resample_to_map_static")
     return out
 
 
