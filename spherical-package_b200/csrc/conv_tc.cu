@@ -405,12 +405,15 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
       if (plan_ok) plan_nti = min(kPlanTaps, ((const PlanHeader *)g.plan)->max_seg);
     }
     const int pitch = g.Cp * 2, zero_off = (int)shw * pitch;
-    for (int tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x) {
+    // A producer that gave up waiting keeps walking the tile loop and its two barriers (doing no work), so
+    // that the named barrier never waits for a thread that left.
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       const int nb = tile % p.nblk, rest = tile / p.nblk;
       const int b = rest / tiles_per_image, t2 = rest % tiles_per_image;
       const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
       const char *img = (const char *)g.xh + (size_t)b * (shw + 1) * pitch;
       producer_bar();  // every producer is done reading the previous tile's taps
+      if (!alive) { producer_bar(); continue; }
       for (int idx = pt; idx < g.K * kTileM; idx += kProducerThreads) {
         const int slot = idx / kTileM, pl = idx % kTileM;
         const int pix = tile_pixel(pl, ty, tx, kTH, g.GH, g.GW);
@@ -434,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         }
       }
       producer_bar();
-      for (int chunk = 0; chunk < p.nchunks; chunk++, it++) {
+      for (int chunk = 0; alive && chunk < p.nchunks; chunk++, it++) {
         const int s = it % S;
         if (!mbar_wait(sm.empty + s, ((it / S) & 1) ^ 1, sm.abort_flag)) { alive = false; break; }
         if (pt == 0) {
@@ -492,7 +495,7 @@ struct DwSmem {
 
 inline size_t dw_stage_bytes(int mbs) { return kDwColBytes + (size_t)mbs * kDwGtBytes; }
 inline size_t dw_smem_bytes(int stages, int mbs, int tap_rows, int nt) {
-  return 1024 + stages * dw_stage_bytes(mbs) + (size_t)tap_rows * kDwPix * nt * sizeof(Tap) + 8 * (2 * stages + 1) + 16;
+  return 1024 + stages * dw_stage_bytes(mbs) + 2 * (size_t)tap_rows * kDwPix * nt * sizeof(Tap) + 8 * (2 * stages + 1) + 16;
 }
 
 template <int NT>
@@ -512,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
     sm.stage = b;
     uint8_t *q = b + (size_t)S * stage_bytes;
     sm.taps = (Tap *)q;
-    q += (size_t)p.tap_rows * kDwPix * g.nt * sizeof(Tap);
+    q += 2 * (size_t)p.tap_rows * kDwPix * g.nt * sizeof(Tap);
     sm.full = (uint64_t *)q;
     sm.empty = sm.full + S;
     sm.tfull = sm.empty + S;
@@ -598,30 +601,41 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
     // table row r holds the taps of slot `slot_base + r`
     int slot_base, dummy;
     chunk_vec(g.Cp, g.K, chunk0, 0, slot_base, dummy);
-    for (int step = step_lo; alive && step < step_hi; step++, it++) {
-      const int b = step / tiles_per_image, t2 = step % tiles_per_image;
+    // The tap table is double buffered: while the columns of one step are gathered from one half, the taps
+    // of the next step are decoded into the other half, so the map loads never sit on the critical path.
+    const size_t tap_half = (size_t)p.tap_rows * kDwPix * g.nt;
+    auto fill_step = [&](int step, Tap *table) {
+      const int t2 = step % tiles_per_image;
       const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
-      const char *img = (const char *)g.xh + (size_t)b * (shw + 1) * g.Cp * 2;
-      producer_bar();
       for (int idx = pt; idx < p.tap_rows * kDwPix; idx += kProducerThreads) {
         const int row = idx / kDwPix, pl = idx % kDwPix;
         int slot;
         if (g.Cp >= 64) { int c0; chunk_vec(g.Cp, g.K, chunk0 + row, 0, slot, c0); }   // one slot per chunk
         else slot = slot_base + row;
         const int pix = tile_pixel(pl, ty, tx, kDwTH, g.GH, g.GW);
-        Tap *dst = sm.taps + (size_t)idx * g.nt;
+        Tap *dst = table + (size_t)idx * g.nt;
         if (pix >= 0 && slot < g.K && (g.Cp < 64 || row < ncg)) fill_taps_any(g, pix, slot, dst);
         else fill_taps_zero(g, dst);
       }
-      producer_bar();
+    };
+    if (step_lo < step_hi) fill_step(step_lo, sm.taps);
+    producer_bar();
+    // A producer that gave up waiting keeps walking the loop and its barriers (doing no work), so that the
+    // named barrier never waits for a thread that left.
+    for (int step = step_lo; step < step_hi; step++, it++) {
+      const int b = step / tiles_per_image;
+      const char *img = (const char *)g.xh + (size_t)b * (shw + 1) * g.Cp * 2;
+      const Tap *taps = sm.taps + (it & 1) * tap_half;
       const int s = it % S;
-      if (!mbar_wait(sm.empty + s, ((it / S) & 1) ^ 1, sm.abort_flag)) { alive = false; break; }
+      if (alive && !mbar_wait(sm.empty + s, ((it / S) & 1) ^ 1, sm.abort_flag)) alive = false;
+      if (!alive) { producer_bar(); continue; }
       uint8_t *st = sm.stage + (size_t)s * stage_bytes;
       if (pt == 0) {
         const uint32_t bytes = (uint32_t)mbs * kDwGtBytes;
         mbar_arrive_expect_tx(sm.full + s, bytes);
         bulk_copy_g2s(st + kDwColBytes, p.gt + ((size_t)step * p.mbs_total + mb0) * (kDwGtBytes / 2), bytes, sm.full + s);
       }
+      if (step + 1 < step_hi) fill_step(step + 1, sm.taps + ((it + 1) & 1) * tap_half);
       // thread pt: 16-byte vector v = pt & 7 of pixel pt >> 3, two chunks of the group at a time
       {
         static_assert(kProducerThreads == kDwPix * 8, "one (pixel, vector) per producer thread");
@@ -639,8 +653,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
           acc_zero(a0);
           acc_zero(a1);
           if (ok0 || ok1) {
-            gather_pair<NT>(img + c00 * 2, img + c01 * 2, sm.taps + (size_t)(row0 * kDwPix + pl) * stride,
-                            sm.taps + (size_t)(row1 * kDwPix + pl) * stride, g.nt, a0, a1);
+            gather_pair<NT>(img + c00 * 2, img + c01 * 2, taps + (size_t)(row0 * kDwPix + pl) * stride,
+                            taps + (size_t)(row1 * kDwPix + pl) * stride, g.nt, a0, a1);
             if (!ok0) acc_zero(a0);
             if (!ok1) acc_zero(a1);
           }
@@ -651,6 +665,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.full + s);
+      producer_bar();  // next table complete, this one no longer read
     }
   }
 

@@ -97,7 +97,7 @@ class EncoderStack:
         g = go
         for li in reversed(range(4)):
             ci, co, (ih, iw), (oh, ow), s = self.layers[li]
-            g = g * (self.acts[li] > 0)                         # ReLU backward (activations were rectified in place)
+            g = torch.ops.aten.threshold_backward(g, self.acts[li], 0)   # ReLU backward on the rectified activations
             gw, gb = self._timed((li, "dw"), lambda: c.conv_backward_weight(
                 g, self.inputs[li], self.maps[li], self.K, self.interp, None, self.prec,
                 ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)]))
