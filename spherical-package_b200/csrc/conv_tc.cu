@@ -269,18 +269,16 @@ constexpr int kRowStep = kProducerThreads / 8;  // pixel rows covered by one pas
 // NTI = entries actually used (0: g.nt).
 template <int STRIDE, int NTI, bool PLAN>
 __device__ __forceinline__ void produce_chunk(const Gather &g, const Tap *taps, const int2 *rest, const PlanView<float> &pv,
-                                              const char *img, int chunk, int pt, uint8_t *As) {
+                                              const char *img, int slot, int c0, int pt, uint8_t *As) {
   const int v = pt & 7, plb = pt >> 3;
   const int stride = STRIDE > 0 ? STRIDE : g.nt;
-  int slot, c0;
-  chunk_vec(g.Cp, g.K, chunk, v, slot, c0);
   const bool valid = slot < g.K;
   const char *imgc = img + c0 * 2;
   const int row0 = (valid ? slot : 0) * kTileM + plb;
   const Tap *trow = taps + (size_t)row0 * stride;
   uint8_t *dst = As + plb * 128 + ((v ^ (plb & 7)) << 4);
-#pragma unroll
   static_assert(128 * 8 / kProducerThreads >= 2 && (128 * 8 / kProducerThreads) % 2 == 0, "items per thread must be even");
+#pragma unroll
   for (int r = 0; r < 128 * 8 / kProducerThreads; r += 2) {
     Acc8 a0, a1;
     acc_zero(a0);
@@ -437,8 +435,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         }
       }
       producer_bar();
+      int cslot = 0, cblock = 0;  // Cp >= 64: chunk = cblock * K + cslot, kept incrementally (no division)
       for (int chunk = 0; alive && chunk < p.nchunks; chunk++, it++) {
         const int s = it % S;
+        int slot, c0;
+        if (g.Cp >= 64) {
+          slot = cslot;
+          c0 = cblock * 64 + (pt & 7) * 8;
+          if (++cslot == g.K) { cslot = 0; cblock++; }
+        } else {
+          chunk_vec(g.Cp, g.K, chunk, pt & 7, slot, c0);
+        }
         if (!mbar_wait(sm.empty + s, ((it / S) & 1) ^ 1, sm.abort_flag)) { alive = false; break; }
         if (pt == 0) {
           const uint32_t bytes = (uint32_t)p.Npb * 128;
@@ -447,13 +454,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         }
         uint8_t *As = sm.A + (size_t)s * kAStageBytes;
         if (MODE == MODE_DIRECT) {
-          produce_chunk<NT, NT, false>(g, sm.taps, nullptr, pv, img, chunk, pt, As);
+          produce_chunk<NT, NT, false>(g, sm.taps, nullptr, pv, img, slot, c0, pt, As);
         } else if (plan_nti >= 3) {
-          produce_chunk<kPlanTaps, 4, true>(g, sm.taps, sm.rest, pv, img, chunk, pt, As);
+          produce_chunk<kPlanTaps, 4, true>(g, sm.taps, sm.rest, pv, img, slot, c0, pt, As);
         } else if (plan_nti == 2) {
-          produce_chunk<kPlanTaps, 2, true>(g, sm.taps, sm.rest, pv, img, chunk, pt, As);
+          produce_chunk<kPlanTaps, 2, true>(g, sm.taps, sm.rest, pv, img, slot, c0, pt, As);
         } else {
-          produce_chunk<kPlanTaps, 1, true>(g, sm.taps, sm.rest, pv, img, chunk, pt, As);
+          produce_chunk<kPlanTaps, 1, true>(g, sm.taps, sm.rest, pv, img, slot, c0, pt, As);
         }
         fence_proxy_async();
         __syncwarp();
@@ -601,6 +608,18 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
     // table row r holds the taps of slot `slot_base + r`
     int slot_base, dummy;
     chunk_vec(g.Cp, g.K, chunk0, 0, slot_base, dummy);
+    // The CTA's column group is fixed, so each thread's (slot, first channel, table row) per chunk of the group
+    // is computed once.
+    int g_coff[kDwGroup], g_trow[kDwGroup];
+    bool g_ok[kDwGroup];
+#pragma unroll
+    for (int gi = 0; gi < kDwGroup; gi++) {
+      int slot = g.K, c0 = 0;
+      if (gi < ncg) chunk_vec(g.Cp, g.K, chunk0 + gi, pt & 7, slot, c0);
+      g_ok[gi] = slot < g.K;
+      g_coff[gi] = c0 * 2;
+      g_trow[gi] = g_ok[gi] ? ((g.Cp >= 64 ? gi : slot - slot_base) * kDwPix + (pt >> 3)) * (NT > 0 ? NT : g.nt) : 0;
+    }
     // The tap table is double buffered: while the columns of one step are gathered from one half, the taps
     // of the next step are decoded into the other half, so the map loads never sit on the critical path.
     const size_t tap_half = (size_t)p.tap_rows * kDwPix * g.nt;
@@ -640,23 +659,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
       {
         static_assert(kProducerThreads == kDwPix * 8, "one (pixel, vector) per producer thread");
         const int v = pt & 7, pl = pt >> 3;
-        const int stride = NT > 0 ? NT : g.nt;
         uint8_t *dst0 = st + pl * 128 + ((v ^ (pl & 7)) << 4);
-        for (int gi = 0; gi < ncg; gi += 2) {
-          int slot0, c00, slot1 = g.K, c01 = 0;
-          chunk_vec(g.Cp, g.K, chunk0 + gi, v, slot0, c00);
-          if (gi + 1 < ncg) chunk_vec(g.Cp, g.K, chunk0 + gi + 1, v, slot1, c01);
-          const bool ok0 = slot0 < g.K, ok1 = slot1 < g.K;
-          const int row0 = ok0 ? (g.Cp >= 64 ? gi : slot0 - slot_base) : 0;
-          const int row1 = ok1 ? (g.Cp >= 64 ? gi + 1 : slot1 - slot_base) : 0;
+#pragma unroll
+        for (int gi = 0; gi < kDwGroup; gi += 2) {
+          if (gi >= ncg) break;
           Acc8 a0, a1;
           acc_zero(a0);
           acc_zero(a1);
-          if (ok0 || ok1) {
-            gather_pair<NT>(img + c00 * 2, img + c01 * 2, taps + (size_t)(row0 * kDwPix + pl) * stride,
-                            taps + (size_t)(row1 * kDwPix + pl) * stride, g.nt, a0, a1);
-            if (!ok0) acc_zero(a0);
-            if (!ok1) acc_zero(a1);
+          if (g_ok[gi] || g_ok[gi + 1]) {
+            gather_pair<NT>(img + g_coff[gi], img + g_coff[gi + 1], taps + g_trow[gi], taps + g_trow[gi + 1], g.nt, a0, a1);
+            if (!g_ok[gi]) acc_zero(a0);
+            if (!g_ok[gi + 1]) acc_zero(a1);
           }
           *(uint4 *)(dst0 + gi * (kDwPix * 128)) = acc_pack(a0);
           if (gi + 1 < ncg) *(uint4 *)(dst0 + (gi + 1) * (kDwPix * 128)) = acc_pack(a1);
