@@ -73,6 +73,15 @@ constexpr bool kAcc32 = true;
 constexpr bool kAcc32 = false;
 #endif
 
+// Pipeline position kept without division: stage index and phase bit advance together.
+struct Ring {
+  int s = 0;
+  uint32_t ph = 0;
+  __device__ __forceinline__ void next(int stages) {
+    if (++s == stages) { s = 0; ph ^= 1u; }
+  }
+};
+
 __device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); }
 
 // One tap-table entry: byte offset of the source pixel inside its image and the tap weight (fp32 bits, or the
@@ -369,16 +378,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
     // ---------------- MMA issuer (one thread) ----------------
     if (lane == 0) {
       const uint32_t idesc = idesc_bf16(kTileM, p.Npb, 0, 0);
-      int it = 0, tl = 0;
+      int tl = 0;
+      Ring ring;
       bool alive = true;
       for (int tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x, tl++) {
         const int buf = tl & 1;
         if (!mbar_wait(sm.tempty + buf, ((tl >> 1) & 1) ^ 1, sm.abort_flag)) break;
         tc_fence_after();
         const uint32_t d = tmem_base + buf * 256;
-        for (int chunk = 0; chunk < p.nchunks; chunk++, it++) {
-          const int s = it % S;
-          if (!mbar_wait(sm.full + s, (it / S) & 1, sm.abort_flag)) { alive = false; break; }
+        for (int chunk = 0; chunk < p.nchunks; chunk++, ring.next(S)) {
+          const int s = ring.s;
+          if (!mbar_wait(sm.full + s, ring.ph, sm.abort_flag)) { alive = false; break; }
           tc_fence_after();
           const uint64_t a0 = smem_desc_sw128(smem_u32(sm.A + (size_t)s * kAStageBytes), 16, 1024);
           const uint64_t b0 = smem_desc_sw128(smem_u32(sm.Bw + (size_t)s * p.Npb * 128), 16, 1024);
@@ -393,7 +403,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
   } else {
     // ---------------- producers: gather Col tiles into swizzled shared memory ----------------
     const int pt = tid - kFirstProducerThread;
-    int it = 0;
+    Ring ring;
     bool alive = true;
     PlanView<float> pv{};
     bool plan_ok = true;
@@ -436,8 +446,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
       }
       producer_bar();
       int cslot = 0, cblock = 0;  // Cp >= 64: chunk = cblock * K + cslot, kept incrementally (no division)
-      for (int chunk = 0; alive && chunk < p.nchunks; chunk++, it++) {
-        const int s = it % S;
+      for (int chunk = 0; alive && chunk < p.nchunks; chunk++, ring.next(S)) {
+        const int s = ring.s;
         int slot, c0;
         if (g.Cp >= 64) {
           slot = cslot;
@@ -446,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         } else {
           chunk_vec(g.Cp, g.K, chunk, pt & 7, slot, c0);
         }
-        if (!mbar_wait(sm.empty + s, ((it / S) & 1) ^ 1, sm.abort_flag)) { alive = false; break; }
+        if (!mbar_wait(sm.empty + s, ring.ph ^ 1u, sm.abort_flag)) { alive = false; break; }
         if (pt == 0) {
           const uint32_t bytes = (uint32_t)p.Npb * 128;
           mbar_arrive_expect_tx(sm.full + s, bytes);
@@ -584,9 +594,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
       const uint32_t idesc = idesc_bf16(128, ncg * kChunk, 0, 1);  // A (gradient) K-major, B (columns) MN-major
       bool alive = true;
       int it = 0;
-      for (int step = step_lo; alive && step < step_hi; step++, it++) {
-        const int s = it % S;
-        if (!mbar_wait(sm.full + s, (it / S) & 1, sm.abort_flag)) { alive = false; break; }
+      Ring ring;
+      for (int step = step_lo; alive && step < step_hi; step++, it++, ring.next(S)) {
+        const int s = ring.s;
+        if (!mbar_wait(sm.full + s, ring.ph, sm.abort_flag)) { alive = false; break; }
         tc_fence_after();
         uint8_t *st = sm.stage + (size_t)s * stage_bytes;
         const uint64_t b0 = smem_desc_sw128(smem_u32(st), kDwPix * 128, 1024);
@@ -623,9 +634,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
     // The tap table is double buffered: while the columns of one step are gathered from one half, the taps
     // of the next step are decoded into the other half, so the map loads never sit on the critical path.
     const size_t tap_half = (size_t)p.tap_rows * kDwPix * g.nt;
-    auto fill_step = [&](int step, Tap *table) {
-      const int t2 = step % tiles_per_image;
-      const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
+    // position (image, tile row, tile column) of the step whose taps are decoded next, advanced without division
+    int nb_ = step_lo / tiles_per_image, nty = (step_lo % tiles_per_image) / p.tiles_x, ntx = (step_lo % tiles_per_image) % p.tiles_x;
+    int cur_b = nb_;
+    auto fill_step = [&](Tap *table) {
+      const int ty = nty, tx = ntx;
+      cur_b = nb_;
+      if (++ntx == p.tiles_x) {
+        ntx = 0;
+        if (++nty == p.tiles_y) { nty = 0; nb_++; }
+      }
       for (int idx = pt; idx < p.tap_rows * kDwPix; idx += kProducerThreads) {
         const int row = idx / kDwPix, pl = idx % kDwPix;
         int slot;
@@ -637,16 +655,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         else fill_taps_zero(g, dst);
       }
     };
-    if (step_lo < step_hi) fill_step(step_lo, sm.taps);
+    if (step_lo < step_hi) fill_step(sm.taps);
     producer_bar();
     // A producer that gave up waiting keeps walking the loop and its barriers (doing no work), so that the
     // named barrier never waits for a thread that left.
-    for (int step = step_lo; step < step_hi; step++, it++) {
-      const int b = step / tiles_per_image;
-      const char *img = (const char *)g.xh + (size_t)b * (shw + 1) * g.Cp * 2;
+    Ring ring;
+    for (int step = step_lo; step < step_hi; step++, it++, ring.next(S)) {
+      const char *img = (const char *)g.xh + (size_t)cur_b * (shw + 1) * g.Cp * 2;  // image of this step
       const Tap *taps = sm.taps + (it & 1) * tap_half;
-      const int s = it % S;
-      if (alive && !mbar_wait(sm.empty + s, ((it / S) & 1) ^ 1, sm.abort_flag)) alive = false;
+      const int s = ring.s;
+      if (alive && !mbar_wait(sm.empty + s, ring.ph ^ 1u, sm.abort_flag)) alive = false;
       if (!alive) { producer_bar(); continue; }
       uint8_t *st = sm.stage + (size_t)s * stage_bytes;
       if (pt == 0) {
@@ -654,7 +672,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         mbar_arrive_expect_tx(sm.full + s, bytes);
         bulk_copy_g2s(st + kDwColBytes, p.gt + ((size_t)step * p.mbs_total + mb0) * (kDwGtBytes / 2), bytes, sm.full + s);
       }
-      if (step + 1 < step_hi) fill_step(step + 1, sm.taps + ((it + 1) & 1) * tap_half);
+      if (step + 1 < step_hi) fill_step(sm.taps + ((it + 1) & 1) * tap_half);  // also moves cur_b on for the next step
       // thread pt: 16-byte vector v = pt & 7 of pixel pt >> 3, two chunks of the group at a time
       {
         static_assert(kProducerThreads == kDwPix * 8, "one (pixel, vector) per producer thread");
