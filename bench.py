@@ -233,12 +233,29 @@ def run_encoder(args, rank, local, world):
     if rank != 0:
         return None
     peaks = measured_peaks()
-    dom = max(per_launch, key=per_launch.get)
-    li, ph = dom
-    ci, co, _, (oh, ow), _ = cfg["layers"][li]
-    dom_flops = 2 * (hi - lo) * co * ci * 9 * oh * ow
+    # Dominant kernel = the kernel (not the single launch) with the largest share of the step.  Layers whose
+    # gathered side has <= 32 (channel, slot) columns run the thin-contraction SIMT kernels, the others the two
+    # tcgen05 kernels (forward-type gather-GEMM for forward and dInput, weight-gradient kernel for dW).
+    def kernel_of(li, ph):
+        ci = cfg["layers"][li][0]
+        if ci * 9 <= 32:
+            return "small_%s (SIMT, thin contraction)" % ph
+        return "tc_dw_kernel" if ph == "dw" else "tc_gemm_kernel"
+
+    def launch_flops(li):
+        ci, co, _, (oh, ow), _ = cfg["layers"][li]
+        return 2 * (hi - lo) * co * ci * 9 * oh * ow
+
+    groups = {}
+    for (li, ph), t in per_launch.items():
+        gk = groups.setdefault(kernel_of(li, ph), [0.0, 0.0, 0])
+        gk[0] += t
+        gk[1] += launch_flops(li)
+        gk[2] += 1
+    dom_kernel = max(groups, key=lambda k: groups[k][0])
+    dom_ms, dom_flops_total, dom_n = groups[dom_kernel]
     tensor_peak = peaks["bf16_tflops_sustained"]
-    achieved = dom_flops / (per_launch[dom] * 1e-3) / 1e12
+    achieved = dom_flops_total / (dom_ms * 1e-3) / 1e12
     out = {
         "metric": "mapped-conv fwd+bwd TFLOP/s", "value": round(value, 3), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
@@ -255,10 +272,16 @@ def run_encoder(args, rank, local, world):
                 "d2h_bytes_per_step": 4 * world, "ms_per_step": round(e2e_ms / args.steps, 3),
                 "api": "spherical_distortion.nn.MappedConvolution + autograd"},
         "gpu_launches": int(launches_per_step * args.steps),
-        "roofline": {"bound": "tensor", "kernel": "layer %d %s (Cin=%d, Cout=%d, %dx%d, local batch %d)"
-                                                  % (li + 1, ph, ci, co, oh, ow, hi - lo),
+        "roofline": {"bound": "tensor", "kernel": dom_kernel, "launches_per_step": dom_n,
+                     "avg_launch_ms": round(dom_ms / dom_n, 3),
+                     "algorithmic_gflop_per_launch": round(dom_flops_total / dom_n / 1e9, 1),
+                     "share_of_conv_time": round(dom_ms / sum(per_launch.values()), 3),
                      "achieved": round(achieved, 2), "peak": tensor_peak, "unit": "TFLOP/s",
-                     "frac": round(achieved / tensor_peak, 4), "traffic": None,
+                     "frac": round(achieved / tensor_peak, 4),
+                     # dram read+write of the layer-4 forward launch of this kernel: 154.3 MB in the batch-4 ncu
+                     # capture (profiles/tc_gemm_kernel_encoder_B4.md), scaled by local batch / 4 (traffic is
+                     # proportional to the batch: activations in, activations out)
+                     "traffic": int(154.3e6 * (hi - lo) / 4), "traffic_of": "layer-4 forward launch, scaled from the batch-4 capture",
                      "peak_source": peaks["source"] + " bf16 sustained (kernel timed inside a long step)",
                      "per_launch_ms": {"L%d.%s" % (k[0] + 1, k[1]): round(v, 3) for k, v in per_launch.items()}},
         "clocks": clocks,

@@ -116,8 +116,10 @@ small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ pl
   for (int m = 0; m < kSmallJ; m++) acc[m] = T(0);
   const T *tb = tbuf + (size_t)b * n_src * kSmallJ;
   if (ok) {
+    int e1 = __ldg(pv.offsets + p * K);
     for (int k = 0; k < K; k++) {
-      const int e0 = __ldg(pv.offsets + p * K + k), e1 = __ldg(pv.offsets + p * K + k + 1);
+      const int e0 = e1;
+      e1 = __ldg(pv.offsets + p * K + k + 1);
       for (int e = e0; e < e1; e++) {
         const int s = __ldg(pv.src + e);
         const T w = __ldg(pv.w + e);

@@ -711,25 +711,46 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
 // =================================================================================================
 
 // (B, C, HW) float32 -> (B, HW + 1, Cp) bf16; channels beyond C and the extra pixel HW of every image are
-// zero (unused taps point there).  32 pixels x 64 channels per block.
+// zero (unused taps point there).  64 pixels x 64 channels per block: 256-byte row segments in, 128-byte
+// pixel rows out.
 __global__ void __launch_bounds__(256) nchw_to_nhwc_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ y,
                                                                  int C, int Cp, int HW) {
-  __shared__ float tile[64][33];
-  const int b = blockIdx.z, c0 = blockIdx.y * 64, p0 = blockIdx.x * 32;
+  __shared__ float tile[64][65];
+  const int b = blockIdx.z, c0 = blockIdx.y * 64, p0 = blockIdx.x * 64;
   const int tid = threadIdx.x;
-  for (int i = tid; i < 64 * 32; i += 256) {
-    const int c = i >> 5, pp = i & 31;
-    tile[c][pp] = (c0 + c < C && p0 + pp < HW) ? __ldg(x + ((size_t)b * C + c0 + c) * HW + p0 + pp) : 0.0f;
+  const bool vec_ok = (HW & 3) == 0;  // rows of every channel start 16-byte aligned
+#pragma unroll
+  for (int it = 0; it < 4; it++) {
+    const int i = tid + it * 256, c = i >> 4, q = (i & 15) * 4;  // channel row, first of 4 pixels
+    float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c0 + c < C) {
+      const float *src = x + ((size_t)b * C + c0 + c) * HW + p0 + q;
+      if (vec_ok && p0 + q + 3 < HW) {
+        f = __ldg((const float4 *)src);
+      } else {
+        if (p0 + q + 0 < HW) f.x = __ldg(src + 0);
+        if (p0 + q + 1 < HW) f.y = __ldg(src + 1);
+        if (p0 + q + 2 < HW) f.z = __ldg(src + 2);
+        if (p0 + q + 3 < HW) f.w = __ldg(src + 3);
+      }
+    }
+    tile[c][q + 0] = f.x;
+    tile[c][q + 1] = f.y;
+    tile[c][q + 2] = f.z;
+    tile[c][q + 3] = f.w;
   }
   __syncthreads();
-  const int pp = tid >> 3, v = tid & 7;
-  if (p0 + pp <= HW && c0 + v * 8 < Cp) {
-    uint4 o;
-    o.x = pack_bf16(tile[v * 8 + 0][pp], tile[v * 8 + 1][pp]);
-    o.y = pack_bf16(tile[v * 8 + 2][pp], tile[v * 8 + 3][pp]);
-    o.z = pack_bf16(tile[v * 8 + 4][pp], tile[v * 8 + 5][pp]);
-    o.w = pack_bf16(tile[v * 8 + 6][pp], tile[v * 8 + 7][pp]);
-    *(uint4 *)(y + ((size_t)b * (HW + 1) + p0 + pp) * Cp + c0 + v * 8) = o;
+#pragma unroll
+  for (int it = 0; it < 2; it++) {
+    const int i = tid + it * 256, pp = i >> 3, v = i & 7;
+    if (p0 + pp <= HW && c0 + v * 8 < Cp) {
+      uint4 o;
+      o.x = pack_bf16(tile[v * 8 + 0][pp], tile[v * 8 + 1][pp]);
+      o.y = pack_bf16(tile[v * 8 + 2][pp], tile[v * 8 + 3][pp]);
+      o.z = pack_bf16(tile[v * 8 + 4][pp], tile[v * 8 + 5][pp]);
+      o.w = pack_bf16(tile[v * 8 + 6][pp], tile[v * 8 + 7][pp]);
+      *(uint4 *)(y + ((size_t)b * (HW + 1) + p0 + pp) * Cp + c0 + v * 8) = o;
+    }
   }
 }
 
@@ -751,8 +772,11 @@ __global__ void weight_image_kernel(const float *__restrict__ w, __nv_bfloat16 *
 
 // Gradient (B, N, GH*GW) float32 -> bf16 tile images [b][ptile][mb][128 rows][64 px]; the 64 pixels of a tile
 // are a 4x16 block of the (GH, GW) grid; 16-byte vector v (8 pixels) of row r sits at position v ^ (r & 7).
+// With `row_part` the kernel also writes the sum of every row over the tile's pixels to
+// row_part[(b * tiles + tile) * mbs_total * 128 + row] (first stage of the bias gradient).
 __global__ void __launch_bounds__(256) grad_image_kernel(const float *__restrict__ gsrc, __nv_bfloat16 *__restrict__ gt, int N,
-                                                          int GH, int GW, int tiles_x, int tiles_y, int mbs_total) {
+                                                          int GH, int GW, int tiles_x, int tiles_y, int mbs_total,
+                                                          float *__restrict__ row_part) {
   const int t2 = blockIdx.x, mb = blockIdx.y, b = blockIdx.z;
   const int ty = t2 / tiles_x, tx = t2 % tiles_x;
   const size_t npix = (size_t)GH * GW;
@@ -772,7 +796,33 @@ __global__ void __launch_bounds__(256) grad_image_kernel(const float *__restrict
     o.z = pack_bf16(f[4], f[5]);
     o.w = pack_bf16(f[6], f[7]);
     *(uint4 *)(dst + r * 64 + ((v ^ (r & 7)) << 3)) = o;
+    if (row_part) {
+      float sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      if (v == 0) row_part[(((size_t)b * tiles_x * tiles_y + t2) * mbs_total + mb) * 128 + r] = sum;
+    }
   }
+}
+
+// Second and third stage of the fused bias gradient: fixed-order sums over the (image, tile) blocks.
+constexpr int kRowSplits = 64;
+__global__ void row_sum_split_kernel(const float *__restrict__ row_part, int64_t nblocks, int rows_total, int C,
+                                     float *__restrict__ part2) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, sp = blockIdx.y;
+  if (c >= C) return;
+  const int64_t lo = nblocks * sp / kRowSplits, hi = nblocks * (sp + 1) / kRowSplits;
+  float s = 0.0f;
+  for (int64_t i = lo; i < hi; i++) s += __ldg(row_part + i * rows_total + c);
+  part2[(size_t)sp * C + c] = s;
+}
+__global__ void row_sum_final_kernel(const float *__restrict__ part2, int C, float *__restrict__ gb) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.0f;
+  for (int sp = 0; sp < kRowSplits; sp++) s += part2[(size_t)sp * C + c];
+  gb[c] = s;
 }
 
 // gw[n*sn + ch*sc + slot*sk] = sum over splits (in order) of partial[split][n][column of (slot, ch)].
@@ -836,7 +886,7 @@ Geometry geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int 
 }
 
 void to_nhwc(const void *src, __nv_bfloat16 *xh, int64_t B, int64_t CH, int Cp, int64_t HW, cudaStream_t st) {
-  nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW + 1, 32), cdiv(Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, Cp, (int)HW);
+  nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW + 1, 64), cdiv(Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, Cp, (int)HW);
 }
 
 template <int MODE, int NT>
@@ -913,7 +963,8 @@ DwGeometry dw_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P,
   if ((SHW + 1) * d.Cp * 2 >= ((int64_t)1 << 31)) d.ok = false;
   d.gt_bytes = align_up((size_t)steps * d.mbs_total * kDwGtBytes, 256);
   d.partial_bytes = align_up((size_t)d.splits * d.mbs_total * 128 * d.nchunks * kChunk * 4, 256);
-  d.bias_bytes = simt_bias_workspace(Cbias, 4);
+  d.bias_bytes = simt_bias_workspace(Cbias, 4) + align_up((size_t)steps * d.mbs_total * 128 * 4, 256) +
+                 align_up((size_t)kRowSplits * Cbias * 4, 256);
   return d;
 }
 
@@ -940,8 +991,14 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
   void *bias_ws = w8 + 256 + d.xh_bytes + d.gt_bytes + d.partial_bytes;
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
   to_nhwc(src, xh, B, CH, d.Cp, SH * SW, st);
-  grad_image_kernel<<<dim3(d.tiles_x * d.tiles_y, d.mbs_total, (unsigned)B), 256, 0, st>>>((const float *)A, gt, (int)Nout, (int)GH,
-                                                                                           (int)GW, d.tiles_x, d.tiles_y, d.mbs_total);
+  // When the operand being imaged is also the tensor whose channel sums give the bias gradient (conv dW:
+  // both are grad_output), the sums ride along with the imaging pass instead of re-reading the tensor.
+  const bool fuse_bias = gbias_src == A && Cbias == Nout && nbias == GH * GW;
+  const int64_t nblocks = B * d.tiles_x * d.tiles_y;
+  float *row_part = (float *)((char *)bias_ws + simt_bias_workspace(Cbias, 4));
+  float *part2 = (float *)((char *)row_part + align_up((size_t)nblocks * d.mbs_total * 128 * 4, 256));
+  grad_image_kernel<<<dim3(d.tiles_x * d.tiles_y, d.mbs_total, (unsigned)B), 256, 0, st>>>(
+      (const float *)A, gt, (int)Nout, (int)GH, (int)GW, d.tiles_x, d.tiles_y, d.mbs_total, fuse_bias ? row_part : nullptr);
   DwParams p{};
   p.g = Gather{xh, (const float *)map, (const float *)iw, nullptr, d.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, d.nt};
   p.gt = gt; p.partial = partial; p.status = status;
@@ -954,6 +1011,11 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
   tc_dw_reduce_kernel<<<cdiv(Nout * CH * K, 256), 256, 0, st>>>(partial, d.splits, d.mbs_total * 128, d.nchunks * kChunk, (int)Nout,
                                                                (int)CH, d.Cp, (int)K, sn, sc, sk, (float *)gw);
   note_launches(4);
+  if (fuse_bias) {
+    row_sum_split_kernel<<<dim3(cdiv(Cbias, 128), kRowSplits), 128, 0, st>>>(row_part, nblocks, d.mbs_total * 128, (int)Cbias, part2);
+    row_sum_final_kernel<<<cdiv(Cbias, 128), 128, 0, st>>>(part2, (int)Cbias, (float *)gb);
+    return launch_status(2);
+  }
   return simt_bias_grad<float>(gbias_src, B, Cbias, nbias, gb, bias_ws, st);
 }
 
