@@ -102,36 +102,53 @@ small_premul_kernel(const T *__restrict__ src, const T *__restrict__ wgt, int64_
   for (int j = 0; j < kSmallJ; j++) t[j] = acc[j];
 }
 
-// Out[b,m,p] = bias[m] + sum_k sum_{e in plan(p*K+k)} w_e * T[b, src_e, m*K+k]; thread = one destination pixel.
+// Out[b,m,p] = bias[m] + sum_k sum_{e in plan(p*K+k)} w_e * T[b, src_e, m*K+k]; thread = one destination pixel of
+// kGatherImages consecutive images, so the plan entries are read once per group of images.
+constexpr int kGatherImages = 4, kGatherM = 4;  // images per thread; output channels per register block
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ plan_blob, const T *__restrict__ bias,
-                         T *__restrict__ out, int K, int M, int n_src, int n_dst) {
-  const int p = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+                         T *__restrict__ out, int K, int M, int n_src, int n_dst, int B) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x, b0 = blockIdx.y * kGatherImages;
   if (p >= n_dst) return;
   bool ok;
   const PlanView<T> pv = plan_view<T>(plan_blob, n_dst * K, ok);
-  T acc[kSmallJ];  // only the first M entries are used (M * K <= kSmallJ)
+  const int nb = min(kGatherImages, B - b0);
+  const size_t img_stride = (size_t)n_src * kSmallJ;
+  const T *tb = tbuf + (size_t)b0 * img_stride;
+  for (int m0 = 0; m0 < M; m0 += kGatherM) {   // one pass for M <= 4 (e.g. RGB inputs)
+    T acc[kGatherImages][kGatherM];
 #pragma unroll
-  for (int m = 0; m < kSmallJ; m++) acc[m] = T(0);
-  const T *tb = tbuf + (size_t)b * n_src * kSmallJ;
-  if (ok) {
-    int e1 = __ldg(pv.offsets + p * K);
-    for (int k = 0; k < K; k++) {
-      const int e0 = e1;
-      e1 = __ldg(pv.offsets + p * K + k + 1);
-      for (int e = e0; e < e1; e++) {
-        const int s = __ldg(pv.src + e);
-        const T w = __ldg(pv.w + e);
+    for (int i = 0; i < kGatherImages; i++)
 #pragma unroll
-        for (int m = 0; m < kSmallJ; m++)
-          if (m < M) acc[m] += w * __ldg(tb + (size_t)s * kSmallJ + m * K + k);
+      for (int m = 0; m < kGatherM; m++) acc[i][m] = T(0);
+    if (ok) {
+      int e1 = __ldg(pv.offsets + p * K);
+      for (int k = 0; k < K; k++) {
+        const int e0 = e1;
+        e1 = __ldg(pv.offsets + p * K + k + 1);
+        for (int e = e0; e < e1; e++) {
+          const T *row = tb + (size_t)__ldg(pv.src + e) * kSmallJ + k;
+          const T w = __ldg(pv.w + e);
+#pragma unroll
+          for (int i = 0; i < kGatherImages; i++)
+            if (i < nb) {
+#pragma unroll
+              for (int m = 0; m < kGatherM; m++)
+                if (m0 + m < M) acc[i][m] += w * __ldg(row + i * img_stride + (m0 + m) * K);
+            }
+        }
       }
     }
-  }
 #pragma unroll
-  for (int m = 0; m < kSmallJ; m++)
-    if (m < M) out[((size_t)b * M + m) * n_dst + p] = acc[m] + (bias ? __ldg(bias + m) : T(0));
+    for (int i = 0; i < kGatherImages; i++)
+      if (i < nb) {
+#pragma unroll
+        for (int m = 0; m < kGatherM; m++)
+          if (m0 + m < M) out[((size_t)(b0 + i) * M + m0 + m) * n_dst + p] = acc[i][m] + (bias ? __ldg(bias + m0 + m) : T(0));
+      }
+  }
 }
 
 // dW partial sums: block = (64 rows of A) x (all <= 32 columns) over the pixel chunks of its split.
@@ -242,8 +259,8 @@ int small_adjoint(const void *src, const void *plan, int64_t CH, int64_t n_src, 
   if (!ws || ws_bytes < small_premul_workspace(B, M, K, n_src, sizeof(T))) return SPH_ERR_WORKSPACE_TOO_SMALL;
   small_premul_kernel<T><<<dim3(cdiv(n_src, 256), (unsigned)B), 256, sizeof(T) * (size_t)CH * kSmallJ, st>>>(
       (const T *)src, (const T *)wgt, sm, sc, sk, (T *)ws, (int)CH, (int)K, (int)M, (int)n_src);
-  small_plan_gather_kernel<T><<<dim3(cdiv(n_dst, 256), (unsigned)B), 256, 0, st>>>((const T *)ws, plan, (const T *)bias, (T *)out,
-                                                                                   (int)K, (int)M, (int)n_src, (int)n_dst);
+  small_plan_gather_kernel<T><<<dim3(cdiv(n_dst, 256), cdiv(B, kGatherImages)), 256, 0, st>>>(
+      (const T *)ws, plan, (const T *)bias, (T *)out, (int)K, (int)M, (int)n_src, (int)n_dst, (int)B);
   return launch_status(2);
 }
 
