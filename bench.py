@@ -388,6 +388,17 @@ def run_pool(args, rank, local, world):
     for _ in range(args.steps):
         step()
     clocks = sampler.stop() if sampler else None
+    # the same kernels on a map with locality (3x3 gnomonic, stride 2: what a pooling layer of a spherical network
+    # uses), same tensor sizes: shows the kernels' bandwidth when the taps are not uniformly random
+    ml = wl.gnomonic_map(x.shape[2], x.shape[3], 2).to(dev)
+    tf_r, tb_r = list(tf), list(tb)
+    tf.clear(), tb.clear()
+    m_random, m = m, ml
+    for _ in range(2 + max(3, args.steps // 2)):
+        step()
+    lf_ms, lb_ms = sum(tf[2:]) / len(tf[2:]), sum(tb[2:]) / len(tb[2:])
+    tf[:], tb[:] = tf_r, tb_r
+    m = m_random
     n = hi - lo
     fwd_bytes = x.numel() * 4 + out.numel() * 4 + idx.numel() * 8 + m.numel() * 4
     f_ms, b_ms = sum(tf) / len(tf), sum(tb) / len(tb)
@@ -405,26 +416,20 @@ def run_pool(args, rank, local, world):
             "roofline": {"bound": "hbm", "kernel": "max_pool_kernel (forward)", "achieved": round(fwd_bytes / (f_ms * 1e-3) / 1e9, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(fwd_bytes / (f_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                          "traffic": None, "fwd_ms": round(f_ms, 4), "bwd_ms": round(b_ms, 4),
-                         "bwd_achieved": round(fwd_bytes / (b_ms * 1e-3) / 1e9, 1)},
+                         "bwd_achieved": round(fwd_bytes / (b_ms * 1e-3) / 1e9, 1),
+                         "local_map": {"map": "3x3 gnomonic, stride 2", "fwd_ms": round(lf_ms, 4), "bwd_ms": round(lb_ms, 4),
+                                       "fwd_gbs": round(fwd_bytes / (lf_ms * 1e-3) / 1e9, 1),
+                                       "fwd_frac": round(fwd_bytes / (lf_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                                       "bwd_gbs": round(fwd_bytes / (lb_ms * 1e-3) / 1e9, 1)}},
             "clocks": clocks}
 
 
-def run_resample(args, rank, local, world):
-    from sphmap import capi, workloads as wl
-    from sphmap.parallel import shard_batch
-    dev = torch.device("cuda", local)
-    B = args.batch if args.batch != 64 else 8
-    cfg = wl.config1(B=B)
-    lo, hi = shard_batch(B, rank, world)
-    x, m = cfg["x"][lo:hi].to(dev), cfg["map"].to(dev)
-    H, W = cfg["out_hw"]
-    plan = capi.plan_build(m, None, m.shape[0] * m.shape[1], 1, 1, H, W)
+def _time_resample(capi, x, m, plan, H, W, steps, warmup, flush):
     y = capi.resample_from_map(x, m, 1)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    out = torch.empty_like(x)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     tg, ts = [], []
-
-    def step():
+    for i in range(warmup + steps):
         flush.zero_()
         ev[0].record()
         capi.resample_from_map(x, m, 1)
@@ -434,20 +439,42 @@ def run_resample(args, rank, local, world):
         capi.resample_to_map(y, plan, H, W)
         ev[3].record()
         torch.cuda.synchronize()
-        tg.append(ev[0].elapsed_time(ev[1]))
-        ts.append(ev[2].elapsed_time(ev[3]))
+        if i >= warmup:
+            tg.append(ev[0].elapsed_time(ev[1]))
+            ts.append(ev[2].elapsed_time(ev[3]))
+    del out
+    return sum(tg) / len(tg), sum(ts) / len(ts)
 
-    for _ in range(args.warmup):
-        step()
-    tg.clear(), ts.clear()
-    barrier_sync(world)
-    for _ in range(args.steps):
-        step()
-    n = hi - lo
-    C, ns = x.shape[1], m.shape[0] * m.shape[1]
-    g_bytes = n * C * ns * 4 + m.numel() * 4 + n * C * min(4 * ns, H * W) * 4
-    s_bytes = n * C * ns * 4 + m.numel() * 4 + n * C * H * W * 4
-    g_ms, s_ms = max_over_ranks(sum(tg) / len(tg), world, dev), max_over_ranks(sum(ts) / len(ts), world, dev)
+
+def _resample_bytes(n, C, ns, H, W, map_numel):
+    g = n * C * ns * 4 + map_numel * 4 + n * C * min(4 * ns, H * W) * 4
+    sc = n * C * ns * 4 + map_numel * 4 + n * C * H * W * 4
+    return g, sc
+
+
+def run_resample(args, rank, local, world):
+    """BASELINE config 1 (B=8), plus the same operators at B=256 so that the kernels run long enough for the
+    bandwidth figure to mean something (the B=8 launches move 40-59 MB, about 6-9 us at the HBM peak)."""
+    from sphmap import capi, workloads as wl
+    from sphmap.parallel import shard_batch
+    dev = torch.device("cuda", local)
+    B = args.batch if args.batch != 64 else 8
+    cfg = wl.config1(B=B)
+    lo, hi = shard_batch(B, rank, world)
+    x, m = cfg["x"][lo:hi].to(dev), cfg["map"].to(dev)
+    H, W = cfg["out_hw"]
+    plan = capi.plan_build(m, None, m.shape[0] * m.shape[1], 1, 1, H, W)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    g_ms, s_ms = _time_resample(capi, x, m, plan, H, W, args.steps, args.warmup, flush)
+    n, C, ns = hi - lo, x.shape[1], m.shape[0] * m.shape[1]
+    g_bytes, s_bytes = _resample_bytes(n, C, ns, H, W, m.numel())
+    # scaled variant: 256 images, seeded the same way
+    gbig = torch.Generator().manual_seed(1)
+    xb = torch.rand(256 // world, C, H, W, generator=gbig).to(dev)
+    gb_ms, sb_ms = _time_resample(capi, xb, m, plan, H, W, max(3, args.steps // 2), 2, flush)
+    gb_bytes, sb_bytes = _resample_bytes(xb.shape[0], C, ns, H, W, m.numel())
+    g_ms, s_ms = max_over_ranks(g_ms, world, dev), max_over_ranks(s_ms, world, dev)
+    gb_ms, sb_ms = max_over_ranks(gb_ms, world, dev), max_over_ranks(sb_ms, world, dev)
     if rank != 0:
         return None
     peaks = measured_peaks()
@@ -460,7 +487,11 @@ def run_resample(args, rank, local, world):
             "roofline": {"bound": "hbm", "kernel": "resample_from_map_kernel", "achieved": round(g_bytes / (g_ms * 1e-3) / 1e9, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(g_bytes / (g_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
                          "traffic": None, "gather_ms": round(g_ms, 4), "scatter_ms": round(s_ms, 4),
-                         "scatter_achieved": round(s_bytes / (s_ms * 1e-3) / 1e9, 1)}}
+                         "scatter_achieved": round(s_bytes / (s_ms * 1e-3) / 1e9, 1),
+                         "batch256": {"gather_ms": round(gb_ms, 4), "gather_gbs": round(gb_bytes / (gb_ms * 1e-3) / 1e9, 1),
+                                      "gather_frac": round(gb_bytes / (gb_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                                      "scatter_ms": round(sb_ms, 4), "scatter_gbs": round(sb_bytes / (sb_ms * 1e-3) / 1e9, 1),
+                                      "scatter_frac": round(sb_bytes / (sb_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)}}}
 
 
 def run_conv(args, rank, local, world):

@@ -55,6 +55,46 @@ max_pool_kernel(const T *__restrict__ x, const T *__restrict__ map, const T *__r
     }
 }
 
+// Nearest-neighbour, unweighted pooling with at most kPoolMaxK slots: the K tap offsets of the output position are
+// decoded first and kept in registers, then every plane issues its K loads back to back (no load depends on
+// another), which is what lets the kernel run at memory speed instead of at K round-trip latencies per plane.
+constexpr int kPoolMaxK = 16;
+
+template <typename T, int PPT>
+__global__ void __launch_bounds__(256)
+max_pool_nearest_kernel(const T *__restrict__ x, const T *__restrict__ map, T *__restrict__ out, int64_t *__restrict__ idx,
+                        int n, int planes, int H, int W, int K) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= n) return;
+  const int p0 = blockIdx.y * PPT;
+  const int np = min(PPT, planes - p0);
+  const size_t hw = (size_t)H * W;
+  int off[kPoolMaxK];
+#pragma unroll
+  for (int k = 0; k < kPoolMaxK; k++) {
+    off[k] = -1;
+    if (k < K) {
+      Taps<T> t;
+      const size_t e = (size_t)o * K + k;
+      decode<T, SPH_NEAREST>(__ldg(map + 2 * e), __ldg(map + 2 * e + 1), H, W, t);
+      off[k] = t.off[0];
+    }
+  }
+  for (int j = 0; j < np; j++) {
+    const T *plane = x + (size_t)(p0 + j) * hw;
+    T v[kPoolMaxK];
+#pragma unroll
+    for (int k = 0; k < kPoolMaxK; k++) v[k] = (k < K && off[k] >= 0) ? __ldg(plane + off[k]) : T(0);
+    T best = (T)(-FLT_MAX);
+    int bk = -1;
+#pragma unroll
+    for (int k = 0; k < kPoolMaxK; k++)
+      if (k < K && v[k] > best) { best = v[k]; bk = k; }
+    out[(size_t)(p0 + j) * n + o] = best;
+    idx[(size_t)(p0 + j) * n + o] = bk < 0 ? (int64_t)-1 : ((int64_t)o * K + bk) * 2;
+  }
+}
+
 // Argmax backward: the gradient of output (p,o) goes back through the one
 // map slot idx names (common/mapped_max_pool.h:60-78, 136-171).  grad_in is
 // zeroed first; contributions are added with red.global.add as in the
@@ -90,6 +130,11 @@ max_unpool_kernel(const T *__restrict__ g, const int64_t *__restrict__ idx, cons
 template <typename T>
 static int pool(const void *x, const void *map, const void *iw, void *out, int64_t *idx, int64_t planes, int64_t H,
                 int64_t W, int64_t n, int64_t K, int64_t P, int interp, cudaStream_t st) {
+  if (interp == SPH_NEAREST && P == 0 && K <= kPoolMaxK) {
+    max_pool_nearest_kernel<T, kPlanesPerThread><<<dim3(cdiv(n, 256), cdiv(planes, kPlanesPerThread)), 256, 0, st>>>(
+        (const T *)x, (const T *)map, (T *)out, idx, (int)n, (int)planes, (int)H, (int)W, (int)K);
+    return launch_status();
+  }
   dim3 grid(cdiv(n, 256), cdiv(planes, kPlanesPerThread));
   SPH_DISPATCH_INTERP(interp, {
     if (P > 0)

@@ -1,4 +1,6 @@
 // resample_from_map (gather) and resample_to_map (adjoint, through a scatter plan).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace sph {
@@ -7,14 +9,14 @@ namespace sph {
 // (batch, channel) planes with the same taps.  Reference kernel:
 // ext_modules/include/cuda/resample.cuh:50-81 (one thread per (c, position), one
 // launch per image); arithmetic: common/resample.h:34-52, 85-107.
-template <typename T, int INTERP, bool WEIGHTED>
+template <typename T, int INTERP, bool WEIGHTED, int PPT>
 __global__ void __launch_bounds__(256)
 resample_from_map_kernel(const T *__restrict__ x, const T *__restrict__ map, const T *__restrict__ iw,
                          T *__restrict__ y, int n, int planes, int H, int W, int P) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
-  const int p0 = blockIdx.y * kPlanesPerThread;
-  const int np = min(kPlanesPerThread, planes - p0);
+  const int p0 = blockIdx.y * PPT;
+  const int np = min(PPT, planes - p0);
   const size_t hw = (size_t)H * W;
   const T *xp = x + (size_t)p0 * hw;
   T *yp = y + (size_t)p0 * n + i;
@@ -22,29 +24,29 @@ resample_from_map_kernel(const T *__restrict__ x, const T *__restrict__ map, con
   if (!WEIGHTED) {
     decode<T, INTERP>(__ldg(map + 2 * (size_t)i), __ldg(map + 2 * (size_t)i + 1), H, W, t);
 #pragma unroll
-    for (int j = 0; j < kPlanesPerThread; j++)
+    for (int j = 0; j < PPT; j++)
       if (j < np) yp[(size_t)j * n] = gather<T, INTERP>(xp + j * hw, t);
   } else {
-    T acc[kPlanesPerThread];
+    T acc[PPT];
 #pragma unroll
-    for (int j = 0; j < kPlanesPerThread; j++) acc[j] = T(0);
+    for (int j = 0; j < PPT; j++) acc[j] = T(0);
     for (int q = 0; q < P; q++) {
       const size_t e = (size_t)i * P + q;
       decode<T, INTERP>(__ldg(map + 2 * e), __ldg(map + 2 * e + 1), H, W, t);
       const T wq = __ldg(iw + e);
 #pragma unroll
-      for (int j = 0; j < kPlanesPerThread; j++)
+      for (int j = 0; j < PPT; j++)
         if (j < np) acc[j] = RN<T>::add(acc[j], RN<T>::mul(wq, gather<T, INTERP>(xp + j * hw, t)));
     }
 #pragma unroll
-    for (int j = 0; j < kPlanesPerThread; j++)
+    for (int j = 0; j < PPT; j++)
       if (j < np) yp[(size_t)j * n] = acc[j];
   }
 }
 
 // Adjoint as a gather: destination pixel p sums its plan segment in stored
 // order.  Replaces the atomicAdd scatter of cuda/resample.cuh:14-47.
-template <typename T>
+template <typename T, int PPT>
 __global__ void __launch_bounds__(256)
 resample_to_map_kernel(const T *__restrict__ x, const void *__restrict__ plan_blob, T *__restrict__ out, int n_dst,
                        int n_src, int planes) {
@@ -52,37 +54,121 @@ resample_to_map_kernel(const T *__restrict__ x, const void *__restrict__ plan_bl
   if (p >= n_dst) return;
   bool ok;
   const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok);
-  const int p0 = blockIdx.y * kPlanesPerThread;
-  const int np = min(kPlanesPerThread, planes - p0);
+  const int p0 = blockIdx.y * PPT;
+  const int np = min(PPT, planes - p0);
   const T *xp = x + (size_t)p0 * n_src;
-  T acc[kPlanesPerThread];
+  T acc[PPT];
 #pragma unroll
-  for (int j = 0; j < kPlanesPerThread; j++) acc[j] = T(0);
+  for (int j = 0; j < PPT; j++) acc[j] = T(0);
   const int e0 = ok ? __ldg(plan.offsets + p) : 0, e1 = ok ? __ldg(plan.offsets + p + 1) : 0;
   for (int e = e0; e < e1; e++) {
     const int s = __ldg(plan.src + e);
     const T w = __ldg(plan.w + e);
 #pragma unroll
-    for (int j = 0; j < kPlanesPerThread; j++)
+    for (int j = 0; j < PPT; j++)
       if (j < np) acc[j] += w * __ldg(xp + (size_t)j * n_src + s);
   }
 #pragma unroll
-  for (int j = 0; j < kPlanesPerThread; j++)
+  for (int j = 0; j < PPT; j++)
     if (j < np) out[(size_t)(p0 + j) * n_dst + p] = acc[j];
+}
+
+// Same operator, four consecutive destination pixels per thread (n_dst a multiple of 4) in a grid-stride loop:
+// the five segment offsets of the next group are requested before the current group is processed, and every
+// plane is written with one 16-byte (float) / two 16-byte (double) stores.  Most of this kernel's traffic is the
+// output it writes; the point is to keep enough bytes in flight per thread.
+template <typename T, int PPT>
+__global__ void __launch_bounds__(256)
+resample_to_map4_kernel(const T *__restrict__ x, const void *__restrict__ plan_blob, T *__restrict__ out, int n_dst,
+                        int n_src, int planes) {
+  bool ok;
+  const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok);
+  const int p0 = blockIdx.y * PPT;
+  const int np = min(PPT, planes - p0);
+  const T *xp = x + (size_t)p0 * n_src;
+  const int stride = gridDim.x * blockDim.x * 4;
+  int p = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  int nxt[5];
+#pragma unroll
+  for (int q = 0; q < 5; q++) nxt[q] = (ok && p < n_dst) ? __ldg(plan.offsets + p + q) : 0;
+  for (; p < n_dst; p += stride) {
+    int off[5];
+#pragma unroll
+    for (int q = 0; q < 5; q++) off[q] = nxt[q];
+    const int pn = p + stride;
+#pragma unroll
+    for (int q = 0; q < 5; q++) nxt[q] = (ok && pn < n_dst) ? __ldg(plan.offsets + pn + q) : 0;
+    T acc[4][PPT];
+#pragma unroll
+    for (int q = 0; q < 4; q++)
+#pragma unroll
+      for (int j = 0; j < PPT; j++) acc[q][j] = T(0);
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      for (int e = off[q]; e < off[q + 1]; e++) {
+        const int s = __ldg(plan.src + e);
+        const T w = __ldg(plan.w + e);
+#pragma unroll
+        for (int j = 0; j < PPT; j++)
+          if (j < np) acc[q][j] += w * __ldg(xp + (size_t)j * n_src + s);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < PPT; j++)
+      if (j < np) {
+        T *o = out + (size_t)(p0 + j) * n_dst + p;
+        if (sizeof(T) == 4) {
+          *(float4 *)o = make_float4((float)acc[0][j], (float)acc[1][j], (float)acc[2][j], (float)acc[3][j]);
+        } else {
+          *(double2 *)o = make_double2((double)acc[0][j], (double)acc[1][j]);
+          *(double2 *)(o + 2) = make_double2((double)acc[2][j], (double)acc[3][j]);
+        }
+      }
+  }
+}
+
+// Planes walked per thread: 8 amortises the tap decode best; small problems use 2 so that enough threads are
+// in flight to cover the memory latency.
+static int planes_per_thread(int64_t n, int64_t planes) {
+  return n * ((planes + 7) / 8) >= (int64_t)148 * 2048 * 2 ? 8 : 2;
+}
+
+template <typename T, int PPT>
+static void from_map_launch(const void *x, const void *map, const void *iw, void *y, int64_t planes, int64_t H, int64_t W,
+                            int64_t n, int64_t P, int interp, cudaStream_t st) {
+  dim3 grid(cdiv(n, 256), cdiv(planes, PPT));
+  SPH_DISPATCH_INTERP(interp, {
+    if (P > 0)
+      resample_from_map_kernel<T, INTERP, true, PPT><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, (const T *)iw, (T *)y,
+                                                                           (int)n, (int)planes, (int)H, (int)W, (int)P);
+    else
+      resample_from_map_kernel<T, INTERP, false, PPT><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, nullptr, (T *)y,
+                                                                            (int)n, (int)planes, (int)H, (int)W, 0);
+  });
 }
 
 template <typename T>
 static int from_map(const void *x, const void *map, const void *iw, void *y, int64_t planes, int64_t H, int64_t W,
                     int64_t n, int64_t P, int interp, cudaStream_t st) {
-  dim3 grid(cdiv(n, 256), cdiv(planes, kPlanesPerThread));
-  SPH_DISPATCH_INTERP(interp, {
-    if (P > 0)
-      resample_from_map_kernel<T, INTERP, true><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, (const T *)iw,
-                                                                       (T *)y, (int)n, (int)planes, (int)H, (int)W, (int)P);
-    else
-      resample_from_map_kernel<T, INTERP, false><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, nullptr, (T *)y,
-                                                                        (int)n, (int)planes, (int)H, (int)W, 0);
-  });
+  if (planes_per_thread(n, planes) == 8) from_map_launch<T, 8>(x, map, iw, y, planes, H, W, n, P, interp, st);
+  else from_map_launch<T, 2>(x, map, iw, y, planes, H, W, n, P, interp, st);
+  return launch_status();
+}
+
+template <typename T>
+static int to_map(const void *x, const void *plan, void *out, int64_t planes, int64_t n_src, int64_t n_dst, cudaStream_t st) {
+  if (n_dst % 4 == 0 && ((uintptr_t)out & 31) == 0 && n_dst * ((planes + 3) / 4) >= (int64_t)148 * 2048 * 4) {
+    const int gx = (int)std::min<int64_t>(cdiv(n_dst / 4, 256), 64);  // each thread walks several groups of four pixels
+    resample_to_map4_kernel<T, 4><<<dim3(gx, cdiv(planes, 4)), 256, 0, st>>>((const T *)x, plan, (T *)out,
+                                                                                              (int)n_dst, (int)n_src, (int)planes);
+    return launch_status();
+  }
+  if (planes_per_thread(n_dst, planes) == 8)
+    resample_to_map_kernel<T, 8><<<dim3(cdiv(n_dst, 256), cdiv(planes, 8)), 256, 0, st>>>((const T *)x, plan, (T *)out, (int)n_dst,
+                                                                                         (int)n_src, (int)planes);
+  else
+    resample_to_map_kernel<T, 2><<<dim3(cdiv(n_dst, 256), cdiv(planes, 2)), 256, 0, st>>>((const T *)x, plan, (T *)out, (int)n_dst,
+                                                                                         (int)n_src, (int)planes);
   return launch_status();
 }
 
@@ -98,7 +184,7 @@ extern "C" int sph_resample_from_map(const void *x, const void *map, const void 
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
   if (interp < 0 || interp > 2) return SPH_ERR_INVALID_ARGUMENT;
   const int64_t n = MH * MW, planes = B * C, lim = (int64_t)1 << 31;
-  if (H * W >= lim || n * (P > 0 ? P : 1) * 2 >= lim || planes / kPlanesPerThread >= 65535) return SPH_ERR_TOO_LARGE;
+  if (H * W >= lim || n * (P > 0 ? P : 1) * 2 >= lim || planes / 2 >= 65535) return SPH_ERR_TOO_LARGE;
   if (n == 0 || planes == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
   return dtype == SPH_F32 ? from_map<float>(x, map, iw, y, planes, H, W, n, P, interp, st)
@@ -110,15 +196,9 @@ extern "C" int sph_resample_to_map(const void *x, const void *plan, void *out, i
   if (!x || !plan || !out || B < 0 || C < 0 || MH <= 0 || MW <= 0 || OH <= 0 || OW <= 0) return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
   const int64_t planes = B * C, lim = (int64_t)1 << 31;
-  if (OH * OW >= lim || MH * MW >= lim || planes / kPlanesPerThread >= 65535) return SPH_ERR_TOO_LARGE;
+  if (OH * OW >= lim || MH * MW >= lim || planes / 2 >= 65535) return SPH_ERR_TOO_LARGE;
   if (planes == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  dim3 grid(cdiv(OH * OW, 256), cdiv(planes, kPlanesPerThread));
-  if (dtype == SPH_F32)
-    resample_to_map_kernel<float><<<grid, 256, 0, st>>>((const float *)x, plan, (float *)out, (int)(OH * OW),
-                                                        (int)(MH * MW), (int)planes);
-  else
-    resample_to_map_kernel<double><<<grid, 256, 0, st>>>((const double *)x, plan, (double *)out, (int)(OH * OW),
-                                                         (int)(MH * MW), (int)planes);
-  return launch_status();
+  return dtype == SPH_F32 ? to_map<float>(x, plan, out, planes, MH * MW, OH * OW, st)
+                          : to_map<double>(x, plan, out, planes, MH * MW, OH * OW, st);
 }

@@ -101,3 +101,18 @@ def test_exact_path_with_wide_channels(impl, dtype, interp, P):
     for a, r in zip(impl.mapped_transposed_conv_backward(got, m, xt, w, bt, K, interp, iw),
                     port.mapped_transposed_conv_backward(got, m, xt, w, bt, K, interp, iw)):
         close(a, r)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_resample_to_map_many_planes(dtype):
+    """Enough (batch, channel) planes to select the four-pixels-per-thread scatter kernel; same bar as the rest."""
+    from _gpu_impl import CApi
+    from oracle import port
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(8, 80, 20, 30, generator=g, dtype=dtype)
+    m = (torch.rand(20, 30, 2, generator=g, dtype=torch.float64) * torch.tensor([130.0, 66.0]) - 1.0).to(dtype)
+    got = CApi().resample_to_map(x, m, 64, 128, 1)
+    ref = port.resample_to_map(x, m, 64, 128, 1)
+    rt = 1e-5 if dtype == torch.float32 else 1e-12
+    torch.testing.assert_close(got, ref, rtol=rt, atol=rt)
+    assert torch.equal(got, CApi().resample_to_map(x, m, 64, 128, 1))      # deterministic
