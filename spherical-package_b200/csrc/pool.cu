@@ -60,7 +60,7 @@ max_pool_kernel(const T *__restrict__ x, const T *__restrict__ map, const T *__r
 // another), which is what lets the kernel run at memory speed instead of at K round-trip latencies per plane.
 constexpr int kPoolMaxK = 16;
 
-template <typename T, int PPT>
+template <typename T, int PPT, int KMAX>
 __global__ void __launch_bounds__(256)
 max_pool_nearest_kernel(const T *__restrict__ x, const T *__restrict__ map, T *__restrict__ out, int64_t *__restrict__ idx,
                         int n, int planes, int H, int W, int K) {
@@ -69,9 +69,9 @@ max_pool_nearest_kernel(const T *__restrict__ x, const T *__restrict__ map, T *_
   const int p0 = blockIdx.y * PPT;
   const int np = min(PPT, planes - p0);
   const size_t hw = (size_t)H * W;
-  int off[kPoolMaxK];
+  int off[KMAX];
 #pragma unroll
-  for (int k = 0; k < kPoolMaxK; k++) {
+  for (int k = 0; k < KMAX; k++) {
     off[k] = -1;
     if (k < K) {
       Taps<T> t;
@@ -80,16 +80,21 @@ max_pool_nearest_kernel(const T *__restrict__ x, const T *__restrict__ map, T *_
       off[k] = t.off[0];
     }
   }
-  for (int j = 0; j < np; j++) {
-    const T *plane = x + (size_t)(p0 + j) * hw;
-    T v[kPoolMaxK];
+  T v[PPT][KMAX];
 #pragma unroll
-    for (int k = 0; k < kPoolMaxK; k++) v[k] = (k < K && off[k] >= 0) ? __ldg(plane + off[k]) : T(0);
+  for (int j = 0; j < PPT; j++) {
+    const T *plane = x + (size_t)(p0 + (j < np ? j : 0)) * hw;
+#pragma unroll
+    for (int k = 0; k < KMAX; k++) v[j][k] = (k < K && off[k] >= 0) ? __ldg(plane + off[k]) : T(0);
+  }
+#pragma unroll
+  for (int j = 0; j < PPT; j++) {
+    if (j >= np) break;
     T best = (T)(-FLT_MAX);
     int bk = -1;
 #pragma unroll
-    for (int k = 0; k < kPoolMaxK; k++)
-      if (k < K && v[k] > best) { best = v[k]; bk = k; }
+    for (int k = 0; k < KMAX; k++)
+      if (k < K && v[j][k] > best) { best = v[j][k]; bk = k; }
     out[(size_t)(p0 + j) * n + o] = best;
     idx[(size_t)(p0 + j) * n + o] = bk < 0 ? (int64_t)-1 : ((int64_t)o * K + bk) * 2;
   }
@@ -131,8 +136,14 @@ template <typename T>
 static int pool(const void *x, const void *map, const void *iw, void *out, int64_t *idx, int64_t planes, int64_t H,
                 int64_t W, int64_t n, int64_t K, int64_t P, int interp, cudaStream_t st) {
   if (interp == SPH_NEAREST && P == 0 && K <= kPoolMaxK) {
-    max_pool_nearest_kernel<T, kPlanesPerThread><<<dim3(cdiv(n, 256), cdiv(planes, kPlanesPerThread)), 256, 0, st>>>(
-        (const T *)x, (const T *)map, (T *)out, idx, (int)n, (int)planes, (int)H, (int)W, (int)K);
+    constexpr int PPT = 4;
+    dim3 grid(cdiv(n, 256), cdiv(planes, PPT));
+#define SPH_POOL_NEAREST(KMAX) \
+    max_pool_nearest_kernel<T, PPT, KMAX><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, (T *)out, idx, (int)n, (int)planes, (int)H, (int)W, (int)K)
+    if (K <= 4) SPH_POOL_NEAREST(4);
+    else if (K <= 9) SPH_POOL_NEAREST(9);
+    else SPH_POOL_NEAREST(16);
+#undef SPH_POOL_NEAREST
     return launch_status();
   }
   dim3 grid(cdiv(n, 256), cdiv(planes, kPlanesPerThread));
@@ -171,7 +182,7 @@ static int check(const void *a, const void *b, const void *c, const void *d, con
     return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
   const int64_t lim = (int64_t)1 << 31;
-  if (IH * IW >= lim || OH * OW * K * (P > 0 ? P : 1) * 2 >= lim || B * C / kPlanesPerThread >= 65535)
+  if (IH * IW >= lim || OH * OW * K * (P > 0 ? P : 1) * 2 >= lim || B * C / 4 >= 65535)
     return SPH_ERR_TOO_LARGE;
   return SPH_OK;
 }
