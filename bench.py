@@ -415,7 +415,9 @@ def run_pool(args, rank, local, world):
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "max_pool_kernel (forward)", "achieved": round(fwd_bytes / (f_ms * 1e-3) / 1e9, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(fwd_bytes / (f_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-                         "traffic": None, "fwd_ms": round(f_ms, 4), "bwd_ms": round(b_ms, 4),
+                         # dram read+write of the forward launch on config 2 (profiles/pool_resample_dram_traffic.md),
+                         # scaled by the local batch
+                         "traffic": int(450.7e6 * n / 8), "fwd_ms": round(f_ms, 4), "bwd_ms": round(b_ms, 4),
                          "bwd_achieved": round(fwd_bytes / (b_ms * 1e-3) / 1e9, 1),
                          "local_map": {"map": "3x3 gnomonic, stride 2", "fwd_ms": round(lf_ms, 4), "bwd_ms": round(lb_ms, 4),
                                        "fwd_gbs": round(fwd_bytes / (lf_ms * 1e-3) / 1e9, 1),
@@ -486,7 +488,8 @@ def run_resample(args, rank, local, world):
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "resample_from_map_kernel", "achieved": round(g_bytes / (g_ms * 1e-3) / 1e9, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(g_bytes / (g_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-                         "traffic": None, "gather_ms": round(g_ms, 4), "scatter_ms": round(s_ms, 4),
+                         # dram read+write of the gather launch at B=8 (profiles/pool_resample_dram_traffic.md), scaled
+                         "traffic": int(49.0e6 * n / 8), "gather_ms": round(g_ms, 4), "scatter_ms": round(s_ms, 4),
                          "scatter_achieved": round(s_bytes / (s_ms * 1e-3) / 1e9, 1),
                          "batch256": {"gather_ms": round(gb_ms, 4), "gather_gbs": round(gb_bytes / (gb_ms * 1e-3) / 1e9, 1),
                                       "gather_frac": round(gb_bytes / (gb_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
