@@ -116,6 +116,11 @@ __device__ __forceinline__ void fill_taps(const Gather &g, int pix, int slot, Ta
 }
 
 __device__ __forceinline__ void fill_taps_any(const Gather &g, int pix, int slot, Tap *dst) {
+  if (g.map == nullptr) {  // identity gather (dense GEMM over the source grid): one tap, the pixel itself
+    dst[0].off = pix * g.Cp * 2;
+    dst[0].w = tap_weight(1.0f);
+    return;
+  }
   SPH_DISPATCH_INTERP(g.interp, fill_taps<INTERP>(g, pix, slot, dst));
 }
 
@@ -230,6 +235,8 @@ struct TcParams {
   const __nv_bfloat16 *wp;  // weight tile images: [nblk][nchunks][Npb rows][64] bf16, 128B-swizzled
   const float *bias;        // (Nout) or null
   float *out;               // (B, Nout, GH*GW)
+  __nv_bfloat16 *out_h;     // if set: write bf16 rows (B, GH*GW, out_pitch) instead (column buffer of the
+  int out_pitch;            // multiply-first adjoint), no bias
   int *status;              // set to 1 if a bounded wait gave up
   int B, Nout, Npb, nblk, nchunks, tiles_x, tiles_y, stages;
 };
@@ -361,7 +368,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
           for (int j = 0; j < 16; j++) { r[j] = h[j]; r[j + 16] = 0; }
         }
         tmem_ld_wait();
-        if (pix >= 0) {
+        if (pix >= 0 && p.out_h) {
+          // 32 consecutive columns of this pixel's row, as bf16 (out_pitch and Npb are multiples of 8)
+          __nv_bfloat16 *hrow = p.out_h + ((size_t)b * npix + pix) * p.out_pitch + nb * p.Npb + n0;
+#pragma unroll
+          for (int j = 0; j < 32; j += 8)
+            if (n0 + j < p.Npb && nb * p.Npb + n0 + j < p.out_pitch)
+              *(uint4 *)(hrow + j) = make_uint4(pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                                                pack_bf16(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
+                                                pack_bf16(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
+                                                pack_bf16(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
+        } else if (pix >= 0) {
 #pragma unroll
           for (int j = 0; j < 32; j++) {
             const int n = nb * p.Npb + n0 + j;
@@ -825,6 +842,68 @@ __global__ void row_sum_final_kernel(const float *__restrict__ part2, int C, flo
   gb[c] = s;
 }
 
+// Weight image of the multiply-first adjoint: rows n = k * Mp + m (slot-major, so that one map slot's M channels
+// are contiguous in the column buffer), columns = source channels; W addressed Wgt[m*sm + ch*sc + k*sk].
+__global__ void premul_weight_image_kernel(const float *__restrict__ w, __nv_bfloat16 *__restrict__ wp, int M, int Mp, int K,
+                                           int CH, int Npb, int nblk, int nchunks, int64_t sm, int64_t sc, int64_t sk) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t total = (int64_t)nblk * nchunks * Npb * kChunk;
+  if (i >= total) return;
+  const int col = (int)(i % kChunk), n = (int)((i / kChunk) % Npb), chunk = (int)((i / ((int64_t)kChunk * Npb)) % nchunks);
+  const int nb = (int)(i / ((int64_t)kChunk * Npb * nchunks));
+  const int ng = nb * Npb + n, k = ng / Mp, m = ng % Mp, ch = chunk * kChunk + col;
+  const float v = (k < K && m < M && ch < CH) ? __ldg(w + m * sm + ch * sc + k * sk) : 0.0f;
+  wp[(((int64_t)nb * nchunks + chunk) * Npb + n) * kChunk + (((col >> 3) ^ (n & 7)) << 3) + (col & 7)] = __float2bfloat16(v);
+}
+
+// Second half of the multiply-first adjoint (the col2im of the reference, through the plan):
+//   Out[b, m, p] = bias[m] + sum_k sum_{e in plan(p*K+k)} w_e * T[b, src_e, k*Mp + m]
+// T is the bf16 column buffer (B, n_src, pitch = K*Mp) written by the GEMM on the source grid.  Thread = one
+// destination pixel and up to 64 output channels (one 128-byte row segment per plan entry).
+__global__ void __launch_bounds__(128)
+plan_gather_rows_kernel(const __nv_bfloat16 *__restrict__ T, const void *__restrict__ plan_blob, const float *__restrict__ bias,
+                        float *__restrict__ out, int K, int M, int Mp, int n_src, int n_dst) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  if (p >= n_dst) return;
+  bool ok;
+  const PlanView<float> pv = plan_view<float>(plan_blob, n_dst * K, ok);
+  const int pitch = K * Mp;
+  const __nv_bfloat16 *tb = T + (size_t)b * n_src * pitch;
+  for (int m0 = 0; m0 < Mp; m0 += 64) {
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; i++) acc[i] = 0.0f;
+    if (ok) {
+      int e1 = __ldg(pv.offsets + p * K);
+      for (int k = 0; k < K; k++) {
+        const int e0 = e1;
+        e1 = __ldg(pv.offsets + p * K + k + 1);
+        for (int e = e0; e < e1; e++) {
+          const float w = __ldg(pv.w + e);
+          const __nv_bfloat16 *row = tb + (size_t)__ldg(pv.src + e) * pitch + k * Mp + m0;
+#pragma unroll
+          for (int v = 0; v < 8; v++) {
+            if (m0 + v * 8 < Mp) {
+              const uint4 q = __ldg((const uint4 *)(row + v * 8));
+              acc[v * 8 + 0] = fmaf(w, bf16_lo(q.x), acc[v * 8 + 0]);
+              acc[v * 8 + 1] = fmaf(w, bf16_hi(q.x), acc[v * 8 + 1]);
+              acc[v * 8 + 2] = fmaf(w, bf16_lo(q.y), acc[v * 8 + 2]);
+              acc[v * 8 + 3] = fmaf(w, bf16_hi(q.y), acc[v * 8 + 3]);
+              acc[v * 8 + 4] = fmaf(w, bf16_lo(q.z), acc[v * 8 + 4]);
+              acc[v * 8 + 5] = fmaf(w, bf16_hi(q.z), acc[v * 8 + 5]);
+              acc[v * 8 + 6] = fmaf(w, bf16_lo(q.w), acc[v * 8 + 6]);
+              acc[v * 8 + 7] = fmaf(w, bf16_hi(q.w), acc[v * 8 + 7]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 64; i++)
+      if (m0 + i < M) out[((size_t)b * M + m0 + i) * n_dst + p] = acc[i] + (bias ? __ldg(bias + m0 + i) : 0.0f);
+  }
+}
+
 // gw[n*sn + ch*sc + slot*sk] = sum over splits (in order) of partial[split][n][column of (slot, ch)].
 __global__ void tc_dw_reduce_kernel(const float *__restrict__ partial, int splits, int rows_total, int ncols_total, int Nout,
                                     int CH, int Cp, int K, int64_t sn, int64_t sc, int64_t sk, float *__restrict__ gw) {
@@ -895,10 +974,62 @@ void launch_gemm(const TcParams &p, int grid, size_t smem, cudaStream_t st) {
   tc_gemm_kernel<MODE, NT><<<grid, kThreads, smem, st>>>(p);
 }
 
+// ---- multiply-first adjoint -------------------------------------------------------------------------
+// When the destination grid of an adjoint (conv dInput, transposed conv forward) is several times larger than the
+// source grid (the map down-samples), gathering per destination pixel repeats the channel contraction for every
+// destination pixel.  It is cheaper to contract first on the small grid - a dense tcgen05 GEMM that writes the
+// bf16 column buffer T[b, o, k*Mp + m] - and then to run the plan gather over rows of T (the reference's own
+// order: GEMM, then mapped_col2im, src/cpp/mapped_convolution_layer.cpp:69-86).
+struct PremulGeometry {
+  Geometry g;     // of the dense GEMM: one slot, CH channels, N = K * Mp
+  int Mp;
+  size_t t_bytes;
+  bool use;
+};
+
+PremulGeometry premul_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t M, int64_t n_dst) {
+  PremulGeometry q{};
+  q.Mp = (int)align_up((size_t)M, 8);
+  q.g = geometry(B, CH, SHW, 1, 0, SPH_NEAREST, K * q.Mp, true);
+  q.t_bytes = align_up((size_t)(B * SHW) * K * q.Mp * 2, 256);
+  q.use = q.g.ok && n_dst >= 3 * SHW && q.t_bytes <= ((size_t)8 << 30) && CH >= 32;
+  return q;
+}
+
+int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan, int64_t CH, int64_t SH, int64_t SW,
+                      int64_t K, int64_t GH, int64_t GW, const void *wgt, int64_t sm_, int64_t sc, int64_t sk, const void *bias,
+                      void *out, int64_t M, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st) {
+  const Geometry &g = q.g;
+  if (!ws || ws_bytes < 256 + g.xh_bytes + g.wp_bytes + q.t_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  int *status = (int *)ws;
+  __nv_bfloat16 *xh = (__nv_bfloat16 *)((char *)ws + 256);
+  __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
+  __nv_bfloat16 *T = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes + g.wp_bytes);
+  if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
+  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st);
+  const int64_t wtotal = (int64_t)g.nblk * g.nchunks * g.Npb * kChunk;
+  premul_weight_image_kernel<<<cdiv(wtotal, 256), 256, 0, st>>>((const float *)wgt, wp, (int)M, q.Mp, (int)K, (int)CH, g.Npb, g.nblk,
+                                                                g.nchunks, sm_, sc, sk);
+  TcParams p{};
+  p.g = Gather{xh, nullptr, nullptr, nullptr, g.Cp, (int)SH, (int)SW, 1, 0, (int)SH, (int)SW, SPH_NEAREST, 1};
+  p.wp = wp; p.bias = nullptr; p.out = nullptr; p.out_h = T; p.out_pitch = (int)(K * q.Mp); p.status = status;
+  p.B = (int)B; p.Nout = (int)(K * q.Mp); p.Npb = g.Npb; p.nblk = g.nblk; p.nchunks = g.nchunks;
+  p.tiles_x = cdiv(SW, kTW); p.tiles_y = cdiv(SH, kTH); p.stages = g.stages;
+  const int64_t tiles = (int64_t)B * p.tiles_x * p.tiles_y * g.nblk;
+  launch_gemm<MODE_DIRECT, 1>(p, (int)(tiles < sm_count() ? tiles : sm_count()), g.smem, st);
+  plan_gather_rows_kernel<<<dim3(cdiv(GH * GW, 128), (unsigned)B), 128, 0, st>>>(T, plan, (const float *)bias, (float *)out, (int)K,
+                                                                                (int)M, q.Mp, (int)(SH * SW), (int)(GH * GW));
+  return launch_status(4);
+}
+
 // Out[b,n,pix] (+bias) on the tensor cores.  src is (B,CH,SH,SW) float32; the GEMM pixels are the (GH,GW) grid.
 int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, const void *plan, int64_t CH, int64_t SH,
             int64_t SW, int64_t K, int64_t P, int64_t GH, int64_t GW, int interp, const void *wgt, int64_t sn, int64_t sc,
             int64_t sk, const void *bias, void *out, int64_t Nout, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st) {
+  if (use_plan) {
+    const PremulGeometry q = premul_geometry(B, CH, SH * SW, K, Nout, GH * GW);
+    if (q.use) return tc_adjoint_premul(q, src, plan, CH, SH, SW, K, GH, GW, wgt, sn, sc, sk, bias, out, Nout, B, ws, ws_bytes, st);
+  }
   const Geometry g = geometry(B, CH, SH * SW, K, P, interp, Nout, !use_plan);
   if (!g.ok)  // shapes the tile kernel does not cover run on the exact SIMT kernels instead
     return simt_gemm<float>(use_plan, src, map, iw, plan, CH, SH, SW, K, P, GH * GW, interp, wgt, sn, sc, sk, bias, out, Nout, B, st);
@@ -925,7 +1056,13 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
   return launch_status(3);
 }
 
-size_t gemm_ws(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int interp, int64_t Nout, bool direct) {
+// n_dst > 0: plan mode with that many destination pixels (may select the multiply-first adjoint)
+size_t gemm_ws(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int interp, int64_t Nout, bool direct,
+               int64_t n_dst = 0) {
+  if (!direct) {
+    const PremulGeometry q = premul_geometry(B, CH, SHW, K, Nout, n_dst);
+    if (q.use) return 256 + q.g.xh_bytes + q.g.wp_bytes + q.t_bytes;
+  }
   const Geometry g = geometry(B, CH, SHW, K, P, interp, Nout, direct);
   return g.ok ? 256 + g.xh_bytes + g.wp_bytes : 0;
 }
@@ -1032,9 +1169,9 @@ size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t 
                           int64_t K, int64_t P, int interp) {
   switch (op) {
     case SPH_CONV_FORWARD: return gemm_ws(B, Cin, IH * IW, K, P, interp, Cout, true);
-    case SPH_CONV_BACKWARD_INPUT: return gemm_ws(B, Cout, OH * OW, K, 0, 0, Cin, false);
+    case SPH_CONV_BACKWARD_INPUT: return gemm_ws(B, Cout, OH * OW, K, 0, 0, Cin, false, IH * IW);
     case SPH_CONV_BACKWARD_WEIGHT: return dw_ws(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
-    case SPH_TCONV_FORWARD: return gemm_ws(B, Cin, IH * IW, K, 0, 0, Cout, false);
+    case SPH_TCONV_FORWARD: return gemm_ws(B, Cin, IH * IW, K, 0, 0, Cout, false, OH * OW);
     case SPH_TCONV_BACKWARD_INPUT: return gemm_ws(B, Cout, OH * OW, K, P, interp, Cin, true);
     case SPH_TCONV_BACKWARD_WEIGHT: return dw_ws(B, Cout, OH * OW, K, P, interp, Cin, IH, IW, Cout);
     default: return 0;

@@ -49,6 +49,8 @@ CASES = [
     (5, 2, 64, 128, 16, 32, 16, 32, 9, 0, 4, False),     # weighted, 4 points, nearest (config-3 class)
     (6, 1, 24, 40, 12, 20, 9, 13, 3, 1, 2, False),       # odd channel counts, weighted bilinear
     (7, 1, 72, 272, 8, 16, 8, 16, 2, 0, 0, False),       # Cout > 256 (two N blocks), Cin padded to 128
+    (8, 2, 32, 64, 32, 64, 16, 32, 9, 1, 0, True),       # stride-2 map: the adjoints multiply first on the small grid
+    (9, 1, 40, 48, 20, 36, 7, 11, 5, 1, 0, False),       # down-sampling random map, ragged sizes, multiply-first adjoint
 ]
 
 
@@ -67,7 +69,7 @@ def test_conv_forward_and_backward_bf16(case):
     _close(gb, rgb, "grad_bias")
 
 
-@pytest.mark.parametrize("case", CASES[:1] + CASES[3:6], ids=lambda c: "s%d" % c[0])
+@pytest.mark.parametrize("case", CASES[:1] + CASES[3:6] + CASES[7:], ids=lambda c: "s%d" % c[0])
 def test_transposed_conv_bf16(case):
     from _gpu_impl import CApi
     seed, B, Cin, Cout, IH, IW, OH, OW, K, interp, P, gn = case
