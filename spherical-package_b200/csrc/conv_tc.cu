@@ -506,8 +506,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
 // weight-gradient kernel
 // =================================================================================================
 constexpr int kDwPix = 64, kDwTH = 4;      // pixels per reduction step (a 4x16 block)
-constexpr int kDwGroup = 4;                // chunks (of 64 columns) per CTA: N <= 256
-constexpr int kDwColBytes = kDwGroup * kDwPix * 128;   // 32 KB of gathered columns per stage
+// A CTA accumulates GRP chunks (of 64 columns) for MBS = 8 / GRP row blocks (of 128 rows): 512 TMEM columns either
+// way.  GRP = 4 holds two row blocks and is what the host selects; GRP = 8 (one row block, more map slots per step)
+// is kept for experiments.
 constexpr int kDwGtBytes = 128 * 128;                  // one 128-row x 64-pixel gradient tile image
 constexpr int kDwMaxTapBytes = 20 * 1024;
 
@@ -527,20 +528,22 @@ struct DwSmem {
   volatile int *abort_flag;
 };
 
-inline size_t dw_stage_bytes(int mbs) { return kDwColBytes + (size_t)mbs * kDwGtBytes; }
-inline size_t dw_smem_bytes(int stages, int mbs, int tap_rows, int nt) {
-  return 1024 + stages * dw_stage_bytes(mbs) + 2 * (size_t)tap_rows * kDwPix * nt * sizeof(Tap) + 8 * (2 * stages + 1) + 16;
+inline size_t dw_stage_bytes(int grp, int mbs) { return (size_t)grp * kDwPix * 128 + (size_t)mbs * kDwGtBytes; }
+inline size_t dw_smem_bytes(int stages, int grp, int mbs, int tap_rows, int nt) {
+  return 1024 + stages * dw_stage_bytes(grp, mbs) + 2 * (size_t)tap_rows * kDwPix * nt * sizeof(Tap) + 8 * (2 * stages + 1) + 16;
 }
 
-template <int NT>
+template <int NT, int GRP>
 __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
+  constexpr int MBS = 8 / GRP;
+  constexpr int kDwColBytes = GRP * kDwPix * 128;  // gathered columns per stage
   extern __shared__ uint8_t smem_raw[];
   const Gather &g = p.g;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int S = p.stages;
-  const int grp = blockIdx.x, split = blockIdx.y, mb0 = blockIdx.z * 2;
-  const int mbs = min(2, p.mbs_total - mb0);
-  const int chunk0 = grp * kDwGroup, ncg = min(kDwGroup, p.nchunks - chunk0);
+  const int grp = blockIdx.x, split = blockIdx.y, mb0 = blockIdx.z * MBS;
+  const int mbs = min(MBS, p.mbs_total - mb0);
+  const int chunk0 = grp * GRP, ncg = min(GRP, p.nchunks - chunk0);
   const size_t stage_bytes = kDwColBytes + (size_t)mbs * kDwGtBytes;
 
   DwSmem sm;
@@ -588,7 +591,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
     for (int mb = 0; mb < mbs; mb++) {
       const int row = (mb0 + mb) * 128 + warp * 32 + lane;
       float *prow = p.partial + ((size_t)split * p.mbs_total * 128 + row) * ncols_total + (size_t)chunk0 * kChunk;
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + mb * 256;
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + mb * (GRP / 4) * 256;
       for (int n0 = 0; n0 < ncg * kChunk; n0 += 32) {
         uint32_t r[32];
         if (have) {
@@ -608,7 +611,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
   } else if (warp == kEpilogueWarps) {
     // ---------------- MMA issuer ----------------
     if (lane == 0 && step_hi > step_lo) {
-      const uint32_t idesc = idesc_bf16(128, ncg * kChunk, 0, 1);  // A (gradient) K-major, B (columns) MN-major
+      // A (gradient) K-major, B (columns) MN-major; the column group is issued in halves of at most 4 chunks (N <= 256)
+      const int nhalves = (ncg + 3) / 4;
+      const uint32_t idesc0 = idesc_bf16(128, min(4, ncg) * kChunk, 0, 1);
+      const uint32_t idesc1 = idesc_bf16(128, max(1, ncg - 4) * kChunk, 0, 1);
       bool alive = true;
       int it = 0;
       Ring ring;
@@ -617,12 +623,15 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         if (!mbar_wait(sm.full + s, ring.ph, sm.abort_flag)) { alive = false; break; }
         tc_fence_after();
         uint8_t *st = sm.stage + (size_t)s * stage_bytes;
-        const uint64_t b0 = smem_desc_sw128(smem_u32(st), kDwPix * 128, 1024);
         for (int mb = 0; mb < mbs; mb++) {
           const uint64_t a0 = smem_desc_sw128(smem_u32(st + kDwColBytes + (size_t)mb * kDwGtBytes), 16, 1024);
+          for (int h = 0; h < nhalves; h++) {
+            const uint64_t b0 = smem_desc_sw128(smem_u32(st + h * 4 * (kDwPix * 128)), kDwPix * 128, 1024);
+            const uint32_t d = tmem_base + (mb * (GRP / 4) + h) * 256;
 #pragma unroll
-          for (int ks = 0; ks < kDwPix / 16; ks++)
-            umma_bf16(tmem_base + mb * 256, a0 + 2 * ks, b0 + (uint64_t)(ks * 16 * 128 >> 4), idesc, (it | ks) != 0);
+            for (int ks = 0; ks < kDwPix / 16; ks++)
+              umma_bf16(d, a0 + 2 * ks, b0 + (uint64_t)(ks * 16 * 128 >> 4), h ? idesc1 : idesc0, (it | ks) != 0);
+          }
         }
         umma_commit(sm.empty + s);
       }
@@ -638,10 +647,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
     chunk_vec(g.Cp, g.K, chunk0, 0, slot_base, dummy);
     // The CTA's column group is fixed, so each thread's (slot, first channel, table row) per chunk of the group
     // is computed once.
-    int g_coff[kDwGroup], g_trow[kDwGroup];
-    bool g_ok[kDwGroup];
+    int g_coff[GRP], g_trow[GRP];
+    bool g_ok[GRP];
 #pragma unroll
-    for (int gi = 0; gi < kDwGroup; gi++) {
+    for (int gi = 0; gi < GRP; gi++) {
       int slot = g.K, c0 = 0;
       if (gi < ncg) chunk_vec(g.Cp, g.K, chunk0 + gi, pt & 7, slot, c0);
       g_ok[gi] = slot < g.K;
@@ -696,7 +705,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         const int v = pt & 7, pl = pt >> 3;
         uint8_t *dst0 = st + pl * 128 + ((v ^ (pl & 7)) << 4);
 #pragma unroll
-        for (int gi = 0; gi < kDwGroup; gi += 2) {
+        for (int gi = 0; gi < GRP; gi += 2) {
           if (gi >= ncg) break;
           Acc8 a0, a1;
           acc_zero(a0);
@@ -1068,7 +1077,7 @@ size_t gemm_ws(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int int
 }
 
 struct DwGeometry {
-  int Cp, nchunks, ngroups, mbs_total, nt, stages, splits, tap_rows, tiles_x, tiles_y;
+  int Cp, nchunks, ngroups, mbs_total, nt, stages, splits, tap_rows, tiles_x, tiles_y, grp;
   size_t xh_bytes, gt_bytes, partial_bytes, bias_bytes, smem;
   bool ok;
 };
@@ -1078,20 +1087,24 @@ DwGeometry dw_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P,
   DwGeometry d{};
   d.Cp = padded_channels(CH);
   d.nchunks = num_chunks(d.Cp, (int)K);
-  d.ngroups = (d.nchunks + kDwGroup - 1) / kDwGroup;
+  // GRP = 8 (one row block, twice the slots per step) leaves room for only two pipeline stages and measured
+  // 1.9x slower on the encoder's layers than GRP = 4 with three stages, so it is not selected.
+  d.grp = 4;
+  d.ngroups = (d.nchunks + d.grp - 1) / d.grp;
   d.mbs_total = (int)((Nout + 127) / 128);
   d.nt = (int)((P > 0 ? P : 1) * (interp == SPH_NEAREST ? 1 : 4));
-  d.tap_rows = d.Cp >= 64 ? kDwGroup : (int)std::min<int64_t>(K, (int64_t)kDwGroup * (64 / d.Cp));
+  d.tap_rows = d.Cp >= 64 ? d.grp : (int)std::min<int64_t>(K, (int64_t)d.grp * (64 / d.Cp));
   d.tiles_x = cdiv(GW, kTW);
   d.tiles_y = cdiv(GH, kDwTH);
-  const int mbs = d.mbs_total >= 2 ? 2 : 1;
+  const int mbs_cta = 8 / d.grp;
+  const int mbs = d.mbs_total >= mbs_cta ? mbs_cta : 1;
   d.ok = (size_t)d.tap_rows * kDwPix * d.nt * sizeof(Tap) <= (size_t)kDwMaxTapBytes;
   d.stages = 4;
-  while (d.stages > 2 && dw_smem_bytes(d.stages, mbs, d.tap_rows, d.nt) > (size_t)kSmemLimit) d.stages--;
-  d.smem = dw_smem_bytes(d.stages, mbs, d.tap_rows, d.nt);
+  while (d.stages > 2 && dw_smem_bytes(d.stages, d.grp, mbs, d.tap_rows, d.nt) > (size_t)kSmemLimit) d.stages--;
+  d.smem = dw_smem_bytes(d.stages, d.grp, mbs, d.tap_rows, d.nt);
   if (d.smem > (size_t)kSmemLimit) d.ok = false;
   const int64_t steps = B * d.tiles_x * d.tiles_y;
-  const int zdim = (d.mbs_total + 1) / 2;
+  const int zdim = (d.mbs_total + mbs_cta - 1) / mbs_cta;
   int64_t s = sm_count() / (d.ngroups * zdim);
   if (s < 1) s = 1;
   if (s > steps) s = steps;
@@ -1105,10 +1118,15 @@ DwGeometry dw_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P,
   return d;
 }
 
+template <int NT, int GRP>
+void launch_dw_g(const DwParams &p, dim3 grid, size_t smem, cudaStream_t st) {
+  cudaFuncSetAttribute(tc_dw_kernel<NT, GRP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  tc_dw_kernel<NT, GRP><<<grid, kThreads, smem, st>>>(p);
+}
 template <int NT>
-void launch_dw(const DwParams &p, dim3 grid, size_t smem, cudaStream_t st) {
-  cudaFuncSetAttribute(tc_dw_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  tc_dw_kernel<NT><<<grid, kThreads, smem, st>>>(p);
+void launch_dw(const DwParams &p, int grp, dim3 grid, size_t smem, cudaStream_t st) {
+  if (grp == 8) launch_dw_g<NT, 8>(p, grid, smem, st);
+  else launch_dw_g<NT, 4>(p, grid, smem, st);
 }
 
 // gw[n,ch,slot] = sum_{b,pix} A[b,n,pix] * im2col(src)[b,pix,(slot,ch)]; gb = sum of gbias_src over batch and pixels.
@@ -1141,10 +1159,10 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
   p.gt = gt; p.partial = partial; p.status = status;
   p.B = (int)B; p.mbs_total = d.mbs_total; p.nchunks = d.nchunks; p.tiles_x = d.tiles_x; p.tiles_y = d.tiles_y;
   p.splits = d.splits; p.stages = d.stages; p.tap_rows = d.tap_rows;
-  dim3 grid(d.ngroups, d.splits, (d.mbs_total + 1) / 2);
-  if (d.nt == 4) launch_dw<4>(p, grid, d.smem, st);
-  else if (d.nt == 1) launch_dw<1>(p, grid, d.smem, st);
-  else launch_dw<0>(p, grid, d.smem, st);
+  dim3 grid(d.ngroups, d.splits, (d.mbs_total + 8 / d.grp - 1) / (8 / d.grp));
+  if (d.nt == 4) launch_dw<4>(p, d.grp, grid, d.smem, st);
+  else if (d.nt == 1) launch_dw<1>(p, d.grp, grid, d.smem, st);
+  else launch_dw<0>(p, d.grp, grid, d.smem, st);
   tc_dw_reduce_kernel<<<cdiv(Nout * CH * K, 256), 256, 0, st>>>(partial, d.splits, d.mbs_total * 128, d.nchunks * kChunk, (int)Nout,
                                                                (int)CH, d.Cp, (int)K, sn, sc, sk, (float *)gw);
   note_launches(4);
