@@ -162,12 +162,16 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
   constexpr int kSdwPix = SdwPix<T>::value;
   __shared__ T As[kSdwPix][64 + 1];
   __shared__ T Cs[kSdwPix][kSmallJ + 1];
-  const int tid = threadIdx.x, tm = tid >> 4, tj = tid & 15;  // 16 x 16 threads: 4 rows x 2 columns each
+  // four quarters of 64 threads: each quarter takes every fourth staged pixel and holds an 8 x 4 register tile
+  // per thread (rows tm + 8 i, columns tj + 8 j); the quarters' sums are kept as separate partials
+  const int tid = threadIdx.x, qtr = tid >> 6, tm = (tid & 63) >> 3, tj = tid & 7;
   const int m0 = blockIdx.y * 64, splits = gridDim.x, J = CH * K;
   const int chunks = (npix + kSdwChunk - 1) / kSdwChunk;
-  T acc[4][2];
+  T acc[8][4];
 #pragma unroll
-  for (int i = 0; i < 4; i++) acc[i][0] = acc[i][1] = T(0);
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = T(0);
   for (int unit = blockIdx.x; unit < B * chunks; unit += splits) {
     const int b = unit / chunks, pbase = (unit % chunks) * kSdwChunk, pend = min(npix, pbase + kSdwChunk);
     for (int p0 = pbase; p0 < pend; p0 += kSdwPix) {
@@ -190,25 +194,29 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
         As[pl][ml] = (pix < pend && m < M) ? __ldg(A + ((size_t)b * M + m) * npix + pix) : T(0);
       }
       __syncthreads();
-#pragma unroll 4
-      for (int pl = 0; pl < kSdwPix; pl++) {
-        const T c0 = Cs[pl][tj], c1 = Cs[pl][tj + 16];
+#pragma unroll 2
+      for (int pl = qtr; pl < kSdwPix; pl += 4) {
+        T c[4], a[8];
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const T a = As[pl][tm + 16 * i];
-          acc[i][0] += a * c0;
-          acc[i][1] += a * c1;
-        }
+        for (int j = 0; j < 4; j++) c[j] = Cs[pl][tj + 8 * j];
+#pragma unroll
+        for (int i = 0; i < 8; i++) a[i] = As[pl][tm + 8 * i];
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+          for (int j = 0; j < 4; j++) acc[i][j] += a[i] * c[j];
       }
       __syncthreads();
     }
   }
+  const size_t prow = (size_t)blockIdx.x * 4 + qtr;  // partial index: (split, quarter)
 #pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const int m = m0 + tm + 16 * i;
+  for (int i = 0; i < 8; i++) {
+    const int m = m0 + tm + 8 * i;
     if (m >= M) continue;
-    if (tj < J) partial[((size_t)blockIdx.x * M + m) * J + tj] = acc[i][0];
-    if (tj + 16 < J) partial[((size_t)blockIdx.x * M + m) * J + tj + 16] = acc[i][1];
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+      if (tj + 8 * j < J) partial[(prow * M + m) * J + tj + 8 * j] = acc[i][j];
   }
 }
 
@@ -231,7 +239,7 @@ size_t small_premul_workspace(int64_t B, int64_t M, int64_t K, int64_t n_src, si
 }
 
 size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts) {
-  return align_up(ts * (size_t)(small_dw_splits(B, npix, M) * M * CH * K), 256) + simt_bias_workspace(Cbias, ts);
+  return align_up(ts * (size_t)(4 * small_dw_splits(B, npix, M) * M * CH * K), 256) + simt_bias_workspace(Cbias, ts);
 }
 
 template <typename T>
@@ -271,7 +279,7 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
   if (!ws || ws_bytes < small_dw_workspace(B, npix, M, CH, K, Cbias, sizeof(T))) return SPH_ERR_WORKSPACE_TOO_SMALL;
   const int splits = small_dw_splits(B, npix, M);
   T *partial = (T *)ws;
-  void *bias_ws = (char *)ws + align_up(sizeof(T) * (size_t)(splits * M * CH * K), 256);
+  void *bias_ws = (char *)ws + align_up(sizeof(T) * (size_t)(4 * splits * M * CH * K), 256);
   dim3 grid(splits, cdiv(M, 64));
 #define SPH_SMALL_DW(W)                                                                                               \
   small_dw_kernel<T, INTERP, W><<<grid, 256, 0, st>>>((const T *)A, (const T *)src, (const T *)map, (const T *)iw, (int)CH, \
@@ -281,7 +289,7 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
     else SPH_SMALL_DW(false);
   });
 #undef SPH_SMALL_DW
-  const int rc = simt_dw_reduce<T>(partial, splits, M, CH * K, K, sm, sc, sk, gw, st);
+  const int rc = simt_dw_reduce<T>(partial, 4 * splits, M, CH * K, K, sm, sc, sk, gw, st);
   if (rc != SPH_OK) return rc;
   note_launches(1);
   return simt_bias_grad<T>(gbias_src, B, Cbias, nbias, gb, bias_ws, st);
