@@ -169,16 +169,36 @@ conv_dw_kernel(ColSrc<T> cs, const T *__restrict__ A, int M, int B, T *__restric
   }
 }
 
-// gw[m,ch,k] = sum over splits, in split order (deterministic).
+// gw[m,ch,k] = sum over splits, in a fixed order (deterministic): 32 outputs per block, sixteen threads per
+// output each summing every sixteenth split, then the sixteen sums in order.
+constexpr int kReduceLanes = 16;
 template <typename T>
-__global__ void dw_reduce_kernel(const T *__restrict__ partial, int splits, int M, int CHK, int K, int64_t sm, int64_t sc,
-                                 int64_t sk, T *__restrict__ gw) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= M * CHK) return;
-  const int m = i / CHK, kk = i % CHK;
-  T s = T(0);
-  for (int z = 0; z < splits; z++) s += partial[(size_t)z * M * CHK + i];
-  gw[m * sm + (kk / K) * sc + (kk % K) * sk] = s;
+__global__ void __launch_bounds__(32 * kReduceLanes) dw_reduce_kernel(const T *__restrict__ partial, int splits, int M, int CHK,
+                                                                      int K, int64_t sm, int64_t sc, int64_t sk,
+                                                                      T *__restrict__ gw) {
+  __shared__ T red[kReduceLanes][32];
+  const int i = blockIdx.x * 32 + threadIdx.x, zl = threadIdx.y;
+  const size_t n = (size_t)M * CHK;
+  T s0 = T(0), s1 = T(0), s2 = T(0), s3 = T(0);
+  if (i < M * CHK) {
+    int z = zl;
+    for (; z + 3 * kReduceLanes < splits; z += 4 * kReduceLanes) {
+      s0 += partial[(size_t)z * n + i];
+      s1 += partial[(size_t)(z + kReduceLanes) * n + i];
+      s2 += partial[(size_t)(z + 2 * kReduceLanes) * n + i];
+      s3 += partial[(size_t)(z + 3 * kReduceLanes) * n + i];
+    }
+    for (; z < splits; z += kReduceLanes) s0 += partial[(size_t)z * n + i];
+  }
+  red[zl][threadIdx.x] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (zl == 0 && i < M * CHK) {
+    T s = red[0][threadIdx.x];
+#pragma unroll
+    for (int j = 1; j < kReduceLanes; j++) s += red[j][threadIdx.x];
+    const int m = i / CHK, kk = i % CHK;
+    gw[m * sm + (kk / K) * sc + (kk % K) * sk] = s;
+  }
 }
 
 // Bias gradient: sum of g over batch and pixels per channel, two fixed-order stages.
@@ -216,7 +236,7 @@ __global__ void bias_final_kernel(const T *__restrict__ part, int C, T *__restri
 template <typename T>
 int simt_dw_reduce(const void *partial, int splits, int64_t M, int64_t CHK, int64_t K, int64_t sm, int64_t sc, int64_t sk,
                    void *gw, cudaStream_t st) {
-  dw_reduce_kernel<T><<<cdiv(M * CHK, 256), 256, 0, st>>>((const T *)partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw);
+  dw_reduce_kernel<T><<<cdiv(M * CHK, 32), dim3(32, kReduceLanes), 0, st>>>((const T *)partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw);
   return launch_status();
 }
 template int simt_dw_reduce<float>(const void *, int, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, void *, cudaStream_t);
@@ -289,7 +309,7 @@ int simt_dw(const void *A, const void *src, const void *map, const void *iw, int
     if (P > 0) conv_dw_kernel<T, INTERP, true><<<grid, 256, 0, st>>>(cs, (const T *)A, (int)M, (int)B, partial);
     else conv_dw_kernel<T, INTERP, false><<<grid, 256, 0, st>>>(cs, (const T *)A, (int)M, (int)B, partial);
   });
-  dw_reduce_kernel<T><<<cdiv(M * CHK, 256), 256, 0, st>>>(partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw);
+  dw_reduce_kernel<T><<<cdiv(M * CHK, 32), dim3(32, kReduceLanes), 0, st>>>(partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw);
   bias_partial_kernel<T><<<dim3((unsigned)Cbias, kBiasSplits), 256, 0, st>>>((const T *)gbias_src, (int)B, (int)Cbias, (int)nbias, bpart);
   bias_final_kernel<T><<<cdiv(Cbias, 128), 128, 0, st>>>(bpart, (int)Cbias, (T *)gb);
   return launch_status(4);

@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(256)
 small_fwd_kernel(const T *__restrict__ src, const T *__restrict__ map, const T *__restrict__ iw, const T *__restrict__ wgt,
                  int64_t sm, int64_t sc, int64_t sk, const T *__restrict__ bias, T *__restrict__ out, int CH, int K, int P,
                  int SH, int SW, int npix, int M) {
-  extern __shared__ unsigned char small_smem[];
+  extern __shared__ __align__(16) unsigned char small_smem[];
   T *ws = (T *)small_smem;
   for (int i = threadIdx.x; i < M * kSmallJ; i += blockDim.x) {
     const int m = i / kSmallJ, j = i % kSmallJ;
@@ -78,7 +78,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 small_premul_kernel(const T *__restrict__ src, const T *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk,
                     T *__restrict__ tbuf, int CH, int K, int M, int n_src) {
-  extern __shared__ unsigned char small_smem[];
+  extern __shared__ __align__(16) unsigned char small_smem[];
   T *ws = (T *)small_smem;  // [CH][kSmallJ]
   for (int i = threadIdx.x; i < CH * kSmallJ; i += blockDim.x) {
     const int ch = i / kSmallJ, j = i % kSmallJ;
@@ -151,60 +151,111 @@ small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ pl
   }
 }
 
-// dW partial sums: block = (64 rows of A) x (all <= 32 columns) over the pixel chunks of its split.
-constexpr int kSdwChunk = 256;
+// dW partial sums: block = (64 rows of A) x (all <= 32 columns) over its share of the (pixel step, image group)
+// units.  Both operands are staged pixel-contiguous ([row][pixel], the layout A already has in memory), and
+// every thread reads 16-byte pixel vectors of its 8 rows and 4 columns, so one shared-memory load feeds four
+// (two for float64) multiply-adds of each accumulator it touches.  The taps of a pixel step are decoded once
+// into shared memory and reused for all images of the unit's group (the map is the same for every image).
+constexpr int kSdwImages = 8;  // images per unit
 template <typename T> struct SdwPix { static constexpr int value = sizeof(T) == 8 ? 32 : 64; };  // pixels staged per step
+template <typename T> struct alignas(16) SdwVec { T v[16 / sizeof(T)]; };
+template <typename T> struct alignas(16) SdwTaps { Taps<T> t; };  // 16-byte aligned so that it moves as vectors
 
 template <typename T, int INTERP, bool WEIGHTED>
 __global__ void __launch_bounds__(256)
 small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__restrict__ map, const T *__restrict__ iw,
-                int CH, int K, int P, int SH, int SW, int npix, int M, int B, T *__restrict__ partial) {
-  constexpr int kSdwPix = SdwPix<T>::value;
-  __shared__ T As[kSdwPix][64 + 1];
-  __shared__ T Cs[kSdwPix][kSmallJ + 1];
-  // four quarters of 64 threads: each quarter takes every fourth staged pixel and holds an 8 x 4 register tile
+                int CH, int K, int P, int SH, int SW, int npix, int M, int B, T *__restrict__ partial,
+                T *__restrict__ bias_partial) {
+  constexpr int kSdwPix = SdwPix<T>::value, VW = 16 / sizeof(T), kPitch = kSdwPix + VW;
+  // rows 17 words apart (mod 32 banks: 4 apart), so the 16-byte reads of consecutive rows do not collide
+  __shared__ __align__(16) T As[64][kPitch];
+  __shared__ __align__(16) T Cs[kSmallJ][kPitch];
+  extern __shared__ __align__(16) unsigned char small_smem[];
+  SdwTaps<T> *tcache = (SdwTaps<T> *)small_smem;  // [K][kSdwPix] decoded taps of the current pixel step (unweighted maps)
+  // four quarters of 64 threads: each quarter takes every fourth pixel vector and holds an 8 x 4 register tile
   // per thread (rows tm + 8 i, columns tj + 8 j); the quarters' sums are kept as separate partials
   const int tid = threadIdx.x, qtr = tid >> 6, tm = (tid & 63) >> 3, tj = tid & 7;
   const int m0 = blockIdx.y * 64, splits = gridDim.x, J = CH * K;
-  const int chunks = (npix + kSdwChunk - 1) / kSdwChunk;
+  const int steps = (npix + kSdwPix - 1) / kSdwPix, groups = (B + kSdwImages - 1) / kSdwImages;
+  const size_t shw = (size_t)SH * SW;
+  // With bias_partial set (and J < kSmallJ) the first padding column of Col is all ones, so that column of the
+  // product is the row sum of A: the bias gradient when A is grad_output.  Pixels past the end have A = 0.
+  const bool ones = bias_partial != nullptr;
+  for (int e = tid; e < (kSmallJ - J) * kPitch; e += 256) Cs[J + e / kPitch][e % kPitch] = (ones && e < kPitch) ? T(1) : T(0);
   T acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = T(0);
-  for (int unit = blockIdx.x; unit < B * chunks; unit += splits) {
-    const int b = unit / chunks, pbase = (unit % chunks) * kSdwChunk, pend = min(npix, pbase + kSdwChunk);
-    for (int p0 = pbase; p0 < pend; p0 += kSdwPix) {
-      {
-        // thread = (pixel, slot group): slots k = group, group + G, ... of its pixel, all channels
-        constexpr int G = 256 / kSdwPix;
-        const int pl = tid % kSdwPix, grp = tid / kSdwPix, pix = p0 + pl;
-        const T *img = src + (size_t)b * CH * SH * SW;
-        const int PP = WEIGHTED ? P : 1;
-        for (int k = grp; k < K; k += G) {
-          const size_t e = ((size_t)pix * K + k) * PP;
-          for (int c = 0; c < CH; c++)
-            Cs[pl][c * K + k] = pix < pend ? gather_slot<T, INTERP, WEIGHTED>(img + (size_t)c * SH * SW, map + 2 * e, iw + e, P, SH, SW)
-                                           : T(0);
+  for (int unit = blockIdx.x; unit < steps * groups; unit += splits) {
+    const int p0 = (unit / groups) * kSdwPix, b0 = (unit % groups) * kSdwImages, b1 = min(B, b0 + kSdwImages);
+    const int pend = min(npix, p0 + kSdwPix);
+    if (!WEIGHTED) {
+      for (int idx = tid; idx < K * kSdwPix; idx += 256) {
+        const int k = idx / kSdwPix, pix = p0 + idx % kSdwPix;
+        Taps<T> t;
+        if (pix < pend) {
+          const size_t e = (size_t)pix * K + k;
+          decode<T, INTERP>(__ldg(map + 2 * e), __ldg(map + 2 * e + 1), SH, SW, t);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; q++) { t.off[q] = -1; t.w[q] = T(0); }
         }
-        for (int j = J + grp; j < kSmallJ; j += G) Cs[pl][j] = T(0);
-      }
-      for (int e = tid; e < 64 * kSdwPix; e += 256) {
-        const int pl = e % kSdwPix, ml = e / kSdwPix, pix = p0 + pl, m = m0 + ml;
-        As[pl][ml] = (pix < pend && m < M) ? __ldg(A + ((size_t)b * M + m) * npix + pix) : T(0);
+        tcache[idx].t = t;
       }
       __syncthreads();
-#pragma unroll 2
-      for (int pl = qtr; pl < kSdwPix; pl += 4) {
-        T c[4], a[8];
+    }
+    for (int b = b0; b < b1; b++) {
+      const T *img = src + (size_t)b * CH * shw;
+      for (int e = tid; e < 64 * kSdwPix; e += 256) {
+        const int pl = e % kSdwPix, ml = e / kSdwPix, pix = p0 + pl, m = m0 + ml;
+        As[ml][pl] = (pix < pend && m < M) ? __ldg(A + ((size_t)b * M + m) * npix + pix) : T(0);
+      }
+      if (!WEIGHTED) {
+        // gathered columns, three (slot, pixel) items per thread at a time so that their loads overlap
+        for (int base = tid; base < K * kSdwPix; base += 3 * 256) {
+          Taps<T> t[3];
+          int row[3], pl[3];
+          bool ok[3];
 #pragma unroll
-        for (int j = 0; j < 4; j++) c[j] = Cs[pl][tj + 8 * j];
+          for (int r = 0; r < 3; r++) {
+            const int idx = base + r * 256;
+            ok[r] = idx < K * kSdwPix;
+            row[r] = ok[r] ? idx / kSdwPix : 0;
+            pl[r] = idx % kSdwPix;
+            t[r] = tcache[ok[r] ? idx : 0].t;
+          }
+          for (int c = 0; c < CH; c++) {
+            T v[3];
 #pragma unroll
-        for (int i = 0; i < 8; i++) a[i] = As[pl][tm + 8 * i];
+            for (int r = 0; r < 3; r++) v[r] = gather<T, INTERP>(img + (size_t)c * shw, t[r]);
 #pragma unroll
-        for (int i = 0; i < 8; i++)
+            for (int r = 0; r < 3; r++)
+              if (ok[r]) Cs[c * K + row[r]][pl[r]] = v[r];
+          }
+        }
+      } else {
+        for (int idx = tid; idx < K * kSdwPix; idx += 256) {
+          const int k = idx / kSdwPix, pl = idx % kSdwPix, pix = p0 + pl;
+          const size_t e = ((size_t)pix * K + k) * P;
+          for (int c = 0; c < CH; c++)
+            Cs[c * K + k][pl] = pix < pend ? gather_slot<T, INTERP, true>(img + (size_t)c * shw, map + 2 * e, iw + e, P, SH, SW) : T(0);
+        }
+      }
+      __syncthreads();
+#pragma unroll 1
+      for (int pv = qtr; pv < kSdwPix / VW; pv += 4) {
+        SdwVec<T> a[8], c[4];
 #pragma unroll
-          for (int j = 0; j < 4; j++) acc[i][j] += a[i] * c[j];
+        for (int i = 0; i < 8; i++) a[i] = *(const SdwVec<T> *)&As[tm + 8 * i][pv * VW];
+#pragma unroll
+        for (int j = 0; j < 4; j++) c[j] = *(const SdwVec<T> *)&Cs[tj + 8 * j][pv * VW];
+#pragma unroll
+        for (int x = 0; x < VW; x++)
+#pragma unroll
+          for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[i][j] += a[i].v[x] * c[j].v[x];
       }
       __syncthreads();
     }
@@ -215,8 +266,10 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
     const int m = m0 + tm + 8 * i;
     if (m >= M) continue;
 #pragma unroll
-    for (int j = 0; j < 4; j++)
+    for (int j = 0; j < 4; j++) {
       if (tj + 8 * j < J) partial[(prow * M + m) * J + tj + 8 * j] = acc[i][j];
+      else if (ones && tj + 8 * j == J) bias_partial[prow * M + m] = acc[i][j];
+    }
   }
 }
 
@@ -225,8 +278,9 @@ bool small_ok(int64_t side_channels, int64_t K, int64_t wide_channels, size_t ts
   return side_channels * K <= kSmallJ && wide_channels * kSmallJ * (int64_t)ts <= 48 * 1024;
 }
 
-static int small_dw_splits(int64_t B, int64_t npix, int64_t M) {
-  const int64_t units = B * ((npix + kSdwChunk - 1) / kSdwChunk), mblocks = (M + 63) / 64;
+static int small_dw_splits(int64_t B, int64_t npix, int64_t M, size_t ts) {
+  const int64_t pix = ts == 8 ? 32 : 64;
+  const int64_t units = ((B + kSdwImages - 1) / kSdwImages) * ((npix + pix - 1) / pix), mblocks = (M + 63) / 64;
   int64_t s = (4 * 148 + mblocks - 1) / mblocks;
   if (s > units) s = units;
   if (s < 1) s = 1;
@@ -239,7 +293,8 @@ size_t small_premul_workspace(int64_t B, int64_t M, int64_t K, int64_t n_src, si
 }
 
 size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts) {
-  return align_up(ts * (size_t)(4 * small_dw_splits(B, npix, M) * M * CH * K), 256) + simt_bias_workspace(Cbias, ts);
+  const size_t parts = 4 * (size_t)small_dw_splits(B, npix, M, ts);
+  return align_up(ts * parts * M * CH * K, 256) + align_up(ts * parts * M, 256) + simt_bias_workspace(Cbias, ts);
 }
 
 template <typename T>
@@ -277,13 +332,23 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
              int64_t P, int64_t npix, int interp, int64_t M, int64_t B, void *gw, int64_t sm, int64_t sc, int64_t sk,
              const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st) {
   if (!ws || ws_bytes < small_dw_workspace(B, npix, M, CH, K, Cbias, sizeof(T))) return SPH_ERR_WORKSPACE_TOO_SMALL;
-  const int splits = small_dw_splits(B, npix, M);
+  const int splits = small_dw_splits(B, npix, M, sizeof(T));
   T *partial = (T *)ws;
-  void *bias_ws = (char *)ws + align_up(sizeof(T) * (size_t)(4 * splits * M * CH * K), 256);
+  T *bias_partial = (T *)((char *)ws + align_up(sizeof(T) * (size_t)(4 * splits * M * CH * K), 256));
+  void *bias_ws = (char *)bias_partial + align_up(sizeof(T) * (size_t)(4 * splits * M), 256);
+  // conv dW: the tensor whose rows are staged is also the one whose channel sums give the bias gradient
+  const bool fuse_bias = gbias_src == A && Cbias == M && nbias == npix && CH * K < kSmallJ;
   dim3 grid(splits, cdiv(M, 64));
-#define SPH_SMALL_DW(W)                                                                                               \
-  small_dw_kernel<T, INTERP, W><<<grid, 256, 0, st>>>((const T *)A, (const T *)src, (const T *)map, (const T *)iw, (int)CH, \
-                                                      (int)K, (int)P, (int)SH, (int)SW, (int)npix, (int)M, (int)B, partial)
+  // tap cache of one pixel step (unweighted maps only)
+  const size_t tap_smem = P > 0 ? 0 : (size_t)K * SdwPix<T>::value * sizeof(SdwTaps<T>);
+#define SPH_SMALL_DW(W)                                                                                                  \
+  do {                                                                                                                   \
+    cudaFuncSetAttribute(small_dw_kernel<T, INTERP, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tap_smem);      \
+    small_dw_kernel<T, INTERP, W><<<grid, 256, tap_smem, st>>>((const T *)A, (const T *)src, (const T *)map,              \
+                                                               (const T *)iw, (int)CH, (int)K, (int)P, (int)SH, (int)SW,  \
+                                                               (int)npix, (int)M, (int)B, partial,                       \
+                                                               fuse_bias ? bias_partial : nullptr);                      \
+  } while (0)
   SPH_DISPATCH_INTERP(interp, {
     if (P > 0) SPH_SMALL_DW(true);
     else SPH_SMALL_DW(false);
@@ -292,6 +357,7 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
   const int rc = simt_dw_reduce<T>(partial, 4 * splits, M, CH * K, K, sm, sc, sk, gw, st);
   if (rc != SPH_OK) return rc;
   note_launches(1);
+  if (fuse_bias) return simt_dw_reduce<T>(bias_partial, 4 * splits, M, 1, 1, 1, 0, 0, gb, st);
   return simt_bias_grad<T>(gbias_src, B, Cbias, nbias, gb, bias_ws, st);
 }
 

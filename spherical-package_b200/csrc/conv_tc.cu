@@ -129,6 +129,23 @@ __device__ __forceinline__ void fill_taps_zero(const Gather &g, Tap *dst) {
   for (int i = 0; i < g.nt; i++) { dst[i].off = zero_off; dst[i].w = 0u; }
 }
 
+// Taps of one unweighted map coordinate (x, y) that is already in registers (P == 0); NT = 1 decodes nearest,
+// NT = 4 bilinear or bispherical.  Same entries as fill_taps writes.
+template <int NT>
+__device__ __forceinline__ void taps_from_xy(const Gather &g, float x, float y, Tap (&dst)[NT]) {
+  const int zero_off = g.SH * g.SW * g.Cp * 2, pitch = g.Cp * 2;
+  Taps<float> t;
+  if (NT == 1) decode<float, SPH_NEAREST>(x, y, g.SH, g.SW, t);
+  else if (g.interp == SPH_BISPHERICAL) decode<float, SPH_BISPHERICAL>(x, y, g.SH, g.SW, t);
+  else decode<float, SPH_BILINEAR>(x, y, g.SH, g.SW, t);
+#pragma unroll
+  for (int i = 0; i < NT; i++) {
+    const bool ok = t.off[i] >= 0;
+    dst[i].off = ok ? t.off[i] * pitch : zero_off;
+    dst[i].w = tap_weight(ok ? t.w[i] : 0.0f);
+  }
+}
+
 // Accumulator of 8 channels: four bf16x2 registers, or eight floats.
 struct Acc8 {
   uint32_t h[4];
@@ -533,7 +550,10 @@ inline size_t dw_smem_bytes(int stages, int grp, int mbs, int tap_rows, int nt) 
   return 1024 + stages * dw_stage_bytes(grp, mbs) + 2 * (size_t)tap_rows * kDwPix * nt * sizeof(Tap) + 8 * (2 * stages + 1) + 16;
 }
 
-template <int NT, int GRP>
+// WT selects warp-private taps (unweighted maps, Cp >= 64, NT > 0): every producer warp decodes the taps of its own
+// four pixels, one step ahead, into its own slice of the table, so the producers share nothing but the stage
+// barriers; otherwise the whole producer group fills one table per step and meets at a named barrier.
+template <int NT, int GRP, bool WT>
 __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
   constexpr int MBS = 8 / GRP;
   constexpr int kDwColBytes = GRP * kDwPix * 128;  // gathered columns per stage
@@ -637,8 +657,102 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
       }
       if (alive) umma_commit(sm.tfull);
     }
+  } else if constexpr (WT && NT > 0) {
+    // ---------------- producers, warp-private taps ----------------
+    const int pt = tid - kFirstProducerThread, pw = pt >> 5;
+    const int v = lane & 7, pxl = lane >> 3, pl = pw * 4 + pxl;  // gathering role: 16-byte vector v of pixel pl
+    constexpr int kEnt = GRP * 4;                                // (chunk, pixel) entries a warp decodes per step
+    static_assert(kEnt <= 32, "one decoding lane per entry");
+    Tap *wt = sm.taps + (size_t)pw * (2 * kEnt * NT);            // this warp's two table halves
+    // decoding role: lane e < kEnt owns chunk e >> 2 of the group and pixel e & 3 of the warp
+    const bool dec = lane < kEnt && (lane >> 2) < ncg;
+    const int e_pl = pw * 4 + (lane & 3);
+    int e_slot = 0;
+    if (dec) { int c0; chunk_vec(g.Cp, g.K, chunk0 + (lane >> 2), 0, e_slot, c0); }
+    int g_coff[GRP];
+#pragma unroll
+    for (int gi = 0; gi < GRP; gi++) {
+      int slot = 0, c0 = 0;
+      if (gi < ncg) chunk_vec(g.Cp, g.K, chunk0 + gi, v, slot, c0);
+      g_coff[gi] = c0 * 2;
+    }
+    const int zero_off = g.SH * g.SW * g.Cp * 2;
+    // position (image, tile row, tile column) of the step whose map coordinate is fetched next
+    int nb_ = step_lo / tiles_per_image, nty = (step_lo % tiles_per_image) / p.tiles_x, ntx = (step_lo % tiles_per_image) % p.tiles_x;
+    int b_dec = 0, pix_dec = -1;
+    float mx = 0.0f, my = 0.0f;
+    auto fetch = [&]() {  // issue the map loads of the next step; they complete under the current step's gather
+      b_dec = nb_;
+      pix_dec = tile_pixel(e_pl, nty, ntx, kDwTH, g.GH, g.GW);
+      if (++ntx == p.tiles_x) {
+        ntx = 0;
+        if (++nty == p.tiles_y) { nty = 0; nb_++; }
+      }
+      if (dec && pix_dec >= 0) {
+        const float *m = g.map + 2 * ((size_t)pix_dec * g.K + e_slot);
+        mx = __ldg(m);
+        my = __ldg(m + 1);
+      }
+    };
+    auto decode_to = [&](Tap *dst) {
+      if (lane < kEnt) {
+        Tap t[NT];
+        if (dec && pix_dec >= 0) taps_from_xy<NT>(g, mx, my, t);
+        else {
+#pragma unroll
+          for (int i = 0; i < NT; i++) { t[i].off = zero_off; t[i].w = 0u; }
+        }
+#pragma unroll
+        for (int i = 0; i < NT; i++) dst[lane * NT + i] = t[i];
+      }
+    };
+    int b_cur = 0;
+    if (step_lo < step_hi) {
+      fetch();
+      b_cur = b_dec;
+      decode_to(wt);
+    }
+    __syncwarp();
+    int it = 0;
+    Ring ring;
+    for (int step = step_lo; step < step_hi; step++, it++, ring.next(S)) {
+      const char *img = (const char *)g.xh + (size_t)b_cur * (shw + 1) * g.Cp * 2;
+      const Tap *taps = wt + (it & 1) * (kEnt * NT) + pxl * NT;
+      const int s = ring.s;
+      const bool ok = mbar_wait(sm.empty + s, ring.ph ^ 1u, sm.abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) break;  // the whole warp leaves together
+      uint8_t *st = sm.stage + (size_t)s * stage_bytes;
+      if (pt == 0) {
+        const uint32_t bytes = (uint32_t)mbs * kDwGtBytes;
+        mbar_arrive_expect_tx(sm.full + s, bytes);
+        bulk_copy_g2s(st + kDwColBytes, p.gt + ((size_t)step * p.mbs_total + mb0) * (kDwGtBytes / 2), bytes, sm.full + s);
+      }
+      const bool more = step + 1 < step_hi;
+      int b_next = b_cur;
+      if (more) {
+        fetch();
+        b_next = b_dec;
+      }
+      uint8_t *dst0 = st + pl * 128 + ((v ^ (pl & 7)) << 4);
+#pragma unroll
+      for (int gi = 0; gi < GRP; gi += 2) {
+        if (gi >= ncg) break;
+        Acc8 a0, a1;
+        acc_zero(a0);
+        acc_zero(a1);
+        // a chunk past the group's end reads the zero taps its decoding lane wrote
+        gather_pair<NT>(img + g_coff[gi], img + g_coff[gi + 1], taps + gi * 4 * NT, taps + (gi + 1) * 4 * NT, NT, a0, a1);
+        *(uint4 *)(dst0 + gi * (kDwPix * 128)) = acc_pack(a0);
+        if (gi + 1 < ncg) *(uint4 *)(dst0 + (gi + 1) * (kDwPix * 128)) = acc_pack(a1);
+      }
+      if (more) decode_to(wt + ((it + 1) & 1) * (kEnt * NT));
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.full + s);
+      b_cur = b_next;
+    }
   } else {
-    // ---------------- producers ----------------
+    // ---------------- producers, shared tap table ----------------
     const int pt = tid - kFirstProducerThread;
     bool alive = true;
     int it = 0;
@@ -1118,15 +1232,16 @@ DwGeometry dw_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P,
   return d;
 }
 
-template <int NT, int GRP>
+template <int NT, int GRP, bool WT>
 void launch_dw_g(const DwParams &p, dim3 grid, size_t smem, cudaStream_t st) {
-  cudaFuncSetAttribute(tc_dw_kernel<NT, GRP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  tc_dw_kernel<NT, GRP><<<grid, kThreads, smem, st>>>(p);
+  cudaFuncSetAttribute(tc_dw_kernel<NT, GRP, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  tc_dw_kernel<NT, GRP, WT><<<grid, kThreads, smem, st>>>(p);
 }
 template <int NT>
-void launch_dw(const DwParams &p, int grp, dim3 grid, size_t smem, cudaStream_t st) {
-  if (grp == 8) launch_dw_g<NT, 8>(p, grid, smem, st);
-  else launch_dw_g<NT, 4>(p, grid, smem, st);
+void launch_dw(const DwParams &p, int grp, bool warp_taps, dim3 grid, size_t smem, cudaStream_t st) {
+  if (grp == 8) launch_dw_g<NT, 8, false>(p, grid, smem, st);
+  else if (warp_taps && NT > 0) launch_dw_g<NT, 4, (NT > 0)>(p, grid, smem, st);
+  else launch_dw_g<NT, 4, false>(p, grid, smem, st);
 }
 
 // gw[n,ch,slot] = sum_{b,pix} A[b,n,pix] * im2col(src)[b,pix,(slot,ch)]; gb = sum of gbias_src over batch and pixels.
@@ -1160,9 +1275,10 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
   p.B = (int)B; p.mbs_total = d.mbs_total; p.nchunks = d.nchunks; p.tiles_x = d.tiles_x; p.tiles_y = d.tiles_y;
   p.splits = d.splits; p.stages = d.stages; p.tap_rows = d.tap_rows;
   dim3 grid(d.ngroups, d.splits, (d.mbs_total + 8 / d.grp - 1) / (8 / d.grp));
-  if (d.nt == 4) launch_dw<4>(p, d.grp, grid, d.smem, st);
-  else if (d.nt == 1) launch_dw<1>(p, d.grp, grid, d.smem, st);
-  else launch_dw<0>(p, d.grp, grid, d.smem, st);
+  const bool warp_taps = d.Cp >= 64 && P == 0;  // one slot per chunk and one coordinate per slot
+  if (d.nt == 4) launch_dw<4>(p, d.grp, warp_taps, grid, d.smem, st);
+  else if (d.nt == 1) launch_dw<1>(p, d.grp, warp_taps, grid, d.smem, st);
+  else launch_dw<0>(p, d.grp, false, grid, d.smem, st);
   tc_dw_reduce_kernel<<<cdiv(Nout * CH * K, 256), 256, 0, st>>>(partial, d.splits, d.mbs_total * 128, d.nchunks * kChunk, (int)Nout,
                                                                (int)CH, d.Cp, (int)K, sn, sc, sk, (float *)gw);
   note_launches(4);
