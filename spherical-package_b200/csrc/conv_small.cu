@@ -16,6 +16,7 @@
 namespace sph {
 
 constexpr int kSmallJ = 32;  // at most this many (channel, slot) columns
+template <typename T> struct alignas(16) SdwVec { T v[16 / sizeof(T)]; };  // 16 bytes of T
 
 template <typename T, int INTERP, bool WEIGHTED>
 __device__ __forceinline__ void small_columns(T (&col)[kSmallJ], const T *__restrict__ src, const T *__restrict__ map,
@@ -73,40 +74,82 @@ small_fwd_kernel(const T *__restrict__ src, const T *__restrict__ map, const T *
   }
 }
 
-// T[b, o, m*K + k] = sum_ch Wgt[m,ch,k] * Src[b,ch,o]; thread = one source position o.
-template <typename T>
+// Row layout of the adjoint's intermediate T: one row of Rp values per source position, element (k, m) at
+// k * Mq + m, where Mq pads the M output channels to 1, 2 or a multiple of 4 so that the plan gather fetches all
+// channels of one (position, slot) with one vector load.
+__host__ __device__ inline int small_mq(int M) { return M <= 2 ? M : (M + 3) / 4 * 4; }
+__host__ __device__ inline int small_row(int M, int K) { return (K * small_mq(M) + 3) / 4 * 4; }
+constexpr int kSmallRowMax = 48;  // M * K <= 32 keeps rows within this
+
+// T[b, o, k*Mq + m] = sum_ch Wgt[m,ch,k] * Src[b,ch,o]; thread = two source positions o (256 apart), so that one
+// read of a weight vector feeds two pixels.  R4 = row length / 4.
+template <typename T, int R4>
 __global__ void __launch_bounds__(256)
 small_premul_kernel(const T *__restrict__ src, const T *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk,
                     T *__restrict__ tbuf, int CH, int K, int M, int n_src) {
+  constexpr int Rp = 4 * R4, kU = 8;  // kU source channels are loaded ahead of their multiply-adds
   extern __shared__ __align__(16) unsigned char small_smem[];
-  T *ws = (T *)small_smem;  // [CH][kSmallJ]
-  for (int i = threadIdx.x; i < CH * kSmallJ; i += blockDim.x) {
-    const int ch = i / kSmallJ, j = i % kSmallJ;
-    ws[i] = j < M * K ? __ldg(wgt + (j / K) * sm + ch * sc + (j % K) * sk) : T(0);
+  T *ws = (T *)small_smem;                   // [CH][Rp] weights
+  T *stage = ws + (size_t)CH * Rp;           // [8 warps][32 rows][Rp] output rows on their way to memory
+  const int Mq = small_mq(M);
+  for (int i = threadIdx.x; i < CH * Rp; i += blockDim.x) {
+    const int ch = i / Rp, r = i % Rp, k = r / Mq, m = r % Mq;
+    ws[i] = (k < K && m < M) ? __ldg(wgt + m * sm + ch * sc + k * sk) : T(0);
   }
   __syncthreads();
-  const int o = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
-  if (o >= n_src) return;
-  T acc[kSmallJ];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int o0 = blockIdx.x * 512 + threadIdx.x, o1 = o0 + 256, b = blockIdx.y;
+  const bool has0 = o0 < n_src, has1 = o1 < n_src;
+  T acc0[Rp], acc1[Rp];
 #pragma unroll
-  for (int j = 0; j < kSmallJ; j++) acc[j] = T(0);
-  const T *s = src + (size_t)b * CH * n_src + o;
-  for (int ch = 0; ch < CH; ch++) {
-    const T v = __ldg(s + (size_t)ch * n_src);
-    const T *wr = ws + ch * kSmallJ;
+  for (int r = 0; r < Rp; r++) acc0[r] = acc1[r] = T(0);
+  const T *s = src + (size_t)b * CH * n_src;
+  for (int c0 = 0; c0 < CH; c0 += kU) {
+    T v0[kU], v1[kU];
 #pragma unroll
-    for (int j = 0; j < kSmallJ; j++) acc[j] += wr[j] * v;
+    for (int u = 0; u < kU; u++) {
+      const bool in = c0 + u < CH;
+      v0[u] = (in && has0) ? __ldg(s + (size_t)(c0 + u) * n_src + o0) : T(0);
+      v1[u] = (in && has1) ? __ldg(s + (size_t)(c0 + u) * n_src + o1) : T(0);
+    }
+#pragma unroll
+    for (int u = 0; u < kU; u++) {
+      if (c0 + u < CH) {
+        const T *wr = ws + (c0 + u) * Rp;
+#pragma unroll
+        for (int r = 0; r < Rp; r++) {
+          acc0[r] += wr[r] * v0[u];
+          acc1[r] += wr[r] * v1[u];
+        }
+      }
+    }
   }
-  T *t = tbuf + ((size_t)b * n_src + o) * kSmallJ;  // one padded row of kSmallJ values per source position
+  // The 32 rows of a warp are contiguous in T: pass them through shared memory so that the stores are
+  // coalesced 16-byte vectors instead of one row per lane.
+  using V = SdwVec<T>;
+  constexpr int VW = 16 / sizeof(T), kRowVecs = Rp / VW;
+  T *wst = stage + (size_t)warp * 32 * Rp;
 #pragma unroll
-  for (int j = 0; j < kSmallJ; j++) t[j] = acc[j];
+  for (int half = 0; half < 2; half++) {
+    const int obase = blockIdx.x * 512 + half * 256 + warp * 32;  // first row of this warp's span
+    if (obase >= n_src) break;
+    const int rows = min(32, n_src - obase);
+#pragma unroll
+    for (int r = 0; r < Rp; r++) wst[lane * Rp + r] = half ? acc1[r] : acc0[r];
+    __syncwarp();
+    V *dst = (V *)(tbuf + ((size_t)b * n_src + obase) * Rp);
+    for (int i = lane; i < rows * kRowVecs; i += 32) dst[i] = ((const V *)wst)[i];
+    __syncwarp();
+  }
 }
 
-// Out[b,m,p] = bias[m] + sum_k sum_{e in plan(p*K+k)} w_e * T[b, src_e, m*K+k]; thread = one destination pixel of
-// kGatherImages consecutive images, so the plan entries are read once per group of images.
-constexpr int kGatherImages = 4, kGatherM = 4;  // images per thread; output channels per register block
+// Out[b,m,p] = bias[m] + sum_k sum_{e in plan(p*K+k)} w_e * T[b, src_e, k*Mq + m]; thread = one destination pixel of
+// kGatherImages consecutive images, so the plan entries are read once per group of images; VM = channels
+// fetched per load (1, 2 or 4).
+constexpr int kGatherImages = 4;
+template <typename T, int VM> struct alignas(sizeof(T) * VM > 16 ? 16 : sizeof(T) * VM) SmallVec { T v[VM]; };
 
-template <typename T>
+template <typename T, int VM>
 __global__ void __launch_bounds__(256)
 small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ plan_blob, const T *__restrict__ bias,
                          T *__restrict__ out, int K, int M, int n_src, int n_dst, int B) {
@@ -115,28 +158,32 @@ small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ pl
   bool ok;
   const PlanView<T> pv = plan_view<T>(plan_blob, n_dst * K, ok);
   const int nb = min(kGatherImages, B - b0);
-  const size_t img_stride = (size_t)n_src * kSmallJ;
+  const int Mq = small_mq(M), Rp = small_row(M, K);
+  const size_t img_stride = (size_t)n_src * Rp;
   const T *tb = tbuf + (size_t)b0 * img_stride;
-  for (int m0 = 0; m0 < M; m0 += kGatherM) {   // one pass for M <= 4 (e.g. RGB inputs)
-    T acc[kGatherImages][kGatherM];
+  for (int m0 = 0; m0 < Mq; m0 += VM) {   // one pass for M <= 4 (e.g. RGB inputs)
+    T acc[kGatherImages][VM];
 #pragma unroll
     for (int i = 0; i < kGatherImages; i++)
 #pragma unroll
-      for (int m = 0; m < kGatherM; m++) acc[i][m] = T(0);
+      for (int m = 0; m < VM; m++) acc[i][m] = T(0);
     if (ok) {
       int e1 = __ldg(pv.offsets + p * K);
       for (int k = 0; k < K; k++) {
         const int e0 = e1;
         e1 = __ldg(pv.offsets + p * K + k + 1);
         for (int e = e0; e < e1; e++) {
-          const T *row = tb + (size_t)__ldg(pv.src + e) * kSmallJ + k;
+          const T *row = tb + (size_t)__ldg(pv.src + e) * Rp + k * Mq + m0;
           const T w = __ldg(pv.w + e);
+          SmallVec<T, VM> v[kGatherImages];
+#pragma unroll
+          for (int i = 0; i < kGatherImages; i++)
+            if (i < nb) v[i] = *(const SmallVec<T, VM> *)(row + i * img_stride);
 #pragma unroll
           for (int i = 0; i < kGatherImages; i++)
             if (i < nb) {
 #pragma unroll
-              for (int m = 0; m < kGatherM; m++)
-                if (m0 + m < M) acc[i][m] += w * __ldg(row + i * img_stride + (m0 + m) * K);
+              for (int m = 0; m < VM; m++) acc[i][m] += w * v[i].v[m];
             }
         }
       }
@@ -145,7 +192,7 @@ small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ pl
     for (int i = 0; i < kGatherImages; i++)
       if (i < nb) {
 #pragma unroll
-        for (int m = 0; m < kGatherM; m++)
+        for (int m = 0; m < VM; m++)
           if (m0 + m < M) out[((size_t)(b0 + i) * M + m0 + m) * n_dst + p] = acc[i][m] + (bias ? __ldg(bias + m0 + m) : T(0));
       }
   }
@@ -158,7 +205,6 @@ small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ pl
 // into shared memory and reused for all images of the unit's group (the map is the same for every image).
 constexpr int kSdwImages = 8;  // images per unit
 template <typename T> struct SdwPix { static constexpr int value = sizeof(T) == 8 ? 32 : 64; };  // pixels staged per step
-template <typename T> struct alignas(16) SdwVec { T v[16 / sizeof(T)]; };
 template <typename T> struct alignas(16) SdwTaps { Taps<T> t; };  // 16-byte aligned so that it moves as vectors
 
 template <typename T, int INTERP, bool WEIGHTED>
@@ -275,7 +321,7 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
 
 // ---- host side ------------------------------------------------------------------------------------------
 bool small_ok(int64_t side_channels, int64_t K, int64_t wide_channels, size_t ts) {
-  return side_channels * K <= kSmallJ && wide_channels * kSmallJ * (int64_t)ts <= 48 * 1024;
+  return side_channels * K <= kSmallJ && wide_channels * kSmallRowMax * (int64_t)ts <= 48 * 1024;
 }
 
 static int small_dw_splits(int64_t B, int64_t npix, int64_t M, size_t ts) {
@@ -288,8 +334,7 @@ static int small_dw_splits(int64_t B, int64_t npix, int64_t M, size_t ts) {
 }
 
 size_t small_premul_workspace(int64_t B, int64_t M, int64_t K, int64_t n_src, size_t ts) {
-  (void)M; (void)K;
-  return align_up(ts * (size_t)(B * n_src) * kSmallJ, 256);
+  return align_up(ts * (size_t)(B * n_src) * small_row((int)M, (int)K), 256);
 }
 
 size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts) {
@@ -315,15 +360,37 @@ int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int6
   return launch_status();
 }
 
+template <typename T, int R4>
+static void launch_premul(const void *src, const void *wgt, int64_t sm, int64_t sc, int64_t sk, void *ws, int64_t CH, int64_t K,
+                          int64_t M, int64_t n_src, int64_t B, cudaStream_t st) {
+  const size_t smem = sizeof(T) * (size_t)(CH + 256) * 4 * R4;  // weights + one staged row per thread
+  cudaFuncSetAttribute(small_premul_kernel<T, R4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  small_premul_kernel<T, R4><<<dim3(cdiv(n_src, 512), (unsigned)B), 256, smem, st>>>(
+      (const T *)src, (const T *)wgt, sm, sc, sk, (T *)ws, (int)CH, (int)K, (int)M, (int)n_src);
+}
+
 template <typename T>
 int small_adjoint(const void *src, const void *plan, int64_t CH, int64_t n_src, int64_t K, int64_t n_dst, const void *wgt,
                   int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out, int64_t M, int64_t B, void *ws,
                   size_t ws_bytes, cudaStream_t st) {
   if (!ws || ws_bytes < small_premul_workspace(B, M, K, n_src, sizeof(T))) return SPH_ERR_WORKSPACE_TOO_SMALL;
-  small_premul_kernel<T><<<dim3(cdiv(n_src, 256), (unsigned)B), 256, sizeof(T) * (size_t)CH * kSmallJ, st>>>(
-      (const T *)src, (const T *)wgt, sm, sc, sk, (T *)ws, (int)CH, (int)K, (int)M, (int)n_src);
-  small_plan_gather_kernel<T><<<dim3(cdiv(n_dst, 256), cdiv(B, kGatherImages)), 256, 0, st>>>(
-      (const T *)ws, plan, (const T *)bias, (T *)out, (int)K, (int)M, (int)n_src, (int)n_dst, (int)B);
+  const int r4 = small_row((int)M, (int)K) / 4;
+  switch (r4) {
+#define SPH_PREMUL_CASE(N) case N: launch_premul<T, N>(src, wgt, sm, sc, sk, ws, CH, K, M, n_src, B, st); break;
+    SPH_PREMUL_CASE(1) SPH_PREMUL_CASE(2) SPH_PREMUL_CASE(3) SPH_PREMUL_CASE(4) SPH_PREMUL_CASE(5) SPH_PREMUL_CASE(6)
+    SPH_PREMUL_CASE(7) SPH_PREMUL_CASE(8) SPH_PREMUL_CASE(9) SPH_PREMUL_CASE(10) SPH_PREMUL_CASE(11) SPH_PREMUL_CASE(12)
+#undef SPH_PREMUL_CASE
+    default: return SPH_ERR_INVALID_ARGUMENT;
+  }
+  const dim3 grid(cdiv(n_dst, 256), cdiv(B, kGatherImages));
+  const int mq = small_mq((int)M);
+#define SPH_GATHER(VM)                                                                                                   \
+  small_plan_gather_kernel<T, VM><<<grid, 256, 0, st>>>((const T *)ws, plan, (const T *)bias, (T *)out, (int)K, (int)M,     \
+                                                        (int)n_src, (int)n_dst, (int)B)
+  if (mq == 1) SPH_GATHER(1);
+  else if (mq == 2) SPH_GATHER(2);
+  else SPH_GATHER(4);
+#undef SPH_GATHER
   return launch_status(2);
 }
 
