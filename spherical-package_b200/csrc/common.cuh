@@ -84,16 +84,27 @@ __device__ __forceinline__ void decode(T x, T y, int H, int W, Taps<T> &t) {
 }
 
 // Interpolated value of one plane at decoded taps: ((w0 v0 + w1 v1) + w2 v2) + w3 v3,
-// each product and sum rounded separately (core/interpolation.h:25-32).
+// each product and sum rounded separately (core/interpolation.h:25-32).  Split into the loads and the
+// arithmetic so that callers can issue the loads of several taps sets before consuming any.
+template <typename T, int INTERP>
+__device__ __forceinline__ void gather_load(const T *__restrict__ plane, const Taps<T> &t, T (&v)[TapCount<INTERP>::value]) {
+#pragma unroll
+  for (int i = 0; i < TapCount<INTERP>::value; i++) v[i] = t.off[i] >= 0 ? __ldg(plane + t.off[i]) : T(0);
+}
+template <typename T, int INTERP>
+__device__ __forceinline__ T gather_combine(const Taps<T> &t, const T (&v)[TapCount<INTERP>::value]) {
+  if constexpr (INTERP == SPH_NEAREST) {
+    return v[0];
+  } else {
+    return RN<T>::add(RN<T>::add(RN<T>::add(RN<T>::mul(t.w[0], v[0]), RN<T>::mul(t.w[1], v[1])), RN<T>::mul(t.w[2], v[2])),
+                      RN<T>::mul(t.w[3], v[3]));
+  }
+}
 template <typename T, int INTERP>
 __device__ __forceinline__ T gather(const T *__restrict__ plane, const Taps<T> &t) {
-  if (INTERP == SPH_NEAREST) return t.off[0] >= 0 ? __ldg(plane + t.off[0]) : T(0);
-  const T v0 = t.off[0] >= 0 ? __ldg(plane + t.off[0]) : T(0);
-  const T v1 = t.off[1] >= 0 ? __ldg(plane + t.off[1]) : T(0);
-  const T v2 = t.off[2] >= 0 ? __ldg(plane + t.off[2]) : T(0);
-  const T v3 = t.off[3] >= 0 ? __ldg(plane + t.off[3]) : T(0);
-  return RN<T>::add(RN<T>::add(RN<T>::add(RN<T>::mul(t.w[0], v0), RN<T>::mul(t.w[1], v1)), RN<T>::mul(t.w[2], v2)),
-                    RN<T>::mul(t.w[3], v3));
+  T v[TapCount<INTERP>::value];
+  gather_load<T, INTERP>(plane, t, v);
+  return gather_combine<T, INTERP>(t, v);
 }
 
 // Value of one map slot: plain, or the weighted sum over its P points

@@ -74,6 +74,134 @@ small_fwd_kernel(const T *__restrict__ src, const T *__restrict__ map, const T *
   }
 }
 
+// float32 forward as a tiled product: a block gathers the columns of 256 pixels into shared memory
+// (Col[j][pixel], thread = pixel), then multiplies them with the weights as a [256 pixels] x [64 outputs] tile:
+// warp w owns outputs 8w..8w+7, lane l pixels 4l..4l+3 and 128+4l..128+4l+3, 64 accumulators per thread held as packed pairs of
+// neighbouring pixels (two-wide FMAs).  Per column every thread reads 8 column values and 8 weights for 64
+// multiply-adds, so shared-memory traffic stays far below the FMA rate; outputs beyond 64 take further passes
+// over the same gathered columns.
+__device__ __forceinline__ void ffma2(unsigned long long &d, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+constexpr int kTilePix = 256, kTileOut = 64;
+
+template <int INTERP, bool WEIGHTED>
+__global__ void __launch_bounds__(256, 2)
+small_fwd_tile_kernel(const float *__restrict__ src, const float *__restrict__ map, const float *__restrict__ iw,
+                      const float *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk, const float *__restrict__ bias,
+                      float *__restrict__ out, int CH, int K, int P, int SH, int SW, int npix, int M) {
+  __shared__ __align__(16) float Cs[kSmallJ][kTilePix];
+  __shared__ __align__(16) float Ws[kSmallJ][kTileOut];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, b = blockIdx.y, J = CH * K;
+  const int p0 = blockIdx.x * kTilePix;
+  const size_t shw = (size_t)SH * SW;
+  // ---- gather: thread = pixel ----
+  {
+    const int pix = p0 + tid;
+    const float *img = src + (size_t)b * CH * shw;
+    if (pix < npix) {
+      const int PP = WEIGHTED ? P : 1;
+      const size_t e0 = (size_t)pix * K * PP;
+      if (!WEIGHTED) {
+        // three slots and up to four channels at a time: all their loads are issued before any is used, so a
+        // pixel costs a few memory round trips instead of one per gathered value
+        constexpr int NTAP = TapCount<INTERP>::value;
+        for (int k0 = 0; k0 < K; k0 += 3) {
+          float mx[3], my[3];
+#pragma unroll
+          for (int u = 0; u < 3; u++)
+            if (k0 + u < K) { mx[u] = __ldg(map + 2 * (e0 + k0 + u)); my[u] = __ldg(map + 2 * (e0 + k0 + u) + 1); }
+          Taps<float> t[3];
+#pragma unroll
+          for (int u = 0; u < 3; u++)
+            if (k0 + u < K) decode<float, INTERP>(mx[u], my[u], SH, SW, t[u]);
+          for (int c0 = 0; c0 < CH; c0 += 4) {
+            float raw[3][4][NTAP];
+#pragma unroll
+            for (int u = 0; u < 3; u++)
+#pragma unroll
+              for (int v = 0; v < 4; v++)
+                if (k0 + u < K && c0 + v < CH) gather_load<float, INTERP>(img + (c0 + v) * shw, t[u], raw[u][v]);
+#pragma unroll
+            for (int u = 0; u < 3; u++)
+#pragma unroll
+              for (int v = 0; v < 4; v++)
+                if (k0 + u < K && c0 + v < CH) Cs[(c0 + v) * K + k0 + u][tid] = gather_combine<float, INTERP>(t[u], raw[u][v]);
+          }
+        }
+      } else {
+        for (int k = 0; k < K; k++) {
+          const size_t e = e0 + (size_t)k * PP;
+          for (int c = 0; c < CH; c++)
+            Cs[c * K + k][tid] = gather_slot<float, INTERP, true>(img + c * shw, map + 2 * e, iw + e, P, SH, SW);
+        }
+      }
+    } else {
+      for (int j = 0; j < J; j++) Cs[j][tid] = 0.0f;
+    }
+  }
+  const bool vec_ok = (npix & 3) == 0;  // 16-byte stores need every output row 16-byte aligned
+  for (int m0 = 0; m0 < M; m0 += kTileOut) {
+    __syncthreads();  // columns complete (first pass) / previous pass done with Ws
+    for (int i = tid; i < J * kTileOut; i += 256) {
+      const int j = i / kTileOut, m = m0 + i % kTileOut;
+      Ws[j][i % kTileOut] = m < M ? __ldg(wgt + m * sm + (j / K) * sc + (j % K) * sk) : 0.0f;
+    }
+    __syncthreads();
+    const int mw = m0 + warp * 8;  // this warp's first output
+    if (mw >= M) continue;
+    unsigned long long acc[8][4];  // [output][pixel pair]
+#pragma unroll
+    for (int m = 0; m < 8; m++) {
+      const float bv = (bias && mw + m < M) ? __ldg(bias + mw + m) : 0.0f;
+#pragma unroll
+      for (int q = 0; q < 4; q++) acc[m][q] = pack2(bv, bv);
+    }
+#pragma unroll 3
+    for (int j = 0; j < J; j++) {
+      const ulonglong2 c0 = *(const ulonglong2 *)&Cs[j][lane * 4], c1 = *(const ulonglong2 *)&Cs[j][128 + lane * 4];
+      const float4 w0 = *(const float4 *)&Ws[j][warp * 8], w1 = *(const float4 *)&Ws[j][warp * 8 + 4];
+      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int m = 0; m < 8; m++) {
+        const unsigned long long ww = pack2(wv[m], wv[m]);
+        ffma2(acc[m][0], c0.x, ww);
+        ffma2(acc[m][1], c0.y, ww);
+        ffma2(acc[m][2], c1.x, ww);
+        ffma2(acc[m][3], c1.y, ww);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < 8; m++) {
+      if (mw + m >= M) break;
+      float v[8];
+#pragma unroll
+      for (int q = 0; q < 4; q++) unpack2(acc[m][q], v[2 * q], v[2 * q + 1]);
+#pragma unroll
+      for (int h = 0; h < 2; h++) {  // the two groups of four pixels
+        const int px = p0 + h * 128 + lane * 4;
+        float *o = out + ((size_t)b * M + mw + m) * npix + px;
+        if (vec_ok && px + 4 <= npix) {
+          *(float4 *)o = make_float4(v[4 * h], v[4 * h + 1], v[4 * h + 2], v[4 * h + 3]);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; q++)
+            if (px + q < npix) o[q] = v[4 * h + q];
+        }
+      }
+    }
+  }
+}
+
 // Row layout of the adjoint's intermediate T: one row of Rp values per source position, element (k, m) at
 // k * Mq + m, where Mq pads the M output channels to 1, 2 or a multiple of 4 so that the plan gather fetches all
 // channels of one (position, slot) with one vector load.
@@ -346,6 +474,20 @@ template <typename T>
 int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K, int64_t P,
               int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out,
               int64_t M, int64_t B, cudaStream_t st) {
+  if constexpr (sizeof(T) == 4) {  // float32: tiled product
+    const dim3 tgrid(cdiv(npix, kTilePix), (unsigned)B);
+#define SPH_FWD_TILE(W)                                                                                                \
+  small_fwd_tile_kernel<INTERP, W><<<tgrid, 256, 0, st>>>((const float *)src, (const float *)map, (const float *)iw,     \
+                                                          (const float *)wgt, sm, sc, sk, (const float *)bias,          \
+                                                          (float *)out, (int)CH, (int)K, (int)P, (int)SH, (int)SW,       \
+                                                          (int)npix, (int)M)
+    SPH_DISPATCH_INTERP(interp, {
+      if (P > 0) SPH_FWD_TILE(true);
+      else SPH_FWD_TILE(false);
+    });
+#undef SPH_FWD_TILE
+    return launch_status();
+  }
   dim3 grid(cdiv(npix, 256), (unsigned)B);
   const size_t smem = sizeof(T) * (size_t)M * kSmallJ;
 #define SPH_SMALL_FWD(W)                                                                                              \
