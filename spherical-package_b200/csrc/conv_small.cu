@@ -332,11 +332,12 @@ small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ pl
 // (two for float64) multiply-adds of each accumulator it touches.  The taps of a pixel step are decoded once
 // into shared memory and reused for all images of the unit's group (the map is the same for every image).
 constexpr int kSdwImages = 8;  // images per unit
+constexpr int kSdwThreads = 128, kSdwParts = kSdwThreads / 64;  // small blocks: four per SM, out of phase with one another
 template <typename T> struct SdwPix { static constexpr int value = sizeof(T) == 8 ? 32 : 64; };  // pixels staged per step
 template <typename T> struct alignas(16) SdwTaps { Taps<T> t; };  // 16-byte aligned so that it moves as vectors
 
 template <typename T, int INTERP, bool WEIGHTED>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kSdwThreads)
 small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__restrict__ map, const T *__restrict__ iw,
                 int CH, int K, int P, int SH, int SW, int npix, int M, int B, T *__restrict__ partial,
                 T *__restrict__ bias_partial) {
@@ -346,8 +347,8 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
   __shared__ __align__(16) T Cs[kSmallJ][kPitch];
   extern __shared__ __align__(16) unsigned char small_smem[];
   SdwTaps<T> *tcache = (SdwTaps<T> *)small_smem;  // [K][kSdwPix] decoded taps of the current pixel step (unweighted maps)
-  // four quarters of 64 threads: each quarter takes every fourth pixel vector and holds an 8 x 4 register tile
-  // per thread (rows tm + 8 i, columns tj + 8 j); the quarters' sums are kept as separate partials
+  // kSdwParts groups of 64 threads: each group takes every kSdwParts-th pixel vector and holds an 8 x 4 register
+  // tile per thread (rows tm + 8 i, columns tj + 8 j); the groups' sums are kept as separate partials
   const int tid = threadIdx.x, qtr = tid >> 6, tm = (tid & 63) >> 3, tj = tid & 7;
   const int m0 = blockIdx.y * 64, splits = gridDim.x, J = CH * K;
   const int steps = (npix + kSdwPix - 1) / kSdwPix, groups = (B + kSdwImages - 1) / kSdwImages;
@@ -355,7 +356,7 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
   // With bias_partial set (and J < kSmallJ) the first padding column of Col is all ones, so that column of the
   // product is the row sum of A: the bias gradient when A is grad_output.  Pixels past the end have A = 0.
   const bool ones = bias_partial != nullptr;
-  for (int e = tid; e < (kSmallJ - J) * kPitch; e += 256) Cs[J + e / kPitch][e % kPitch] = (ones && e < kPitch) ? T(1) : T(0);
+  for (int e = tid; e < (kSmallJ - J) * kPitch; e += kSdwThreads) Cs[J + e / kPitch][e % kPitch] = (ones && e < kPitch) ? T(1) : T(0);
   T acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; i++)
@@ -365,7 +366,7 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
     const int p0 = (unit / groups) * kSdwPix, b0 = (unit % groups) * kSdwImages, b1 = min(B, b0 + kSdwImages);
     const int pend = min(npix, p0 + kSdwPix);
     if (!WEIGHTED) {
-      for (int idx = tid; idx < K * kSdwPix; idx += 256) {
+      for (int idx = tid; idx < K * kSdwPix; idx += kSdwThreads) {
         const int k = idx / kSdwPix, pix = p0 + idx % kSdwPix;
         Taps<T> t;
         if (pix < pend) {
@@ -381,19 +382,19 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
     }
     for (int b = b0; b < b1; b++) {
       const T *img = src + (size_t)b * CH * shw;
-      for (int e = tid; e < 64 * kSdwPix; e += 256) {
+      for (int e = tid; e < 64 * kSdwPix; e += kSdwThreads) {
         const int pl = e % kSdwPix, ml = e / kSdwPix, pix = p0 + pl, m = m0 + ml;
         As[ml][pl] = (pix < pend && m < M) ? __ldg(A + ((size_t)b * M + m) * npix + pix) : T(0);
       }
       if (!WEIGHTED) {
         // gathered columns, three (slot, pixel) items per thread at a time so that their loads overlap
-        for (int base = tid; base < K * kSdwPix; base += 3 * 256) {
+        for (int base = tid; base < K * kSdwPix; base += 3 * kSdwThreads) {
           Taps<T> t[3];
           int row[3], pl[3];
           bool ok[3];
 #pragma unroll
           for (int r = 0; r < 3; r++) {
-            const int idx = base + r * 256;
+            const int idx = base + r * kSdwThreads;
             ok[r] = idx < K * kSdwPix;
             row[r] = ok[r] ? idx / kSdwPix : 0;
             pl[r] = idx % kSdwPix;
@@ -409,7 +410,7 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
           }
         }
       } else {
-        for (int idx = tid; idx < K * kSdwPix; idx += 256) {
+        for (int idx = tid; idx < K * kSdwPix; idx += kSdwThreads) {
           const int k = idx / kSdwPix, pl = idx % kSdwPix, pix = p0 + pl;
           const size_t e = ((size_t)pix * K + k) * P;
           for (int c = 0; c < CH; c++)
@@ -418,7 +419,7 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
       }
       __syncthreads();
 #pragma unroll 1
-      for (int pv = qtr; pv < kSdwPix / VW; pv += 4) {
+      for (int pv = qtr; pv < kSdwPix / VW; pv += kSdwParts) {
         SdwVec<T> a[8], c[4];
 #pragma unroll
         for (int i = 0; i < 8; i++) a[i] = *(const SdwVec<T> *)&As[tm + 8 * i][pv * VW];
@@ -434,7 +435,7 @@ small_dw_kernel(const T *__restrict__ A, const T *__restrict__ src, const T *__r
       __syncthreads();
     }
   }
-  const size_t prow = (size_t)blockIdx.x * 4 + qtr;  // partial index: (split, quarter)
+  const size_t prow = (size_t)blockIdx.x * kSdwParts + qtr;  // partial index: (split, thread group)
 #pragma unroll
   for (int i = 0; i < 8; i++) {
     const int m = m0 + tm + 8 * i;
@@ -455,7 +456,7 @@ bool small_ok(int64_t side_channels, int64_t K, int64_t wide_channels, size_t ts
 static int small_dw_splits(int64_t B, int64_t npix, int64_t M, size_t ts) {
   const int64_t pix = ts == 8 ? 32 : 64;
   const int64_t units = ((B + kSdwImages - 1) / kSdwImages) * ((npix + pix - 1) / pix), mblocks = (M + 63) / 64;
-  int64_t s = (4 * 148 + mblocks - 1) / mblocks;
+  int64_t s = (8 * 148 + mblocks - 1) / mblocks;
   if (s > units) s = units;
   if (s < 1) s = 1;
   return (int)s;
@@ -466,7 +467,7 @@ size_t small_premul_workspace(int64_t B, int64_t M, int64_t K, int64_t n_src, si
 }
 
 size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts) {
-  const size_t parts = 4 * (size_t)small_dw_splits(B, npix, M, ts);
+  const size_t parts = kSdwParts * (size_t)small_dw_splits(B, npix, M, ts);
   return align_up(ts * parts * M * CH * K, 256) + align_up(ts * parts * M, 256) + simt_bias_workspace(Cbias, ts);
 }
 
@@ -543,8 +544,8 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
   if (!ws || ws_bytes < small_dw_workspace(B, npix, M, CH, K, Cbias, sizeof(T))) return SPH_ERR_WORKSPACE_TOO_SMALL;
   const int splits = small_dw_splits(B, npix, M, sizeof(T));
   T *partial = (T *)ws;
-  T *bias_partial = (T *)((char *)ws + align_up(sizeof(T) * (size_t)(4 * splits * M * CH * K), 256));
-  void *bias_ws = (char *)bias_partial + align_up(sizeof(T) * (size_t)(4 * splits * M), 256);
+  T *bias_partial = (T *)((char *)ws + align_up(sizeof(T) * (size_t)(kSdwParts * splits * M * CH * K), 256));
+  void *bias_ws = (char *)bias_partial + align_up(sizeof(T) * (size_t)(kSdwParts * splits * M), 256);
   // conv dW: the tensor whose rows are staged is also the one whose channel sums give the bias gradient
   const bool fuse_bias = gbias_src == A && Cbias == M && nbias == npix && CH * K < kSmallJ;
   dim3 grid(splits, cdiv(M, 64));
@@ -553,7 +554,7 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
 #define SPH_SMALL_DW(W)                                                                                                  \
   do {                                                                                                                   \
     cudaFuncSetAttribute(small_dw_kernel<T, INTERP, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tap_smem);      \
-    small_dw_kernel<T, INTERP, W><<<grid, 256, tap_smem, st>>>((const T *)A, (const T *)src, (const T *)map,              \
+    small_dw_kernel<T, INTERP, W><<<grid, kSdwThreads, tap_smem, st>>>((const T *)A, (const T *)src, (const T *)map,              \
                                                                (const T *)iw, (int)CH, (int)K, (int)P, (int)SH, (int)SW,  \
                                                                (int)npix, (int)M, (int)B, partial,                       \
                                                                fuse_bias ? bias_partial : nullptr);                      \
@@ -563,10 +564,10 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
     else SPH_SMALL_DW(false);
   });
 #undef SPH_SMALL_DW
-  const int rc = simt_dw_reduce<T>(partial, 4 * splits, M, CH * K, K, sm, sc, sk, gw, st);
+  const int rc = simt_dw_reduce<T>(partial, kSdwParts * splits, M, CH * K, K, sm, sc, sk, gw, st);
   if (rc != SPH_OK) return rc;
   note_launches(1);
-  if (fuse_bias) return simt_dw_reduce<T>(bias_partial, 4 * splits, M, 1, 1, 1, 0, 0, gb, st);
+  if (fuse_bias) return simt_dw_reduce<T>(bias_partial, kSdwParts * splits, M, 1, 1, 1, 0, 0, gb, st);
   return simt_bias_grad<T>(gbias_src, B, Cbias, nbias, gb, bias_ws, st);
 }
 
