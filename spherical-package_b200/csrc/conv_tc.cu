@@ -329,6 +329,61 @@ __device__ __forceinline__ void produce_chunk(const Gather &g, const Tap *taps, 
   }
 }
 
+// 32 bytes (two neighbouring 16-byte vectors) with one load; the address is 32-byte aligned.
+__device__ __forceinline__ void ldg32(const char *p, uint4 &a, uint4 &b) {
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+               : "l"(p));
+}
+
+// The same share cut the other way, for Cp >= 16: thread = (pixel pt >> 2, vector pair pt & 3), i.e. one pixel and
+// 32 bytes of it per thread.  What limits these kernels is the SM's 128-byte-per-cycle data path into the register
+// file, which the gathered bytes share with the tap-table reads and the tensor core's operand reads; taking two
+// vectors of one pixel instead of one vector of two pixels halves the tap bytes a thread reads per gathered byte
+// (and the load instructions, with 32-byte loads).  c0 is the first channel of the pair.
+template <int STRIDE, int NTI, bool PLAN>
+__device__ __forceinline__ void produce_chunk_pair(const Gather &g, const Tap *taps, const int2 *rest, const PlanView<float> &pv,
+                                                   const char *img, int slot, int c0, int pt, uint8_t *As) {
+  static_assert(kProducerThreads == kTileM * 4, "one (pixel, vector pair) per producer thread");
+  static_assert(STRIDE > 0 && NTI > 0, "static tap counts only");
+  const int vp = pt & 3, pl = pt >> 2;
+  const bool valid = slot < g.K;
+  const char *imgc = img + c0 * 2;
+  const int row = (valid ? slot : 0) * kTileM + pl;
+  const Tap *trow = taps + (size_t)row * STRIDE;
+  Acc8 a0, a1;
+  acc_zero(a0);
+  acc_zero(a1);
+  if (valid) {
+    uint4 qa[NTI], qb[NTI];
+    uint32_t w[NTI];
+#pragma unroll
+    for (int t = 0; t < NTI; t++) {
+      const Tap a = trow[t];
+      w[t] = a.w;
+      ldg32(imgc + a.off, qa[t], qb[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < NTI; t++) {
+      acc_fma(a0, w[t], qa[t]);
+      acc_fma(a1, w[t], qb[t]);
+    }
+    if (PLAN) {
+      const int2 rr = rest[row];
+      for (int e = rr.x; e < rr.y; e++) {
+        uint4 xa, xb;
+        ldg32(imgc + (size_t)__ldg(pv.src + e) * (g.Cp * 2), xa, xb);
+        const uint32_t we = tap_weight(__ldg(pv.w + e));
+        acc_fma(a0, we, xa);
+        acc_fma(a1, we, xb);
+      }
+    }
+  }
+  uint8_t *drow = As + pl * 128;
+  *(uint4 *)(drow + (((2 * vp) ^ (pl & 7)) << 4)) = acc_pack(a0);
+  *(uint4 *)(drow + (((2 * vp + 1) ^ (pl & 7)) << 4)) = acc_pack(a1);
+}
+
 template <int MODE, int NT>
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -461,6 +516,23 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         const int pix = tile_pixel(pl, ty, tx, kTH, g.GH, g.GW);
         Tap *dst = sm.taps + (size_t)idx * g.nt;
         if (MODE == MODE_DIRECT) {
+          if constexpr (NT == 4) {
+            if (g.P == 0 && g.map != nullptr) {
+              // entry built in registers and stored as two 16-byte vectors (field-by-field stores at this
+              // 32-byte stride collide eight ways)
+              Tap t[4];
+              if (pix >= 0) {
+                const float *m = g.map + 2 * ((size_t)pix * g.K + slot);
+                taps_from_xy<4>(g, __ldg(m), __ldg(m + 1), t);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++) { t[i].off = zero_off; t[i].w = 0u; }
+              }
+              ((uint4 *)dst)[0] = make_uint4((uint32_t)t[0].off, t[0].w, (uint32_t)t[1].off, t[1].w);
+              ((uint4 *)dst)[1] = make_uint4((uint32_t)t[2].off, t[2].w, (uint32_t)t[3].off, t[3].w);
+              continue;
+            }
+          }
           if (pix >= 0) fill_taps_any(g, pix, slot, dst);
           else fill_taps_zero(g, dst);
         } else {
@@ -469,26 +541,34 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
             e0 = __ldg(pv.offsets + pix * g.K + slot);
             e1 = __ldg(pv.offsets + pix * g.K + slot + 1);
           }
+          Tap t[kPlanTaps];
 #pragma unroll
           for (int i = 0; i < kPlanTaps; i++) {
             const bool in = e0 + i < e1;
-            dst[i].off = in ? __ldg(pv.src + e0 + i) * pitch : zero_off;
-            dst[i].w = tap_weight(in ? __ldg(pv.w + e0 + i) : 0.0f);
+            t[i].off = in ? __ldg(pv.src + e0 + i) * pitch : zero_off;
+            t[i].w = tap_weight(in ? __ldg(pv.w + e0 + i) : 0.0f);
           }
+          static_assert(kPlanTaps == 4, "two 16-byte stores per entry");
+          ((uint4 *)dst)[0] = make_uint4((uint32_t)t[0].off, t[0].w, (uint32_t)t[1].off, t[1].w);
+          ((uint4 *)dst)[1] = make_uint4((uint32_t)t[2].off, t[2].w, (uint32_t)t[3].off, t[3].w);
           sm.rest[idx] = make_int2(min(e0 + kPlanTaps, e1), e1);
         }
       }
       producer_bar();
       int cslot = 0, cblock = 0;  // Cp >= 64: chunk = cblock * K + cslot, kept incrementally (no division)
+      // (pixel, vector pair) threads when a pair lies inside one slot and the tap count is static; else
+      // (two pixels, one vector)
+      const bool pairs = g.Cp >= 16 && (MODE == MODE_PLAN || NT > 0);
+      const int vsel = pairs ? (pt & 3) * 2 : (pt & 7);  // this thread's (first) 16-byte vector of a chunk row
       for (int chunk = 0; alive && chunk < p.nchunks; chunk++, ring.next(S)) {
         const int s = ring.s;
         int slot, c0;
         if (g.Cp >= 64) {
           slot = cslot;
-          c0 = cblock * 64 + (pt & 7) * 8;
+          c0 = cblock * 64 + vsel * 8;
           if (++cslot == g.K) { cslot = 0; cblock++; }
         } else {
-          chunk_vec(g.Cp, g.K, chunk, pt & 7, slot, c0);
+          chunk_vec(g.Cp, g.K, chunk, vsel, slot, c0);
         }
         if (!mbar_wait(sm.empty + s, ring.ph ^ 1u, sm.abort_flag)) { alive = false; break; }
         if (pt == 0) {
@@ -498,7 +578,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         }
         uint8_t *As = sm.A + (size_t)s * kAStageBytes;
         if (MODE == MODE_DIRECT) {
-          produce_chunk<NT, NT, false>(g, sm.taps, nullptr, pv, img, slot, c0, pt, As);
+          if constexpr (NT > 0) {
+            if (pairs) produce_chunk_pair<(NT > 0 ? NT : 1), (NT > 0 ? NT : 1), false>(g, sm.taps, nullptr, pv, img, slot, c0, pt, As);
+            else produce_chunk<NT, NT, false>(g, sm.taps, nullptr, pv, img, slot, c0, pt, As);
+          } else {
+            produce_chunk<NT, NT, false>(g, sm.taps, nullptr, pv, img, slot, c0, pt, As);
+          }
+        } else if (pairs) {
+          if (plan_nti >= 3) produce_chunk_pair<kPlanTaps, 4, true>(g, sm.taps, sm.rest, pv, img, slot, c0, pt, As);
+          else if (plan_nti == 2) produce_chunk_pair<kPlanTaps, 2, true>(g, sm.taps, sm.rest, pv, img, slot, c0, pt, As);
+          else produce_chunk_pair<kPlanTaps, 1, true>(g, sm.taps, sm.rest, pv, img, slot, c0, pt, As);
         } else if (plan_nti >= 3) {
           produce_chunk<kPlanTaps, 4, true>(g, sm.taps, sm.rest, pv, img, slot, c0, pt, As);
         } else if (plan_nti == 2) {
