@@ -384,6 +384,92 @@ __device__ __forceinline__ void produce_chunk_pair(const Gather &g, const Tap *t
   *(uint4 *)(drow + (((2 * vp + 1) ^ (pl & 7)) << 4)) = acc_pack(a1);
 }
 
+// All chunks of one tile for the common shape (Cp >= 64, static tap count, (pixel, vector pair) threads) with
+// the per-chunk instruction count pared down: 32-bit shared-space addresses kept in registers, the tap row and the
+// image pointer advanced incrementally with the (channel block, slot) cursor, no generic-address arithmetic.
+// Returns false if a wait gave up.
+template <int STRIDE, int NTI, bool PLAN>
+__device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem &sm, const PlanView<float> &pv, const char *img,
+                                                  int nb, int pt, int lane, Ring &ring) {
+  static_assert(kProducerThreads == kTileM * 4, "one (pixel, vector pair) per producer thread");
+  const Gather &g = p.g;
+  const int S = p.stages, vp = pt & 3, pl = pt >> 2;
+  const uint32_t tap_slot_bytes = kTileM * STRIDE * sizeof(Tap);
+  const uint32_t taps0 = smem_u32(sm.taps) + pl * (STRIDE * (uint32_t)sizeof(Tap));
+  const uint32_t a0s = smem_u32(sm.A) + pl * 128 + (((2 * vp) ^ (pl & 7)) << 4);
+  const uint32_t a1s = smem_u32(sm.A) + pl * 128 + (((2 * vp + 1) ^ (pl & 7)) << 4);
+  const uint32_t full0 = smem_u32(sm.full), empty0 = smem_u32(sm.empty);
+  const uint32_t bbytes = (uint32_t)p.Npb * 128;
+  const __nv_bfloat16 *wsrc = p.wp + (size_t)nb * p.nchunks * p.Npb * kChunk;
+  const char *imgc = img + vp * 32;  // advanced by 128 bytes per channel block
+  uint32_t taps_s = taps0;
+  int slot = 0;
+  for (int chunk = 0; chunk < p.nchunks; chunk++, ring.next(S)) {
+    const int s = ring.s;
+    if (!mbar_wait_s(empty0 + 8 * s, ring.ph ^ 1u, sm.abort_flag)) return false;
+    if (pt == 0) {
+      mbar_arrive_expect_tx(sm.full + s, bbytes);
+      bulk_copy_g2s(sm.Bw + (size_t)s * bbytes, wsrc + (size_t)chunk * p.Npb * kChunk, bbytes, sm.full + s);
+    }
+    uint4 qa[NTI], qb[NTI];
+    uint32_t w[NTI];
+    {
+      // table entry of (slot, pixel): NTI taps of 8 bytes, read as 16-byte vectors where the entry is 16-byte
+      // aligned (STRIDE even), else tap by tap
+      uint32_t tw[2 * ((NTI + 1) / 2) * 2];
+      if constexpr (STRIDE % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < (NTI + 1) / 2; i++) {
+          const uint4 t2 = lds128(taps_s + 16 * i);
+          tw[4 * i] = t2.x; tw[4 * i + 1] = t2.y; tw[4 * i + 2] = t2.z; tw[4 * i + 3] = t2.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NTI; i++) {
+          const uint2 t1 = lds64(taps_s + 8 * i);
+          tw[2 * i] = t1.x; tw[2 * i + 1] = t1.y;
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < NTI; t++) {
+        w[t] = tw[2 * t + 1];
+        ldg32(imgc + (int)tw[2 * t], qa[t], qb[t]);
+      }
+    }
+    Acc8 a0, a1;
+    acc_zero(a0);
+    acc_zero(a1);
+#pragma unroll
+    for (int t = 0; t < NTI; t++) {
+      acc_fma(a0, w[t], qa[t]);
+      acc_fma(a1, w[t], qb[t]);
+    }
+    if (PLAN) {
+      const int2 rr = sm.rest[slot * kTileM + pl];
+      for (int e = rr.x; e < rr.y; e++) {
+        uint4 xa, xb;
+        ldg32(imgc + (size_t)__ldg(pv.src + e) * (g.Cp * 2), xa, xb);
+        const uint32_t we = tap_weight(__ldg(pv.w + e));
+        acc_fma(a0, we, xa);
+        acc_fma(a1, we, xb);
+      }
+    }
+    sts128(a0s + s * kAStageBytes, acc_pack(a0));
+    sts128(a1s + s * kAStageBytes, acc_pack(a1));
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_s(full0 + 8 * s);
+    // cursor: next slot of this channel block, or slot 0 of the next block
+    taps_s += tap_slot_bytes;
+    if (++slot == g.K) {
+      slot = 0;
+      taps_s = taps0;
+      imgc += 128;
+    }
+  }
+  return true;
+}
+
 template <int MODE, int NT>
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -555,6 +641,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         }
       }
       producer_bar();
+      if (g.Cp >= 64 && (MODE == MODE_PLAN || NT > 0)) {  // the common shape: lean per-chunk loop
+        if (MODE == MODE_PLAN) {
+          if (plan_nti >= 3) alive = produce_tile_lean<kPlanTaps, 4, true>(p, sm, pv, img, nb, pt, lane, ring);
+          else if (plan_nti == 2) alive = produce_tile_lean<kPlanTaps, 2, true>(p, sm, pv, img, nb, pt, lane, ring);
+          else alive = produce_tile_lean<kPlanTaps, 1, true>(p, sm, pv, img, nb, pt, lane, ring);
+        } else {
+          alive = produce_tile_lean<(NT > 0 ? NT : 1), (NT > 0 ? NT : 1), false>(p, sm, pv, img, nb, pt, lane, ring);
+        }
+        continue;
+      }
       int cslot = 0, cblock = 0;  // Cp >= 64: chunk = cblock * K + cslot, kept incrementally (no division)
       // (pixel, vector pair) threads when a pair lies inside one slot and the tap count is static; else
       // (two pixels, one vector)

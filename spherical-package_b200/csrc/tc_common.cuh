@@ -60,6 +60,47 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
   }
 }
 
+// ---- the same on 32-bit shared-space addresses (hot loops keep them in registers) -------------------
+__device__ __forceinline__ bool mbar_try_wait_s(uint32_t bar_s, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar_s), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_s(uint32_t bar_s, uint32_t parity, volatile int *abort_flag) {
+  if (mbar_try_wait_s(bar_s, parity, kSuspendHintNs)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+    if (mbar_try_wait_s(bar_s, parity, kSuspendHintNs)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void mbar_arrive_s(uint32_t bar_s) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_s) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr_s) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr_s));
+  return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr_s) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr_s));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr_s, const uint4 &v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr_s), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 // Make generic-proxy shared-memory writes visible to the async proxy (tcgen05.mma operand reads).
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
