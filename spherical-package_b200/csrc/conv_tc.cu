@@ -19,6 +19,8 @@
 // reference does the same work per image as im2col kernel + cuBLAS SGEMM + bias
 // kernel with a (Cin*K, OH*OW) column buffer in HBM
 // (src/cuda/mapped_convolution_layer.cu:16-193).
+#include <cuda.h>
+#include <string.h>
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -40,6 +42,19 @@ constexpr int kSmemLimit = 227 * 1024;
 constexpr int kTmemCols = 512;
 
 enum { MODE_DIRECT = 0, MODE_PLAN = 1 };
+
+// Developer aid (-DSPH_TC_TIMING): cycles one thread of every role of tc_gemm_kernel spends in each phase, summed
+// over all CTAs; read with sph_debug_tc_timing().
+#ifdef SPH_TC_TIMING
+__device__ unsigned long long g_tc_timing[16];
+#define TC_TIC(var) const long long var = clock64()
+#define TC_TOC(var, slot) atomicAdd(&g_tc_timing[slot], (unsigned long long)(clock64() - var))
+#define TC_COUNT(slot) atomicAdd(&g_tc_timing[slot], 1ull)
+#else
+#define TC_TIC(var)
+#define TC_TOC(var, slot)
+#define TC_COUNT(slot)
+#endif
 
 // ---- column <-> (slot, channel) mapping -------------------------------------------------------
 // Channels are padded to Cp (a multiple of 8 that divides 64, or a multiple of 64).  With Cp >= 64 a chunk
@@ -256,6 +271,7 @@ struct TcParams {
   int out_pitch;            // multiply-first adjoint), no bias
   int *status;              // set to 1 if a bounded wait gave up
   int B, Nout, Npb, nblk, nchunks, tiles_x, tiles_y, stages;
+  int use_out_map;          // outputs leave through the tensor map passed beside these parameters
 };
 
 struct Smem {
@@ -265,7 +281,11 @@ struct Smem {
   uint64_t *full, *empty, *tfull, *tempty;
   uint32_t *tmem_ptr;
   volatile int *abort_flag;
+  float *ostage;  // [4 epilogue warps][kOutStageCh channels][32 pixels] output rows on their way to memory
 };
+
+constexpr int kOutStageCh = 16;
+constexpr int kOutStageBytes = kEpilogueWarps * kOutStageCh * 32 * 4;
 
 inline size_t gemm_smem_bytes(int stages, int Npb, int K, int nt, bool direct) {
   size_t s = 1024;  // alignment slack
@@ -273,6 +293,7 @@ inline size_t gemm_smem_bytes(int stages, int Npb, int K, int nt, bool direct) {
   s += (size_t)K * kTileM * nt * sizeof(Tap);
   if (!direct) s += (size_t)K * kTileM * sizeof(int2);
   s += 8 * (2 * stages + 4) + 16;
+  s += kOutStageBytes + 128;
   return s;
 }
 
@@ -292,6 +313,7 @@ __device__ inline Smem carve(uint8_t *raw, const TcParams &p, bool direct) {
   s.tempty = s.tfull + 2;
   s.tmem_ptr = (uint32_t *)(s.tempty + 2);
   s.abort_flag = (volatile int *)(s.tmem_ptr + 1);
+  s.ostage = (float *)(((uintptr_t)(s.abort_flag + 1) + 127) & ~(uintptr_t)127);  // tensor stores read 128-byte aligned rows
   return s;
 }
 
@@ -471,7 +493,7 @@ __device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem 
 }
 
 template <int MODE, int NT>
-__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) {
+__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, const __grid_constant__ CUtensorMap out_map) {
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = carve(smem_raw, p, MODE == MODE_DIRECT);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -511,9 +533,47 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
       const int b = rest / tiles_per_image, t2 = rest % tiles_per_image;
       const int pix = tile_pixel(warp * 32 + lane, t2 / p.tiles_x, t2 % p.tiles_x, kTH, g.GH, g.GW);
       const int buf = tl & 1;
+      TC_TIC(t_wait);
       if (!mbar_wait(sm.tfull + buf, (tl >> 1) & 1, sm.abort_flag)) break;
+      if (tid == 0) { TC_TOC(t_wait, 5); }
+      TC_TIC(t_drain);
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * 256;
+      const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
+      if (p.use_out_map) {
+        // This warp's 32 pixels are two rows of 16.  Sixteen channels at a time go through shared memory as
+        // [channel][row][x] and leave as one tiled tensor store (box 16 x 2 x 16 channels) issued by lane 0, so the
+        // outputs cost this warp shared-memory stores only; the copy engine writes the 64-byte row segments and
+        // clips whatever lies outside the image or beyond the last channel.
+        const uint32_t st_s = smem_u32(sm.ostage) + warp * (kOutStageCh * 32 * 4);
+        const uint32_t st_lane = st_s + lane * 4;
+        for (int n0 = 0; n0 < p.Npb; n0 += kOutStageCh) {
+          uint32_t h[16];
+          tmem_ld_32x16(taddr + n0, h);
+          float bv[16];
+#pragma unroll
+          for (int j = 0; j < 16; j++) {
+            const int n = nb * p.Npb + n0 + j;
+            bv[j] = (p.bias && n < p.Nout) ? __ldg(p.bias + n) : 0.0f;
+          }
+          tmem_ld_wait();
+          if (lane == 0) bulk_wait_read();  // the previous pass has left the staging rows
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 16; j++) sts32(st_lane + j * 128, __float_as_uint(__uint_as_float(h[j]) + bv[j]));
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            tensor_store_4d(&out_map, st_s, tx * kTW, ty * kTH + 2 * warp, nb * p.Npb + n0, b);
+            bulk_commit();
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.tempty + buf);
+        if (tid == 0) { TC_TOC(t_drain, 6); }
+        continue;
+      }
       float *orow = p.out + ((size_t)b * p.Nout) * npix + (pix >= 0 ? pix : 0);
       for (int n0 = 0; n0 < p.Npb; n0 += 32) {
         uint32_t r[32];
@@ -548,7 +608,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.tempty + buf);
+      if (tid == 0) { TC_TOC(t_drain, 6); }
     }
+    bulk_wait_all();  // this thread's bulk copies are complete before the CTA may exit
   } else if (warp == kEpilogueWarps) {
     // ---------------- MMA issuer (one thread) ----------------
     if (lane == 0) {
@@ -558,12 +620,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
       bool alive = true;
       for (int tile = blockIdx.x; alive && tile < total_tiles; tile += gridDim.x, tl++) {
         const int buf = tl & 1;
+        TC_TIC(t_te);
         if (!mbar_wait(sm.tempty + buf, ((tl >> 1) & 1) ^ 1, sm.abort_flag)) break;
+        TC_TOC(t_te, 4);
         tc_fence_after();
         const uint32_t d = tmem_base + buf * 256;
         for (int chunk = 0; chunk < p.nchunks; chunk++, ring.next(S)) {
           const int s = ring.s;
+          TC_TIC(t_full);
           if (!mbar_wait(sm.full + s, ring.ph, sm.abort_flag)) { alive = false; break; }
+          TC_TOC(t_full, 3);
           tc_fence_after();
           const uint64_t a0 = smem_desc_sw128(smem_u32(sm.A + (size_t)s * kAStageBytes), 16, 1024);
           const uint64_t b0 = smem_desc_sw128(smem_u32(sm.Bw + (size_t)s * p.Npb * 128), 16, 1024);
@@ -595,8 +661,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
       const int b = rest / tiles_per_image, t2 = rest % tiles_per_image;
       const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
       const char *img = (const char *)g.xh + (size_t)b * (shw + 1) * pitch;
+      TC_TIC(t_b0);
       producer_bar();  // every producer is done reading the previous tile's taps
+      if (pt == 0) { TC_TOC(t_b0, 2); }
       if (!alive) { producer_bar(); continue; }
+      TC_TIC(t_fill);
       for (int idx = pt; idx < g.K * kTileM; idx += kProducerThreads) {
         const int slot = idx / kTileM, pl = idx % kTileM;
         const int pix = tile_pixel(pl, ty, tx, kTH, g.GH, g.GW);
@@ -641,6 +710,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         }
       }
       producer_bar();
+      if (pt == 0) { TC_TOC(t_fill, 0); TC_COUNT(7); }
+      TC_TIC(t_loop);
       if (g.Cp >= 64 && (MODE == MODE_PLAN || NT > 0)) {  // the common shape: lean per-chunk loop
         if (MODE == MODE_PLAN) {
           if (plan_nti >= 3) alive = produce_tile_lean<kPlanTaps, 4, true>(p, sm, pv, img, nb, pt, lane, ring);
@@ -649,6 +720,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p) 
         } else {
           alive = produce_tile_lean<(NT > 0 ? NT : 1), (NT > 0 ? NT : 1), false>(p, sm, pv, img, nb, pt, lane, ring);
         }
+        if (pt == 0) { TC_TOC(t_loop, 1); }
         continue;
       }
       int cslot = 0, cblock = 0;  // Cp >= 64: chunk = cblock * K + cslot, kept incrementally (no division)
@@ -1276,10 +1348,40 @@ void to_nhwc(const void *src, __nv_bfloat16 *xh, int64_t B, int64_t CH, int Cp, 
   nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW + 1, 64), cdiv(Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, Cp, (int)HW);
 }
 
+// Tensor map of the float32 output (B, Nout, GH, GW) with the epilogue's box: 16 pixels x 2 rows x kOutStageCh channels.
+// Needs rows that start 16-byte aligned; returns false (plain stores are used then) if the map cannot be made.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void *f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return (EncodeTiledFn)f;
+  }();
+  return fn;
+}
+
+bool make_out_map(CUtensorMap *m, float *out, int64_t B, int64_t Nout, int64_t GH, int64_t GW) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || out == nullptr || (GW & 3) != 0 || ((uintptr_t)out & 15) != 0) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)GW, (cuuint64_t)GH, (cuuint64_t)Nout, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)GW * 4, (cuuint64_t)GW * GH * 4, (cuuint64_t)Nout * GW * GH * 4};
+  const cuuint32_t box[4] = {(cuuint32_t)kTW, 2, (cuuint32_t)kOutStageCh, 1}, estr[4] = {1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int MODE, int NT>
-void launch_gemm(const TcParams &p, int grid, size_t smem, cudaStream_t st) {
+void launch_gemm(TcParams p, int grid, size_t smem, cudaStream_t st) {
+  CUtensorMap out_map;
+  memset(&out_map, 0, sizeof(out_map));
+  p.use_out_map = (p.out_h == nullptr && make_out_map(&out_map, p.out, p.B, p.Nout, p.g.GH, p.g.GW)) ? 1 : 0;
   cudaFuncSetAttribute(tc_gemm_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  tc_gemm_kernel<MODE, NT><<<grid, kThreads, smem, st>>>(p);
+  tc_gemm_kernel<MODE, NT><<<grid, kThreads, smem, st>>>(p, out_map);
 }
 
 // ---- multiply-first adjoint -------------------------------------------------------------------------
@@ -1540,3 +1642,16 @@ int tc_tconv_backward_weight(const void *gout, const void *x, const void *map, c
 }
 
 }  // namespace sph
+
+#ifdef SPH_TC_TIMING
+// out[16]: accumulated counters of tc_gemm_kernel (0 fill, 1 chunk loop, 2 tile barrier, 3 MMA wait for operands,
+// 4 MMA wait for a free accumulator, 5 epilogue wait for the accumulator, 6 epilogue drain, 7 tiles); reset != 0 clears.
+extern "C" int sph_debug_tc_timing(unsigned long long *out, int reset) {
+  if (out && cudaMemcpyFromSymbol(out, sph::g_tc_timing, sizeof(unsigned long long) * 16) != cudaSuccess) return 1;
+  if (reset) {
+    unsigned long long z[16] = {0};
+    if (cudaMemcpyToSymbol(sph::g_tc_timing, z, sizeof(z)) != cudaSuccess) return 1;
+  }
+  return 0;
+}
+#endif

@@ -114,6 +114,28 @@ __device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gm
                : "memory");
 }
 
+// ---- bulk async copy shared -> global (store), tracked in bulk groups of the issuing thread ----------
+// Both addresses 16-byte aligned, size a multiple of 16 bytes.  Shared-memory writes made with ordinary stores
+// must be followed by fence_proxy_async() before the copy is issued.
+__device__ __forceinline__ void bulk_store_s2g(void *dst_gmem, uint32_t src_s, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem), "r"(src_s), "r"(bytes) : "memory");
+}
+// Tiled tensor store shared -> global through a tensor map (4-D box, coordinates innermost first).  The innermost
+// coordinate times the element size must be a multiple of 16 bytes; boxes that stick out of the tensor are clipped.
+__device__ __forceinline__ void tensor_store_4d(const void *tmap, uint32_t src_s, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tmap), "r"(src_s),
+               "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until the copies issued by this thread have read their shared-memory source (it may be overwritten then)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// until the copies issued by this thread are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void sts32(uint32_t addr_s, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr_s), "r"(v) : "memory");
+}
+
 // ---- tensor memory ----------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
