@@ -916,22 +916,25 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
     }
   } else if constexpr (WT && NT > 0) {
     // ---------------- producers, warp-private taps ----------------
+    // Thread = (chunk pair h, pixel pl, vector pair vp): one pixel and 32 bytes of it for two chunks of the group;
+    // a warp covers 8 pixels of one chunk pair and decodes exactly the 16 (chunk, pixel) tap entries it reads.
+    static_assert(GRP == 4 && kProducerThreads == 2 * kDwPix * 4, "two chunk pairs x 64 pixels x 4 vector pairs");
     const int pt = tid - kFirstProducerThread, pw = pt >> 5;
-    const int v = lane & 7, pxl = lane >> 3, pl = pw * 4 + pxl;  // gathering role: 16-byte vector v of pixel pl
-    constexpr int kEnt = GRP * 4;                                // (chunk, pixel) entries a warp decodes per step
-    static_assert(kEnt <= 32, "one decoding lane per entry");
-    Tap *wt = sm.taps + (size_t)pw * (2 * kEnt * NT);            // this warp's two table halves
-    // decoding role: lane e < kEnt owns chunk e >> 2 of the group and pixel e & 3 of the warp
-    const bool dec = lane < kEnt && (lane >> 2) < ncg;
-    const int e_pl = pw * 4 + (lane & 3);
+    const int h = pt >> 8, pl = (pt & 255) >> 2, vp = pt & 3, pxl = lane >> 2;
+    constexpr int kEnt = 16;                                   // (chunk of the pair, pixel) entries per warp and step
+    constexpr uint32_t kEntBytes = NT * sizeof(Tap);
+    const uint32_t wt_s = smem_u32(sm.taps) + pw * (2 * kEnt * kEntBytes);  // this warp's two table halves
+    // decoding role: lane e < 16 owns chunk 2h + (e >> 3) of the group and pixel e & 7 of the warp
+    const bool dec = lane < kEnt && (2 * h + (lane >> 3)) < ncg;
+    const int e_pl = (pw & 7) * 8 + (lane & 7);
     int e_slot = 0;
-    if (dec) { int c0; chunk_vec(g.Cp, g.K, chunk0 + (lane >> 2), 0, e_slot, c0); }
-    int g_coff[GRP];
+    if (dec) { int c0; chunk_vec(g.Cp, g.K, chunk0 + 2 * h + (lane >> 3), 0, e_slot, c0); }
+    int coff[2];
 #pragma unroll
-    for (int gi = 0; gi < GRP; gi++) {
+    for (int c = 0; c < 2; c++) {
       int slot = 0, c0 = 0;
-      if (gi < ncg) chunk_vec(g.Cp, g.K, chunk0 + gi, v, slot, c0);
-      g_coff[gi] = c0 * 2;
+      if (2 * h + c < ncg) chunk_vec(g.Cp, g.K, chunk0 + 2 * h + c, 2 * vp, slot, c0);
+      coff[c] = c0 * 2;
     }
     const int zero_off = g.SH * g.SW * g.Cp * 2;
     // position (image, tile row, tile column) of the step whose map coordinate is fetched next
@@ -951,7 +954,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         my = __ldg(m + 1);
       }
     };
-    auto decode_to = [&](Tap *dst) {
+    auto decode_to = [&](uint32_t dst_s) {
       if (lane < kEnt) {
         Tap t[NT];
         if (dec && pix_dec >= 0) taps_from_xy<NT>(g, mx, my, t);
@@ -959,30 +962,44 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
 #pragma unroll
           for (int i = 0; i < NT; i++) { t[i].off = zero_off; t[i].w = 0u; }
         }
+        const uint32_t d = dst_s + lane * kEntBytes;
+        if constexpr (NT == 4) {
+          sts128(d, make_uint4((uint32_t)t[0].off, t[0].w, (uint32_t)t[1].off, t[1].w));
+          sts128(d + 16, make_uint4((uint32_t)t[2].off, t[2].w, (uint32_t)t[3].off, t[3].w));
+        } else {
 #pragma unroll
-        for (int i = 0; i < NT; i++) dst[lane * NT + i] = t[i];
+          for (int i = 0; i < NT; i++) {
+            sts32(d + 8 * i, (uint32_t)t[i].off);
+            sts32(d + 8 * i + 4, t[i].w);
+          }
+        }
       }
     };
     int b_cur = 0;
     if (step_lo < step_hi) {
       fetch();
       b_cur = b_dec;
-      decode_to(wt);
+      decode_to(wt_s);
     }
     __syncwarp();
+    const uint32_t stage0_s = smem_u32(sm.stage);
+    const uint32_t full0 = smem_u32(sm.full), empty0 = smem_u32(sm.empty);
+    // this thread's two 16-byte slots of a chunk's row pl (128-byte swizzle)
+    const uint32_t d0 = pl * 128 + (((2 * vp) ^ (pl & 7)) << 4), d1 = pl * 128 + (((2 * vp + 1) ^ (pl & 7)) << 4);
     int it = 0;
     Ring ring;
     for (int step = step_lo; step < step_hi; step++, it++, ring.next(S)) {
       const char *img = (const char *)g.xh + (size_t)b_cur * (shw + 1) * g.Cp * 2;
-      const Tap *taps = wt + (it & 1) * (kEnt * NT) + pxl * NT;
+      const uint32_t taps_s = wt_s + (it & 1) * (kEnt * kEntBytes) + pxl * kEntBytes;
       const int s = ring.s;
-      const bool ok = mbar_wait(sm.empty + s, ring.ph ^ 1u, sm.abort_flag);
+      const bool ok = mbar_wait_s(empty0 + 8 * s, ring.ph ^ 1u, sm.abort_flag);
       if (!__all_sync(0xffffffffu, ok)) break;  // the whole warp leaves together
-      uint8_t *st = sm.stage + (size_t)s * stage_bytes;
+      const uint32_t st_s = stage0_s + (uint32_t)(s * stage_bytes);
       if (pt == 0) {
         const uint32_t bytes = (uint32_t)mbs * kDwGtBytes;
         mbar_arrive_expect_tx(sm.full + s, bytes);
-        bulk_copy_g2s(st + kDwColBytes, p.gt + ((size_t)step * p.mbs_total + mb0) * (kDwGtBytes / 2), bytes, sm.full + s);
+        bulk_copy_g2s(sm.stage + (size_t)s * stage_bytes + kDwColBytes, p.gt + ((size_t)step * p.mbs_total + mb0) * (kDwGtBytes / 2),
+                      bytes, sm.full + s);
       }
       const bool more = step + 1 < step_hi;
       int b_next = b_cur;
@@ -990,22 +1007,44 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
         fetch();
         b_next = b_dec;
       }
-      uint8_t *dst0 = st + pl * 128 + ((v ^ (pl & 7)) << 4);
 #pragma unroll
-      for (int gi = 0; gi < GRP; gi += 2) {
+      for (int c = 0; c < 2; c++) {
+        const int gi = 2 * h + c;
         if (gi >= ncg) break;
+        uint4 qa[NT], qb[NT];
+        uint32_t w[NT];
+        const uint32_t trow = taps_s + c * (8 * kEntBytes);
+        if constexpr (NT == 4) {
+          const uint4 ta = lds128(trow), tb = lds128(trow + 16);
+          w[0] = ta.y; w[1] = ta.w; w[2] = tb.y; w[3] = tb.w;
+          const char *ic = img + coff[c];
+          ldg32(ic + (int)ta.x, qa[0], qb[0]);
+          ldg32(ic + (int)ta.z, qa[1], qb[1]);
+          ldg32(ic + (int)tb.x, qa[2], qb[2]);
+          ldg32(ic + (int)tb.z, qa[3], qb[3]);
+        } else {
+#pragma unroll
+          for (int t = 0; t < NT; t++) {
+            const uint2 tt = lds64(trow + 8 * t);
+            w[t] = tt.y;
+            ldg32(img + coff[c] + (int)tt.x, qa[t], qb[t]);
+          }
+        }
         Acc8 a0, a1;
         acc_zero(a0);
         acc_zero(a1);
-        // a chunk past the group's end reads the zero taps its decoding lane wrote
-        gather_pair<NT>(img + g_coff[gi], img + g_coff[gi + 1], taps + gi * 4 * NT, taps + (gi + 1) * 4 * NT, NT, a0, a1);
-        *(uint4 *)(dst0 + gi * (kDwPix * 128)) = acc_pack(a0);
-        if (gi + 1 < ncg) *(uint4 *)(dst0 + (gi + 1) * (kDwPix * 128)) = acc_pack(a1);
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+          acc_fma(a0, w[t], qa[t]);
+          acc_fma(a1, w[t], qb[t]);
+        }
+        sts128(st_s + gi * (kDwPix * 128) + d0, acc_pack(a0));
+        sts128(st_s + gi * (kDwPix * 128) + d1, acc_pack(a1));
       }
-      if (more) decode_to(wt + ((it + 1) & 1) * (kEnt * NT));
+      if (more) decode_to(wt_s + ((it + 1) & 1) * (kEnt * kEntBytes));
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(sm.full + s);
+      if (lane == 0) mbar_arrive_s(full0 + 8 * s);
       b_cur = b_next;
     }
   } else {
