@@ -1220,11 +1220,19 @@ __global__ void __launch_bounds__(256) grad_image_kernel(const float *__restrict
   for (int i = threadIdx.x; i < 128 * 8; i += 256) {
     const int r = i >> 3, v = i & 7, n = mb * 128 + r;
     float f[8];
+    {
+      // the 8 pixels of vector v are consecutive in one image row: two 16-byte loads when the row segment is
+      // inside the image and 16-byte aligned
+      const int y = ty * kDwTH + (v >> 1), x0 = tx * kTW + (v & 1) * 8;
+      const float *src = gsrc + ((size_t)b * N + n) * npix + (size_t)y * GW + x0;
+      if (n < N && y < GH && x0 + 8 <= GW && (GW & 3) == 0 && ((uintptr_t)gsrc & 15) == 0) {
+        const float4 a = __ldg((const float4 *)src), c = __ldg((const float4 *)src + 1);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+        f[4] = c.x; f[5] = c.y; f[6] = c.z; f[7] = c.w;
+      } else {
 #pragma unroll
-    for (int e = 0; e < 8; e++) {
-      const int l = v * 8 + e;
-      const int y = ty * kDwTH + (l >> 4), x = tx * kTW + (l & 15);
-      f[e] = (n < N && y < GH && x < GW) ? __ldg(gsrc + ((size_t)b * N + n) * npix + (size_t)y * GW + x) : 0.0f;
+        for (int e = 0; e < 8; e++) f[e] = (n < N && y < GH && x0 + e < GW) ? __ldg(src + e) : 0.0f;
+      }
     }
     uint4 o;
     o.x = pack_bf16(f[0], f[1]);
