@@ -426,6 +426,37 @@ __device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem 
   const char *imgc = img + vp * 32;  // advanced by 128 bytes per channel block
   uint32_t taps_s = taps0;
   int slot = 0;
+  uint4 qa[NTI], qb[NTI];
+  uint32_t w[NTI];
+  // The gather loads roll one chunk ahead: right after a chunk's values are folded into the accumulators, the loads
+  // of the next chunk are issued into the same registers - before the tile is stored, fenced and handed over and the
+  // next stage waited for - so a thread always has its loads in flight.
+  auto issue = [&]() {
+    // table entry of (slot, pixel): NTI taps of 8 bytes, read as 16-byte vectors where the entry is 16-byte aligned
+    // (STRIDE even), else tap by tap
+    uint32_t tw[2 * ((NTI + 1) / 2) * 2];
+    if constexpr (STRIDE % 2 == 0) {
+#pragma unroll
+      for (int i = 0; i < (NTI + 1) / 2; i++) {
+        const uint4 t2 = lds128(taps_s + 16 * i);
+        tw[4 * i] = t2.x; tw[4 * i + 1] = t2.y; tw[4 * i + 2] = t2.z; tw[4 * i + 3] = t2.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < NTI; i++) {
+        const uint2 t1 = lds64(taps_s + 8 * i);
+        tw[2 * i] = t1.x; tw[2 * i + 1] = t1.y;
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < NTI; t++) {
+      w[t] = tw[2 * t + 1];
+      ldg32(imgc + (int)tw[2 * t], qa[t], qb[t]);
+    }
+  };
+  // (plan mode keeps the loads inside the chunk: with its overflow loop the rolling form spills registers)
+  constexpr bool kRoll = !PLAN;
+  if (kRoll) issue();
   for (int chunk = 0; chunk < p.nchunks; chunk++, ring.next(S)) {
     const int s = ring.s;
     if (!mbar_wait_s(empty0 + 8 * s, ring.ph ^ 1u, sm.abort_flag)) return false;
@@ -433,31 +464,7 @@ __device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem 
       mbar_arrive_expect_tx(sm.full + s, bbytes);
       bulk_copy_g2s(sm.Bw + (size_t)s * bbytes, wsrc + (size_t)chunk * p.Npb * kChunk, bbytes, sm.full + s);
     }
-    uint4 qa[NTI], qb[NTI];
-    uint32_t w[NTI];
-    {
-      // table entry of (slot, pixel): NTI taps of 8 bytes, read as 16-byte vectors where the entry is 16-byte
-      // aligned (STRIDE even), else tap by tap
-      uint32_t tw[2 * ((NTI + 1) / 2) * 2];
-      if constexpr (STRIDE % 2 == 0) {
-#pragma unroll
-        for (int i = 0; i < (NTI + 1) / 2; i++) {
-          const uint4 t2 = lds128(taps_s + 16 * i);
-          tw[4 * i] = t2.x; tw[4 * i + 1] = t2.y; tw[4 * i + 2] = t2.z; tw[4 * i + 3] = t2.w;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < NTI; i++) {
-          const uint2 t1 = lds64(taps_s + 8 * i);
-          tw[2 * i] = t1.x; tw[2 * i + 1] = t1.y;
-        }
-      }
-#pragma unroll
-      for (int t = 0; t < NTI; t++) {
-        w[t] = tw[2 * t + 1];
-        ldg32(imgc + (int)tw[2 * t], qa[t], qb[t]);
-      }
-    }
+    if (!kRoll) issue();
     Acc8 a0, a1;
     acc_zero(a0);
     acc_zero(a1);
@@ -476,18 +483,19 @@ __device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem 
         acc_fma(a1, we, xb);
       }
     }
-    sts128(a0s + s * kAStageBytes, acc_pack(a0));
-    sts128(a1s + s * kAStageBytes, acc_pack(a1));
-    fence_proxy_async();
-    __syncwarp();
-    if (lane == 0) mbar_arrive_s(full0 + 8 * s);
-    // cursor: next slot of this channel block, or slot 0 of the next block
+    // cursor: next slot of this channel block, or slot 0 of the next block; its loads go out now
     taps_s += tap_slot_bytes;
     if (++slot == g.K) {
       slot = 0;
       taps_s = taps0;
       imgc += 128;
     }
+    if (kRoll && chunk + 1 < p.nchunks) issue();
+    sts128(a0s + s * kAStageBytes, acc_pack(a0));
+    sts128(a1s + s * kAStageBytes, acc_pack(a1));
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) mbar_arrive_s(full0 + 8 * s);
   }
   return true;
 }
