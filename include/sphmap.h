@@ -182,6 +182,34 @@ int sph_mapped_conv_backward_weight(const void *gout, const void *x, const void 
                                     int interp, int precision, void *ws, size_t ws_bytes, void *stream);
 
 /* ------------------------------------------------------------------------
+ * Mapped convolution with a fused ReLU: y = max(0, conv(x) + bias).  No counterpart
+ * in the reference, which applies the activation as a separate operator (two more
+ * passes over the output in forward, three in backward); arguments are those of the
+ * three functions above.
+ *   relu_forward          writes y; the clamp happens in the kernels' epilogue
+ *   relu_backward_input   gout is the gradient w.r.t. y and act_out is y itself
+ *   relu_backward_weight  (same shape as gout): the kernels read gout * (act_out > 0)
+ *                         wherever they read gout, so no masked copy is made
+ * Supported where the convolution runs on the thin-contraction kernels
+ * (Cin * K <= 32, either precision) or on the bf16 tensor-core kernels; any other
+ * shape returns SPH_ERR_UNSUPPORTED before launching anything, and the caller
+ * applies the activation itself.  Workspace sizes are those of the unfused ops.
+ * ---------------------------------------------------------------------- */
+int sph_mapped_conv_relu_forward(const void *x, const void *map, const void *iw, const void *weight,
+                                 const void *bias, void *out, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                                 int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                 int precision, void *ws, size_t ws_bytes, void *stream);
+int sph_mapped_conv_relu_backward_input(const void *gout, const void *act_out, const void *plan,
+                                        const void *weight, void *gx, int64_t B, int64_t Cin, int64_t Cout,
+                                        int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int dtype,
+                                        int precision, void *ws, size_t ws_bytes, void *stream);
+int sph_mapped_conv_relu_backward_weight(const void *gout, const void *act_out, const void *x, const void *map,
+                                         const void *iw, void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout,
+                                         int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
+                                         int dtype, int interp, int precision, void *ws, size_t ws_bytes,
+                                         void *stream);
+
+/* ------------------------------------------------------------------------
  * Mapped transposed convolution.  weight (Cin,Cout,K), bias (Cout),
  * x (B,Cin,IH,IW), out / gout (B,Cout,OH,OW); the map has the INPUT's size,
  * (IH,IW,K[,P],2), and points into the (OH,OW) output grid.

@@ -42,7 +42,10 @@ extern "C" const char *sph_status_string(int status) {
 
 extern "C" int sph_version(void) { return 100; }
 
-namespace sph { unsigned long long g_launch_count = 0; }
+namespace sph {
+unsigned long long g_launch_count = 0;
+thread_local Fusion g_fusion;
+}  // namespace sph
 extern "C" unsigned long long sph_launch_count(void) { return __atomic_load_n(&sph::g_launch_count, __ATOMIC_RELAXED); }
 
 extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
@@ -85,6 +88,7 @@ extern "C" int sph_mapped_conv_forward(const void *x, const void *map, const voi
     return SPH_BY_DTYPE(small_fwd, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, st);
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
+  if (fusion_active()) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_gemm, false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1,
                       bias, out, Cout, B, st);
 }
@@ -99,11 +103,14 @@ extern "C" int sph_mapped_conv_backward_input(const void *gout, const void *plan
   if (!gout || !plan || !weight || !gx) return SPH_ERR_INVALID_ARGUMENT;
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  // the thin kernels stream grad_output once per operator; masking it in both would cost more than one masking pass
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4) && g_fusion.mask) return SPH_ERR_UNSUPPORTED;
   if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
     return SPH_BY_DTYPE(small_adjoint, gout, plan, Cout, OH * OW, K, IH * IW, weight, K, Cin * K, 1, nullptr, gx, Cin, B, ws,
                         ws_bytes, st);
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st);
+  if (fusion_active()) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_gemm, true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH * IW, 0, weight, K, Cin * K, 1,
                       nullptr, gx, Cin, B, st);
 }
@@ -122,13 +129,54 @@ extern "C" int sph_mapped_conv_backward_weight(const void *gout, const void *x, 
     if (cudaMemsetAsync(gw, 0, ts * (size_t)(Cout * Cin * K), st) != cudaSuccess) return SPH_ERR_CUDA;
     return cudaMemsetAsync(gb, 0, ts * (size_t)Cout, st) == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
   }
+  if (small_ok(Cin, K, Cout, ts) && g_fusion.mask) return SPH_ERR_UNSUPPORTED;  // see backward_input
   if (small_ok(Cin, K, Cout, ts))
     return SPH_BY_DTYPE(small_dw, gout, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout,
                         OH * OW, gb, ws, ws_bytes, st);
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
+  if (fusion_active()) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_dw, gout, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout,
                       OH * OW, gb, ws, ws_bytes, st);
+}
+
+// ---- convolution with a fused ReLU (no counterpart in the reference; see sphmap.h) -------------------------
+namespace {
+struct FusionScope {
+  FusionScope(bool relu_out, const void *mask) { sph::g_fusion.relu_out = relu_out; sph::g_fusion.mask = mask; }
+  ~FusionScope() { sph::g_fusion = sph::Fusion{}; }
+};
+}  // namespace
+
+extern "C" int sph_mapped_conv_relu_forward(const void *x, const void *map, const void *iw, const void *weight,
+                                            const void *bias, void *out, int64_t B, int64_t Cin, int64_t Cout,
+                                            int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
+                                            int dtype, int interp, int precision, void *ws, size_t ws_bytes,
+                                            void *stream) {
+  FusionScope scope(true, nullptr);
+  return sph_mapped_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision,
+                                 ws, ws_bytes, stream);
+}
+
+extern "C" int sph_mapped_conv_relu_backward_input(const void *gout, const void *act_out, const void *plan,
+                                                   const void *weight, void *gx, int64_t B, int64_t Cin, int64_t Cout,
+                                                   int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int dtype,
+                                                   int precision, void *ws, size_t ws_bytes, void *stream) {
+  if (!act_out) return SPH_ERR_INVALID_ARGUMENT;
+  FusionScope scope(false, act_out);
+  return sph_mapped_conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, dtype, precision, ws, ws_bytes,
+                                        stream);
+}
+
+extern "C" int sph_mapped_conv_relu_backward_weight(const void *gout, const void *act_out, const void *x,
+                                                    const void *map, const void *iw, void *gw, void *gb, int64_t B,
+                                                    int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
+                                                    int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                                    int precision, void *ws, size_t ws_bytes, void *stream) {
+  if (!act_out) return SPH_ERR_INVALID_ARGUMENT;
+  FusionScope scope(false, act_out);
+  return sph_mapped_conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision,
+                                         ws, ws_bytes, stream);
 }
 
 extern "C" int sph_mapped_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias,

@@ -7,6 +7,17 @@
 
 namespace sph {
 
+// Activation fused into the convolution kernels, set by the *_relu entry points for the duration of one call on
+// the calling thread: relu_out clamps the forward outputs at zero in the epilogue; mask (the saved activation
+// output, same shape as grad_output) makes every kernel that reads grad_output see grad_output * (mask > 0).
+// Code paths that cannot honour it return SPH_ERR_UNSUPPORTED before launching anything.
+struct Fusion {
+  bool relu_out = false;
+  const void *mask = nullptr;
+};
+extern thread_local Fusion g_fusion;
+inline bool fusion_active() { return g_fusion.relu_out || g_fusion.mask != nullptr; }
+
 // ---- exact SIMT kernels (conv_simt.cu) -----------------------------------
 template <typename T>
 int simt_gemm(bool use_plan, const void *src, const void *map, const void *iw, const void *plan, int64_t CH, int64_t SH,

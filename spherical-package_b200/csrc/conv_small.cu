@@ -52,7 +52,7 @@ template <typename T, int INTERP, bool WEIGHTED>
 __global__ void __launch_bounds__(256)
 small_fwd_kernel(const T *__restrict__ src, const T *__restrict__ map, const T *__restrict__ iw, const T *__restrict__ wgt,
                  int64_t sm, int64_t sc, int64_t sk, const T *__restrict__ bias, T *__restrict__ out, int CH, int K, int P,
-                 int SH, int SW, int npix, int M) {
+                 int SH, int SW, int npix, int M, int relu) {
   extern __shared__ __align__(16) unsigned char small_smem[];
   T *ws = (T *)small_smem;
   for (int i = threadIdx.x; i < M * kSmallJ; i += blockDim.x) {
@@ -70,7 +70,7 @@ small_fwd_kernel(const T *__restrict__ src, const T *__restrict__ map, const T *
     T acc = bias ? __ldg(bias + m) : T(0);
 #pragma unroll
     for (int j = 0; j < kSmallJ; j++) acc += wr[j] * col[j];
-    o[(size_t)m * npix] = acc;
+    o[(size_t)m * npix] = (relu && !(acc > T(0))) ? T(0) : acc;
   }
 }
 
@@ -98,7 +98,7 @@ template <int INTERP, bool WEIGHTED>
 __global__ void __launch_bounds__(256, 2)
 small_fwd_tile_kernel(const float *__restrict__ src, const float *__restrict__ map, const float *__restrict__ iw,
                       const float *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk, const float *__restrict__ bias,
-                      float *__restrict__ out, int CH, int K, int P, int SH, int SW, int npix, int M) {
+                      float *__restrict__ out, int CH, int K, int P, int SH, int SW, int npix, int M, int relu) {
   __shared__ __align__(16) float Cs[kSmallJ][kTilePix];
   __shared__ __align__(16) float Ws[kSmallJ][kTileOut];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, b = blockIdx.y, J = CH * K;
@@ -186,6 +186,10 @@ small_fwd_tile_kernel(const float *__restrict__ src, const float *__restrict__ m
       float v[8];
 #pragma unroll
       for (int q = 0; q < 4; q++) unpack2(acc[m][q], v[2 * q], v[2 * q + 1]);
+      if (relu) {
+#pragma unroll
+        for (int q = 0; q < 8; q++) v[q] = v[q] > 0.0f ? v[q] : 0.0f;
+      }
 #pragma unroll
       for (int h = 0; h < 2; h++) {  // the two groups of four pixels
         const int px = p0 + h * 128 + lane * 4;
@@ -481,7 +485,7 @@ int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int6
   small_fwd_tile_kernel<INTERP, W><<<tgrid, 256, 0, st>>>((const float *)src, (const float *)map, (const float *)iw,     \
                                                           (const float *)wgt, sm, sc, sk, (const float *)bias,          \
                                                           (float *)out, (int)CH, (int)K, (int)P, (int)SH, (int)SW,       \
-                                                          (int)npix, (int)M)
+                                                          (int)npix, (int)M, g_fusion.relu_out ? 1 : 0)
     SPH_DISPATCH_INTERP(interp, {
       if (P > 0) SPH_FWD_TILE(true);
       else SPH_FWD_TILE(false);
@@ -494,7 +498,7 @@ int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int6
 #define SPH_SMALL_FWD(W)                                                                                              \
   small_fwd_kernel<T, INTERP, W><<<grid, 256, smem, st>>>((const T *)src, (const T *)map, (const T *)iw, (const T *)wgt, sm, \
                                                           sc, sk, (const T *)bias, (T *)out, (int)CH, (int)K, (int)P,   \
-                                                          (int)SH, (int)SW, (int)npix, (int)M)
+                                                          (int)SH, (int)SW, (int)npix, (int)M, g_fusion.relu_out ? 1 : 0)
   SPH_DISPATCH_INTERP(interp, {
     if (P > 0) SPH_SMALL_FWD(true);
     else SPH_SMALL_FWD(false);

@@ -272,6 +272,7 @@ struct TcParams {
   int *status;              // set to 1 if a bounded wait gave up
   int B, Nout, Npb, nblk, nchunks, tiles_x, tiles_y, stages;
   int use_out_map;          // outputs leave through the tensor map passed beside these parameters
+  int relu;                 // clamp the outputs at zero (fused activation)
 };
 
 struct Smem {
@@ -568,7 +569,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
           if (lane == 0) bulk_wait_read();  // the previous pass has left the staging rows
           __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 16; j++) sts32(st_lane + j * 128, __float_as_uint(__uint_as_float(h[j]) + bv[j]));
+          for (int j = 0; j < 16; j++) {
+            float o = __uint_as_float(h[j]) + bv[j];
+            if (p.relu) o = fmaxf(o, 0.0f);
+            sts32(st_lane + j * 128, __float_as_uint(o));
+          }
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) {
@@ -608,8 +613,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
 #pragma unroll
           for (int j = 0; j < 32; j++) {
             const int n = nb * p.Npb + n0 + j;
-            if (n < p.Nout && n0 + j < p.Npb)
-              orow[(size_t)n * npix] = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + n) : 0.0f);
+            if (n < p.Nout && n0 + j < p.Npb) {
+              float o = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + n) : 0.0f);
+              if (p.relu) o = fmaxf(o, 0.0f);
+              orow[(size_t)n * npix] = o;
+            }
           }
         }
       }
@@ -1157,25 +1165,35 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
 // (B, C, HW) float32 -> (B, HW + 1, Cp) bf16; channels beyond C and the extra pixel HW of every image are
 // zero (unused taps point there).  64 pixels x 64 channels per block: 256-byte row segments in, 128-byte
 // pixel rows out.
+// With `mask` (same shape as x) elements whose mask value is not positive are taken as zero (gradient of a fused ReLU).
 __global__ void __launch_bounds__(256) nchw_to_nhwc_bf16_kernel(const float *__restrict__ x, __nv_bfloat16 *__restrict__ y,
-                                                                 int C, int Cp, int HW) {
+                                                                 int C, int Cp, int HW, const float *__restrict__ mask) {
   __shared__ float tile[64][65];
   const int b = blockIdx.z, c0 = blockIdx.y * 64, p0 = blockIdx.x * 64;
   const int tid = threadIdx.x;
-  const bool vec_ok = (HW & 3) == 0;  // rows of every channel start 16-byte aligned
+  // rows of every channel start 16-byte aligned
+  const bool vec_ok = (HW & 3) == 0 && (((uintptr_t)x | (uintptr_t)mask) & 15) == 0;
 #pragma unroll
   for (int it = 0; it < 4; it++) {
     const int i = tid + it * 256, c = i >> 4, q = (i & 15) * 4;  // channel row, first of 4 pixels
     float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
     if (c0 + c < C) {
       const float *src = x + ((size_t)b * C + c0 + c) * HW + p0 + q;
+      const float *msk = mask ? mask + (src - x) : nullptr;
       if (vec_ok && p0 + q + 3 < HW) {
         f = __ldg((const float4 *)src);
+        if (msk) {
+          const float4 m = __ldg((const float4 *)msk);
+          f.x = m.x > 0.0f ? f.x : 0.0f;
+          f.y = m.y > 0.0f ? f.y : 0.0f;
+          f.z = m.z > 0.0f ? f.z : 0.0f;
+          f.w = m.w > 0.0f ? f.w : 0.0f;
+        }
       } else {
-        if (p0 + q + 0 < HW) f.x = __ldg(src + 0);
-        if (p0 + q + 1 < HW) f.y = __ldg(src + 1);
-        if (p0 + q + 2 < HW) f.z = __ldg(src + 2);
-        if (p0 + q + 3 < HW) f.w = __ldg(src + 3);
+        if (p0 + q + 0 < HW) f.x = (!msk || __ldg(msk + 0) > 0.0f) ? __ldg(src + 0) : 0.0f;
+        if (p0 + q + 1 < HW) f.y = (!msk || __ldg(msk + 1) > 0.0f) ? __ldg(src + 1) : 0.0f;
+        if (p0 + q + 2 < HW) f.z = (!msk || __ldg(msk + 2) > 0.0f) ? __ldg(src + 2) : 0.0f;
+        if (p0 + q + 3 < HW) f.w = (!msk || __ldg(msk + 3) > 0.0f) ? __ldg(src + 3) : 0.0f;
       }
     }
     tile[c][q + 0] = f.x;
@@ -1220,7 +1238,7 @@ __global__ void weight_image_kernel(const float *__restrict__ w, __nv_bfloat16 *
 // row_part[(b * tiles + tile) * mbs_total * 128 + row] (first stage of the bias gradient).
 __global__ void __launch_bounds__(256) grad_image_kernel(const float *__restrict__ gsrc, __nv_bfloat16 *__restrict__ gt, int N,
                                                           int GH, int GW, int tiles_x, int tiles_y, int mbs_total,
-                                                          float *__restrict__ row_part) {
+                                                          float *__restrict__ row_part, const float *__restrict__ mask) {
   const int t2 = blockIdx.x, mb = blockIdx.y, b = blockIdx.z;
   const int ty = t2 / tiles_x, tx = t2 % tiles_x;
   const size_t npix = (size_t)GH * GW;
@@ -1233,13 +1251,21 @@ __global__ void __launch_bounds__(256) grad_image_kernel(const float *__restrict
       // inside the image and 16-byte aligned
       const int y = ty * kDwTH + (v >> 1), x0 = tx * kTW + (v & 1) * 8;
       const float *src = gsrc + ((size_t)b * N + n) * npix + (size_t)y * GW + x0;
-      if (n < N && y < GH && x0 + 8 <= GW && (GW & 3) == 0 && ((uintptr_t)gsrc & 15) == 0) {
+      const float *msk = mask ? mask + (src - gsrc) : nullptr;  // same shape: a fused ReLU's output
+      if (n < N && y < GH && x0 + 8 <= GW && (GW & 3) == 0 && (((uintptr_t)gsrc | (uintptr_t)mask) & 15) == 0) {
         const float4 a = __ldg((const float4 *)src), c = __ldg((const float4 *)src + 1);
         f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
         f[4] = c.x; f[5] = c.y; f[6] = c.z; f[7] = c.w;
+        if (msk) {
+          const float4 ma = __ldg((const float4 *)msk), mc = __ldg((const float4 *)msk + 1);
+          const float mv[8] = {ma.x, ma.y, ma.z, ma.w, mc.x, mc.y, mc.z, mc.w};
+#pragma unroll
+          for (int e = 0; e < 8; e++) f[e] = mv[e] > 0.0f ? f[e] : 0.0f;
+        }
       } else {
 #pragma unroll
-        for (int e = 0; e < 8; e++) f[e] = (n < N && y < GH && x0 + e < GW) ? __ldg(src + e) : 0.0f;
+        for (int e = 0; e < 8; e++)
+          f[e] = (n < N && y < GH && x0 + e < GW && (!msk || __ldg(msk + e) > 0.0f)) ? __ldg(src + e) : 0.0f;
       }
     }
     uint4 o;
@@ -1399,8 +1425,10 @@ Geometry geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int 
   return g;
 }
 
-void to_nhwc(const void *src, __nv_bfloat16 *xh, int64_t B, int64_t CH, int Cp, int64_t HW, cudaStream_t st) {
-  nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW + 1, 64), cdiv(Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, Cp, (int)HW);
+void to_nhwc(const void *src, __nv_bfloat16 *xh, int64_t B, int64_t CH, int Cp, int64_t HW, cudaStream_t st,
+             const void *mask = nullptr) {
+  nchw_to_nhwc_bf16_kernel<<<dim3(cdiv(HW + 1, 64), cdiv(Cp, 64), (unsigned)B), 256, 0, st>>>((const float *)src, xh, (int)CH, Cp, (int)HW,
+                                                                                          (const float *)mask);
 }
 
 // Tensor map of the float32 output (B, Nout, GH, GW) with the epilogue's box: 16 pixels x 2 rows x kOutStageCh channels.
@@ -1471,7 +1499,7 @@ int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
   __nv_bfloat16 *T = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes + g.wp_bytes);
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
-  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st);
+  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, g_fusion.mask);  // adjoint: src is grad_output
   const int64_t wtotal = (int64_t)g.nblk * g.nchunks * g.Npb * kChunk;
   premul_weight_image_kernel<<<cdiv(wtotal, 256), 256, 0, st>>>((const float *)wgt, wp, (int)M, q.Mp, (int)K, (int)CH, g.Npb, g.nblk,
                                                                 g.nchunks, sm_, sc, sk);
@@ -1496,6 +1524,7 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
     if (q.use) return tc_adjoint_premul(q, src, plan, CH, SH, SW, K, GH, GW, wgt, sn, sc, sk, bias, out, Nout, B, ws, ws_bytes, st);
   }
   const Geometry g = geometry(B, CH, SH * SW, K, P, interp, Nout, !use_plan);
+  if (!g.ok && fusion_active()) return SPH_ERR_UNSUPPORTED;
   if (!g.ok)  // shapes the tile kernel does not cover run on the exact SIMT kernels instead
     return simt_gemm<float>(use_plan, src, map, iw, plan, CH, SH, SW, K, P, GH * GW, interp, wgt, sn, sc, sk, bias, out, Nout, B, st);
   if (!ws || ws_bytes < 256 + g.xh_bytes + g.wp_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
@@ -1503,13 +1532,14 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
   __nv_bfloat16 *xh = (__nv_bfloat16 *)((char *)ws + 256);
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
-  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st);
+  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, use_plan ? g_fusion.mask : nullptr);
   const int64_t wtotal = (int64_t)g.nblk * g.nchunks * g.Npb * kChunk;
   weight_image_kernel<<<cdiv(wtotal, 256), 256, 0, st>>>((const float *)wgt, wp, (int)Nout, (int)CH, g.Cp, (int)K, g.Npb, g.nblk,
                                                          g.nchunks, sn, sc, sk);
   TcParams p{};
   p.g = Gather{xh, (const float *)map, (const float *)iw, plan, g.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, g.nt};
   p.wp = wp; p.bias = (const float *)bias; p.out = (float *)out; p.status = status;
+  p.relu = (!use_plan && g_fusion.relu_out) ? 1 : 0;
   p.B = (int)B; p.Nout = (int)Nout; p.Npb = g.Npb; p.nblk = g.nblk; p.nchunks = g.nchunks;
   p.tiles_x = cdiv(GW, kTW); p.tiles_y = cdiv(GH, kTH); p.stages = g.stages;
   const int64_t tiles = (int64_t)B * p.tiles_x * p.tiles_y * g.nblk;
@@ -1591,6 +1621,8 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
           int64_t P, int64_t GH, int64_t GW, int interp, int64_t Nout, int64_t B, void *gw, int64_t sn, int64_t sc, int64_t sk,
           const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st) {
   const DwGeometry d = dw_geometry(B, CH, SH * SW, K, P, interp, Nout, GH, GW, Cbias);
+  // a masked gradient needs its bias sums from the (masked) imaging pass
+  if (fusion_active() && (!d.ok || !(gbias_src == A && Cbias == Nout && nbias == GH * GW))) return SPH_ERR_UNSUPPORTED;
   if (!d.ok)
     return simt_dw<float>(A, src, map, iw, CH, SH, SW, K, P, GH * GW, interp, Nout, B, gw, sn, sc, sk, gbias_src, Cbias, nbias, gb,
                           ws, ws_bytes, st);
@@ -1610,7 +1642,8 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
   float *row_part = (float *)((char *)bias_ws + simt_bias_workspace(Cbias, 4));
   float *part2 = (float *)((char *)row_part + align_up((size_t)nblocks * d.mbs_total * 128 * 4, 256));
   grad_image_kernel<<<dim3(d.tiles_x * d.tiles_y, d.mbs_total, (unsigned)B), 256, 0, st>>>(
-      (const float *)A, gt, (int)Nout, (int)GH, (int)GW, d.tiles_x, d.tiles_y, d.mbs_total, fuse_bias ? row_part : nullptr);
+      (const float *)A, gt, (int)Nout, (int)GH, (int)GW, d.tiles_x, d.tiles_y, d.mbs_total, fuse_bias ? row_part : nullptr,
+      (const float *)g_fusion.mask);
   DwParams p{};
   p.g = Gather{xh, (const float *)map, (const float *)iw, nullptr, d.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, d.nt};
   p.gt = gt; p.partial = partial; p.status = status;

@@ -264,8 +264,10 @@ struct ConvArgs {
   int dtype, interp, prec;
 };
 
+// relu: the fused variant (sph_mapped_conv_relu_*, an extension without a reference counterpart); shapes the
+// library does not fuse fall back to the plain operator plus a separate activation.
 torch::Tensor conv_forward_impl(torch::Tensor x, torch::Tensor map, const torch::Tensor *iw, torch::Tensor weight,
-                                torch::Tensor bias, int64_t K, InterpolationType it) {
+                                torch::Tensor bias, int64_t K, InterpolationType it, bool relu = false) {
   TORCH_CHECK(x.dim() == 4 && weight.dim() == 3 && bias.dim() == 1, "input (B,C,H,W), weight (Cout,Cin,K), bias (Cout)");
   check(x, "input", x);
   check_float(map, "sample_map", x);
@@ -282,15 +284,26 @@ torch::Tensor conv_forward_impl(torch::Tensor x, torch::Tensor map, const torch:
   const size_t wb = sph_conv_workspace_bytes(SPH_CONV_FORWARD, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
                                              a.interp, a.prec);
   torch::Tensor ws = workspace(wb, x);
+  if (relu) {
+    const int rc = sph_mapped_conv_relu_forward(x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr, weight.data_ptr(),
+                                                bias.data_ptr(), out.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K,
+                                                a.P, a.dtype, a.interp, a.prec, ws.data_ptr(), wb, stream());
+    if (rc != SPH_ERR_UNSUPPORTED) {
+      ok(rc, "sph_mapped_conv_relu_forward");
+      return out;
+    }
+  }
   ok(sph_mapped_conv_forward(x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr, weight.data_ptr(), bias.data_ptr(),
                              out.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp, a.prec,
                              ws.data_ptr(), wb, stream()),
      "sph_mapped_conv_forward");
+  if (relu) out.clamp_min_(0);
   return out;
 }
 
 std::vector<torch::Tensor> conv_backward_impl(torch::Tensor go, torch::Tensor map, const torch::Tensor *iw, torch::Tensor x,
-                                              torch::Tensor weight, torch::Tensor bias, int64_t K, InterpolationType it) {
+                                              torch::Tensor weight, torch::Tensor bias, int64_t K, InterpolationType it,
+                                              const torch::Tensor *act_out = nullptr) {
   TORCH_CHECK(x.dim() == 4 && go.dim() == 4 && weight.dim() == 3, "input/grad_output (B,C,H,W), weight (Cout,Cin,K)");
   go = go.contiguous();  // the reference never checks grad_output; make it dense here
   check(x, "input", x);
@@ -311,12 +324,31 @@ std::vector<torch::Tensor> conv_backward_impl(torch::Tensor go, torch::Tensor ma
   size_t wb = sph_conv_workspace_bytes(SPH_CONV_BACKWARD_INPUT, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
                                        a.dtype, a.interp, a.prec);
   torch::Tensor ws = workspace(wb, x);
+  size_t wb2 = sph_conv_workspace_bytes(SPH_CONV_BACKWARD_WEIGHT, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
+                                        a.interp, a.prec);
+  torch::Tensor ws2 = workspace(wb2, x);
+  if (act_out) {  // gradient of the fused ReLU: the kernels read grad_output * (act_out > 0)
+    TORCH_CHECK(act_out->is_contiguous() && act_out->sizes() == go.sizes() && act_out->dtype() == go.dtype() &&
+                    act_out->device() == go.device(),
+                "activation output must be a contiguous tensor like grad_output");
+    const int rc = sph_mapped_conv_relu_backward_input(go.data_ptr(), act_out->data_ptr(), plan.data_ptr(), weight.data_ptr(),
+                                                       gx.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.dtype,
+                                                       a.prec, ws.data_ptr(), wb, stream());
+    if (rc != SPH_ERR_UNSUPPORTED) {
+      ok(rc, "sph_mapped_conv_relu_backward_input");
+      ok(sph_mapped_conv_relu_backward_weight(go.data_ptr(), act_out->data_ptr(), x.data_ptr(), map.data_ptr(),
+                                              iw ? iw->data_ptr() : nullptr, gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout,
+                                              a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp, a.prec, ws2.data_ptr(), wb2,
+                                              stream()),
+         "sph_mapped_conv_relu_backward_weight");
+      return {gx, gw, gb};
+    }
+    go = at::threshold_backward(go, *act_out, 0);
+  }
   ok(sph_mapped_conv_backward_input(go.data_ptr(), plan.data_ptr(), weight.data_ptr(), gx.data_ptr(), a.B, a.Cin, a.Cout,
                                     a.IH, a.IW, a.OH, a.OW, a.K, a.dtype, a.prec, ws.data_ptr(), wb, stream()),
      "sph_mapped_conv_backward_input");
-  wb = sph_conv_workspace_bytes(SPH_CONV_BACKWARD_WEIGHT, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
-                                a.interp, a.prec);
-  torch::Tensor ws2 = workspace(wb, x);
+  wb = wb2;
   ok(sph_mapped_conv_backward_weight(go.data_ptr(), x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr,
                                      gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
                                      a.dtype, a.interp, a.prec, ws2.data_ptr(), wb, stream()),
@@ -331,6 +363,16 @@ torch::Tensor mapped_conv_forward(torch::Tensor x, torch::Tensor map, torch::Ten
 std::vector<torch::Tensor> mapped_conv_backward(torch::Tensor go, torch::Tensor map, torch::Tensor x, torch::Tensor w,
                                                 torch::Tensor b, int64_t K, InterpolationType it) {
   return conv_backward_impl(go, map, nullptr, x, w, b, K, it);
+}
+// fused ReLU variants (extension; interp_weights optional)
+torch::Tensor mapped_conv_relu_forward(torch::Tensor x, torch::Tensor map, c10::optional<torch::Tensor> iw, torch::Tensor w,
+                                       torch::Tensor b, int64_t K, InterpolationType it) {
+  return conv_forward_impl(x, map, iw ? &*iw : nullptr, w, b, K, it, true);
+}
+std::vector<torch::Tensor> mapped_conv_relu_backward(torch::Tensor go, torch::Tensor act_out, torch::Tensor map,
+                                                     c10::optional<torch::Tensor> iw, torch::Tensor x, torch::Tensor w,
+                                                     torch::Tensor b, int64_t K, InterpolationType it) {
+  return conv_backward_impl(go, map, iw ? &*iw : nullptr, x, w, b, K, it, &act_out);
 }
 torch::Tensor weighted_mapped_conv_forward(torch::Tensor x, torch::Tensor map, torch::Tensor iw, torch::Tensor w,
                                            torch::Tensor b, int64_t K, InterpolationType it) {
@@ -447,6 +489,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("weighted_mapped_max_unpool", &weighted_mapped_max_unpool);
   m.def("mapped_conv_forward", &mapped_conv_forward);
   m.def("mapped_conv_backward", &mapped_conv_backward);
+  m.def("mapped_conv_relu_forward", &mapped_conv_relu_forward);
+  m.def("mapped_conv_relu_backward", &mapped_conv_relu_backward);
   m.def("weighted_mapped_conv_forward", &weighted_mapped_conv_forward);
   m.def("weighted_mapped_conv_backward", &weighted_mapped_conv_backward);
   m.def("mapped_transposed_conv_forward", &mapped_transposed_conv_forward);

@@ -45,6 +45,23 @@ class _MappedConv(torch.autograd.Function):
         return gx, gw, gb, None, None, None, None
 
 
+class _MappedConvReLU(torch.autograd.Function):
+    """relu(mapped_convolution(...)) with the activation fused into the kernels; not in the reference."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, sample_map, kernel_size, interp, interp_weights):
+        out = _conv.mapped_conv_relu_forward(x, sample_map, interp_weights, weight, bias, kernel_size, interp)
+        ctx.save_for_backward(x, weight, bias, sample_map, *_scalars(kernel_size, interp), interp_weights, out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, weight, bias, sample_map, kernel_size, interp, interp_weights, out = ctx.saved_tensors
+        gx, gw, gb = _conv.mapped_conv_relu_backward(grad_output, out, sample_map, interp_weights, x, weight, bias,
+                                                     kernel_size, InterpolationType(interp))
+        return gx, gw, gb, None, None, None, None
+
+
 class _MappedTransposedConv(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, sample_map, oh, ow, kernel_size, interp, interp_weights):
@@ -133,9 +150,13 @@ class _Unresample(torch.autograd.Function):
         return _wres.weighted_resample_to_map(grad_output, sample_map, interp_weights, h, w, interp), None, None, None
 
 
-def mapped_convolution(input, weight, bias, sample_map, kernel_size, interp, interp_weights=None):
+def mapped_convolution(input, weight, bias, sample_map, kernel_size, interp, interp_weights=None, activation=None):
+    """`activation` (None or "relu") is an extension of this library: the ReLU runs inside the convolution kernels
+    instead of as separate passes over the output and its gradient."""
     check_args(input, sample_map, interp_weights, weight.shape[1], weight.shape[2])
-    return _MappedConv.apply(input, weight, bias, sample_map, kernel_size, interp, interp_weights)
+    assert activation in (None, "relu"), "activation must be None or 'relu'"
+    fn = _MappedConvReLU if activation == "relu" else _MappedConv
+    return fn.apply(input, weight, bias, sample_map, kernel_size, interp, interp_weights)
 
 
 def mapped_transposed_convolution(input, weight, bias, sample_map, output_height, output_width, kernel_size, interp,

@@ -22,11 +22,14 @@ def _uniform_init(module, fan):
 
 
 class MappedConvolution(nn.Module):
-    """weight (out_channels, in_channels, kernel_size); output size = map size."""
+    """weight (out_channels, in_channels, kernel_size); output size = map size.  `activation="relu"` (an extension,
+    default None = the reference's layer) fuses the activation into the convolution kernels."""
 
-    def __init__(self, in_channels, out_channels, kernel_size=1, interpolation=InterpolationType.BILINEAR, bias=True):
+    def __init__(self, in_channels, out_channels, kernel_size=1, interpolation=InterpolationType.BILINEAR, bias=True,
+                 activation=None):
         super().__init__()
         self.in_channels, self.out_channels, self.kernel_size, self.interp = in_channels, out_channels, kernel_size, interpolation
+        self.activation = activation
         self.weight = nn.Parameter(torch.empty(out_channels, in_channels, kernel_size))
         self.bias = nn.Parameter(torch.empty(out_channels))
         self.reset_parameters()
@@ -37,7 +40,8 @@ class MappedConvolution(nn.Module):
         _uniform_init(self, self.in_channels * self.kernel_size)
 
     def forward(self, x, sample_map, interp_weights=None):
-        return F.mapped_convolution(x, self.weight, self.bias, sample_map, self.kernel_size, self.interp, interp_weights)
+        return F.mapped_convolution(x, self.weight, self.bias, sample_map, self.kernel_size, self.interp, interp_weights,
+                                    self.activation)
 
 
 class MappedTransposedConvolution(nn.Module):

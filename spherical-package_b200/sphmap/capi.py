@@ -24,7 +24,9 @@ SYMBOLS = [
     "sph_resample_to_map", "sph_resample_to_map_static", "sph_mapped_max_pool", "sph_mapped_max_unpool", "sph_conv_workspace_bytes",
     "sph_mapped_conv_forward", "sph_mapped_conv_backward_input", "sph_mapped_conv_backward_weight",
     "sph_mapped_tconv_forward", "sph_mapped_tconv_backward_input", "sph_mapped_tconv_backward_weight",
+    "sph_mapped_conv_relu_forward", "sph_mapped_conv_relu_backward_input", "sph_mapped_conv_relu_backward_weight",
 ]
+ERR_UNSUPPORTED = 2
 
 if not os.path.exists(LIB_PATH):
     raise ImportError("libsphmap.so not built (run spherical-package_b200/build.py): " + LIB_PATH)
@@ -40,6 +42,10 @@ _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_s
 
 class SphError(RuntimeError):
     pass
+
+
+class Unsupported(SphError):
+    """A fused entry point declined the shape (SPH_ERR_UNSUPPORTED); raised only when the caller asked for no fallback."""
 
 
 def _ok(rc, what):
@@ -184,6 +190,63 @@ def conv_backward_weight(go, x, smap, K, interp, iw=None, precision=EXACT, ws=No
                                             *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)), _int(_dt(x)),
                                             _int(int(interp)), _int(precision), _ptr(ws[0]), _sz(ws[1]), _stream()),
         "sph_mapped_conv_backward_weight")
+    return gw, gb
+
+
+def conv_relu_forward(x, smap, weight, bias, K, interp, iw=None, precision=EXACT, out=None, ws=None):
+    """max(0, conv(x) + bias) with the clamp fused into the kernels where the library supports it (see
+    include/sphmap.h); elsewhere the unfused forward followed by an in-place clamp."""
+    B, Cin, IH, IW = x.shape
+    OH, OW = smap.shape[:2]
+    Cout = weight.shape[0]
+    if out is None:
+        out = torch.empty(B, Cout, OH, OW, dtype=x.dtype, device=x.device)
+    if ws is None:
+        ws = conv_workspace(CONV_FORWARD, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
+    rc = lib.sph_mapped_conv_relu_forward(_ptr(x), _ptr(smap), _ptr(iw), _ptr(weight), _ptr(bias), _ptr(out),
+                                          *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)), _int(_dt(x)),
+                                          _int(int(interp)), _int(precision), _ptr(ws[0]), _sz(ws[1]), _stream())
+    if rc == ERR_UNSUPPORTED:
+        return conv_forward(x, smap, weight, bias, K, interp, iw, precision, out, ws).clamp_(min=0)
+    _ok(rc, "sph_mapped_conv_relu_forward")
+    return out
+
+
+def conv_relu_backward_input(go, act_out, plan, weight, IH, IW, K, precision=EXACT, out=None, ws=None, fallback=True):
+    """Gradient w.r.t. the input of conv_relu_forward: `go` is the gradient w.r.t. its output `act_out`.  Shapes
+    the library does not fuse take one masking pass and the plain operator (or raise Unsupported if fallback=False)."""
+    B, Cout, OH, OW = go.shape
+    Cin = weight.shape[1]
+    if out is None:
+        out = torch.empty(B, Cin, int(IH), int(IW), dtype=go.dtype, device=go.device)
+    if ws is None:
+        ws = conv_workspace(CONV_BACKWARD_INPUT, B, Cin, Cout, IH, IW, OH, OW, K, 0, _dt(go), 0, precision, go)
+    rc = lib.sph_mapped_conv_relu_backward_input(_ptr(go), _ptr(act_out), _ptr(plan), _ptr(weight), _ptr(out),
+                                                 *_ints(B, Cin, Cout, IH, IW, OH, OW, K), _int(_dt(go)), _int(precision),
+                                                 _ptr(ws[0]), _sz(ws[1]), _stream())
+    if rc == ERR_UNSUPPORTED:
+        if not fallback:
+            raise Unsupported("sph_mapped_conv_relu_backward_input")
+        return conv_backward_input(torch.ops.aten.threshold_backward(go, act_out, 0), plan, weight, IH, IW, K, precision, out, ws)
+    _ok(rc, "sph_mapped_conv_relu_backward_input")
+    return out
+
+
+def conv_relu_backward_weight(go, act_out, x, smap, K, interp, iw=None, precision=EXACT, ws=None, fallback=True):
+    B, Cin, IH, IW = x.shape
+    _, Cout, OH, OW = go.shape
+    gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
+    gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
+    if ws is None:
+        ws = conv_workspace(CONV_BACKWARD_WEIGHT, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
+    rc = lib.sph_mapped_conv_relu_backward_weight(_ptr(go), _ptr(act_out), _ptr(x), _ptr(smap), _ptr(iw), _ptr(gw), _ptr(gb),
+                                                  *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)), _int(_dt(x)),
+                                                  _int(int(interp)), _int(precision), _ptr(ws[0]), _sz(ws[1]), _stream())
+    if rc == ERR_UNSUPPORTED:
+        if not fallback:
+            raise Unsupported("sph_mapped_conv_relu_backward_weight")
+        return conv_backward_weight(torch.ops.aten.threshold_backward(go, act_out, 0), x, smap, K, interp, iw, precision, ws)
+    _ok(rc, "sph_mapped_conv_relu_backward_weight")
     return gw, gb
 
 

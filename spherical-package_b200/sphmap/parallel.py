@@ -45,9 +45,11 @@ class EncoderStack:
     """The four-layer spherical encoder of the benchmark (mapped conv + ReLU per layer), driven straight
     through the C ABI: forward, backward (dInput, dW, dBias per layer) and gradient allreduce.  Buffers
     are allocated once; `step` enqueues one forward+backward pass and returns the loss tensor
-    sum(out * grad_output) (device scalar)."""
+    sum(out * grad_output) (device scalar).  With `fuse_relu` (default) the activation runs inside the
+    convolution kernels (sph_mapped_conv_relu_*); without it as separate passes over the activations, the way the
+    reference's operators compose."""
 
-    def __init__(self, cfg, device, precision, local_batch, reducer=None, timers=None):
+    def __init__(self, cfg, device, precision, local_batch, reducer=None, timers=None, fuse_relu=True):
         from . import capi
         self.c = capi
         self.prec = precision
@@ -59,6 +61,8 @@ class EncoderStack:
         self.b = [t.to(device) for t in cfg["biases"]]
         self.maps = [t.to(device) for t in cfg["maps"]]
         self.reducer = reducer
+        self.fuse_relu = fuse_relu
+        self.fused_bwd = [fuse_relu] * 4   # per layer: backward kernels mask the gradient themselves (else one masking pass)
         self.timers = timers          # optional {(layer, phase): [start_event, end_event]} to time single launches
         self.plans, self.acts, self.ws = [], [], {}
         f32 = dict(dtype=torch.float32, device=device)
@@ -86,10 +90,10 @@ class EncoderStack:
         h = x
         for li in range(4):
             self.inputs.append(h)
-            out = self._timed((li, "fwd"), lambda: c.conv_forward(h, self.maps[li], self.w[li], self.b[li], self.K,
-                                                                  self.interp, None, self.prec, out=self.acts[li],
-                                                                  ws=self.ws[(li, c.CONV_FORWARD)]))
-            h = out.relu_()
+            fwd = c.conv_relu_forward if self.fuse_relu else c.conv_forward
+            out = self._timed((li, "fwd"), lambda: fwd(h, self.maps[li], self.w[li], self.b[li], self.K, self.interp, None,
+                                                       self.prec, out=self.acts[li], ws=self.ws[(li, c.CONV_FORWARD)]))
+            h = out if self.fuse_relu else out.relu_()
         return h
 
     def backward(self, go):
@@ -97,16 +101,30 @@ class EncoderStack:
         g = go
         for li in reversed(range(4)):
             ci, co, (ih, iw), (oh, ow), s = self.layers[li]
-            g = torch.ops.aten.threshold_backward(g, self.acts[li], 0)   # ReLU backward on the rectified activations
-            gw, gb = self._timed((li, "dw"), lambda: c.conv_backward_weight(
-                g, self.inputs[li], self.maps[li], self.K, self.interp, None, self.prec,
-                ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)]))
+            gw = None
+            if self.fused_bwd[li]:   # the kernels read g * (activation > 0) wherever they read g
+                try:
+                    gw, gb = self._timed((li, "dw"), lambda: c.conv_relu_backward_weight(
+                        g, self.acts[li], self.inputs[li], self.maps[li], self.K, self.interp, None, self.prec,
+                        ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)], fallback=False))
+                except c.Unsupported:
+                    self.fused_bwd[li] = False
+            if not self.fused_bwd[li]:
+                g = torch.ops.aten.threshold_backward(g, self.acts[li], 0)   # ReLU backward on the rectified activations
+                gw, gb = self._timed((li, "dw"), lambda: c.conv_backward_weight(
+                    g, self.inputs[li], self.maps[li], self.K, self.interp, None, self.prec,
+                    ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)]))
             self.gw[li], self.gb[li] = gw, gb
             if self.reducer is not None:
                 self.reducer.submit(gw, gb)
-            g = self._timed((li, "dx"), lambda: c.conv_backward_input(
-                g, self.plans[li], self.w[li], ih, iw, self.K, self.prec, out=self.gx[li],
-                ws=self.ws[(li, c.CONV_BACKWARD_INPUT)]))
+            if self.fused_bwd[li]:
+                g = self._timed((li, "dx"), lambda: c.conv_relu_backward_input(
+                    g, self.acts[li], self.plans[li], self.w[li], ih, iw, self.K, self.prec, out=self.gx[li],
+                    ws=self.ws[(li, c.CONV_BACKWARD_INPUT)]))
+            else:
+                g = self._timed((li, "dx"), lambda: c.conv_backward_input(
+                    g, self.plans[li], self.w[li], ih, iw, self.K, self.prec, out=self.gx[li],
+                    ws=self.ws[(li, c.CONV_BACKWARD_INPUT)]))
         if self.reducer is not None:
             self.reducer.finish()
         return g

@@ -1,0 +1,110 @@
+"""Fused ReLU (sph_mapped_conv_relu_*): the kernels clamp the forward output and read grad_output * (output > 0) in
+backward.  Because masked elements are exactly zero either way, results must be bit-identical to the plain operator
+followed by a separate ReLU / masked gradient, on every path (thin kernels, tensor-core kernels, and the fallback
+for shapes the library does not fuse)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # name, B, Cin, Cout, IH, IW, OH, OW, K, interp, dtype, precision
+    ("thin_fp32", 3, 3, 20, 24, 40, 12, 20, 9, 1, torch.float32, "exact"),
+    ("thin_fp64", 2, 2, 70, 10, 16, 10, 16, 4, 2, torch.float64, "exact"),
+    ("thin_bf16", 2, 3, 64, 32, 64, 16, 32, 9, 1, torch.float32, "bf16"),
+    ("tc_bf16", 2, 64, 96, 24, 48, 24, 48, 9, 1, torch.float32, "bf16"),
+    ("tc_bf16_down", 2, 64, 128, 32, 64, 8, 16, 9, 1, torch.float32, "bf16"),       # multiply-first adjoint
+    ("tc_bf16_odd", 1, 72, 40, 13, 22, 13, 22, 5, 0, torch.float32, "bf16"),         # width not a multiple of 4
+    ("fallback_exact", 2, 8, 12, 12, 20, 12, 20, 9, 1, torch.float32, "exact"),       # SIMT GEMM: not fused
+]
+
+
+def _inputs(c):
+    name, B, Cin, Cout, IH, IW, OH, OW, K, interp, dtype, prec = c
+    g = torch.Generator().manual_seed(hash(name) % 1000)
+    x = torch.randn(B, Cin, IH, IW, generator=g, dtype=dtype).cuda()
+    w = (torch.randn(Cout, Cin, K, generator=g, dtype=dtype) / (Cin * K) ** 0.5).cuda()
+    b = (torch.randn(Cout, generator=g, dtype=dtype) * 0.1).cuda()
+    m = (torch.rand(OH, OW, K, 2, generator=g, dtype=dtype) * torch.tensor([IW + 1.0, IH + 1.0], dtype=dtype) - 1).cuda()
+    go = torch.randn(B, Cout, OH, OW, generator=g, dtype=dtype).cuda()
+    return x, w, b, m, go
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_c_abi_fused_equals_unfused(case):
+    from sphmap import capi
+    name, B, Cin, Cout, IH, IW, OH, OW, K, interp, dtype, prec = case
+    p = capi.BF16 if prec == "bf16" else capi.EXACT
+    x, w, b, m, go = _inputs(case)
+    y_ref = capi.conv_forward(x, m, w, b, K, interp, precision=p).clamp_(min=0)
+    y = capi.conv_relu_forward(x, m, w, b, K, interp, precision=p)
+    assert torch.equal(y, y_ref)
+    assert (y == 0).any() and (y > 0).any()
+    plan = capi.plan_build(m, None, OH * OW, K, interp, IH, IW)
+    gm = go * (y > 0)
+    gx_ref = capi.conv_backward_input(gm, plan, w, IH, IW, K, precision=p)
+    gw_ref, gb_ref = capi.conv_backward_weight(gm, x, m, K, interp, precision=p)
+    gx = capi.conv_relu_backward_input(go, y, plan, w, IH, IW, K, precision=p)
+    gw, gb = capi.conv_relu_backward_weight(go, y, x, m, K, interp, precision=p)
+    assert torch.equal(gx, gx_ref)
+    assert torch.equal(gw, gw_ref)
+    assert torch.equal(gb, gb_ref)
+
+
+def test_fused_entry_points_refuse_what_they_do_not_fuse():
+    from sphmap import capi
+    case = CASES[-1]
+    name, B, Cin, Cout, IH, IW, OH, OW, K, interp, dtype, prec = case
+    x, w, b, m, go = _inputs(case)
+    out = torch.empty(B, Cout, OH, OW, dtype=dtype, device="cuda")
+    ws = capi.conv_workspace(capi.CONV_FORWARD, B, Cin, Cout, IH, IW, OH, OW, K, 0, capi.F32, interp, capi.EXACT, x)
+    rc = capi.lib.sph_mapped_conv_relu_forward(capi._ptr(x), capi._ptr(m), capi._ptr(None), capi._ptr(w), capi._ptr(b),
+                                               capi._ptr(out), *capi._ints(B, Cin, Cout, IH, IW, OH, OW, K, 0),
+                                               capi._int(capi.F32), capi._int(interp), capi._int(capi.EXACT),
+                                               capi._ptr(ws[0]), capi._sz(ws[1]), capi._stream())
+    assert rc == capi.ERR_UNSUPPORTED
+
+
+@pytest.mark.parametrize("precision", ["fp32", "bf16"])
+def test_layer_with_fused_activation_matches_layer_plus_relu(precision):
+    import _spherical_distortion_ext._C as C
+    from spherical_distortion.nn import InterpolationType, MappedConvolution
+    old = C.get_precision()
+    C.set_precision(precision)
+    try:
+        g = torch.Generator().manual_seed(3)
+        for cin, cout in ((3, 32), (64, 64)):
+            x = torch.randn(2, cin, 16, 32, generator=g).cuda().requires_grad_(True)
+            m = (torch.rand(16, 32, 9, 2, generator=g) * torch.tensor([32.0, 16.0]) - 0.5).cuda()
+            plain = MappedConvolution(cin, cout, 9, InterpolationType.BILINEAR).cuda()
+            fused = MappedConvolution(cin, cout, 9, InterpolationType.BILINEAR, activation="relu").cuda()
+            fused.load_state_dict(plain.state_dict())
+            go = torch.randn(2, cout, 16, 32, generator=g).cuda()
+            y0 = torch.relu(plain(x, m))
+            y0.backward(go)
+            gx0, gw0, gb0 = x.grad.clone(), plain.weight.grad.clone(), plain.bias.grad.clone()
+            x.grad = None
+            y1 = fused(x, m)
+            y1.backward(go)
+            assert torch.equal(y1, y0)
+            assert torch.equal(x.grad, gx0)
+            assert torch.equal(fused.weight.grad, gw0)
+            assert torch.equal(fused.bias.grad, gb0)
+    finally:
+        C.set_precision(old)
+
+
+def test_encoder_stack_fused_equals_unfused():
+    from sphmap import capi, workloads as wl
+    from sphmap.parallel import EncoderStack
+    cfg = wl.config4(B=2, H=64, W=128)
+    dev = torch.device("cuda")
+    x, go = cfg["x"].to(dev), cfg["grad_output"].to(dev)
+    res = []
+    for fuse in (False, True):
+        st = EncoderStack(cfg, dev, capi.BF16, 2, fuse_relu=fuse)
+        loss = st.step(x, go)
+        res.append((loss.clone(), [t.clone() for t in st.gw], [t.clone() for t in st.gb], st.gx[0].clone()))
+    assert torch.equal(res[0][0], res[1][0])
+    for a, b in zip(res[0][1] + res[0][2] + [res[0][3]], res[1][1] + res[1][2] + [res[1][3]]):
+        assert torch.equal(a, b)
