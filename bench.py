@@ -302,10 +302,10 @@ def run_encoder(args, rank, local, world):
                      "share_of_conv_time": round(dom_ms / sum(per_launch.values()), 3),
                      "achieved": round(achieved, 2), "peak": tensor_peak, "unit": "TFLOP/s",
                      "frac": round(achieved / tensor_peak, 4),
-                     # dram read+write of the layer-4 forward launch of this kernel: 154.3 MB in the batch-4 ncu
+                     # dram read+write of the layer-4 forward launch of this kernel: 156.8 MB in the batch-4 ncu
                      # capture (profiles/tc_gemm_kernel_encoder_B4.md), scaled by local batch / 4 (traffic is
                      # proportional to the batch: activations in, activations out)
-                     "traffic": int(154.3e6 * (hi - lo) / 4), "traffic_of": "layer-4 forward launch, scaled from the batch-4 capture",
+                     "traffic": int(156.8e6 * (hi - lo) / 4), "traffic_of": "layer-4 forward launch, scaled from the batch-4 capture",
                      "peak_source": peaks["source"] + " bf16 sustained (kernel timed inside a long step)",
                      "per_launch_ms": {"L%d.%s" % (k[0] + 1, k[1]): round(v, 3) for k, v in per_launch.items()}},
         "clocks": clocks,

@@ -155,7 +155,8 @@ int sph_mapped_max_unpool(const void *g, const int64_t *idx, const void *map, co
  * Replaces spherical::MappedConvForward / MappedConvBackward,
  * ext_modules/include/layers/mapped_convolution_layer.h:62-134 (weighted:
  * weighted_mapped_convolution_layer.h:69-162).
- * ws/ws_bytes: scratch of at least sph_conv_workspace_bytes(op, ...) bytes.
+ * ws/ws_bytes: scratch of at least sph_conv_workspace_bytes(op, ...) bytes, 256-byte aligned
+ * (SPH_ERR_INVALID_ARGUMENT otherwise on the bf16 path).
  * ---------------------------------------------------------------------- */
 enum sph_conv_op {
   SPH_CONV_FORWARD = 0,

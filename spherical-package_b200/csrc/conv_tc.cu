@@ -1494,6 +1494,7 @@ int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan
                       void *out, int64_t M, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st) {
   const Geometry &g = q.g;
   if (!ws || ws_bytes < 256 + g.xh_bytes + g.wp_bytes + q.t_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  if ((uintptr_t)ws & 255) return SPH_ERR_INVALID_ARGUMENT;  // vector loads and bulk copies assume the alignment
   int *status = (int *)ws;
   __nv_bfloat16 *xh = (__nv_bfloat16 *)((char *)ws + 256);
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
@@ -1528,6 +1529,7 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
   if (!g.ok)  // shapes the tile kernel does not cover run on the exact SIMT kernels instead
     return simt_gemm<float>(use_plan, src, map, iw, plan, CH, SH, SW, K, P, GH * GW, interp, wgt, sn, sc, sk, bias, out, Nout, B, st);
   if (!ws || ws_bytes < 256 + g.xh_bytes + g.wp_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  if ((uintptr_t)ws & 255) return SPH_ERR_INVALID_ARGUMENT;  // vector loads and bulk copies assume the alignment
   int *status = (int *)ws;
   __nv_bfloat16 *xh = (__nv_bfloat16 *)((char *)ws + 256);
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
@@ -1627,6 +1629,7 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
     return simt_dw<float>(A, src, map, iw, CH, SH, SW, K, P, GH * GW, interp, Nout, B, gw, sn, sc, sk, gbias_src, Cbias, nbias, gb,
                           ws, ws_bytes, st);
   if (!ws || ws_bytes < 256 + d.xh_bytes + d.gt_bytes + d.partial_bytes + d.bias_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  if ((uintptr_t)ws & 255) return SPH_ERR_INVALID_ARGUMENT;  // vector loads and bulk copies assume the alignment
   char *w8 = (char *)ws;
   int *status = (int *)w8;
   __nv_bfloat16 *xh = (__nv_bfloat16 *)(w8 + 256);

@@ -50,12 +50,14 @@ constexpr uint32_t kSuspendHintNs = 100000u;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
   if (mbar_try_wait(bar, parity, kSuspendHintNs)) return true;
   const uint64_t t0 = global_timer_ns();
-  for (;;) {
+  for (uint32_t spin = 1;; spin++) {
     if (mbar_try_wait(bar, parity, kSuspendHintNs)) return true;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
-      *abort_flag = 1;
-      return false;
+    if ((spin & 15u) == 0) {  // the abort flag and the clock are looked at every 16th failed try only
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
     }
   }
 }
@@ -75,12 +77,14 @@ __device__ __forceinline__ bool mbar_try_wait_s(uint32_t bar_s, uint32_t parity,
 __device__ __forceinline__ bool mbar_wait_s(uint32_t bar_s, uint32_t parity, volatile int *abort_flag) {
   if (mbar_try_wait_s(bar_s, parity, kSuspendHintNs)) return true;
   const uint64_t t0 = global_timer_ns();
-  for (;;) {
+  for (uint32_t spin = 1;; spin++) {
     if (mbar_try_wait_s(bar_s, parity, kSuspendHintNs)) return true;
-    if (*abort_flag) return false;
-    if (global_timer_ns() - t0 > kWaitLimitNs) {
-      *abort_flag = 1;
-      return false;
+    if ((spin & 15u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        return false;
+      }
     }
   }
 }
