@@ -57,6 +57,29 @@ int sph_version(void);
 unsigned long long sph_launch_count(void);
 
 /* ------------------------------------------------------------------------
+ * Device status.  Every wait inside the tensor-core kernels (mbarrier waits
+ * between the gathering, MMA-issuing and draining warps) is bounded: after
+ * 4 s of wall time the waiting warp gives up, all roles of that CTA leave
+ * their loops, tensor memory is freed, the kernel returns normally, and the
+ * give-up is recorded (a) as 1 in the first 32-bit word of the workspace the
+ * call was given and (b) in a sticky word on the device.  Outputs of such a
+ * launch are invalid.  The launch itself still returned SPH_OK (nothing
+ * synchronises), so a host that wants to know asks here:
+ *   sph_device_status  copies the sticky word of the CURRENT device to
+ *       *status (host pointer; 0 = no wait ever gave up) and clears it if
+ *       reset != 0.  Blocks until the device's queued work is done.
+ *   sph_debug_bounded_wait  self check of that mechanism: one small kernel
+ *       allocates tensor memory and waits, with the given limit
+ *       (nanoseconds, at most 1e9), on a barrier nothing arrives at; it must
+ *       write 1 to *status (DEVICE pointer), set the sticky word, free its
+ *       tensor memory and return.
+ * The reference has no counterpart: its CUDA_CHECK ends the process
+ * (ext_modules/include/cuda_helper.h:5-10).
+ * ---------------------------------------------------------------------- */
+int sph_device_status(int *status, int reset);
+int sph_debug_bounded_wait(unsigned long long limit_ns, int *status, void *stream);
+
+/* ------------------------------------------------------------------------
  * resample_from_map ("Unresample"): y[b,c,i] = interp(x[b,c], map[i]).
  * Replaces spherical::ResampleFromMap, ext_modules/include/layers/
  * resample_layer.h:62-82 (weighted twin: weighted_resample_layer.h:77-105).
@@ -156,7 +179,9 @@ int sph_mapped_max_unpool(const void *g, const int64_t *idx, const void *map, co
  * ext_modules/include/layers/mapped_convolution_layer.h:62-134 (weighted:
  * weighted_mapped_convolution_layer.h:69-162).
  * ws/ws_bytes: scratch of at least sph_conv_workspace_bytes(op, ...) bytes, 256-byte aligned
- * (SPH_ERR_INVALID_ARGUMENT otherwise on the bf16 path).
+ * (SPH_ERR_INVALID_ARGUMENT otherwise on the bf16 path).  On the bf16 path the first 32-bit
+ * word of ws is the call's status word (0, or 1 after a bounded wait gave up: see
+ * sph_device_status).
  * ---------------------------------------------------------------------- */
 enum sph_conv_op {
   SPH_CONV_FORWARD = 0,

@@ -13,6 +13,7 @@ git-ignored folder) under the module names of setup.py:62-195, so that
 expects.
 
 Usage:  python oracle/build_ref.py [--reference /path/to/Spherical-Package] [-j N]
+(the default is $SPHERICAL_PACKAGE_REFERENCE, else the folder `reference` beside this repository)
 """
 import argparse
 import os
@@ -63,8 +64,15 @@ def _compile(ref, name, base, cxx):
     return name, "built"
 
 
-def build(reference="/root/reference", jobs=4, quiet=False):
+def default_reference():
+    """Where the reference checkout is looked for: $SPHERICAL_PACKAGE_REFERENCE, else a folder named `reference`
+    beside this repository."""
+    return os.environ.get("SPHERICAL_PACKAGE_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(reference=None, jobs=4, quiet=False):
     """Compile every module of MODULES; returns the output directory."""
+    reference = reference or default_reference()
     if not os.path.isdir(os.path.join(reference, "ext_modules")):
         raise FileNotFoundError("reference checkout not found at " + reference)
     os.makedirs(OUT, exist_ok=True)
@@ -82,7 +90,7 @@ def build(reference="/root/reference", jobs=4, quiet=False):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=default_reference())
     ap.add_argument("-j", type=int, default=4)
     a = ap.parse_args()
     build(a.reference, a.j)

@@ -21,3 +21,4 @@ set_precision = _C.set_precision
 get_precision = _C.get_precision
 clear_plan_cache = _C.clear_plan_cache
 plan_cache_size = _C.plan_cache_size
+device_status = _C.device_status

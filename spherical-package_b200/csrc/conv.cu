@@ -44,7 +44,6 @@ extern "C" int sph_version(void) { return 100; }
 
 namespace sph {
 unsigned long long g_launch_count = 0;
-thread_local Fusion g_fusion;
 }  // namespace sph
 extern "C" unsigned long long sph_launch_count(void) { return __atomic_load_n(&sph::g_launch_count, __ATOMIC_RELAXED); }
 
@@ -74,10 +73,11 @@ extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64
 
 #define SPH_BY_DTYPE(fn, ...) (dtype == SPH_F32 ? fn<float>(__VA_ARGS__) : fn<double>(__VA_ARGS__))
 
-extern "C" int sph_mapped_conv_forward(const void *x, const void *map, const void *iw, const void *weight,
-                                       const void *bias, void *out, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
-                                       int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
-                                       int precision, void *ws, size_t ws_bytes, void *stream) {
+namespace {
+
+int conv_forward(const void *x, const void *map, const void *iw, const void *weight, const void *bias, void *out, int64_t B,
+                 int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
+                 int interp, int precision, void *ws, size_t ws_bytes, void *stream, const Fusion &fz) {
   const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
   const int rc = check_dims(d, dtype, interp, precision);
   if (rc != SPH_OK) return rc;
@@ -85,18 +85,18 @@ extern "C" int sph_mapped_conv_forward(const void *x, const void *map, const voi
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
-    return SPH_BY_DTYPE(small_fwd, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, st);
+    return SPH_BY_DTYPE(small_fwd, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, st,
+                        fz.relu_out);
   if (precision == SPH_PRECISION_BF16)
-    return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
-  if (fusion_active()) return SPH_ERR_UNSUPPORTED;
+    return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
+  if (fz.active()) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_gemm, false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1,
                       bias, out, Cout, B, st);
 }
 
-extern "C" int sph_mapped_conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx,
-                                              int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
-                                              int64_t OW, int64_t K, int dtype, int precision, void *ws,
-                                              size_t ws_bytes, void *stream) {
+int conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx, int64_t B, int64_t Cin, int64_t Cout,
+                        int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int dtype, int precision, void *ws,
+                        size_t ws_bytes, void *stream, const Fusion &fz) {
   const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, 0};
   const int rc = check_dims(d, dtype, 0, precision);
   if (rc != SPH_OK) return rc;
@@ -104,21 +104,20 @@ extern "C" int sph_mapped_conv_backward_input(const void *gout, const void *plan
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
   // the thin kernels stream grad_output once per operator; masking it in both would cost more than one masking pass
-  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4) && g_fusion.mask) return SPH_ERR_UNSUPPORTED;
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4) && fz.mask) return SPH_ERR_UNSUPPORTED;
   if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
     return SPH_BY_DTYPE(small_adjoint, gout, plan, Cout, OH * OW, K, IH * IW, weight, K, Cin * K, 1, nullptr, gx, Cin, B, ws,
                         ws_bytes, st);
   if (precision == SPH_PRECISION_BF16)
-    return tc_conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st);
-  if (fusion_active()) return SPH_ERR_UNSUPPORTED;
+    return tc_conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st, fz);
+  if (fz.active()) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_gemm, true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH * IW, 0, weight, K, Cin * K, 1,
                       nullptr, gx, Cin, B, st);
 }
 
-extern "C" int sph_mapped_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw,
-                                               void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
-                                               int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
-                                               int interp, int precision, void *ws, size_t ws_bytes, void *stream) {
+int conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb, int64_t B,
+                         int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
+                         int dtype, int interp, int precision, void *ws, size_t ws_bytes, void *stream, const Fusion &fz) {
   const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
   const int rc = check_dims(d, dtype, interp, precision);
   if (rc != SPH_OK) return rc;
@@ -129,33 +128,51 @@ extern "C" int sph_mapped_conv_backward_weight(const void *gout, const void *x, 
     if (cudaMemsetAsync(gw, 0, ts * (size_t)(Cout * Cin * K), st) != cudaSuccess) return SPH_ERR_CUDA;
     return cudaMemsetAsync(gb, 0, ts * (size_t)Cout, st) == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
   }
-  if (small_ok(Cin, K, Cout, ts) && g_fusion.mask) return SPH_ERR_UNSUPPORTED;  // see backward_input
+  if (small_ok(Cin, K, Cout, ts) && fz.mask) return SPH_ERR_UNSUPPORTED;  // see conv_backward_input
   if (small_ok(Cin, K, Cout, ts))
     return SPH_BY_DTYPE(small_dw, gout, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout,
                         OH * OW, gb, ws, ws_bytes, st);
   if (precision == SPH_PRECISION_BF16)
-    return tc_conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
-  if (fusion_active()) return SPH_ERR_UNSUPPORTED;
+    return tc_conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
+  if (fz.active()) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_dw, gout, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout,
                       OH * OW, gb, ws, ws_bytes, st);
 }
 
-// ---- convolution with a fused ReLU (no counterpart in the reference; see sphmap.h) -------------------------
-namespace {
-struct FusionScope {
-  FusionScope(bool relu_out, const void *mask) { sph::g_fusion.relu_out = relu_out; sph::g_fusion.mask = mask; }
-  ~FusionScope() { sph::g_fusion = sph::Fusion{}; }
-};
 }  // namespace
 
+extern "C" int sph_mapped_conv_forward(const void *x, const void *map, const void *iw, const void *weight,
+                                       const void *bias, void *out, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                                       int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                       int precision, void *ws, size_t ws_bytes, void *stream) {
+  return conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws, ws_bytes,
+                      stream, Fusion{});
+}
+
+extern "C" int sph_mapped_conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx,
+                                              int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
+                                              int64_t OW, int64_t K, int dtype, int precision, void *ws,
+                                              size_t ws_bytes, void *stream) {
+  return conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, dtype, precision, ws, ws_bytes, stream,
+                             Fusion{});
+}
+
+extern "C" int sph_mapped_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw,
+                                               void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                                               int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
+                                               int interp, int precision, void *ws, size_t ws_bytes, void *stream) {
+  return conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws,
+                              ws_bytes, stream, Fusion{});
+}
+
+// ---- convolution with a fused ReLU (no counterpart in the reference; see sphmap.h) -------------------------
 extern "C" int sph_mapped_conv_relu_forward(const void *x, const void *map, const void *iw, const void *weight,
                                             const void *bias, void *out, int64_t B, int64_t Cin, int64_t Cout,
                                             int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
                                             int dtype, int interp, int precision, void *ws, size_t ws_bytes,
                                             void *stream) {
-  FusionScope scope(true, nullptr);
-  return sph_mapped_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision,
-                                 ws, ws_bytes, stream);
+  return conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws, ws_bytes,
+                      stream, Fusion{true, nullptr});
 }
 
 extern "C" int sph_mapped_conv_relu_backward_input(const void *gout, const void *act_out, const void *plan,
@@ -163,9 +180,8 @@ extern "C" int sph_mapped_conv_relu_backward_input(const void *gout, const void 
                                                    int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int dtype,
                                                    int precision, void *ws, size_t ws_bytes, void *stream) {
   if (!act_out) return SPH_ERR_INVALID_ARGUMENT;
-  FusionScope scope(false, act_out);
-  return sph_mapped_conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, dtype, precision, ws, ws_bytes,
-                                        stream);
+  return conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, dtype, precision, ws, ws_bytes, stream,
+                             Fusion{false, act_out});
 }
 
 extern "C" int sph_mapped_conv_relu_backward_weight(const void *gout, const void *act_out, const void *x,
@@ -174,9 +190,8 @@ extern "C" int sph_mapped_conv_relu_backward_weight(const void *gout, const void
                                                     int64_t OW, int64_t K, int64_t P, int dtype, int interp,
                                                     int precision, void *ws, size_t ws_bytes, void *stream) {
   if (!act_out) return SPH_ERR_INVALID_ARGUMENT;
-  FusionScope scope(false, act_out);
-  return sph_mapped_conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision,
-                                         ws, ws_bytes, stream);
+  return conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws,
+                              ws_bytes, stream, Fusion{false, act_out});
 }
 
 extern "C" int sph_mapped_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias,

@@ -7,16 +7,15 @@
 
 namespace sph {
 
-// Activation fused into the convolution kernels, set by the *_relu entry points for the duration of one call on
-// the calling thread: relu_out clamps the forward outputs at zero in the epilogue; mask (the saved activation
-// output, same shape as grad_output) makes every kernel that reads grad_output see grad_output * (mask > 0).
-// Code paths that cannot honour it return SPH_ERR_UNSUPPORTED before launching anything.
+// Activation fused into the convolution kernels, passed down by the *_relu entry points: relu_out clamps the
+// forward outputs at zero in the epilogue; mask (the saved activation output, same shape as grad_output) makes
+// every kernel that reads grad_output see grad_output * (mask > 0).  Code paths that cannot honour it return
+// SPH_ERR_UNSUPPORTED before launching anything.
 struct Fusion {
   bool relu_out = false;
   const void *mask = nullptr;
+  bool active() const { return relu_out || mask != nullptr; }
 };
-extern thread_local Fusion g_fusion;
-inline bool fusion_active() { return g_fusion.relu_out || g_fusion.mask != nullptr; }
 
 // ---- exact SIMT kernels (conv_simt.cu) -----------------------------------
 template <typename T>
@@ -43,7 +42,7 @@ size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_
 template <typename T>
 int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K, int64_t P,
               int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out,
-              int64_t M, int64_t B, cudaStream_t st);
+              int64_t M, int64_t B, cudaStream_t st, bool relu_out = false);
 template <typename T>
 int small_adjoint(const void *src, const void *plan, int64_t CH, int64_t n_src, int64_t K, int64_t n_dst, const void *wgt,
                   int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out, int64_t M, int64_t B, void *ws,
@@ -58,13 +57,13 @@ size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t 
                           int64_t K, int64_t P, int interp);
 int tc_conv_forward(const void *x, const void *map, const void *iw, const void *weight, const void *bias, void *out,
                     int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
-                    int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st);
+                    int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz = Fusion{});
 int tc_conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx, int64_t B, int64_t Cin,
                            int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
-                           size_t ws_bytes, cudaStream_t st);
+                           size_t ws_bytes, cudaStream_t st, const Fusion &fz = Fusion{});
 int tc_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb,
                             int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
-                            int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st);
+                            int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz = Fusion{});
 int tc_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out, int64_t B,
                      int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
                      size_t ws_bytes, cudaStream_t st);

@@ -478,14 +478,14 @@ size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_
 template <typename T>
 int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K, int64_t P,
               int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out,
-              int64_t M, int64_t B, cudaStream_t st) {
+              int64_t M, int64_t B, cudaStream_t st, bool relu_out) {
   if constexpr (sizeof(T) == 4) {  // float32: tiled product
     const dim3 tgrid(cdiv(npix, kTilePix), (unsigned)B);
 #define SPH_FWD_TILE(W)                                                                                                \
   small_fwd_tile_kernel<INTERP, W><<<tgrid, 256, 0, st>>>((const float *)src, (const float *)map, (const float *)iw,     \
                                                           (const float *)wgt, sm, sc, sk, (const float *)bias,          \
                                                           (float *)out, (int)CH, (int)K, (int)P, (int)SH, (int)SW,       \
-                                                          (int)npix, (int)M, g_fusion.relu_out ? 1 : 0)
+                                                          (int)npix, (int)M, relu_out ? 1 : 0)
     SPH_DISPATCH_INTERP(interp, {
       if (P > 0) SPH_FWD_TILE(true);
       else SPH_FWD_TILE(false);
@@ -498,7 +498,7 @@ int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int6
 #define SPH_SMALL_FWD(W)                                                                                              \
   small_fwd_kernel<T, INTERP, W><<<grid, 256, smem, st>>>((const T *)src, (const T *)map, (const T *)iw, (const T *)wgt, sm, \
                                                           sc, sk, (const T *)bias, (T *)out, (int)CH, (int)K, (int)P,   \
-                                                          (int)SH, (int)SW, (int)npix, (int)M, g_fusion.relu_out ? 1 : 0)
+                                                          (int)SH, (int)SW, (int)npix, (int)M, relu_out ? 1 : 0)
   SPH_DISPATCH_INTERP(interp, {
     if (P > 0) SPH_SMALL_FWD(true);
     else SPH_SMALL_FWD(false);
@@ -578,7 +578,7 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
 #define SPH_INSTANTIATE_SMALL(T)                                                                                          \
   template int small_fwd<T>(const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, \
                             int, const void *, int64_t, int64_t, int64_t, const void *, void *, int64_t, int64_t,          \
-                            cudaStream_t);                                                                                 \
+                            cudaStream_t, bool);                                                                           \
   template int small_adjoint<T>(const void *, const void *, int64_t, int64_t, int64_t, int64_t, const void *, int64_t,     \
                                 int64_t, int64_t, const void *, void *, int64_t, int64_t, void *, size_t, cudaStream_t);   \
   template int small_dw<T>(const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t,     \

@@ -43,6 +43,10 @@ constexpr int kTmemCols = 512;
 
 enum { MODE_DIRECT = 0, MODE_PLAN = 1 };
 
+// Sticky per-device record of a bounded wait that gave up in any kernel of this file (the kernels also write 1 into
+// the first word of the call's workspace); read and cleared by sph_device_status().
+__device__ int g_wait_status;
+
 // Developer aid (-DSPH_TC_TIMING): cycles one thread of every role of tc_gemm_kernel spends in each phase, summed
 // over all CTAs; read with sph_debug_tc_timing().
 #ifdef SPH_TC_TIMING
@@ -789,7 +793,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
   tc_fence_before();
   __syncthreads();
   if (warp == kEpilogueWarps) tmem_dealloc(tmem_base, kTmemCols);
-  if (tid == 0 && *sm.abort_flag) *p.status = 1;
+  if (tid == 0 && *sm.abort_flag) {
+    *p.status = 1;
+    g_wait_status = 1;
+  }
 }
 
 // =================================================================================================
@@ -1155,7 +1162,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_dw_kernel(const DwParams p) {
   tc_fence_before();
   __syncthreads();
   if (warp == kEpilogueWarps) tmem_dealloc(tmem_base, kTmemCols);
-  if (tid == 0 && *sm.abort_flag) *p.status = 1;
+  if (tid == 0 && *sm.abort_flag) {
+    *p.status = 1;
+    g_wait_status = 1;
+  }
 }
 
 // =================================================================================================
@@ -1491,7 +1501,7 @@ PremulGeometry premul_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, in
 
 int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan, int64_t CH, int64_t SH, int64_t SW,
                       int64_t K, int64_t GH, int64_t GW, const void *wgt, int64_t sm_, int64_t sc, int64_t sk, const void *bias,
-                      void *out, int64_t M, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st) {
+                      void *out, int64_t M, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz) {
   const Geometry &g = q.g;
   if (!ws || ws_bytes < 256 + g.xh_bytes + g.wp_bytes + q.t_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
   if ((uintptr_t)ws & 255) return SPH_ERR_INVALID_ARGUMENT;  // vector loads and bulk copies assume the alignment
@@ -1500,7 +1510,7 @@ int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
   __nv_bfloat16 *T = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes + g.wp_bytes);
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
-  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, g_fusion.mask);  // adjoint: src is grad_output
+  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, fz.mask);  // adjoint: src is grad_output
   const int64_t wtotal = (int64_t)g.nblk * g.nchunks * g.Npb * kChunk;
   premul_weight_image_kernel<<<cdiv(wtotal, 256), 256, 0, st>>>((const float *)wgt, wp, (int)M, q.Mp, (int)K, (int)CH, g.Npb, g.nblk,
                                                                 g.nchunks, sm_, sc, sk);
@@ -1519,13 +1529,14 @@ int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan
 // Out[b,n,pix] (+bias) on the tensor cores.  src is (B,CH,SH,SW) float32; the GEMM pixels are the (GH,GW) grid.
 int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, const void *plan, int64_t CH, int64_t SH,
             int64_t SW, int64_t K, int64_t P, int64_t GH, int64_t GW, int interp, const void *wgt, int64_t sn, int64_t sc,
-            int64_t sk, const void *bias, void *out, int64_t Nout, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st) {
+            int64_t sk, const void *bias, void *out, int64_t Nout, int64_t B, void *ws, size_t ws_bytes, cudaStream_t st,
+            const Fusion &fz = Fusion{}) {
   if (use_plan) {
     const PremulGeometry q = premul_geometry(B, CH, SH * SW, K, Nout, GH * GW);
-    if (q.use) return tc_adjoint_premul(q, src, plan, CH, SH, SW, K, GH, GW, wgt, sn, sc, sk, bias, out, Nout, B, ws, ws_bytes, st);
+    if (q.use) return tc_adjoint_premul(q, src, plan, CH, SH, SW, K, GH, GW, wgt, sn, sc, sk, bias, out, Nout, B, ws, ws_bytes, st, fz);
   }
   const Geometry g = geometry(B, CH, SH * SW, K, P, interp, Nout, !use_plan);
-  if (!g.ok && fusion_active()) return SPH_ERR_UNSUPPORTED;
+  if (!g.ok && fz.active()) return SPH_ERR_UNSUPPORTED;
   if (!g.ok)  // shapes the tile kernel does not cover run on the exact SIMT kernels instead
     return simt_gemm<float>(use_plan, src, map, iw, plan, CH, SH, SW, K, P, GH * GW, interp, wgt, sn, sc, sk, bias, out, Nout, B, st);
   if (!ws || ws_bytes < 256 + g.xh_bytes + g.wp_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
@@ -1534,14 +1545,14 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
   __nv_bfloat16 *xh = (__nv_bfloat16 *)((char *)ws + 256);
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
-  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, use_plan ? g_fusion.mask : nullptr);
+  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, use_plan ? fz.mask : nullptr);
   const int64_t wtotal = (int64_t)g.nblk * g.nchunks * g.Npb * kChunk;
   weight_image_kernel<<<cdiv(wtotal, 256), 256, 0, st>>>((const float *)wgt, wp, (int)Nout, (int)CH, g.Cp, (int)K, g.Npb, g.nblk,
                                                          g.nchunks, sn, sc, sk);
   TcParams p{};
   p.g = Gather{xh, (const float *)map, (const float *)iw, plan, g.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, g.nt};
   p.wp = wp; p.bias = (const float *)bias; p.out = (float *)out; p.status = status;
-  p.relu = (!use_plan && g_fusion.relu_out) ? 1 : 0;
+  p.relu = (!use_plan && fz.relu_out) ? 1 : 0;
   p.B = (int)B; p.Nout = (int)Nout; p.Npb = g.Npb; p.nblk = g.nblk; p.nchunks = g.nchunks;
   p.tiles_x = cdiv(GW, kTW); p.tiles_y = cdiv(GH, kTH); p.stages = g.stages;
   const int64_t tiles = (int64_t)B * p.tiles_x * p.tiles_y * g.nblk;
@@ -1621,10 +1632,11 @@ void launch_dw(const DwParams &p, int grp, bool warp_taps, dim3 grid, size_t sme
 // gw[n,ch,slot] = sum_{b,pix} A[b,n,pix] * im2col(src)[b,pix,(slot,ch)]; gb = sum of gbias_src over batch and pixels.
 int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K,
           int64_t P, int64_t GH, int64_t GW, int interp, int64_t Nout, int64_t B, void *gw, int64_t sn, int64_t sc, int64_t sk,
-          const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st) {
+          const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st,
+          const Fusion &fz = Fusion{}) {
   const DwGeometry d = dw_geometry(B, CH, SH * SW, K, P, interp, Nout, GH, GW, Cbias);
   // a masked gradient needs its bias sums from the (masked) imaging pass
-  if (fusion_active() && (!d.ok || !(gbias_src == A && Cbias == Nout && nbias == GH * GW))) return SPH_ERR_UNSUPPORTED;
+  if (fz.active() && (!d.ok || !(gbias_src == A && Cbias == Nout && nbias == GH * GW))) return SPH_ERR_UNSUPPORTED;
   if (!d.ok)
     return simt_dw<float>(A, src, map, iw, CH, SH, SW, K, P, GH * GW, interp, Nout, B, gw, sn, sc, sk, gbias_src, Cbias, nbias, gb,
                           ws, ws_bytes, st);
@@ -1646,7 +1658,7 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
   float *part2 = (float *)((char *)row_part + align_up((size_t)nblocks * d.mbs_total * 128 * 4, 256));
   grad_image_kernel<<<dim3(d.tiles_x * d.tiles_y, d.mbs_total, (unsigned)B), 256, 0, st>>>(
       (const float *)A, gt, (int)Nout, (int)GH, (int)GW, d.tiles_x, d.tiles_y, d.mbs_total, fuse_bias ? row_part : nullptr,
-      (const float *)g_fusion.mask);
+      (const float *)fz.mask);
   DwParams p{};
   p.g = Gather{xh, (const float *)map, (const float *)iw, nullptr, d.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, d.nt};
   p.gt = gt; p.partial = partial; p.status = status;
@@ -1692,23 +1704,23 @@ size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t 
 
 int tc_conv_forward(const void *x, const void *map, const void *iw, const void *weight, const void *bias, void *out,
                     int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
-                    int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st) {
+                    int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz) {
   return tc_gemm(false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH, OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, ws,
-                 ws_bytes, st);
+                 ws_bytes, st, fz);
 }
 
 int tc_conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx, int64_t B, int64_t Cin,
                            int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
-                           size_t ws_bytes, cudaStream_t st) {
+                           size_t ws_bytes, cudaStream_t st, const Fusion &fz) {
   return tc_gemm(true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH, IW, 0, weight, K, Cin * K, 1, nullptr, gx, Cin, B, ws,
-                 ws_bytes, st);
+                 ws_bytes, st, fz);
 }
 
 int tc_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb,
                             int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
-                            int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st) {
+                            int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz) {
   return tc_dw(gout, x, map, iw, Cin, IH, IW, K, P, OH, OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout, OH * OW, gb, ws,
-               ws_bytes, st);
+               ws_bytes, st, fz);
 }
 
 int tc_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out, int64_t B,
@@ -1733,6 +1745,58 @@ int tc_tconv_backward_weight(const void *gout, const void *x, const void *map, c
 }
 
 }  // namespace sph
+
+// ---- device status and the bounded-wait self check ---------------------------------------------------------
+namespace sph {
+namespace {
+// One CTA allocates tensor memory, then every thread waits on an mbarrier that nothing ever arrives at.  The wait is
+// the same bounded wait the convolution kernels use, with the caller's (short) limit: it must run out, the CTA must
+// free its tensor memory and return normally, and the give-up must show in *status and in the sticky device word.
+__global__ void __launch_bounds__(128) bounded_wait_check_kernel(unsigned long long limit_ns, int *status) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_ptr;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    tc::mbar_init(&bar, 1);
+    abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 0) {
+    tc::tmem_alloc(&tmem_ptr, 32);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t taddr = tmem_ptr;
+  const bool done = tc::mbar_wait(&bar, 0, &abort_flag, limit_ns);
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tc::tmem_dealloc(taddr, 32);
+  if (tid == 0) {
+    *status = (abort_flag && !done) ? 1 : 0;
+    if (abort_flag) g_wait_status = 1;
+  }
+}
+}  // namespace
+}  // namespace sph
+
+extern "C" int sph_device_status(int *status, int reset) {
+  if (!status) return SPH_ERR_INVALID_ARGUMENT;
+  if (cudaMemcpyFromSymbol(status, sph::g_wait_status, sizeof(int)) != cudaSuccess) return SPH_ERR_CUDA;
+  if (reset) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(sph::g_wait_status, &zero, sizeof(int)) != cudaSuccess) return SPH_ERR_CUDA;
+  }
+  return SPH_OK;
+}
+
+extern "C" int sph_debug_bounded_wait(unsigned long long limit_ns, int *status, void *stream) {
+  if (!status || limit_ns == 0 || limit_ns > 1000000000ull) return SPH_ERR_INVALID_ARGUMENT;
+  sph::bounded_wait_check_kernel<<<1, 128, 0, (cudaStream_t)stream>>>(limit_ns, status);
+  return sph::launch_status();
+}
 
 #ifdef SPH_TC_TIMING
 // out[16]: accumulated counters of tc_gemm_kernel (0 fill, 1 chunk loop, 2 tile barrier, 3 MMA wait for operands,

@@ -222,7 +222,10 @@ extern "C" int sph_resample_to_map_static(const void *x, const void *map, const 
                                           int64_t MH, int64_t MW, int64_t OH, int64_t OW, int64_t P, int dtype, int interp,
                                           void *stream) {
   if (!x || !map || !out || P < 0 || (P > 0 && !iw) || interp < 0 || interp > 2) return SPH_ERR_INVALID_ARGUMENT;
+  if (B < 0 || C < 0 || MH <= 0 || MW <= 0 || OH <= 0 || OW <= 0) return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
+  // everything sph_resample_to_map would refuse is refused here, before the shared array is touched
+  if (OH * OW >= ((int64_t)1 << 31) || MH * MW >= ((int64_t)1 << 31) || B * C / 2 >= 65535) return SPH_ERR_TOO_LARGE;
   PlanLayout L;
   if (!plan_layout(MH * MW, 1, P, interp, OH, OW, dtype, L)) return SPH_ERR_TOO_LARGE;
   if (L.total > (size_t)SPH_STATIC_SCRATCH_BYTES) return SPH_ERR_STATIC_SCRATCH_EXCEEDED;

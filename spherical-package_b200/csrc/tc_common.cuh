@@ -47,14 +47,15 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // leaves its loop and the kernel reports status 1.
 constexpr uint64_t kWaitLimitNs = 4000000000ull;
 constexpr uint32_t kSuspendHintNs = 100000u;
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity, kSuspendHintNs)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t spin = 1;; spin++) {
     if (mbar_try_wait(bar, parity, kSuspendHintNs)) return true;
     if ((spin & 15u) == 0) {  // the abort flag and the clock are looked at every 16th failed try only
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         return false;
       }

@@ -46,6 +46,19 @@ void ok(int status, const char *what) {
   TORCH_CHECK(status == SPH_OK, what, ": ", sph_status_string(status));
 }
 
+// SPHERICAL_MAPPED_CHECK_STATUS=1: after every convolution call wait for the device and raise if a bounded wait inside
+// a tensor-core kernel gave up (off by default: the check synchronises).
+void maybe_check_device(const char *what) {
+  static const bool on = [] {
+    const char *e = std::getenv("SPHERICAL_MAPPED_CHECK_STATUS");
+    return e && *e && std::string(e) != "0";
+  }();
+  if (!on) return;
+  int v = 0;
+  ok(sph_device_status(&v, 1), "sph_device_status");
+  TORCH_CHECK(v == 0, what, ": a bounded wait inside a tensor-core kernel gave up; the results are invalid");
+}
+
 int dtype_of(const torch::Tensor &t) {
   TORCH_CHECK(t.scalar_type() == torch::kFloat || t.scalar_type() == torch::kDouble,
               "mapped operators support float32 and float64 tensors only");
@@ -290,6 +303,7 @@ torch::Tensor conv_forward_impl(torch::Tensor x, torch::Tensor map, const torch:
                                                 a.P, a.dtype, a.interp, a.prec, ws.data_ptr(), wb, stream());
     if (rc != SPH_ERR_UNSUPPORTED) {
       ok(rc, "sph_mapped_conv_relu_forward");
+      maybe_check_device("mapped convolution");
       return out;
     }
   }
@@ -298,6 +312,7 @@ torch::Tensor conv_forward_impl(torch::Tensor x, torch::Tensor map, const torch:
                              ws.data_ptr(), wb, stream()),
      "sph_mapped_conv_forward");
   if (relu) out.clamp_min_(0);
+  maybe_check_device("mapped convolution");
   return out;
 }
 
@@ -334,16 +349,31 @@ std::vector<torch::Tensor> conv_backward_impl(torch::Tensor go, torch::Tensor ma
     const int rc = sph_mapped_conv_relu_backward_input(go.data_ptr(), act_out->data_ptr(), plan.data_ptr(), weight.data_ptr(),
                                                        gx.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.dtype,
                                                        a.prec, ws.data_ptr(), wb, stream());
+    // The two fused operators are eligible independently (the weight-gradient kernel's tap table is smaller than the
+    // gather-GEMM's), so each one that declines falls back on its own to a masked copy and the plain operator.
+    bool have_gx = false;
     if (rc != SPH_ERR_UNSUPPORTED) {
       ok(rc, "sph_mapped_conv_relu_backward_input");
-      ok(sph_mapped_conv_relu_backward_weight(go.data_ptr(), act_out->data_ptr(), x.data_ptr(), map.data_ptr(),
-                                              iw ? iw->data_ptr() : nullptr, gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout,
-                                              a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp, a.prec, ws2.data_ptr(), wb2,
-                                              stream()),
-         "sph_mapped_conv_relu_backward_weight");
-      return {gx, gw, gb};
+      have_gx = true;
+      const int rc2 = sph_mapped_conv_relu_backward_weight(go.data_ptr(), act_out->data_ptr(), x.data_ptr(), map.data_ptr(),
+                                                           iw ? iw->data_ptr() : nullptr, gw.data_ptr(), gb.data_ptr(), a.B,
+                                                           a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp,
+                                                           a.prec, ws2.data_ptr(), wb2, stream());
+      if (rc2 != SPH_ERR_UNSUPPORTED) {
+        ok(rc2, "sph_mapped_conv_relu_backward_weight");
+        maybe_check_device("mapped convolution");
+        return {gx, gw, gb};
+      }
     }
     go = at::threshold_backward(go, *act_out, 0);
+    if (have_gx) {
+      ok(sph_mapped_conv_backward_weight(go.data_ptr(), x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr,
+                                         gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
+                                         a.dtype, a.interp, a.prec, ws2.data_ptr(), wb2, stream()),
+         "sph_mapped_conv_backward_weight");
+      maybe_check_device("mapped convolution");
+      return {gx, gw, gb};
+    }
   }
   ok(sph_mapped_conv_backward_input(go.data_ptr(), plan.data_ptr(), weight.data_ptr(), gx.data_ptr(), a.B, a.Cin, a.Cout,
                                     a.IH, a.IW, a.OH, a.OW, a.K, a.dtype, a.prec, ws.data_ptr(), wb, stream()),
@@ -353,6 +383,7 @@ std::vector<torch::Tensor> conv_backward_impl(torch::Tensor go, torch::Tensor ma
                                      gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
                                      a.dtype, a.interp, a.prec, ws2.data_ptr(), wb, stream()),
      "sph_mapped_conv_backward_weight");
+  maybe_check_device("mapped convolution");
   return {gx, gw, gb};
 }
 
@@ -409,6 +440,7 @@ torch::Tensor tconv_forward_impl(torch::Tensor x, torch::Tensor map, const torch
   ok(sph_mapped_tconv_forward(x.data_ptr(), plan.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(), a.B, a.Cin,
                               a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.dtype, a.prec, ws.data_ptr(), wb, stream()),
      "sph_mapped_tconv_forward");
+  maybe_check_device("mapped convolution");
   return out;
 }
 
@@ -444,6 +476,7 @@ std::vector<torch::Tensor> tconv_backward_impl(torch::Tensor go, torch::Tensor m
                                       gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
                                       a.dtype, a.interp, a.prec, ws2.data_ptr(), wb, stream()),
      "sph_mapped_tconv_backward_weight");
+  maybe_check_device("mapped convolution");
   return {gx, gw, gb};
 }
 
@@ -503,4 +536,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("clear_plan_cache", &clear_plan_cache);
   m.def("plan_cache_size", &plan_cache_size);
   m.def("abi_version", []() { return sph_version(); });
+  m.def(
+      "device_status",
+      [](bool reset) {
+        int v = -1;
+        ok(sph_device_status(&v, reset ? 1 : 0), "sph_device_status");
+        return v;
+      },
+      py::arg("reset") = true,
+      "1 if a bounded wait inside a tensor-core kernel gave up on the current device since the last reset (results of "
+      "that launch are invalid), else 0; waits for the device's queued work");
 }

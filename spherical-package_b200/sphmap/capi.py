@@ -25,6 +25,7 @@ SYMBOLS = [
     "sph_mapped_conv_forward", "sph_mapped_conv_backward_input", "sph_mapped_conv_backward_weight",
     "sph_mapped_tconv_forward", "sph_mapped_tconv_backward_input", "sph_mapped_tconv_backward_weight",
     "sph_mapped_conv_relu_forward", "sph_mapped_conv_relu_backward_input", "sph_mapped_conv_relu_backward_weight",
+    "sph_device_status", "sph_debug_bounded_wait",
 ]
 ERR_UNSUPPORTED = 2
 
@@ -79,6 +80,32 @@ def _P(iw):
 
 def _bytes(n, like):
     return torch.empty(max(int(n), 1), dtype=torch.uint8, device=like.device)
+
+
+def device_status(reset=True):
+    """Sticky status word of the current device: 1 if a bounded wait inside a tensor-core kernel ever gave up (the
+    outputs of that launch are invalid), else 0.  Waits for the device's queued work."""
+    v = ctypes.c_int(-1)
+    _ok(lib.sph_device_status(ctypes.byref(v), _int(1 if reset else 0)), "sph_device_status")
+    return v.value
+
+
+def check_device_status():
+    if device_status() != 0:
+        raise SphError("a bounded wait inside a tensor-core kernel gave up: results of that launch are invalid")
+
+
+def workspace_status(ws):
+    """Status word (first 32 bits) of a bf16-path workspace returned by conv_workspace(); synchronises."""
+    return int(ws[0][:4].view(torch.int32).item()) if ws[1] >= 4 else 0
+
+
+def debug_bounded_wait(limit_ns=1000000):
+    """Runs the library's self check of its bounded waits (a wait nothing satisfies, with a short limit) and returns
+    the status the kernel wrote: 1 = the wait ran out and the kernel returned normally."""
+    st = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    _ok(lib.sph_debug_bounded_wait(ctypes.c_ulonglong(int(limit_ns)), _ptr(st), _stream()), "sph_debug_bounded_wait")
+    return int(st.item())
 
 
 def resample_from_map(x, smap, interp, iw=None):

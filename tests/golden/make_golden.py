@@ -1,7 +1,8 @@
 """Generate the golden fixtures of tests/golden/ from the reference itself.
 
-Run in a container that has the reference checkout (default /root/reference)
-and the compiled reference CPU modules (python oracle/build_ref.py):
+Run in a container that has the reference checkout ($SPHERICAL_PACKAGE_REFERENCE,
+else the folder `reference` beside this repository, or --reference PATH) and the
+compiled reference CPU modules (python oracle/build_ref.py):
 
     python tests/golden/make_golden.py
 
@@ -37,6 +38,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
 from oracle import ref  # noqa: E402
+from oracle.build_ref import default_reference  # noqa: E402
 
 
 # --------------------------------------------------------------------------
@@ -246,7 +248,7 @@ def random_cases():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=default_reference())
     a = ap.parse_args()
     assert ref.available(), "build the reference modules first: python oracle/build_ref.py"
     kats = [evaluate(c) for c in harvest(a.reference)]

@@ -94,6 +94,51 @@ def test_layer_with_fused_activation_matches_layer_plus_relu(precision):
         C.set_precision(old)
 
 
+@pytest.mark.parametrize("level", ["c_abi", "layer"])
+def test_weighted_bilinear_three_points_bf16(level):
+    """Weighted bilinear map with three points per slot (12 taps), 64 channels, bf16: the gather-GEMM fuses the mask,
+    the weight-gradient kernel declines (its tap table is the smaller one), and each side must fall back on its own
+    with results identical to the unfused composition."""
+    import _spherical_distortion_ext._C as C
+    from sphmap import capi
+    from spherical_distortion.nn import InterpolationType, MappedConvolution
+    g = torch.Generator().manual_seed(17)
+    B, Cin, Cout, H, W, K, P = 2, 64, 48, 12, 24, 9, 3
+    x = torch.randn(B, Cin, H, W, generator=g).cuda()
+    m = (torch.rand(H, W, K, P, 2, generator=g) * torch.tensor([W + 1.0, H + 1.0]) - 1).cuda()
+    iw = torch.rand(H, W, K, P, generator=g).cuda()
+    go = torch.randn(B, Cout, H, W, generator=g).cuda()
+    if level == "c_abi":
+        w = (torch.randn(Cout, Cin, K, generator=g) / (Cin * K) ** 0.5).cuda()
+        b = (torch.randn(Cout, generator=g) * 0.1).cuda()
+        y = capi.conv_relu_forward(x, m, w, b, K, 1, iw, capi.BF16)
+        assert torch.equal(y, capi.conv_forward(x, m, w, b, K, 1, iw, capi.BF16).clamp_(min=0))
+        plan = capi.plan_build(m, iw, H * W, K, 1, H, W)
+        gm = go * (y > 0)
+        assert torch.equal(capi.conv_relu_backward_input(go, y, plan, w, H, W, K, capi.BF16),
+                           capi.conv_backward_input(gm, plan, w, H, W, K, capi.BF16))
+        got, want = capi.conv_relu_backward_weight(go, y, x, m, K, 1, iw, capi.BF16), capi.conv_backward_weight(gm, x, m, K, 1, iw, capi.BF16)
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+        return
+    old = C.get_precision()
+    C.set_precision("bf16")
+    try:
+        x.requires_grad_(True)
+        plain = MappedConvolution(Cin, Cout, K, InterpolationType.BILINEAR).cuda()
+        fused = MappedConvolution(Cin, Cout, K, InterpolationType.BILINEAR, activation="relu").cuda()
+        fused.load_state_dict(plain.state_dict())
+        y0 = torch.relu(plain(x, m, iw))
+        y0.backward(go)
+        gx0 = x.grad.clone()
+        x.grad = None
+        y1 = fused(x, m, iw)
+        y1.backward(go)
+        assert torch.equal(y1, y0) and torch.equal(x.grad, gx0)
+        assert torch.equal(fused.weight.grad, plain.weight.grad) and torch.equal(fused.bias.grad, plain.bias.grad)
+    finally:
+        C.set_precision(old)
+
+
 def test_encoder_stack_fused_equals_unfused():
     from sphmap import capi, workloads as wl
     from sphmap.parallel import EncoderStack
