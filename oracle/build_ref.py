@@ -36,6 +36,12 @@ MODULES = {
     "_weighted_mapped_transposed_convolution": "weighted_mapped_transposed_convolution_layer",
     "_mapped_max_pooling": "mapped_max_pooling_layer",
     "_weighted_mapped_max_pooling": "weighted_mapped_max_pooling_layer",
+    "_mapped_avg_pooling": "mapped_avg_pooling_layer",
+    "_weighted_mapped_avg_pooling": "weighted_mapped_avg_pooling_layer",
+    "_uv_resample": "uv_resample_layer",
+    "_voting_resample": "voting_resample_layer",
+    "_convolution": "convolution_layer",
+    "_transposed_convolution": "transposed_convolution_layer",
 }
 
 

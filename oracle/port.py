@@ -142,3 +142,54 @@ def mapped_transposed_conv_backward(go, sample_map, x, weight, bias, kernel_size
     _call("sph_o_tconv_backward", x, _p(go), _p(x), _p(sample_map), _p(iw), _p(weight), _p(gx), _p(gw), _p(gb),
           *_i(B, Cin, Cout, IH, IW, OH, OW, kernel_size, _P(iw)), ctypes.c_int(int(interp)))
     return gx, gw, gb
+
+
+def mapped_avg_pool(x, sample_map, kernel_size, interp, interp_weights=None):
+    x, sample_map, iw = _prep(x, sample_map, interp_weights)
+    B, C, IH, IW = x.shape
+    OH, OW = sample_map.shape[:2]
+    out = torch.empty(B, C, OH, OW, dtype=x.dtype)
+    _call("sph_o_avg_pool", x, _p(x), _p(sample_map), _p(iw), _p(out), *_i(B, C, IH, IW, OH, OW, kernel_size, _P(iw)),
+          ctypes.c_int(int(interp)))
+    return out
+
+
+def mapped_avg_unpool(g, sample_map, ih, iw_, kernel_size, interp, interp_weights=None):
+    g, sample_map, iw = _prep(g, sample_map, interp_weights)
+    B, C, OH, OW = g.shape
+    gin = torch.empty(B, C, int(ih), int(iw_), dtype=g.dtype)
+    _call("sph_o_avg_unpool", g, _p(g), _p(sample_map), _p(iw), _p(gin), *_i(B, C, ih, iw_, OH, OW, kernel_size, _P(iw)),
+          ctypes.c_int(int(interp)))
+    return gin
+
+
+def resample_from_uv_maps(tex, quad_idx, tex_uv, interp):
+    """tex (B,C,NT,TH,TW), quad_idx (IH,IW) int64, tex_uv (IH,IW,2) -> (B,C,IH,IW)."""
+    tex, quad_idx, tex_uv = _prep(tex, quad_idx, tex_uv)
+    B, C, NT, TH, TW = tex.shape
+    IH, IW = quad_idx.shape
+    out = torch.empty(B, C, IH, IW, dtype=tex.dtype)
+    _call("sph_o_resample_from_uv", tex, _p(tex), _p(quad_idx), _p(tex_uv), _p(out), *_i(B, C, NT, TH, TW, IH, IW),
+          ctypes.c_int(int(interp)))
+    return out
+
+
+def resample_to_uv_maps(x, quad_idx, tex_uv, num_textures, tex_h, tex_w, interp):
+    """x (B,C,IH,IW) -> (B,C,NT,TH,TW)."""
+    x, quad_idx, tex_uv = _prep(x, quad_idx, tex_uv)
+    B, C, IH, IW = x.shape
+    tex = torch.empty(B, C, int(num_textures), int(tex_h), int(tex_w), dtype=x.dtype)
+    _call("sph_o_resample_to_uv", x, _p(x), _p(quad_idx), _p(tex_uv), _p(tex), *_i(B, C, num_textures, tex_h, tex_w, IH, IW),
+          ctypes.c_int(int(interp)))
+    return tex
+
+
+def voting_resample_to_map(x, sample_map, oh, ow, num_candidates):
+    """x (B,C,IH,IW) int64 labels, sample_map (IH,IW,2) int64 (x, y) -> (B,C,oh,ow) int64."""
+    x, sample_map = _prep(x, sample_map)
+    B, C, IH, IW = x.shape
+    out = torch.empty(B, C, int(oh), int(ow), dtype=torch.int64)
+    f = lib().sph_o_voting_resample
+    f.restype = None
+    f(_p(x), _p(sample_map), _p(out), *_i(B, C, IH, IW, oh, ow, num_candidates))
+    return out

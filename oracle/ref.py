@@ -109,3 +109,36 @@ def mapped_transposed_conv_backward(go, sample_map, x, weight, bias, kernel_size
             go, sample_map, iw, x, weight, bias, int(kernel_size), interp_enum(interp)))
     return tuple(mod("_mapped_transposed_convolution").mapped_transposed_conv_backward(
         go, sample_map, x, weight, bias, int(kernel_size), interp_enum(interp)))
+
+
+def mapped_avg_pool(x, sample_map, kernel_size, interp, interp_weights=None):
+    x, sample_map, iw = _c(x, sample_map, interp_weights)
+    if iw is not None:
+        return mod("_weighted_mapped_avg_pooling").weighted_mapped_avg_pool(x, sample_map, iw, int(kernel_size),
+                                                                            interp_enum(interp))
+    return mod("_mapped_avg_pooling").mapped_avg_pool(x, sample_map, int(kernel_size), interp_enum(interp))
+
+
+def mapped_avg_unpool(g, sample_map, ih, iw_, kernel_size, interp, interp_weights=None):
+    g, sample_map, iw = _c(g, sample_map, interp_weights)
+    if iw is not None:
+        return mod("_weighted_mapped_avg_pooling").weighted_mapped_avg_unpool(g, sample_map, iw, int(ih), int(iw_),
+                                                                              int(kernel_size), interp_enum(interp))
+    return mod("_mapped_avg_pooling").mapped_avg_unpool(g, sample_map, int(ih), int(iw_), int(kernel_size),
+                                                        interp_enum(interp))
+
+
+def resample_from_uv_maps(tex, quad_idx, tex_uv, interp):
+    tex, quad_idx, tex_uv = _c(tex, quad_idx, tex_uv)
+    return mod("_uv_resample").resample_from_uv_maps(tex, quad_idx, tex_uv, interp_enum(interp))
+
+
+def resample_to_uv_maps(x, quad_idx, tex_uv, num_textures, tex_h, tex_w, interp):
+    x, quad_idx, tex_uv = _c(x, quad_idx, tex_uv)
+    return mod("_uv_resample").resample_to_uv_maps(x, quad_idx, tex_uv, int(num_textures), int(tex_h), int(tex_w),
+                                                   interp_enum(interp))
+
+
+def voting_resample_to_map(x, sample_map, oh, ow, num_candidates):
+    x, sample_map = _c(x, sample_map)
+    return mod("_voting_resample").voting_resample_to_map(x, sample_map, int(oh), int(ow), int(num_candidates))

@@ -299,3 +299,74 @@ void FN(sph_o_tconv_backward)(const T *go, const T *x, const T *map, const T *iw
   }
   free(col);
 }
+
+/* ---- mapped average pool --------------------------------------------------
+ * common/mapped_avg_pool.h:12-39 (plain) and :71-107 (weighted): the K slot
+ * values are added in slot order and the sum is divided by kernel_size;
+ * src/cpp/mapped_avg_pooling_layer.cpp:8-38. */
+void FN(sph_o_avg_pool)(const T *x, const T *map, const T *iw, T *out, int64_t B, int64_t C, int64_t IH,
+                        int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int interp) {
+  const int64_t n = OH * OW, PP = P ? P : 1;
+#pragma omp parallel for schedule(static)
+  for (int64_t bc = 0; bc < B * C; bc++) {
+    const T *plane = x + bc * IH * IW;
+    for (int64_t o = 0; o < n; o++) {
+      T acc = (T)0;
+      for (int64_t k = 0; k < K; k++) {
+        const int64_t e = (o * K + k) * PP;
+        acc += P ? FN(gather_w)(plane, map + e * 2, iw + e, P, IH, IW, interp)
+                 : FN(gather)(plane, map + e * 2, IH, IW, interp);
+      }
+      out[bc * n + o] = acc / (T)K;
+    }
+  }
+}
+
+/* common/mapped_avg_pool.h:41-69 and :109-143: grad / kernel_size goes back
+ * through every slot; src/cpp/mapped_avg_pooling_layer.cpp:40-72. */
+void FN(sph_o_avg_unpool)(const T *g, const T *map, const T *iw, T *gin, int64_t B, int64_t C, int64_t IH,
+                          int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int interp) {
+  const int64_t n = OH * OW, PP = P ? P : 1;
+  memset(gin, 0, sizeof(T) * (size_t)(B * C * IH * IW));
+#pragma omp parallel for schedule(static)
+  for (int64_t bc = 0; bc < B * C; bc++) {
+    T *plane = gin + bc * IH * IW;
+    for (int64_t o = 0; o < n; o++) {
+      const T v = g[bc * n + o] / (T)K;
+      for (int64_t k = 0; k < K; k++) {
+        const int64_t e = (o * K + k) * PP;
+        if (P) FN(scatter_w)(v, map + e * 2, iw + e, P, IH, IW, interp, plane);
+        else FN(scatter)(v, map + e * 2, IH, IW, interp, plane);
+      }
+    }
+  }
+}
+
+/* ---- UV-map resampling (tangent-image textures) ---------------------------
+ * common/resample.h:133-159 (gather) and :161-187 (scatter);
+ * src/cpp/uv_resample_layer.cpp:8-72.  tex is (B,C,NT,TH,TW); quad (IH,IW)
+ * names the texture of every image pixel, uv (IH,IW,2) the position inside
+ * it in texel units.  A quad index outside [0,NT) contributes nothing here
+ * (the reference would address out of bounds). */
+void FN(sph_o_resample_from_uv)(const T *tex, const int64_t *quad, const T *uv, T *out, int64_t B, int64_t C,
+                                int64_t NT, int64_t TH, int64_t TW, int64_t IH, int64_t IW, int interp) {
+  const int64_t n = IH * IW;
+#pragma omp parallel for schedule(static)
+  for (int64_t bc = 0; bc < B * C; bc++)
+    for (int64_t i = 0; i < n; i++) {
+      const int64_t q = quad[i];
+      out[bc * n + i] = (q >= 0 && q < NT) ? FN(gather)(tex + (bc * NT + q) * TH * TW, uv + 2 * i, TH, TW, interp) : (T)0;
+    }
+}
+
+void FN(sph_o_resample_to_uv)(const T *x, const int64_t *quad, const T *uv, T *tex, int64_t B, int64_t C,
+                              int64_t NT, int64_t TH, int64_t TW, int64_t IH, int64_t IW, int interp) {
+  const int64_t n = IH * IW;
+  memset(tex, 0, sizeof(T) * (size_t)(B * C * NT * TH * TW));
+#pragma omp parallel for schedule(static)
+  for (int64_t bc = 0; bc < B * C; bc++)
+    for (int64_t i = 0; i < n; i++) {
+      const int64_t q = quad[i];
+      if (q >= 0 && q < NT) FN(scatter)(x[bc * n + i], uv + 2 * i, TH, TW, interp, tex + (bc * NT + q) * TH * TW);
+    }
+}
