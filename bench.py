@@ -204,55 +204,73 @@ def run_encoder(args, rank, local, world):
     import _spherical_distortion_ext as ext
     from spherical_distortion.nn import InterpolationType, MappedConvolution
     ext.set_precision(args.precision)
-    mods = []
-    for li, (ci, co, _, _, _) in enumerate(cfg["layers"]):
-        m = MappedConvolution(ci, co, 9, InterpolationType.BILINEAR, activation="relu").to(dev)
-        with torch.no_grad():
-            m.weight.copy_(cfg["weights"][li])
-            m.bias.copy_(cfg["biases"][li])
-        mods.append(m)
     maps = [t.to(dev) for t in cfg["maps"]]
-    params = [p for m in mods for p in (m.weight, m.bias)]
     loss_host = torch.empty((), dtype=torch.float32).pin_memory()
-
-    # The input batch of step i+1 is copied host->device on a side stream while step i computes (what a
-    # prefetching data loader does); every step's copy and its loss read-back lie inside the timed region.
     copy_stream = torch.cuda.Stream(device=dev)
-    staged = {"x": None, "ev": None}
 
-    def stage_next():
-        with torch.cuda.stream(copy_stream):
-            staged["x"] = x_host.to(dev, non_blocking=True)
-            staged["ev"] = torch.cuda.Event()
-            staged["ev"].record(copy_stream)
-
-    def e2e_step():
-        if staged["x"] is None:
-            stage_next()
-        torch.cuda.current_stream().wait_event(staged["ev"])
-        xb = staged["x"]
-        xb.record_stream(torch.cuda.current_stream())
-        stage_next()
-        h = xb
-        for m, sm in zip(mods, maps):
-            h = m(h, sm)   # ReLU fused into the layer (activation="relu")
-        loss = (h * go).sum()
-        for p in params:
-            p.grad = None
-        loss.backward()
+    def make_e2e(fused):
+        """One training step through the layer API.  fused: MappedConvolution(activation="relu") (this library's
+        extension); otherwise MappedConvolution followed by torch.relu, the composition the reference's API offers."""
+        mods = []
+        for li, (ci, co, _, _, _) in enumerate(cfg["layers"]):
+            m = MappedConvolution(ci, co, 9, InterpolationType.BILINEAR, activation="relu" if fused else None).to(dev)
+            with torch.no_grad():
+                m.weight.copy_(cfg["weights"][li])
+                m.bias.copy_(cfg["biases"][li])
+            mods.append(m)
+        params = [p for m in mods for p in (m.weight, m.bias)]
+        pending = []
         if world > 1:
-            flat = torch.cat([p.grad.reshape(-1) for p in params])
-            dist.all_reduce(flat)
-        loss_host.copy_(loss.detach(), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            # gradient exchange as a training loop does it: each parameter's gradient is sum-allreduced in place as soon
+            # as autograd has produced it, overlapping the rest of backward; the step waits for all of them at the end
+            for p in params:
+                p.register_post_accumulate_grad_hook(lambda t: pending.append(dist.all_reduce(t.grad, async_op=True)))
+        # The input batch of step i+1 is copied host->device on a side stream while step i computes (what a
+        # prefetching data loader does); every step's copy and its loss read-back lie inside the timed region.
+        staged = {"x": None, "ev": None}
+
+        def stage_next():
+            with torch.cuda.stream(copy_stream):
+                staged["x"] = x_host.to(dev, non_blocking=True)
+                staged["ev"] = torch.cuda.Event()
+                staged["ev"].record(copy_stream)
+
+        def e2e_step():
+            if staged["x"] is None:
+                stage_next()
+            torch.cuda.current_stream().wait_event(staged["ev"])
+            xb = staged["x"]
+            xb.record_stream(torch.cuda.current_stream())
+            stage_next()
+            h = xb
+            for m, sm in zip(mods, maps):
+                h = m(h, sm) if fused else torch.relu(m(h, sm))
+            loss = (h * go).sum()
+            for p in params:
+                p.grad = None
+            loss.backward()
+            for w in pending:
+                w.wait()
+            pending.clear()
+            loss_host.copy_(loss.detach(), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        return e2e_step
 
     del stack
     torch.cuda.empty_cache()
-    if args.skip_e2e:
-        e2e_ms, e2e_value = float("nan"), float("nan")
-    else:
-        e2e_ms, _ = timed_loop(e2e_step, args.steps, args.warmup, world, dev)
-        e2e_value = flops_step * args.steps / (e2e_ms * 1e-3) / 1e12
+    e2e = {}
+    for name, fused in (("e2e", True), ("e2e_unfused", False)):
+        if args.skip_e2e:
+            e2e[name] = (float("nan"), float("nan"))
+            continue
+        t_ms, _ = timed_loop(make_e2e(fused), args.steps, args.warmup, world, dev)
+        e2e[name] = (t_ms, flops_step * args.steps / (t_ms * 1e-3) / 1e12)
+        torch.cuda.empty_cache()
+    e2e_ms, e2e_value = e2e["e2e"]
+    status = capi.device_status()   # a bounded wait that gave up inside a tensor-core kernel invalidates the run
+    if status != 0:
+        raise SystemExit("device status %d: a bounded wait inside a tensor-core kernel gave up; results invalid" % status)
 
     if rank != 0:
         return None
@@ -285,7 +303,7 @@ def run_encoder(args, rank, local, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 3),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16" if args.precision == "bf16" else "f32", "data": "synthetic",
-        "config": {"workload": "spherical encoder stack (BASELINE config 4): 4x bilinear mapped conv + ReLU on 3x3 "
+        "config": {"workload": "spherical encoder stack: 4x bilinear mapped conv + ReLU on 3x3 "
                                "gnomonic maps, 3->64->128->256->256, %dx%d -> %dx%d, fwd+bwd+dW allreduce"
                                % (args.height, 2 * args.height, args.height // 4, args.height // 2),
                    "global_batch": B, "parallelism": "batch-sharded dp%d" % world, "precision": args.precision,
@@ -295,6 +313,9 @@ def run_encoder(args, rank, local, world):
         "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 4 * world,
                 "d2h_bytes_per_step": 4 * world, "ms_per_step": round(e2e_ms / args.steps, 3),
                 "api": "spherical_distortion.nn.MappedConvolution(activation='relu') + autograd"},
+        "e2e_unfused": {"value": round(e2e["e2e_unfused"][1], 3), "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 4 * world,
+                        "d2h_bytes_per_step": 4 * world, "ms_per_step": round(e2e["e2e_unfused"][0] / args.steps, 3),
+                        "api": "spherical_distortion.nn.MappedConvolution + torch.relu + autograd (the reference's API, no fused activation)"},
         "gpu_launches": int(launches_per_step * args.steps),
         "roofline": {"bound": "tensor", "kernel": dom_kernel, "launches_per_step": dom_n,
                      "avg_launch_ms": round(dom_ms / dom_n, 3),
@@ -302,19 +323,29 @@ def run_encoder(args, rank, local, world):
                      "share_of_conv_time": round(dom_ms / sum(per_launch.values()), 3),
                      "achieved": round(achieved, 2), "peak": tensor_peak, "unit": "TFLOP/s",
                      "frac": round(achieved / tensor_peak, 4),
-                     # dram read+write of the layer-4 forward launch of this kernel: 156.8 MB in the batch-4 ncu
-                     # capture (profiles/tc_gemm_kernel_encoder_B4.md), scaled by local batch / 4 (traffic is
-                     # proportional to the batch: activations in, activations out)
-                     "traffic": int(156.8e6 * (hi - lo) / 4), "traffic_of": "layer-4 forward launch, scaled from the batch-4 capture",
+                     # DRAM read+write of this kernel's layer-4 forward launch: 156.8 MB in an ncu capture at batch 4,
+                     # scaled by local batch / 4 (activations in, activations out: proportional to the batch)
+                     "traffic": int(156.8e6 * (hi - lo) / 4),
+                     "traffic_of": "layer-4 forward launch; constant from an ncu capture at batch 4 scaled by the batch, not measured in this run",
                      "peak_source": peaks["source"] + " bf16 sustained (kernel timed inside a long step)",
                      "per_launch_ms": {"L%d.%s" % (k[0] + 1, k[1]): round(v, 3) for k, v in per_launch.items()}},
         "clocks": clocks,
     }
+    if world == 1 and not args.skip_extras:
+        # the other benchmark workloads (max pooling, tangent-image resampling, weighted conv on a random map), a few
+        # steps each, so that one default run reports every workload next to the headline
+        del maps, go, x_dev
+        torch.cuda.empty_cache()
+        sub = argparse.Namespace(**vars(args))
+        sub.steps, sub.warmup, sub.batch = max(3, min(args.steps, 5)), 3, 64
+        extra = {}
+        for name, fn in (("pool", run_pool), ("resample", run_resample), ("conv3", run_conv)):
+            r = fn(sub, rank, local, world)
+            extra[name] = {k: r[k] for k in ("metric", "value", "unit", "ms_per_step", "dtype", "config", "roofline", "cpu_baseline")}
+            torch.cuda.empty_cache()
+        out["extra"] = extra
     if world == 1 and not args.skip_cpu:
-        impl, kind = pick_cpu_impl()
-        cores = os.cpu_count()
-        torch.set_num_threads(cores)
-        os.environ["OMP_NUM_THREADS"] = str(cores)
+        impl, kind, cores = _cpu_setup()
         images = 4
         secs = cpu_encoder_seconds(cfg, impl, images)
         out["cpu_baseline"] = {"value": round(3 * wl.encoder_flops(images, args.height, 2 * args.height) / secs / 1e12, 5),
@@ -343,7 +374,8 @@ def run_reference(args, rank, world):
     return {"impl": "reference", "metric": "mapped-conv fwd+bwd TFLOP/s", "value": v, "unit": "TFLOP/s",
             "n_gpus": world, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": round(t / steps * 1e3, 1),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "spherical encoder stack (BASELINE config 4) on the reference CPU path", "sample": sample},
+            "config": {"workload": "spherical encoder stack (4x bilinear mapped conv + ReLU, 3->64->128->256->256, %dx%d input) "
+                                   "on the reference CPU path" % (args.height, 2 * args.height), "sample": sample},
             "cpu_baseline": {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": kind, "sample": sample},
             "e2e": {"value": v, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
@@ -351,6 +383,25 @@ def run_reference(args, rank, world):
 # ---------------------------------------------------------------------------
 # HBM-bound workloads: max pooling (config 2) and tangent-image resampling (config 1)
 # ---------------------------------------------------------------------------
+def _cpu_time(fn, reps=3):
+    """Median wall time of `fn` on the host cores after one warm-up call."""
+    fn()
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        fn()
+        ts.append(time.perf_counter() - t0)
+    return sorted(ts)[len(ts) // 2]
+
+
+def _cpu_setup():
+    impl, kind = pick_cpu_impl()
+    cores = os.cpu_count()
+    torch.set_num_threads(cores)
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    return impl, kind, cores
+
+
 def run_pool(args, rank, local, world):
     from sphmap import capi, workloads as wl
     from sphmap.parallel import shard_batch
@@ -407,17 +458,25 @@ def run_pool(args, rank, local, world):
         return None
     peaks = measured_peaks()
     gbs = 2 * fwd_bytes * world / ((f_ms + b_ms) * 1e-3) / 1e9
-    return {"metric": "mapped max pool fwd+bwd HBM GB/s", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": world,
+    cpu = None
+    if world == 1 and not args.skip_cpu:
+        impl, kind, cores = _cpu_setup()
+        cx, cm, cg = cfg["x"], cfg["map"], cfg["grad_output"]
+        _, cidx = impl.mapped_max_pool(cx, cm, 9, 0)
+        tfc = _cpu_time(lambda: impl.mapped_max_pool(cx, cm, 9, 0))
+        tbc = _cpu_time(lambda: impl.mapped_max_unpool(cg, cidx.clamp_min(0), cm, cx.shape[2], cx.shape[3], 9, 0))
+        cpu = {"value": round(2 * fwd_bytes / (tfc + tbc) / 1e9, 2), "unit": "GB/s", "cores": cores, "kind": kind,
+               "sample": "the same tensors, forward %.3f s + backward %.3f s" % (tfc, tbc)}
+    return {"metric": "mapped max pool fwd+bwd HBM GB/s", "cpu_baseline": cpu, "value": round(gbs, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(f_ms + b_ms, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "mapped max pool (BASELINE config 2): B=%d C=64 256x512 -> 128x256, K=9, nearest, "
+            "config": {"workload": "mapped max pool: B=%d C=64 256x512 -> 128x256, K=9, nearest, "
                                    "uniform-random map" % B, "l2": "256 MB flush before every launch", "local_batch": n},
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "max_pool_kernel (forward)", "achieved": round(fwd_bytes / (f_ms * 1e-3) / 1e9, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(fwd_bytes / (f_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-                         # dram read+write of the forward launch on config 2 (profiles/pool_resample_dram_traffic.md),
-                         # scaled by the local batch
-                         "traffic": int(450.7e6 * n / 8), "fwd_ms": round(f_ms, 4), "bwd_ms": round(b_ms, 4),
+                         # DRAM read+write of the forward launch from an ncu capture at B=8, scaled by the local batch
+                         "traffic": int(450.7e6 * n / 8), "traffic_of": "constant from an ncu capture, not measured in this run", "fwd_ms": round(f_ms, 4), "bwd_ms": round(b_ms, 4),
                          "bwd_achieved": round(fwd_bytes / (b_ms * 1e-3) / 1e9, 1),
                          "local_map": {"map": "3x3 gnomonic, stride 2", "fwd_ms": round(lf_ms, 4), "bwd_ms": round(lb_ms, 4),
                                        "fwd_gbs": round(fwd_bytes / (lf_ms * 1e-3) / 1e9, 1),
@@ -455,7 +514,7 @@ def _resample_bytes(n, C, ns, H, W, map_numel):
 
 
 def run_resample(args, rank, local, world):
-    """BASELINE config 1 (B=8), plus the same operators at B=256 so that the kernels run long enough for the
+    """Tangent-image resampling (B=8), plus the same operators at B=256 so that the kernels run long enough for the
     bandwidth figure to mean something (the B=8 launches move 40-59 MB, about 6-9 us at the HBM peak)."""
     from sphmap import capi, workloads as wl
     from sphmap.parallel import shard_batch
@@ -480,16 +539,25 @@ def run_resample(args, rank, local, world):
     if rank != 0:
         return None
     peaks = measured_peaks()
-    return {"metric": "tangent-image resample HBM GB/s", "value": round((g_bytes + s_bytes) * world / ((g_ms + s_ms) * 1e-3) / 1e9, 1),
+    cpu = None
+    if world == 1 and not args.skip_cpu:
+        impl, kind, cores = _cpu_setup()
+        cx, cm = cfg["x"], cfg["map"]
+        cy = impl.resample_from_map(cx, cm, 1)
+        tg = _cpu_time(lambda: impl.resample_from_map(cx, cm, 1))
+        ts = _cpu_time(lambda: impl.resample_to_map(cy, cm, H, W, 1))
+        cpu = {"value": round((g_bytes + s_bytes) / (tg + ts) / 1e9, 2), "unit": "GB/s", "cores": cores, "kind": kind,
+               "sample": "the same tensors (B=%d), gather %.3f s + scatter %.3f s" % (B, tg, ts)}
+    return {"metric": "tangent-image resample HBM GB/s", "cpu_baseline": cpu, "value": round((g_bytes + s_bytes) * world / ((g_ms + s_ms) * 1e-3) / 1e9, 1),
             "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(g_ms + s_ms, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "tangent-image resampling (BASELINE config 1): B=%d C=3 512x1024 <-> 20x64x64, bilinear" % B,
+            "config": {"workload": "tangent-image resampling: B=%d C=3 512x1024 <-> 20x64x64, bilinear" % B,
                        "l2": "256 MB flush before every launch"},
             "gpu_launches": 2 * args.steps,
             "roofline": {"bound": "hbm", "kernel": "resample_from_map_kernel", "achieved": round(g_bytes / (g_ms * 1e-3) / 1e9, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(g_bytes / (g_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
-                         # dram read+write of the gather launch at B=8 (profiles/pool_resample_dram_traffic.md), scaled
-                         "traffic": int(49.0e6 * n / 8), "gather_ms": round(g_ms, 4), "scatter_ms": round(s_ms, 4),
+                         # DRAM read+write of the gather launch from an ncu capture at B=8, scaled by the local batch
+                         "traffic": int(49.0e6 * n / 8), "traffic_of": "constant from an ncu capture, not measured in this run", "gather_ms": round(g_ms, 4), "scatter_ms": round(s_ms, 4),
                          "scatter_achieved": round(s_bytes / (s_ms * 1e-3) / 1e9, 1),
                          "batch256": {"gather_ms": round(gb_ms, 4), "gather_gbs": round(gb_bytes / (gb_ms * 1e-3) / 1e9, 1),
                                       "gather_frac": round(gb_bytes / (gb_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
@@ -498,7 +566,7 @@ def run_resample(args, rank, local, world):
 
 
 def run_conv(args, rank, local, world):
-    """BASELINE config 3: weighted (4-point, nearest) mapped conv forward + backward and the transposed conv,
+    """Weighted (4-point, nearest) mapped conv forward + backward on a uniform-random map, and the transposed conv,
     every operator timed alone with CUDA events (L2 flushed in between)."""
     from sphmap import capi, workloads as wl
     from sphmap.parallel import shard_batch
@@ -543,10 +611,20 @@ def run_conv(args, rank, local, world):
     gflop_t = 2 * B * 128 * 64 * 9 * (H // 2) * (W // 2) / 1e9
     conv_ms = ms["conv.fwd"] + ms["conv.dx"] + ms["conv.dw"]
     peaks = measured_peaks()
-    return {"metric": "mapped-conv fwd+bwd TFLOP/s", "value": round(3 * gflop_conv / conv_ms, 2), "unit": "TFLOP/s", "n_gpus": world,
+    cpu = None
+    if world == 1 and not args.skip_cpu:
+        impl, kind, cores = _cpu_setup()
+        c1 = {k: (v[:1] if k in ("x", "grad_output") else v) for k, v in cfg.items() if torch.is_tensor(v)}
+        t0 = time.perf_counter()
+        impl.mapped_conv_forward(c1["x"], c1["map"], c1["weight"], c1["bias"], 9, 0, c1["iw"])
+        impl.mapped_conv_backward(c1["grad_output"], c1["map"], c1["x"], c1["weight"], c1["bias"], 9, 0, c1["iw"])
+        secs = time.perf_counter() - t0
+        cpu = {"value": round(3 * gflop_conv / B / secs / 1e3, 4), "unit": "TFLOP/s", "cores": cores, "kind": kind,
+               "sample": "1 image of the same batch, forward + backward, %.1f s" % secs}
+    return {"metric": "mapped-conv fwd+bwd TFLOP/s", "cpu_baseline": cpu, "value": round(3 * gflop_conv / conv_ms, 2), "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(conv_ms, 3), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if args.precision == "bf16" else "f32", "data": "synthetic",
-            "config": {"workload": "BASELINE config 3: weighted (P=4, nearest) mapped conv B=%d 64->128 256x512 K=9, uniform-random map; "
+            "config": {"workload": "weighted (P=4, nearest) mapped conv B=%d 64->128 256x512 K=9, uniform-random map; "
                                    "transposed conv 128->64 128x256->256x512" % B, "precision": args.precision,
                        "l2": "256 MB flush before every launch",
                        "mpix_per_s": round(B * H * W / (conv_ms * 1e-3) / 1e6, 1)},
@@ -569,6 +647,7 @@ def main():
     ap.add_argument("--height", type=int, default=512, help="input height of the encoder stack (width = 2x)")
     ap.add_argument("--skip-e2e", action="store_true", help="encoder: only the device-resident arm (for profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    ap.add_argument("--skip-extras", action="store_true", help="encoder: do not also time the pooling / resampling / weighted-conv workloads")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

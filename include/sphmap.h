@@ -118,6 +118,66 @@ int sph_plan_build(const void *map, const void *iw, int64_t n_src, int64_t K, in
 int sph_resample_to_map(const void *x, const void *plan, void *out, int64_t B, int64_t C, int64_t MH,
                         int64_t MW, int64_t OH, int64_t OW, int dtype, void *stream);
 
+/* resample_to_map followed by the weight-sum normalisation,
+ *   out = scatter(x) / (scatter(1) + 1e-12),
+ * in one pass: every destination pixel divides its sum by the sum of its own
+ * segment's weights.  The reference composes this in Python
+ * (layers/functional/sphere_ops.py:74-80, 110-116). */
+int sph_resample_to_map_normalized(const void *x, const void *plan, void *out, int64_t B, int64_t C, int64_t MH,
+                                   int64_t MW, int64_t OH, int64_t OW, int dtype, void *stream);
+
+/* ------------------------------------------------------------------------
+ * UV-map resampling between an image and NT square textures (tangent
+ * images).  quad_idx (IH,IW) int64 names the texture of every image pixel,
+ * tex_uv (IH,IW,2) its (x, y) position inside that texture in texel units;
+ * tex is (B,C,NT,TH,TW).  Interpolation and its zero padding act inside the
+ * named texture; a texture index outside [0,NT) contributes nothing.
+ *   from_uv_maps   out[b,c,i] = interp(tex[b,c,quad[i]], uv[i])      (gather)
+ *   to_uv_maps     the adjoint: sph_plan_build_uv once per (quad, uv), then
+ *                  sph_resample_to_map(x, plan, tex, B, C, IH, IW,
+ *                  OH = NT*TH, OW = TW, ...)
+ * Replaces spherical::ResampleFromUVMaps / ResampleToUVMaps,
+ * ext_modules/include/layers/uv_resample_layer.h:48-100.
+ * sph_plan_bytes(n_src = IH*IW, 1, 0, interp, NT*TH, TW, dtype) sizes the plan.
+ * ---------------------------------------------------------------------- */
+int sph_resample_from_uv_maps(const void *tex, const int64_t *quad_idx, const void *tex_uv, void *out, int64_t B,
+                              int64_t C, int64_t NT, int64_t TH, int64_t TW, int64_t IH, int64_t IW, int dtype,
+                              int interp, void *stream);
+int sph_plan_build_uv(const void *tex_uv, const int64_t *quad_idx, int64_t n_src, int64_t NT, int64_t TH, int64_t TW,
+                      int interp, int dtype, void *plan, size_t plan_bytes, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Voting resample of integer labels: out[b,c,o] = the label carried by most
+ * of the input pixels whose map entry is output pixel o (the smallest such
+ * label on ties, 0 where nothing lands).  `plan` is a nearest-neighbour plan
+ * (sph_plan_build with interp = 0, K = 1, P = 0) of the map given as
+ * floating-point (x, y) coordinates of type plan_dtype; labels and out are
+ * int64.  Labels outside [0, num_candidates) cast no vote.  Replaces
+ * spherical::VotingResampleToMap,
+ * ext_modules/include/layers/voting_resample_layer.h:32-58, without its
+ * (C, OH, OW, num_candidates) vote tensor.
+ * ---------------------------------------------------------------------- */
+int sph_voting_resample_to_map(const int64_t *labels, const void *plan, int plan_dtype, int64_t *out, int64_t B,
+                               int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t num_candidates,
+                               void *stream);
+
+/* ------------------------------------------------------------------------
+ * Equirectangular kernel maps built on the device.  For every pixel
+ * (y, x) = (oy*stride, ox*stride) of an H x W equirectangular image, the
+ * kh x kw kernel grid around it in fractional pixel coordinates (x, y) of the
+ * same image: map is (ceil(H/stride), ceil(W/stride), kh*kw, 2) of `dtype`.
+ *   SPH_MAP_GRID                 offsets on the lat/lon grid (no wrap)
+ *   SPH_MAP_INVERSE_GNOMONIC     tangent-plane grid projected back onto the
+ *                                sphere; longitude wrapped to [-pi, pi)
+ *   SPH_MAP_INVERSE_EQUIRECT     longitude step divided by cos(latitude)
+ * Replaces grid_projection_map, inverse_gnomonic_projection_map and
+ * inverse_equirectangular_projection_map of the reference's
+ * layers/util/mapping_functions.py:44-163 (host tensor code there).
+ * ---------------------------------------------------------------------- */
+enum sph_map_kind { SPH_MAP_GRID = 0, SPH_MAP_INVERSE_GNOMONIC = 1, SPH_MAP_INVERSE_EQUIRECT = 2 };
+int sph_build_kernel_map(void *map, int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t stride, int64_t dilation,
+                         int kind, int dtype, void *stream);
+
 /* ------------------------------------------------------------------------
  * resample_to_map for callers that cannot allocate device memory.
  * Has no counterpart in the reference.  It is for hosts that must not call
@@ -167,6 +227,32 @@ int sph_mapped_max_pool(const void *x, const void *map, const void *iw, void *ou
 int sph_mapped_max_unpool(const void *g, const int64_t *idx, const void *map, const void *iw, void *grad_in,
                           int64_t B, int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
                           int64_t P, int dtype, int interp, void *stream);
+
+/* Deterministic argmax backward: the same operator with no float atomics and
+ * no zero-fill pass.  `plan` is a scatter plan over the FLATTENED map slots,
+ * i.e. built by sph_plan_build(map, iw, n_src = OH*OW*K, K = 1, P, interp,
+ * dst = (IH,IW)); every input pixel then sums, in map order, the gradients
+ * of the outputs whose winning slot (idx) has a tap on it.  Results do not
+ * depend on scheduling (run-to-run bit identical).  No counterpart in the
+ * reference, whose CUDA kernel scatters with atomicAdd
+ * (ext_modules/include/cuda/mapped_max_pool.cuh:57-95). */
+int sph_mapped_max_unpool_planned(const void *g, const int64_t *idx, const void *plan, void *grad_in, int64_t B,
+                                  int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
+                                  int dtype, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Mapped average pooling.  out[b,c,o] = (sum_k interp(x[b,c], map[o,k])) / K,
+ * slots added in order.  The backward sends g[b,c,o] / K back through every
+ * slot; `plan` is the flattened-slot plan described above (n_src = OH*OW*K,
+ * K = 1, dst = (IH,IW)); grad_in is fully written.  Replaces
+ * spherical::MappedAvgPoolforward / MappedAvgPoolbackward,
+ * ext_modules/include/layers/mapped_avg_pooling_layer.h:40-86 (weighted:
+ * weighted_mapped_avg_pooling_layer.h:48-106).
+ * ---------------------------------------------------------------------- */
+int sph_mapped_avg_pool(const void *x, const void *map, const void *iw, void *out, int64_t B, int64_t C, int64_t IH,
+                        int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp, void *stream);
+int sph_mapped_avg_unpool(const void *g, const void *plan, void *grad_in, int64_t B, int64_t C, int64_t IH, int64_t IW,
+                          int64_t OH, int64_t OW, int64_t K, int dtype, void *stream);
 
 /* ------------------------------------------------------------------------
  * Mapped convolution.  weight (Cout,Cin,K), bias (Cout), x (B,Cin,IH,IW),

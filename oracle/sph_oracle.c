@@ -44,7 +44,10 @@
  * label with the most votes, the smallest such label on ties (torch.argmax
  * returns the first maximum), 0 where nobody voted.  Labels outside
  * [0, num_candidates) cast no vote here (the reference would write out of
- * bounds). */
+ * bounds).  Channels are independent here; the reference steps its vote
+ * tensor by OH*OW per channel instead of OH*OW*num_candidates
+ * (common/resample.h:127-129), so with more than one channel its votes
+ * overlap and only the one-channel case is pinned against it. */
 void sph_o_voting_resample(const int64_t *x, const int64_t *map, int64_t *out, int64_t B, int64_t C, int64_t IH,
                            int64_t IW, int64_t OH, int64_t OW, int64_t num_candidates) {
   const int64_t n = IH * IW, m = OH * OW;

@@ -22,7 +22,7 @@ OUT = os.path.join(HERE, "_spherical_distortion_ext")
 OBJ = os.path.join(HERE, "build", "obj")
 INCLUDE = os.path.join(ROOT, "include")
 
-CU_SOURCES = ["resample.cu", "plan.cu", "pool.cu", "conv.cu", "conv_simt.cu", "conv_small.cu", "conv_tc.cu"]
+CU_SOURCES = ["resample.cu", "plan.cu", "pool.cu", "maps.cu", "conv.cu", "conv_simt.cu", "conv_small.cu", "conv_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
               "-Xcompiler", "-fPIC", "-I" + INCLUDE, "-I" + CSRC]
 # extra compiler flags for developer builds, e.g. SPHMAP_NVCC_FLAGS="-DSPH_TC_TIMING" (per-role cycle counters)

@@ -6,10 +6,19 @@
 namespace sph {
 
 // Visit every valid tap of map slot s (= position * K + k): f(key, id, weight).
+// With `quad` (UV maps: the destination is NT textures of H x W and position s / K writes into texture quad[s / K],
+// ext_modules/include/common/resample.h:161-187) the key is offset by that texture; a texture index outside
+// [0, NT) has no taps.
 template <typename T, int INTERP, bool WEIGHTED, typename F>
 __device__ __forceinline__ void for_each_tap(const T *__restrict__ map, const T *__restrict__ iw, int s, int K, int PP,
-                                             int H, int W, F f) {
+                                             int H, int W, const int64_t *__restrict__ quad, int NT, F f) {
   const int k = s % K;
+  int base = 0;
+  if (quad) {
+    const int64_t q = __ldg(quad + s / K);
+    if (q < 0 || q >= NT) return;
+    base = (int)q * H * W;
+  }
   Taps<T> t;
   for (int q = 0; q < PP; q++) {
     const size_t e = (size_t)s * PP + q;
@@ -17,23 +26,24 @@ __device__ __forceinline__ void for_each_tap(const T *__restrict__ map, const T 
     const T wq = WEIGHTED ? __ldg(iw + e) : T(1);
 #pragma unroll
     for (int i = 0; i < TapCount<INTERP>::value; i++)
-      if (t.off[i] >= 0) f(t.off[i] * K + k, (int)(e * 4 + i), WEIGHTED ? wq * t.w[i] : t.w[i]);
+      if (t.off[i] >= 0) f((base + t.off[i]) * K + k, (int)(e * 4 + i), WEIGHTED ? wq * t.w[i] : t.w[i]);
   }
 }
 
 template <typename T, int INTERP, bool WEIGHTED>
-__global__ void plan_count_kernel(const T *map, const T *iw, int n_slots, int K, int PP, int H, int W, int *cnt) {
+__global__ void plan_count_kernel(const T *map, const T *iw, int n_slots, int K, int PP, int H, int W, const int64_t *quad,
+                                  int NT, int *cnt) {
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= n_slots) return;
-  for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, [&](int key, int, T) { atomicAdd(cnt + key, 1); });
+  for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, quad, NT, [&](int key, int, T) { atomicAdd(cnt + key, 1); });
 }
 
 template <typename T, int INTERP, bool WEIGHTED>
-__global__ void plan_fill_kernel(const T *map, const T *iw, int n_slots, int K, int PP, int H, int W,
-                                 const int *offsets, int *cursor, int *ids, T *w) {
+__global__ void plan_fill_kernel(const T *map, const T *iw, int n_slots, int K, int PP, int H, int W, const int64_t *quad,
+                                 int NT, const int *offsets, int *cursor, int *ids, T *w) {
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= n_slots) return;
-  for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, [&](int key, int id, T wt) {
+  for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, quad, NT, [&](int key, int id, T wt) {
     const int pos = offsets[key] + atomicAdd(cursor + key, 1);
     ids[pos] = id;
     w[pos] = wt;
@@ -144,7 +154,8 @@ __global__ void plan_header_kernel(PlanHeader *dst, PlanHeader h) { *dst = h; }
 
 template <typename T>
 static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int64_t P, int interp, int64_t H,
-                 int64_t W, int dtype, void *plan, const PlanLayout &L, cudaStream_t st) {
+                 int64_t W, int dtype, void *plan, const PlanLayout &L, cudaStream_t st, const int64_t *quad = nullptr,
+                 int NT = 1) {
   char *base = (char *)plan;
   int *offsets = (int *)(base + L.off_offsets), *src = (int *)(base + L.off_src);
   int *cursor = (int *)(base + L.off_cursor), *sums = (int *)(base + L.off_sums);
@@ -154,9 +165,9 @@ static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int6
   const int gb = cdiv(n_slots, 256);
   SPH_DISPATCH_INTERP(interp, {
     if (P > 0)
-      plan_count_kernel<T, INTERP, true><<<gb, 256, 0, st>>>((const T *)map, (const T *)iw, n_slots, (int)K, PP, (int)H, (int)W, cursor);
+      plan_count_kernel<T, INTERP, true><<<gb, 256, 0, st>>>((const T *)map, (const T *)iw, n_slots, (int)K, PP, (int)H, (int)W, quad, NT, cursor);
     else
-      plan_count_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, cursor);
+      plan_count_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, quad, NT, cursor);
   });
   scan_sums_kernel<<<L.n_scan_blocks, kScanThreads, 0, st>>>(cursor, nk, sums);
   scan_top_kernel<<<1, kScanThreads, 0, st>>>(sums, L.n_scan_blocks);
@@ -164,9 +175,9 @@ static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int6
   if (cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)nk, st) != cudaSuccess) return SPH_ERR_CUDA;
   SPH_DISPATCH_INTERP(interp, {
     if (P > 0)
-      plan_fill_kernel<T, INTERP, true><<<gb, 256, 0, st>>>((const T *)map, (const T *)iw, n_slots, (int)K, PP, (int)H, (int)W, offsets, cursor, src, w);
+      plan_fill_kernel<T, INTERP, true><<<gb, 256, 0, st>>>((const T *)map, (const T *)iw, n_slots, (int)K, PP, (int)H, (int)W, quad, NT, offsets, cursor, src, w);
     else
-      plan_fill_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, offsets, cursor, src, w);
+      plan_fill_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, quad, NT, offsets, cursor, src, w);
   });
   PlanHeader h;
   h.magic = kPlanMagic;
@@ -205,6 +216,21 @@ extern "C" int sph_plan_build(const void *map, const void *iw, int64_t n_src, in
   cudaStream_t st = (cudaStream_t)stream;
   return dtype == SPH_F32 ? build<float>(map, iw, n_src, K, P, interp, dstH, dstW, dtype, plan, L, st)
                           : build<double>(map, iw, n_src, K, P, interp, dstH, dstW, dtype, plan, L, st);
+}
+
+// Plan of the UV-map scatter (resample_to_uv_maps): the destination is NT textures of TH x TW, laid out as one
+// (NT*TH) x TW image; interpolation and its zero padding act inside the texture quad_idx names.
+extern "C" int sph_plan_build_uv(const void *tex_uv, const int64_t *quad_idx, int64_t n_src, int64_t NT, int64_t TH,
+                                 int64_t TW, int interp, int dtype, void *plan, size_t plan_bytes, void *stream) {
+  if (!tex_uv || !quad_idx || !plan || NT <= 0 || interp < 0 || interp > 2) return SPH_ERR_INVALID_ARGUMENT;
+  if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
+  PlanLayout L;
+  if (!plan_layout(n_src, 1, 0, interp, NT * TH, TW, dtype, L)) return SPH_ERR_TOO_LARGE;
+  if (plan_bytes < L.total) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  if (((uintptr_t)plan & 255) != 0) return SPH_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == SPH_F32 ? build<float>(tex_uv, nullptr, n_src, 1, 0, interp, TH, TW, dtype, plan, L, st, quad_idx, (int)NT)
+                          : build<double>(tex_uv, nullptr, n_src, 1, 0, interp, TH, TW, dtype, plan, L, st, quad_idx, (int)NT);
 }
 
 // ---- resample_to_map without any allocation ---------------------------------------------------

@@ -1,4 +1,4 @@
-// Mapped max pooling: forward (value + argmax index) and argmax backward.
+// Mapped max pooling (forward: value + argmax index; argmax backward) and mapped average pooling (forward).
 #include <float.h>
 
 #include "common.cuh"
@@ -12,7 +12,10 @@ namespace sph {
 // per output position walks kPlanesPerThread planes; the whole batch is one
 // launch (the reference launches once per image:
 // src/cuda/mapped_max_pooling_layer.cu:11-36).
-template <typename T, int INTERP, bool WEIGHTED>
+//
+// AVG = true turns the same walk into mapped average pooling: the K slot values are added in slot order and the sum
+// is divided by K (ext_modules/include/common/mapped_avg_pool.h:12-39, 71-107); idx is not written.
+template <typename T, int INTERP, bool WEIGHTED, bool AVG>
 __global__ void __launch_bounds__(256)
 max_pool_kernel(const T *__restrict__ x, const T *__restrict__ map, const T *__restrict__ iw, T *__restrict__ out,
                 int64_t *__restrict__ idx, int n, int planes, int H, int W, int K, int P) {
@@ -26,7 +29,7 @@ max_pool_kernel(const T *__restrict__ x, const T *__restrict__ map, const T *__r
   T best[kPlanesPerThread];
   int bk[kPlanesPerThread];
 #pragma unroll
-  for (int j = 0; j < kPlanesPerThread; j++) { best[j] = (T)(-FLT_MAX); bk[j] = -1; }
+  for (int j = 0; j < kPlanesPerThread; j++) { best[j] = AVG ? T(0) : (T)(-FLT_MAX); bk[j] = -1; }
   for (int k = 0; k < K; k++) {
     const size_t e = ((size_t)o * K + k) * PP;
     if (!WEIGHTED) {
@@ -36,22 +39,28 @@ max_pool_kernel(const T *__restrict__ x, const T *__restrict__ map, const T *__r
       for (int j = 0; j < kPlanesPerThread; j++)
         if (j < np) {
           const T v = gather<T, INTERP>(xp + j * hw, t);
-          if (v > best[j]) { best[j] = v; bk[j] = k; }
+          if (AVG) best[j] = RN<T>::add(best[j], v);
+          else if (v > best[j]) { best[j] = v; bk[j] = k; }
         }
     } else {
 #pragma unroll
       for (int j = 0; j < kPlanesPerThread; j++)
         if (j < np) {
           const T v = gather_slot<T, INTERP, true>(xp + j * hw, map + 2 * e, iw + e, P, H, W);
-          if (v > best[j]) { best[j] = v; bk[j] = k; }
+          if (AVG) best[j] = RN<T>::add(best[j], v);
+          else if (v > best[j]) { best[j] = v; bk[j] = k; }
         }
     }
   }
 #pragma unroll
   for (int j = 0; j < kPlanesPerThread; j++)
     if (j < np) {
-      out[(size_t)(p0 + j) * n + o] = best[j];
-      idx[(size_t)(p0 + j) * n + o] = bk[j] < 0 ? (int64_t)-1 : ((int64_t)o * K + bk[j]) * PP * 2;
+      if (AVG) {
+        out[(size_t)(p0 + j) * n + o] = best[j] / (T)K;
+      } else {
+        out[(size_t)(p0 + j) * n + o] = best[j];
+        idx[(size_t)(p0 + j) * n + o] = bk[j] < 0 ? (int64_t)-1 : ((int64_t)o * K + bk[j]) * PP * 2;
+      }
     }
 }
 
@@ -132,9 +141,100 @@ max_unpool_kernel(const T *__restrict__ g, const int64_t *__restrict__ idx, cons
   }
 }
 
+// Deterministic argmax backward.  `plan_blob` is a scatter plan built over the FLATTENED map slots
+// (sph_plan_build with n_src = OH*OW*K positions and K = 1), so the segment of input pixel q lists every
+// (output position o, slot k) whose taps touch q, as s = o*K + k, in map order, with the tap weight.  The pixel sums,
+// in that fixed order, the entries whose slot is the one the forward pass selected: idx[p,o] == s * 2 * PP.  No
+// zero-fill, no atomics, results independent of scheduling (the reference scatters with atomicAdd:
+// ext_modules/include/cuda/mapped_max_pool.cuh:57-95).
+// STAGED: the winning slot of every output of the CTA's PL planes is first decoded into shared memory as one byte
+// (255 = none), so the per-entry test reads a byte of shared memory instead of 8 random bytes of idx.
+template <typename T, int PL, bool STAGED>
+__global__ void __launch_bounds__(512)
+max_unpool_plan_kernel(const T *__restrict__ g, const int64_t *__restrict__ idx, const void *__restrict__ plan_blob,
+                       T *__restrict__ gin, int n, int n_dst, int planes, int K, int PP, int chunk) {
+  extern __shared__ uint8_t ksm[];  // [PL][n]
+  const int p0 = blockIdx.y * PL;
+  const int np = min(PL, planes - p0);
+  if (STAGED) {
+    for (int i = threadIdx.x; i < PL * n; i += blockDim.x) {
+      const int j = i / n, o = i - j * n;
+      int k = -1;
+      if (j < np) {
+        const int64_t s = idx[(size_t)(p0 + j) * n + o];
+        if (s >= 0) {
+          const int64_t slot = s / (2 * PP), kk = slot - (int64_t)o * K;
+          if (kk >= 0 && kk < K && slot * 2 * PP == s) k = (int)kk;
+        }
+      }
+      ksm[i] = k < 0 ? (uint8_t)255 : (uint8_t)k;
+    }
+    __syncthreads();
+  }
+  bool ok;
+  const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok);
+  const int q_end = min((int)((blockIdx.x + 1) * (int64_t)chunk), n_dst);
+  for (int q = blockIdx.x * chunk + threadIdx.x; q < q_end; q += blockDim.x) {
+    T acc[PL];
+#pragma unroll
+    for (int j = 0; j < PL; j++) acc[j] = T(0);
+    const int e0 = ok ? __ldg(plan.offsets + q) : 0, e1 = ok ? __ldg(plan.offsets + q + 1) : 0;
+    for (int e = e0; e < e1; e++) {
+      const int s = __ldg(plan.src + e);
+      const T w = __ldg(plan.w + e);
+      const int o = s / K, k = s - o * K;
+#pragma unroll
+      for (int j = 0; j < PL; j++)
+        if (j < np) {
+          const bool hit = STAGED ? ksm[j * n + o] == (uint8_t)k
+                                  : __ldg(idx + (size_t)(p0 + j) * n + o) == (int64_t)s * 2 * PP;
+          if (hit) acc[j] += w * __ldg(g + (size_t)(p0 + j) * n + o);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < PL; j++)
+      if (j < np) gin[(size_t)(p0 + j) * n_dst + q] = acc[j];
+  }
+}
+
+template <typename T>
+static int unpool_planned(const void *g, const int64_t *idx, const void *plan, void *gin, int64_t planes, int64_t n_dst,
+                          int64_t n, int64_t K, int64_t P, cudaStream_t st) {
+  const int PP = (int)(P > 0 ? P : 1);
+  constexpr int PL = 4;
+  const size_t stage = (size_t)PL * n;
+  if (K <= 254 && stage <= 200 * 1024) {
+    // CTAs = plane groups x pixel chunks, at least two waves of the SMs; one CTA per SM (shared memory)
+    const int groups = cdiv(planes, PL);
+    int chunks = cdiv((int64_t)2 * 148, groups);
+    if (chunks > cdiv(n_dst, 512)) chunks = cdiv(n_dst, 512);
+    const int chunk = cdiv(cdiv(n_dst, chunks), 512) * 512;
+    cudaFuncSetAttribute(max_unpool_plan_kernel<T, PL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage);
+    max_unpool_plan_kernel<T, PL, true><<<dim3(cdiv(n_dst, chunk), groups), 512, stage, st>>>(
+        (const T *)g, idx, plan, (T *)gin, (int)n, (int)n_dst, (int)planes, (int)K, PP, chunk);
+  } else {
+    const int chunk = 2048;
+    max_unpool_plan_kernel<T, PL, false><<<dim3(cdiv(n_dst, chunk), cdiv(planes, PL)), 512, 0, st>>>(
+        (const T *)g, idx, plan, (T *)gin, (int)n, (int)n_dst, (int)planes, (int)K, PP, chunk);
+  }
+  return launch_status();
+}
+
 template <typename T>
 static int pool(const void *x, const void *map, const void *iw, void *out, int64_t *idx, int64_t planes, int64_t H,
-                int64_t W, int64_t n, int64_t K, int64_t P, int interp, cudaStream_t st) {
+                int64_t W, int64_t n, int64_t K, int64_t P, int interp, cudaStream_t st, bool avg = false) {
+  if (avg) {
+    dim3 grid(cdiv(n, 256), cdiv(planes, kPlanesPerThread));
+    SPH_DISPATCH_INTERP(interp, {
+      if (P > 0)
+        max_pool_kernel<T, INTERP, true, true><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, (const T *)iw, (T *)out,
+                                                                     nullptr, (int)n, (int)planes, (int)H, (int)W, (int)K, (int)P);
+      else
+        max_pool_kernel<T, INTERP, false, true><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, nullptr, (T *)out, nullptr,
+                                                                      (int)n, (int)planes, (int)H, (int)W, (int)K, 0);
+    });
+    return launch_status();
+  }
   if (interp == SPH_NEAREST && P == 0 && K <= kPoolMaxK) {
     constexpr int PPT = 4;
     dim3 grid(cdiv(n, 256), cdiv(planes, PPT));
@@ -149,10 +249,10 @@ static int pool(const void *x, const void *map, const void *iw, void *out, int64
   dim3 grid(cdiv(n, 256), cdiv(planes, kPlanesPerThread));
   SPH_DISPATCH_INTERP(interp, {
     if (P > 0)
-      max_pool_kernel<T, INTERP, true><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, (const T *)iw, (T *)out, idx,
+      max_pool_kernel<T, INTERP, true, false><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, (const T *)iw, (T *)out, idx,
                                                              (int)n, (int)planes, (int)H, (int)W, (int)K, (int)P);
     else
-      max_pool_kernel<T, INTERP, false><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, nullptr, (T *)out, idx, (int)n,
+      max_pool_kernel<T, INTERP, false, false><<<grid, 256, 0, st>>>((const T *)x, (const T *)map, nullptr, (T *)out, idx, (int)n,
                                                               (int)planes, (int)H, (int)W, (int)K, 0);
   });
   return launch_status();
@@ -214,4 +314,30 @@ extern "C" int sph_mapped_max_unpool(const void *g, const int64_t *idx, const vo
                ? SPH_OK : SPH_ERR_CUDA;
   return dtype == SPH_F32 ? unpool<float>(g, idx, map, iw, grad_in, B * C, IH, IW, OH * OW, K, P, interp, st)
                           : unpool<double>(g, idx, map, iw, grad_in, B * C, IH, IW, OH * OW, K, P, interp, st);
+}
+
+extern "C" int sph_mapped_max_unpool_planned(const void *g, const int64_t *idx, const void *plan, void *grad_in, int64_t B,
+                                             int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
+                                             int dtype, void *stream) {
+  const int rc = check(g, plan, grad_in, idx, nullptr, B, C, IH, IW, OH, OW, K, 0, dtype, 0);
+  if (rc != SPH_OK) return rc;
+  if (P < 0 || OH * OW * K >= ((int64_t)1 << 31) / (2 * (P > 0 ? P : 1))) return P < 0 ? SPH_ERR_INVALID_ARGUMENT : SPH_ERR_TOO_LARGE;
+  if (B * C == 0) return SPH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (OH * OW == 0)
+    return cudaMemsetAsync(grad_in, 0, (dtype == SPH_F64 ? 8 : 4) * (size_t)(B * C * IH * IW), st) == cudaSuccess
+               ? SPH_OK : SPH_ERR_CUDA;
+  return dtype == SPH_F32 ? unpool_planned<float>(g, idx, plan, grad_in, B * C, IH * IW, OH * OW, K, P, st)
+                          : unpool_planned<double>(g, idx, plan, grad_in, B * C, IH * IW, OH * OW, K, P, st);
+}
+
+extern "C" int sph_mapped_avg_pool(const void *x, const void *map, const void *iw, void *out, int64_t B, int64_t C, int64_t IH,
+                                   int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                   void *stream) {
+  const int rc = check(x, map, out, out, iw, B, C, IH, IW, OH, OW, K, P, dtype, interp);
+  if (rc != SPH_OK) return rc;
+  if (B * C == 0 || OH * OW == 0) return SPH_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  return dtype == SPH_F32 ? pool<float>(x, map, iw, out, nullptr, B * C, IH, IW, OH * OW, K, P, interp, st, true)
+                          : pool<double>(x, map, iw, out, nullptr, B * C, IH, IW, OH * OW, K, P, interp, st, true);
 }

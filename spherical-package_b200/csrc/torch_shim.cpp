@@ -24,6 +24,7 @@ enum class InterpolationType { NEAREST = 0, BILINEAR = 1, BISPHERICAL = 2 };   /
 enum class DistortionType { SIMPLE_RADIAL = 0, BROWN = 1, FISHEYE = 2 };       // include/enums.h:6-10
 
 int g_precision = -1;
+bool g_deterministic_unpool = true;  // argmax backward through a plan (fixed summation order) instead of float atomics
 
 int precision() {
   if (g_precision < 0) {
@@ -115,9 +116,12 @@ std::list<PlanKey> g_plans;
 std::mutex g_plan_mu;
 constexpr size_t kMaxPlans = 64;
 
+// uv_textures > 0: `iw` is the int64 texture-index tensor of a UV map and the plan is built by sph_plan_build_uv for
+// uv_textures textures of (dstH / uv_textures) x dstW texels.
 torch::Tensor get_plan(const torch::Tensor &map, const torch::Tensor *iw, int64_t n_src, int64_t K, int64_t P, int interp,
-                       int64_t dstH, int64_t dstW) {
+                       int64_t dstH, int64_t dstW, int64_t uv_textures = 0) {
   const int dtype = dtype_of(map), device = map.get_device();
+  if (uv_textures > 0) K = -uv_textures;  // keeps UV plans apart from ordinary ones in the cache
   std::lock_guard<std::mutex> lock(g_plan_mu);
   for (auto it = g_plans.begin(); it != g_plans.end();) {
     if (it->map_s.expired() || (it->iw_p && it->iw_s.expired())) {
@@ -137,12 +141,17 @@ torch::Tensor get_plan(const torch::Tensor &map, const torch::Tensor *iw, int64_
     }
     ++it;
   }
-  const size_t bytes = sph_plan_bytes(n_src, K, P, interp, dstH, dstW, dtype);
+  const size_t bytes = sph_plan_bytes(n_src, uv_textures > 0 ? 1 : K, P, interp, dstH, dstW, dtype);
   TORCH_CHECK(bytes > 0, "sample map too large for a scatter plan");
   torch::Tensor blob = torch::empty({(int64_t)bytes}, map.options().dtype(torch::kUInt8));
-  ok(sph_plan_build(map.data_ptr(), iw ? iw->data_ptr() : nullptr, n_src, K, P, interp, dstH, dstW, dtype, blob.data_ptr(),
-                    bytes, at::cuda::getCurrentCUDAStream().stream()),
-     "sph_plan_build");
+  if (uv_textures > 0)
+    ok(sph_plan_build_uv(map.data_ptr(), iw->data_ptr<int64_t>(), n_src, uv_textures, dstH / uv_textures, dstW, interp, dtype,
+                         blob.data_ptr(), bytes, at::cuda::getCurrentCUDAStream().stream()),
+       "sph_plan_build_uv");
+  else
+    ok(sph_plan_build(map.data_ptr(), iw ? iw->data_ptr() : nullptr, n_src, K, P, interp, dstH, dstW, dtype, blob.data_ptr(),
+                      bytes, at::cuda::getCurrentCUDAStream().stream()),
+       "sph_plan_build");
   PlanKey k{c10::weak_intrusive_ptr<c10::StorageImpl>(map.storage().getWeakStorageImpl()),
             iw ? c10::weak_intrusive_ptr<c10::StorageImpl>(iw->storage().getWeakStorageImpl())
                : c10::weak_intrusive_ptr<c10::StorageImpl>(map.storage().getWeakStorageImpl()),
@@ -216,6 +225,129 @@ torch::Tensor weighted_resample_from_map(torch::Tensor x, torch::Tensor map, tor
   return resample_from_map_impl(x, map, &iw, it);
 }
 
+// scatter(x) / (scatter(1) + 1e-12) in one pass (the normalisation of layers/functional/sphere_ops.py:74-80)
+torch::Tensor resample_to_map_normalized(torch::Tensor x, torch::Tensor map, c10::optional<torch::Tensor> iw, int64_t oh,
+                                         int64_t ow, InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4, "input must have 4 dimensions");
+  check(x, "input", x);
+  check_float(map, "sample_map", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw ? &*iw : nullptr, false, 1);
+  TORCH_CHECK(x.size(2) == m.H && x.size(3) == m.W, "input spatial size must match the sample map");
+  TORCH_CHECK(oh > 0 && ow > 0, "output size must be positive");
+  c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor plan = get_plan(map, iw ? &*iw : nullptr, m.H * m.W, 1, m.P, (int)it, oh, ow);
+  torch::Tensor out = torch::empty({x.size(0), x.size(1), oh, ow}, x.options());
+  ok(sph_resample_to_map_normalized(x.data_ptr(), plan.data_ptr(), out.data_ptr(), x.size(0), x.size(1), m.H, m.W, oh, ow,
+                                    dtype_of(x), stream()),
+     "sph_resample_to_map_normalized");
+  return out;
+}
+
+// ---- UV-map resampling (include/layers/uv_resample_layer.h:48-100) ----------
+void check_uv(const torch::Tensor &quad, const torch::Tensor &uv, const torch::Tensor &like) {
+  check(quad, "quad_idx", like);
+  check_float(uv, "tex_uv", like);
+  TORCH_CHECK(quad.scalar_type() == torch::kLong && quad.dim() == 2, "quad_idx must be an int64 (H, W) tensor");
+  TORCH_CHECK(uv.dim() == 3 && uv.size(0) == quad.size(0) && uv.size(1) == quad.size(1) && uv.size(2) == 2,
+              "tex_uv must be (H, W, 2) like quad_idx");
+}
+
+torch::Tensor resample_from_uv_maps(torch::Tensor tex, torch::Tensor quad, torch::Tensor uv, InterpolationType it) {
+  TORCH_CHECK(tex.dim() == 5, "input must be (B, C, textures, TH, TW)");
+  check(tex, "input", tex);
+  check_uv(quad, uv, tex);
+  c10::cuda::CUDAGuard guard(tex.device());
+  torch::Tensor out = torch::empty({tex.size(0), tex.size(1), quad.size(0), quad.size(1)}, tex.options());
+  ok(sph_resample_from_uv_maps(tex.data_ptr(), quad.data_ptr<int64_t>(), uv.data_ptr(), out.data_ptr(), tex.size(0), tex.size(1),
+                               tex.size(2), tex.size(3), tex.size(4), quad.size(0), quad.size(1), dtype_of(tex), (int)it,
+                               stream()),
+     "sph_resample_from_uv_maps");
+  return out;
+}
+
+torch::Tensor resample_to_uv_maps(torch::Tensor x, torch::Tensor quad, torch::Tensor uv, int64_t nt, int64_t th, int64_t tw,
+                                  InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4, "input must have 4 dimensions");
+  x = x.contiguous();
+  check(x, "input", x);
+  check_uv(quad, uv, x);
+  TORCH_CHECK(x.size(2) == quad.size(0) && x.size(3) == quad.size(1), "input spatial size must match quad_idx");
+  TORCH_CHECK(nt > 0 && th > 0 && tw > 0, "texture sizes must be positive");
+  c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor plan = get_plan(uv, &quad, quad.size(0) * quad.size(1), 1, 0, (int)it, nt * th, tw, nt);
+  torch::Tensor out = torch::empty({x.size(0), x.size(1), nt, th, tw}, x.options());
+  ok(sph_resample_to_map(x.data_ptr(), plan.data_ptr(), out.data_ptr(), x.size(0), x.size(1), x.size(2), x.size(3), nt * th, tw,
+                         dtype_of(x), stream()),
+     "sph_resample_to_map (uv)");
+  return out;
+}
+
+// ---- voting resample (include/layers/voting_resample_layer.h:32-58) ---------
+torch::Tensor voting_resample_to_map(torch::Tensor x, torch::Tensor map, int64_t oh, int64_t ow, int64_t num_candidates) {
+  TORCH_CHECK(x.dim() == 4 && x.scalar_type() == torch::kLong, "input must be an int64 (B, C, H, W) tensor");
+  TORCH_CHECK(map.dim() == 3 && map.size(2) == 2 && map.scalar_type() == torch::kLong, "sample_map must be an int64 (H, W, 2) tensor");
+  check(x, "input", x);
+  check(map, "sample_map", x);
+  TORCH_CHECK(x.size(2) == map.size(0) && x.size(3) == map.size(1), "input spatial size must match the sample map");
+  TORCH_CHECK(oh > 0 && ow > 0 && num_candidates > 0, "output size and number of candidates must be positive");
+  c10::cuda::CUDAGuard guard(x.device());
+  // integer coordinates are exact in float64; the nearest-neighbour plan then inverts the map
+  torch::Tensor mapf = map.to(torch::kDouble);
+  const int64_t n_src = map.size(0) * map.size(1);
+  const size_t bytes = sph_plan_bytes(n_src, 1, 0, SPH_NEAREST, oh, ow, SPH_F64);
+  TORCH_CHECK(bytes > 0, "sample map too large for a scatter plan");
+  torch::Tensor plan = torch::empty({(int64_t)bytes}, x.options().dtype(torch::kUInt8));
+  ok(sph_plan_build(mapf.data_ptr(), nullptr, n_src, 1, 0, SPH_NEAREST, oh, ow, SPH_F64, plan.data_ptr(), bytes, stream()),
+     "sph_plan_build");
+  torch::Tensor out = torch::empty({x.size(0), x.size(1), oh, ow}, x.options());
+  ok(sph_voting_resample_to_map(x.data_ptr<int64_t>(), plan.data_ptr(), SPH_F64, out.data_ptr<int64_t>(), x.size(0), x.size(1),
+                                x.size(2), x.size(3), oh, ow, num_candidates, stream()),
+     "sph_voting_resample_to_map");
+  return out;
+}
+
+// ---- equirectangular kernel maps built on the device (layers/util/mapping_functions.py:44-163) ----
+torch::Tensor build_kernel_map(int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t stride, int64_t dilation,
+                               const std::string &kind, torch::Tensor like) {
+  TORCH_CHECK(like.is_cuda(), "`like` must be a CUDA tensor (it gives the device and dtype of the map)");
+  const int k = kind == "grid" ? SPH_MAP_GRID : kind == "inverse_gnomonic" ? SPH_MAP_INVERSE_GNOMONIC
+              : kind == "inverse_equirectangular" ? SPH_MAP_INVERSE_EQUIRECT : -1;
+  TORCH_CHECK(k >= 0, "kind must be 'grid', 'inverse_gnomonic' or 'inverse_equirectangular', got ", kind);
+  TORCH_CHECK(H > 0 && W > 0 && kh > 0 && kw > 0 && stride > 0 && dilation > 0, "sizes must be positive");
+  c10::cuda::CUDAGuard guard(like.device());
+  torch::Tensor map = torch::empty({(H + stride - 1) / stride, (W + stride - 1) / stride, kh * kw, 2}, like.options());
+  ok(sph_build_kernel_map(map.data_ptr(), H, W, kh, kw, stride, dilation, k, dtype_of(like), stream()), "sph_build_kernel_map");
+  return map;
+}
+
+// ---- standard convolution (include/layers/convolution_layer.h:52-131, transposed_convolution_layer.h) ----
+// Not part of the mapped-operator path: the reference's own im2col + GEMM convolution computes what ATen's
+// convolution computes, so these delegate to ATen (cuDNN) with the reference's argument order.
+torch::Tensor conv_forward(torch::Tensor x, torch::Tensor w, torch::Tensor b, int64_t kh, int64_t kw, int64_t sh, int64_t sw,
+                           int64_t ph, int64_t pw, int64_t dh, int64_t dw) {
+  TORCH_CHECK(w.dim() == 4 && w.size(2) == kh && w.size(3) == kw, "weight must be (Cout, Cin, kernel_h, kernel_w)");
+  return at::conv2d(x, w, b, {sh, sw}, {ph, pw}, {dh, dw}, 1);
+}
+std::vector<torch::Tensor> conv_backward(torch::Tensor go, torch::Tensor x, torch::Tensor w, torch::Tensor b, int64_t kh,
+                                         int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw) {
+  auto r = at::convolution_backward(go.contiguous(), x, w, c10::nullopt, {sh, sw}, {ph, pw}, {dh, dw}, false, {0, 0}, 1,
+                                    {true, true, false});
+  return {std::get<0>(r), std::get<1>(r), go.sum({0, 2, 3})};
+}
+torch::Tensor transposed_conv_forward(torch::Tensor x, torch::Tensor w, torch::Tensor b, int64_t kh, int64_t kw, int64_t sh,
+                                      int64_t sw, int64_t ph, int64_t pw, int64_t dh, int64_t dw) {
+  TORCH_CHECK(w.dim() == 4 && w.size(2) == kh && w.size(3) == kw, "weight must be (Cin, Cout, kernel_h, kernel_w)");
+  return at::conv_transpose2d(x, w, b, {sh, sw}, {ph, pw}, {0, 0}, 1, {dh, dw});
+}
+std::vector<torch::Tensor> transposed_conv_backward(torch::Tensor go, torch::Tensor x, torch::Tensor w, torch::Tensor b,
+                                                    int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph, int64_t pw,
+                                                    int64_t dh, int64_t dw) {
+  auto r = at::convolution_backward(go.contiguous(), x, w, c10::nullopt, {sh, sw}, {ph, pw}, {dh, dw}, true, {0, 0}, 1,
+                                    {true, true, false});
+  return {std::get<0>(r), std::get<1>(r), go.sum({0, 2, 3})};
+}
+
 // ---- max pooling (include/layers/mapped_max_pooling_layer.h:42-97) ---------
 std::vector<torch::Tensor> max_pool_impl(torch::Tensor x, torch::Tensor map, const torch::Tensor *iw, int64_t K,
                                          InterpolationType it) {
@@ -248,11 +380,67 @@ torch::Tensor max_unpool_impl(torch::Tensor g, torch::Tensor idx, torch::Tensor 
   TORCH_CHECK(ih > 0 && iwidth > 0, "input size must be positive");
   c10::cuda::CUDAGuard guard(g.device());
   torch::Tensor gin = torch::empty({g.size(0), g.size(1), ih, iwidth}, g.options());
+  if (g_deterministic_unpool) {
+    // plan over the flattened map slots: every input pixel sums the winners that touch it in a fixed order
+    torch::Tensor plan = get_plan(map, iw, m.H * m.W * m.K, 1, m.P, (int)it, ih, iwidth);
+    ok(sph_mapped_max_unpool_planned(g.data_ptr(), idx.data_ptr<int64_t>(), plan.data_ptr(), gin.data_ptr(), g.size(0),
+                                     g.size(1), ih, iwidth, m.H, m.W, m.K, m.P, dtype_of(g), stream()),
+       "sph_mapped_max_unpool_planned");
+    return gin;
+  }
   ok(sph_mapped_max_unpool(g.data_ptr(), idx.data_ptr<int64_t>(), map.data_ptr(), iw ? iw->data_ptr() : nullptr,
                            gin.data_ptr(), g.size(0), g.size(1), ih, iwidth, m.H, m.W, m.K, m.P, dtype_of(g), (int)it,
                            stream()),
      "sph_mapped_max_unpool");
   return gin;
+}
+
+// ---- average pooling (include/layers/mapped_avg_pooling_layer.h:40-86, weighted twin) ----
+torch::Tensor avg_pool_impl(torch::Tensor x, torch::Tensor map, const torch::Tensor *iw, int64_t K, InterpolationType it) {
+  TORCH_CHECK(x.dim() == 4, "input must have 4 dimensions");
+  check(x, "input", x);
+  check_float(map, "sample_map", x);
+  if (iw) check_float(*iw, "interp_weights", x);
+  const MapInfo m = map_info(map, iw, true, K);
+  c10::cuda::CUDAGuard guard(x.device());
+  torch::Tensor out = torch::empty({x.size(0), x.size(1), m.H, m.W}, x.options());
+  ok(sph_mapped_avg_pool(x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr, out.data_ptr(), x.size(0), x.size(1),
+                         x.size(2), x.size(3), m.H, m.W, m.K, m.P, dtype_of(x), (int)it, stream()),
+     "sph_mapped_avg_pool");
+  return out;
+}
+
+torch::Tensor avg_unpool_impl(torch::Tensor g, torch::Tensor map, const torch::Tensor *iw, int64_t ih, int64_t iwidth, int64_t K,
+                              InterpolationType it) {
+  TORCH_CHECK(g.dim() == 4, "grad_output must have 4 dimensions");
+  g = g.contiguous();
+  check(g, "grad_output", g);
+  check_float(map, "sample_map", g);
+  if (iw) check_float(*iw, "interp_weights", g);
+  const MapInfo m = map_info(map, iw, true, K);
+  TORCH_CHECK(g.size(2) == m.H && g.size(3) == m.W, "grad_output spatial size must match the sample map");
+  TORCH_CHECK(ih > 0 && iwidth > 0, "input size must be positive");
+  c10::cuda::CUDAGuard guard(g.device());
+  torch::Tensor plan = get_plan(map, iw, m.H * m.W * m.K, 1, m.P, (int)it, ih, iwidth);
+  torch::Tensor gin = torch::empty({g.size(0), g.size(1), ih, iwidth}, g.options());
+  ok(sph_mapped_avg_unpool(g.data_ptr(), plan.data_ptr(), gin.data_ptr(), g.size(0), g.size(1), ih, iwidth, m.H, m.W, m.K,
+                           dtype_of(g), stream()),
+     "sph_mapped_avg_unpool");
+  return gin;
+}
+
+torch::Tensor mapped_avg_pool(torch::Tensor x, torch::Tensor map, int64_t K, InterpolationType it) {
+  return avg_pool_impl(x, map, nullptr, K, it);
+}
+torch::Tensor mapped_avg_unpool(torch::Tensor g, torch::Tensor map, int64_t ih, int64_t iw, int64_t K, InterpolationType it) {
+  return avg_unpool_impl(g, map, nullptr, ih, iw, K, it);
+}
+torch::Tensor weighted_mapped_avg_pool(torch::Tensor x, torch::Tensor map, torch::Tensor w, int64_t K, InterpolationType it) {
+  return avg_pool_impl(x, map, &w, K, it);
+}
+torch::Tensor weighted_mapped_avg_unpool(torch::Tensor g, torch::Tensor map, torch::Tensor w, int64_t ih, int64_t iw, int64_t K,
+                                         InterpolationType it) {
+  return avg_unpool_impl(g, map, &w, ih, iw, K, it);
 }
 
 std::vector<torch::Tensor> mapped_max_pool(torch::Tensor x, torch::Tensor map, int64_t K, InterpolationType it) {
@@ -520,6 +708,25 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mapped_max_unpool", &mapped_max_unpool);
   m.def("weighted_mapped_max_pool", &weighted_mapped_max_pool);
   m.def("weighted_mapped_max_unpool", &weighted_mapped_max_unpool);
+  m.def("mapped_avg_pool", &mapped_avg_pool);
+  m.def("mapped_avg_unpool", &mapped_avg_unpool);
+  m.def("weighted_mapped_avg_pool", &weighted_mapped_avg_pool);
+  m.def("weighted_mapped_avg_unpool", &weighted_mapped_avg_unpool);
+  m.def("resample_from_uv_maps", &resample_from_uv_maps);
+  m.def("resample_to_uv_maps", &resample_to_uv_maps);
+  m.def("voting_resample_to_map", &voting_resample_to_map);
+  m.def("resample_to_map_normalized", &resample_to_map_normalized, py::arg("input"), py::arg("sample_map"),
+        py::arg("interp_weights"), py::arg("output_height"), py::arg("output_width"), py::arg("interpolation"),
+        "scatter(input) / (scatter(1) + 1e-12) through the sample map, in one pass");
+  m.def("build_kernel_map", &build_kernel_map, py::arg("H"), py::arg("W"), py::arg("kernel_h"), py::arg("kernel_w"),
+        py::arg("stride"), py::arg("dilation"), py::arg("kind"), py::arg("like"),
+        "equirectangular kernel sample map (ceil(H/stride), ceil(W/stride), kh*kw, 2) built on the device");
+  m.def("conv_forward", &conv_forward);
+  m.def("conv_backward", &conv_backward);
+  m.def("transposed_conv_forward", &transposed_conv_forward);
+  m.def("transposed_conv_backward", &transposed_conv_backward);
+  m.def("set_deterministic_unpool", [](bool on) { g_deterministic_unpool = on; },
+        "true (default): argmax backward sums through a scatter plan in a fixed order; false: float atomics as the reference");
   m.def("mapped_conv_forward", &mapped_conv_forward);
   m.def("mapped_conv_backward", &mapped_conv_backward);
   m.def("mapped_conv_relu_forward", &mapped_conv_relu_forward);

@@ -2,8 +2,9 @@
 parameter names/shapes and forward signatures of the reference
 (layers/nn/mapped_convolution_layer.py:11-59,
 layers/nn/mapped_transposed_convolution_layer.py:10-56,
-layers/nn/mapped_max_pooling_layer.py:8-32, layers/nn/resample_layer.py:13-52),
-so that existing state_dicts load unchanged.
+layers/nn/mapped_max_pooling_layer.py:8-32, layers/nn/mapped_avg_pooling_layer.py:7-46,
+layers/nn/resample_layer.py:13-87, layers/nn/convolution_layer.py:10-52,
+layers/nn/transposed_convolution_layer.py:10-56), so that existing state_dicts load unchanged.
 """
 import math
 
@@ -94,3 +95,71 @@ class Unresample(nn.Module):
 
     def forward(self, x, sample_map, interp_weights=None):
         return F.unresample(x, sample_map, self.interp, interp_weights)
+
+
+class MappedAvgPool(nn.Module):
+    def __init__(self, kernel_size, interpolation=InterpolationType.BILINEAR):
+        super().__init__()
+        self.kernel_size, self.interp = kernel_size, interpolation
+
+    def forward(self, x, sample_map, interp_weights=None):
+        return F.mapped_avg_pool(x, sample_map, self.kernel_size, self.interp, interp_weights)
+
+
+class MappedAvgUnpool(nn.Module):
+    """x (B, C, IH, IW) with a map of its own size pointing into the (oh, ow) output."""
+
+    def __init__(self, kernel_size, interpolation=InterpolationType.BILINEAR):
+        super().__init__()
+        self.kernel_size, self.interp = kernel_size, interpolation
+
+    def forward(self, x, oh, ow, sample_map, interp_weights=None):
+        return F.mapped_avg_unpool(x, oh, ow, sample_map, self.kernel_size, self.interp, interp_weights)
+
+
+class ResampleFromUV(nn.Module):
+    """Gathers an image from N textures: x (B, C, N, TH, TW), quad_idx (H, W) int64, tex_uv (H, W, 2)."""
+
+    def __init__(self, interpolation=InterpolationType.BILINEAR):
+        super().__init__()
+        assert interpolation in [InterpolationType.NEAREST, InterpolationType.BILINEAR], "Unsupported interpolation type"
+        self.interp = interpolation
+
+    def forward(self, x, quad_idx, tex_uv):
+        assert x.dim() == 5, "Input expected to be 5 dimensional tensor ({} != {})".format(x.dim(), 5)
+        assert quad_idx.dim() == 2 and quad_idx.dtype == torch.int64, "quad_idx expected to be 2 dimension tensor of type long"
+        assert tex_uv.shape[:2] == quad_idx.shape, \
+            "tex_uv expected to have same first two dimensions as quad_idx ({} != {})".format(tex_uv.shape[:2], quad_idx.shape)
+        return F.uv_resample(x, quad_idx, tex_uv, self.interp)
+
+
+def _pair(v):
+    return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
+
+
+class _StandardConv(nn.Module):
+    transposed = False
+
+    def __init__(self, in_channels, out_channels, kernel_size=1, stride=1, padding=0, dilation=1):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.kernel_size, self.stride, self.padding, self.dilation = _pair(kernel_size), _pair(stride), _pair(padding), _pair(dilation)
+        shape = (in_channels, out_channels) if self.transposed else (out_channels, in_channels)
+        self.weight = nn.Parameter(torch.empty(*shape, *self.kernel_size))
+        self.bias = nn.Parameter(torch.empty(out_channels))
+        _uniform_init(self, in_channels * self.kernel_size[0] * self.kernel_size[1])
+
+
+class Convolution(_StandardConv):
+    """Plain 2-D convolution with the reference layer's parameters: weight (out, in, kh, kw)."""
+
+    def forward(self, x):
+        return F.convolution(x, self.weight, self.bias, self.kernel_size, self.stride, self.padding, self.dilation)
+
+
+class TransposedConvolution(_StandardConv):
+    """Plain 2-D transposed convolution: weight (in, out, kh, kw)."""
+    transposed = True
+
+    def forward(self, x):
+        return F.transposed_convolution(x, self.weight, self.bias, self.kernel_size, self.stride, self.padding, self.dilation)

@@ -25,7 +25,9 @@ SYMBOLS = [
     "sph_mapped_conv_forward", "sph_mapped_conv_backward_input", "sph_mapped_conv_backward_weight",
     "sph_mapped_tconv_forward", "sph_mapped_tconv_backward_input", "sph_mapped_tconv_backward_weight",
     "sph_mapped_conv_relu_forward", "sph_mapped_conv_relu_backward_input", "sph_mapped_conv_relu_backward_weight",
-    "sph_device_status", "sph_debug_bounded_wait",
+    "sph_device_status", "sph_debug_bounded_wait", "sph_mapped_max_unpool_planned", "sph_mapped_avg_pool",
+    "sph_mapped_avg_unpool", "sph_resample_to_map_normalized", "sph_resample_from_uv_maps", "sph_plan_build_uv",
+    "sph_voting_resample_to_map", "sph_build_kernel_map",
 ]
 ERR_UNSUPPORTED = 2
 
@@ -171,6 +173,96 @@ def mapped_max_unpool(g, idx, smap, ih, iw_, K, interp, iw=None, out=None):
                                   *_ints(B, C, ih, iw_, OH, OW, K, _P(iw)), _int(_dt(g)), _int(int(interp)), _stream()),
         "sph_mapped_max_unpool")
     return out
+
+
+def slot_plan_build(smap, iw, K, interp, dstH, dstW):
+    """Scatter plan over the flattened map slots of a (OH, OW, K, [P,] 2) map (n_src = OH*OW*K positions, one slot
+    each): what the deterministic argmax backward and the average-pool backward consume."""
+    OH, OW = smap.shape[:2]
+    return plan_build(smap, iw, OH * OW * K, 1, interp, dstH, dstW)
+
+
+def mapped_max_unpool_planned(g, idx, plan, ih, iw_, K, P=0, out=None):
+    B, C, OH, OW = g.shape
+    if out is None:
+        out = torch.empty(B, C, int(ih), int(iw_), dtype=g.dtype, device=g.device)
+    _ok(lib.sph_mapped_max_unpool_planned(_ptr(g), _ptr(idx), _ptr(plan), _ptr(out), *_ints(B, C, ih, iw_, OH, OW, K, P),
+                                          _int(_dt(g)), _stream()), "sph_mapped_max_unpool_planned")
+    return out
+
+
+def mapped_avg_pool(x, smap, K, interp, iw=None):
+    B, C, IH, IW = x.shape
+    OH, OW = smap.shape[:2]
+    out = torch.empty(B, C, OH, OW, dtype=x.dtype, device=x.device)
+    _ok(lib.sph_mapped_avg_pool(_ptr(x), _ptr(smap), _ptr(iw), _ptr(out), *_ints(B, C, IH, IW, OH, OW, K, _P(iw)),
+                                _int(_dt(x)), _int(int(interp)), _stream()), "sph_mapped_avg_pool")
+    return out
+
+
+def mapped_avg_unpool(g, plan, ih, iw_, K):
+    B, C, OH, OW = g.shape
+    out = torch.empty(B, C, int(ih), int(iw_), dtype=g.dtype, device=g.device)
+    _ok(lib.sph_mapped_avg_unpool(_ptr(g), _ptr(plan), _ptr(out), *_ints(B, C, ih, iw_, OH, OW, K), _int(_dt(g)), _stream()),
+        "sph_mapped_avg_unpool")
+    return out
+
+
+def resample_to_map_normalized(x, plan, oh, ow, out=None):
+    B, C, MH, MW = x.shape
+    if out is None:
+        out = torch.empty(B, C, int(oh), int(ow), dtype=x.dtype, device=x.device)
+    _ok(lib.sph_resample_to_map_normalized(_ptr(x), _ptr(plan), _ptr(out), *_ints(B, C, MH, MW, oh, ow), _int(_dt(x)),
+                                           _stream()), "sph_resample_to_map_normalized")
+    return out
+
+
+def resample_from_uv_maps(tex, quad, uv, interp):
+    B, C, NT, TH, TW = tex.shape
+    IH, IW = quad.shape
+    out = torch.empty(B, C, IH, IW, dtype=tex.dtype, device=tex.device)
+    _ok(lib.sph_resample_from_uv_maps(_ptr(tex), _ptr(quad), _ptr(uv), _ptr(out), *_ints(B, C, NT, TH, TW, IH, IW),
+                                      _int(_dt(tex)), _int(int(interp)), _stream()), "sph_resample_from_uv_maps")
+    return out
+
+
+def uv_plan_build(quad, uv, NT, TH, TW, interp):
+    IH, IW = quad.shape
+    n = lib.sph_plan_bytes(*_ints(IH * IW, 1, 0), _int(int(interp)), *_ints(NT * TH, TW), _int(_dt(uv)))
+    if n == 0:
+        raise SphError("sph_plan_bytes: map too large")
+    plan = _bytes(n, uv)
+    _ok(lib.sph_plan_build_uv(_ptr(uv), _ptr(quad), *_ints(IH * IW, NT, TH, TW), _int(int(interp)), _int(_dt(uv)), _ptr(plan),
+                              _sz(n), _stream()), "sph_plan_build_uv")
+    return plan
+
+
+def resample_to_uv_maps(x, quad, uv, NT, TH, TW, interp):
+    plan = uv_plan_build(quad, uv, NT, TH, TW, interp)
+    B, C = x.shape[:2]
+    return resample_to_map(x, plan, NT * TH, TW).view(B, C, NT, TH, TW)
+
+
+def voting_resample_to_map(labels, smap, oh, ow, num_candidates):
+    """labels (B,C,IH,IW) int64, smap (IH,IW,2) int64 (x, y) -> (B,C,oh,ow) int64."""
+    B, C, IH, IW = labels.shape
+    mapf = smap.to(torch.float64)
+    plan = plan_build(mapf, None, IH * IW, 1, NEAREST, oh, ow)
+    out = torch.empty(B, C, int(oh), int(ow), dtype=torch.int64, device=labels.device)
+    _ok(lib.sph_voting_resample_to_map(_ptr(labels), _ptr(plan), _int(F64), _ptr(out), *_ints(B, C, IH, IW, oh, ow, num_candidates),
+                                       _stream()), "sph_voting_resample_to_map")
+    return out
+
+
+MAP_GRID, MAP_INVERSE_GNOMONIC, MAP_INVERSE_EQUIRECT = 0, 1, 2
+
+
+def build_kernel_map(H, W, kh, kw, stride=1, dilation=1, kind=MAP_INVERSE_GNOMONIC, dtype=torch.float32, device="cuda"):
+    OH, OW = (H + stride - 1) // stride, (W + stride - 1) // stride
+    m = torch.empty(OH, OW, kh * kw, 2, dtype=dtype, device=device)
+    _ok(lib.sph_build_kernel_map(_ptr(m), *_ints(H, W, kh, kw, stride, dilation), _int(kind), _int(_dt(m)), _stream()),
+        "sph_build_kernel_map")
+    return m
 
 
 def conv_workspace(op, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, like):

@@ -19,6 +19,12 @@ reference_kats.pt
     the gradients for an all-ones upstream gradient), after checking that the
     forward output equals the hand-computed vector.
 
+reference_siblings.pt
+    Seeded random cases of the operators beside the path that share its kernels: mapped average pooling and its
+    backward (plain and weighted), UV-map gather / scatter and voting resampling, evaluated with the reference's
+    compiled CPU modules; and the equirectangular kernel maps (grid, inverse gnomonic, inverse equirectangular) as
+    the reference's own Python builders (layers/util/mapping_functions.py) return them in float32 and float64.
+
 reference_random.pt
     Seeded random cases for everything the reference's tests do not pin
     (nearest / bispherical conv and pooling, every weighted op, float32, index
@@ -246,16 +252,92 @@ def random_cases():
     return cases
 
 
+# --------------------------------------------------------------------------
+# Part 3: sibling operators and kernel maps
+# --------------------------------------------------------------------------
+def sibling_cases(reference):
+    cases = []
+    seed = 2000
+    for dtype in (torch.float64, torch.float32):
+        for interp in (0, 1, 2):
+            for P in (0, 3):
+                seed += 1
+                g = torch.Generator().manual_seed(seed)
+                B, C, IH, IW, OH, OW, K = 2, 3, 6, 9, 5, 7, 4
+                x = torch.randn(B, C, IH, IW, generator=g, dtype=dtype)
+                shape = (OH, OW, K, P) if P else (OH, OW, K)
+                m = _coords(g, shape, IW, IH, dtype)
+                iw = torch.rand(OH, OW, K, P, generator=g, dtype=dtype) if P else None
+                gp = torch.randn(B, C, OH, OW, generator=g, dtype=dtype)
+                cases.append(dict(op="avgpool", seed=seed, interp=interp, kernel_size=K, input=x, sample_map=m,
+                                  interp_weights=iw, grad_output=gp,
+                                  ref_output=ref.mapped_avg_pool(x, m, K, interp, iw),
+                                  ref_grads=[ref.mapped_avg_unpool(gp, m, IH, IW, K, interp, iw)]))
+            # UV maps: 5 textures of 6 x 7 texels gathered into / scattered from an 8 x 11 image
+            seed += 1
+            g = torch.Generator().manual_seed(seed)
+            B, C, NT, TH, TW, IH, IW = 2, 3, 5, 6, 7, 8, 11
+            tex = torch.randn(B, C, NT, TH, TW, generator=g, dtype=dtype)
+            quad = torch.randint(0, NT, (IH, IW), generator=g)
+            uv = _coords(g, (IH, IW), TW, TH, dtype)
+            img = torch.randn(B, C, IH, IW, generator=g, dtype=dtype)
+            cases.append(dict(op="uv", seed=seed, interp=interp, input=tex, quad_idx=quad, tex_uv=uv, grad_output=img,
+                              ref_output=ref.resample_from_uv_maps(tex, quad, uv, interp),
+                              ref_grads=[ref.resample_to_uv_maps(img, quad, uv, NT, TH, TW, interp)]))
+    for seed, (IH, IW, OH, OW, NC) in ((2101, (12, 16, 5, 7, 6)), (2102, (6, 6, 9, 9, 3)), (2103, (20, 24, 2, 3, 11))):
+        g = torch.Generator().manual_seed(seed)
+        # one channel: with more, the reference's vote tensor overlaps channels (it steps the channel by OH*OW instead
+        # of OH*OW*num_candidates, ext_modules/include/common/resample.h:127-129), which pins nothing useful
+        lab = torch.randint(0, NC, (2, 1, IH, IW), generator=g)
+        m = torch.stack((torch.randint(-1, OW + 1, (IH, IW), generator=g), torch.randint(-1, OH + 1, (IH, IW), generator=g)), -1)
+        cases.append(dict(op="voting", seed=seed, input=lab, sample_map=m, oh=OH, ow=OW, num_candidates=NC,
+                          ref_output=ref.voting_resample_to_map(lab, m, OH, OW, NC)))
+    # kernel maps from the reference's own Python builders (its package is mounted unmodified on this repo's extension)
+    sys.path.insert(0, os.path.join(ROOT, "spherical-package_b200"))
+    from _spherical_distortion_ext import reference_compat as rc
+    rc.install_placeholders()
+    rc.mount_reference_layers(os.path.join(reference, "layers"))
+    import spherical_distortion.util as u
+    for kind, fn in (("grid", u.grid_projection_map), ("inverse_gnomonic", u.inverse_gnomonic_projection_map),
+                     ("inverse_equirectangular", u.inverse_equirectangular_projection_map)):
+        for (H, W, kh, kw, stride, dil) in ((8, 16, 3, 3, 1, 1), (12, 20, 3, 3, 2, 1), (7, 10, 5, 3, 1, 2), (9, 14, 2, 2, 3, 1)):
+            c = dict(op="map", kind=kind, H=H, W=W, kh=kh, kw=kw, stride=stride, dilation=dil)
+            for name, dt in (("f32", torch.float32), ("f64", torch.float64)):
+                old = torch.get_default_dtype()
+                torch.set_default_dtype(dt)
+                try:
+                    c[name] = fn((H, W), (kh, kw), stride, dil).clone()
+                finally:
+                    torch.set_default_dtype(old)
+            cases.append(c)
+    for c in cases:
+        for k, v in list(c.items()):
+            if torch.is_tensor(v):
+                c[k] = v.detach().clone()
+            elif isinstance(v, list):
+                c[k] = [t.detach().clone() for t in v]
+    return cases
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=default_reference())
+    ap.add_argument("--only", nargs="+", default=["kats", "random", "siblings"], choices=["kats", "random", "siblings"],
+                    help="which fixture files to (re)write; the reference's scatters add with OpenMP atomics, so a rewritten "
+                         "file differs from the committed one in the last bit of some gradients")
     a = ap.parse_args()
     assert ref.available(), "build the reference modules first: python oracle/build_ref.py"
-    kats = [evaluate(c) for c in harvest(a.reference)]
-    torch.save(kats, os.path.join(HERE, "reference_kats.pt"))
-    print("reference_kats.pt: %d cases" % len(kats))
-    for c in kats:
-        print("  ", c["name"], c["op"], "interp", c["interp"], tuple(c["input"].shape))
-    rnd = random_cases()
-    torch.save(rnd, os.path.join(HERE, "reference_random.pt"))
-    print("reference_random.pt: %d cases" % len(rnd))
+    if "kats" in a.only:
+        kats = [evaluate(c) for c in harvest(a.reference)]
+        torch.save(kats, os.path.join(HERE, "reference_kats.pt"))
+        print("reference_kats.pt: %d cases" % len(kats))
+        for c in kats:
+            print("  ", c["name"], c["op"], "interp", c["interp"], tuple(c["input"].shape))
+    if "random" in a.only:
+        rnd = random_cases()
+        torch.save(rnd, os.path.join(HERE, "reference_random.pt"))
+        print("reference_random.pt: %d cases" % len(rnd))
+    if "siblings" in a.only:
+        sib = sibling_cases(a.reference)
+        torch.save(sib, os.path.join(HERE, "reference_siblings.pt"))
+        print("reference_siblings.pt: %d cases" % len(sib))

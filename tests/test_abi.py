@@ -63,6 +63,14 @@ def test_plugin_package_has_the_reference_module_and_function_names():
         "_mapped_transposed_convolution": ["mapped_transposed_conv_forward", "mapped_transposed_conv_backward"],
         "_weighted_mapped_transposed_convolution": ["weighted_mapped_transposed_conv_forward",
                                                     "weighted_mapped_transposed_conv_backward"],
+        # modules beside the path that the reference's Python layer imports unconditionally
+        "_mapped_avg_pooling": ["mapped_avg_pool", "mapped_avg_unpool"],
+        "_weighted_mapped_avg_pooling": ["weighted_mapped_avg_pool", "weighted_mapped_avg_unpool"],
+        "_uv_resample": ["resample_to_uv_maps", "resample_from_uv_maps"],
+        "_voting_resample": ["voting_resample_to_map"],
+        "_convolution": ["conv_forward", "conv_backward"],
+        "_transposed_convolution": ["transposed_conv_forward", "transposed_conv_backward"],
+        "_distort": ["create_distortion_sample_map", "DistortionType"],
     }
     for mod, names in expect.items():
         m = importlib.import_module("_spherical_distortion_ext." + mod)
@@ -104,3 +112,30 @@ def test_workload_generators_have_the_configured_shapes():
     assert abs(wl.encoder_flops(64) / 1e9 - 4049.08) < 0.01
     c4 = wl.config4(B=1, H=64, W=128)
     assert [tuple(m.shape[:2]) for m in c4["maps"]] == [(32, 64), (16, 32), (16, 32), (16, 32)]
+
+
+def test_reference_python_layer_imports_unmodified_on_this_package():
+    """The reference's own `layers/` folder, mounted as `spherical_distortion` without a change, imports completely on
+    top of this package: every native module name it asks for resolves (the mesh / lens-distortion modules and the
+    absent third-party packages through import-time stand-ins).  Needs the reference checkout
+    ($SPHERICAL_PACKAGE_REFERENCE or a folder `reference` beside the repository); run in a child process so that the
+    mirror package of the same name, which other tests import, is not disturbed."""
+    import subprocess
+    import sys
+    from oracle.build_ref import default_reference
+    layers = os.path.join(default_reference(), "layers")
+    if not os.path.isdir(layers):
+        pytest.skip("reference checkout not present")
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "from _spherical_distortion_ext import reference_compat as rc\n"
+        "rc.install_placeholders(); rc.mount_reference_layers(%r)\n"
+        "import spherical_distortion.nn as nn, spherical_distortion.functional as F, spherical_distortion.util as u\n"
+        "assert nn.__file__.startswith(%r)\n"
+        "for n in ('MappedConvolution','MappedTransposedConvolution','MappedMaxPool','MappedAvgPool','Resample','Unresample','ResampleFromUV','Convolution'): getattr(nn, n)\n"
+        "for n in ('mapped_convolution','mapped_max_pool','mapped_avg_pool','resample','unresample','uv_resample','voting_resample','convolution'): getattr(F, n)\n"
+        "print('imported', tuple(u.inverse_gnomonic_projection_map((8, 16), (3, 3)).shape))\n"
+    ) % (os.path.join(ROOT, "spherical-package_b200"), layers, layers)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "imported (8, 16, 9, 2)" in r.stdout

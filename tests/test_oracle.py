@@ -103,3 +103,44 @@ def test_port_matches_live_reference_float32_config0_shape():
     a = port.mapped_conv_forward(x, m, w, b, 9, 1)
     r = ref.mapped_conv_forward(x, m, w, b, 9, 1)
     torch.testing.assert_close(a, r, rtol=1e-5, atol=1e-5)
+
+
+def _run_sibling(c, impl):
+    if c["op"] == "avgpool":
+        x, m, iw, it, K = c["input"], c["sample_map"], c["interp_weights"], c["interp"], c["kernel_size"]
+        return impl.mapped_avg_pool(x, m, K, it, iw), [impl.mapped_avg_unpool(c["grad_output"], m, x.shape[2], x.shape[3], K, it, iw)]
+    if c["op"] == "uv":
+        tex = c["input"]
+        return (impl.resample_from_uv_maps(tex, c["quad_idx"], c["tex_uv"], c["interp"]),
+                [impl.resample_to_uv_maps(c["grad_output"], c["quad_idx"], c["tex_uv"], *tex.shape[2:], c["interp"])])
+    if c["op"] == "voting":
+        return impl.voting_resample_to_map(c["input"], c["sample_map"], c["oh"], c["ow"], c["num_candidates"]), []
+    raise ValueError(c["op"])
+
+
+def test_port_matches_reference_on_sibling_operators(golden_dir):
+    """Average pooling, UV-map and voting resampling of the plain-C oracle against the compiled reference's outputs."""
+    n = 0
+    for c in _load(golden_dir, "reference_siblings.pt"):
+        if c["op"] == "map":
+            continue
+        out, grads = _run_sibling(c, port)
+        if c["op"] == "voting":
+            assert torch.equal(out, c["ref_output"]), c["seed"]
+        else:
+            # gathers add K values in the reference's order: bit exact; the scatters add in any order there
+            assert torch.equal(out, c["ref_output"]), (c["op"], c["seed"], c["interp"])
+            for a, b in zip(grads, c["ref_grads"]):
+                torch.testing.assert_close(a, b, **_tol(a.dtype))
+        n += 1
+    assert n == 21
+
+
+def test_workload_gnomonic_map_matches_reference_builder(golden_dir):
+    """The benchmark's own map generator (sphmap.workloads.gnomonic_map) against the reference's Python builder."""
+    from sphmap import workloads as wl
+    for c in _load(golden_dir, "reference_siblings.pt"):
+        if c["op"] == "map" and c["kind"] == "inverse_gnomonic" and c["kh"] == c["kw"] and c["dilation"] == 1:
+            got = wl.gnomonic_map(c["H"], c["W"], c["stride"], c["kh"], dtype=torch.float64)
+            ok = ~torch.isnan(c["f64"])   # even kernels: the reference's zero differential evaluates to 0/0
+            torch.testing.assert_close(got[ok], c["f64"][ok], rtol=0, atol=1e-9)
