@@ -2,6 +2,7 @@
 #include <float.h>
 
 #include "common.cuh"
+#include "plan_walk.cuh"
 
 namespace sph {
 
@@ -146,55 +147,50 @@ max_unpool_kernel(const T *__restrict__ g, const int64_t *__restrict__ idx, cons
 // (output position o, slot k) whose taps touch q, as s = o*K + k, in map order, with the tap weight.  The pixel sums,
 // in that fixed order, the entries whose slot is the one the forward pass selected: idx[p,o] == s * 2 * PP.  No
 // zero-fill, no atomics, results independent of scheduling (the reference scatters with atomicAdd:
-// ext_modules/include/cuda/mapped_max_pool.cuh:57-95).
+// ext_modules/include/cuda/mapped_max_pool.cuh:57-95).  The plan is walked warp-cooperatively (plan_walk.cuh).
 // STAGED: the winning slot of every output of the CTA's PL planes is first decoded into shared memory as one byte
 // (255 = none), so the per-entry test reads a byte of shared memory instead of 8 random bytes of idx.
 template <typename T, int PL, bool STAGED>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(1024)
 max_unpool_plan_kernel(const T *__restrict__ g, const int64_t *__restrict__ idx, const void *__restrict__ plan_blob,
-                       T *__restrict__ gin, int n, int n_dst, int planes, int K, int PP, int chunk) {
-  extern __shared__ uint8_t ksm[];  // [PL][n]
+                       T *__restrict__ gin, int n, int n_dst, int planes, int K, int PP, int chunk, FastDiv divK) {
+  extern __shared__ unsigned char unpool_smem[];
+  T *cbuf = (T *)unpool_smem;
+  uint8_t *ksm = unpool_smem + (size_t)(blockDim.x >> 5) * walk_smem_per_warp<T, PL, false>();  // [PL][n]
   const int p0 = blockIdx.y * PL;
   const int np = min(PL, planes - p0);
   if (STAGED) {
-    for (int i = threadIdx.x; i < PL * n; i += blockDim.x) {
-      const int j = i / n, o = i - j * n;
-      int k = -1;
-      if (j < np) {
-        const int64_t s = idx[(size_t)(p0 + j) * n + o];
-        if (s >= 0) {
-          const int64_t slot = s / (2 * PP), kk = slot - (int64_t)o * K;
-          if (kk >= 0 && kk < K && slot * 2 * PP == s) k = (int)kk;
+    for (int j = 0; j < PL; j++)
+      for (int o = threadIdx.x; o < n; o += blockDim.x) {
+        int k = -1;
+        if (j < np) {
+          const int64_t s = __ldg(idx + (size_t)(p0 + j) * n + o);
+          if (s >= 0) {
+            const int64_t slot = s / (2 * PP), kk = slot - (int64_t)o * K;
+            if (kk >= 0 && kk < K && slot * 2 * PP == s) k = (int)kk;
+          }
         }
+        ksm[(size_t)j * n + o] = k < 0 ? (uint8_t)255 : (uint8_t)k;
       }
-      ksm[i] = k < 0 ? (uint8_t)255 : (uint8_t)k;
-    }
     __syncthreads();
   }
   bool ok;
   const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok);
-  const int q_end = min((int)((blockIdx.x + 1) * (int64_t)chunk), n_dst);
-  for (int q = blockIdx.x * chunk + threadIdx.x; q < q_end; q += blockDim.x) {
-    T acc[PL];
-#pragma unroll
-    for (int j = 0; j < PL; j++) acc[j] = T(0);
-    const int e0 = ok ? __ldg(plan.offsets + q) : 0, e1 = ok ? __ldg(plan.offsets + q + 1) : 0;
-    for (int e = e0; e < e1; e++) {
-      const int s = __ldg(plan.src + e);
-      const T w = __ldg(plan.w + e);
-      const int o = s / K, k = s - o * K;
-#pragma unroll
-      for (int j = 0; j < PL; j++)
-        if (j < np) {
-          const bool hit = STAGED ? ksm[j * n + o] == (uint8_t)k
-                                  : __ldg(idx + (size_t)(p0 + j) * n + o) == (int64_t)s * 2 * PP;
-          if (hit) acc[j] += w * __ldg(g + (size_t)(p0 + j) * n + o);
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < PL; j++)
-      if (j < np) gin[(size_t)(p0 + j) * n_dst + q] = acc[j];
-  }
+  const int q_begin = blockIdx.x * chunk, q_end = min(q_begin + chunk, n_dst);
+  const T *gp = g + (size_t)p0 * n;
+  const int64_t *ip = idx + (size_t)p0 * n;
+  struct Slot { int o, k, s; };
+  plan_walk<T, PL, false>(plan, ok, n_dst, q_begin, q_end, cbuf,
+                          [&](int s) {
+                            const int o = (int)divK.div((unsigned)s);
+                            return Slot{o, s - o * K, s};
+                          },
+                          [&](const Slot &e, T w, int j) {
+                            const bool hit = STAGED ? ksm[j * n + e.o] == (uint8_t)e.k
+                                                    : __ldg(ip + (size_t)j * n + e.o) == (int64_t)e.s * 2 * PP;
+                            return hit ? w * __ldg(gp + (size_t)j * n + e.o) : T(0);
+                          },
+                          gin + (size_t)p0 * n_dst, np);
 }
 
 template <typename T>
@@ -202,20 +198,24 @@ static int unpool_planned(const void *g, const int64_t *idx, const void *plan, v
                           int64_t n, int64_t K, int64_t P, cudaStream_t st) {
   const int PP = (int)(P > 0 ? P : 1);
   constexpr int PL = 4;
+  const int groups = cdiv(planes, PL);
   const size_t stage = (size_t)PL * n;
-  if (K <= 254 && stage <= 200 * 1024) {
-    // CTAs = plane groups x pixel chunks, at least two waves of the SMs; one CTA per SM (shared memory)
-    const int groups = cdiv(planes, PL);
-    int chunks = cdiv((int64_t)2 * 148, groups);
-    if (chunks > cdiv(n_dst, 512)) chunks = cdiv(n_dst, 512);
-    const int chunk = cdiv(cdiv(n_dst, chunks), 512) * 512;
-    cudaFuncSetAttribute(max_unpool_plan_kernel<T, PL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage);
-    max_unpool_plan_kernel<T, PL, true><<<dim3(cdiv(n_dst, chunk), groups), 512, stage, st>>>(
-        (const T *)g, idx, plan, (T *)gin, (int)n, (int)n_dst, (int)planes, (int)K, PP, chunk);
+  if (K <= 254 && stage + 32 * (size_t)walk_smem_per_warp<T, PL, false>() <= 200 * 1024) {
+    // one CTA of 32 warps per SM (the staged slots fill its shared memory); CTAs = plane groups x pixel chunks
+    int chunks = cdiv((int64_t)148 * 2, groups);
+    if (chunks > cdiv(n_dst, 1024)) chunks = cdiv(n_dst, 1024);
+    const int chunk = cdiv(cdiv(n_dst, chunks), 1024) * 1024;
+    const size_t smem = stage + 32 * (size_t)walk_smem_per_warp<T, PL, false>();
+    cudaFuncSetAttribute(max_unpool_plan_kernel<T, PL, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    max_unpool_plan_kernel<T, PL, true><<<dim3(cdiv(n_dst, chunk), groups), 1024, smem, st>>>(
+        (const T *)g, idx, plan, (T *)gin, (int)n, (int)n_dst, (int)planes, (int)K, PP, chunk, FastDiv::make((unsigned)K));
   } else {
-    const int chunk = 2048;
-    max_unpool_plan_kernel<T, PL, false><<<dim3(cdiv(n_dst, chunk), cdiv(planes, PL)), 512, 0, st>>>(
-        (const T *)g, idx, plan, (T *)gin, (int)n, (int)n_dst, (int)planes, (int)K, PP, chunk);
+    int64_t chunks = ((int64_t)148 * 16 + groups - 1) / groups;
+    if (chunks > (n_dst + 255) / 256) chunks = (n_dst + 255) / 256;
+    const int chunk = (int)(((n_dst + chunks - 1) / chunks + 255) / 256 * 256);
+    const size_t smem = 8 * (size_t)walk_smem_per_warp<T, PL, false>();
+    max_unpool_plan_kernel<T, PL, false><<<dim3(cdiv(n_dst, chunk), groups), 256, smem, st>>>(
+        (const T *)g, idx, plan, (T *)gin, (int)n, (int)n_dst, (int)planes, (int)K, PP, chunk, FastDiv::make((unsigned)K));
   }
   return launch_status();
 }

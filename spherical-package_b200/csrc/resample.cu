@@ -2,6 +2,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "plan_walk.cuh"
 
 namespace sph {
 
@@ -64,107 +65,32 @@ resample_from_map_kernel(const T *__restrict__ x, const T *__restrict__ map, con
 //   div  > 1   x[s / div] / div           mapped average unpooling: the plan runs over the flattened map slots
 //                                         s = o * K + k and every slot carries grad[o] / K
 //                                         (common/mapped_avg_pool.h:41-69, 109-143)
-template <typename T>
+template <typename T, bool DIV>
 struct SrcValue {
   int div;
-  __device__ __forceinline__ T operator()(const T *__restrict__ plane, int s) const {
-    if (div == 1) return __ldg(plane + s);
-    return __ldg(plane + s / div) / (T)div;
-  }
+  FastDiv fd;
+  __device__ __forceinline__ int index(int s) const { return DIV ? (int)fd.div((unsigned)s) : s; }
+  __device__ __forceinline__ T value(T v) const { return DIV ? v / (T)div : v; }
 };
 
-// Adjoint as a gather: destination pixel p sums its plan segment in stored
-// order.  Replaces the atomicAdd scatter of cuda/resample.cuh:14-47.
+// Adjoint as a gather through the plan (plan_walk.cuh): a CTA takes a chunk of destination pixels and PL planes.
 // NORM: the sum is divided by (sum of the segment's weights + 1e-12), i.e. scatter(x) / (scatter(1) + 1e-12), the
 // weight-sum normalisation the reference composes in Python (layers/functional/sphere_ops.py:74-80).
-template <typename T, int PPT, bool NORM>
+template <typename T, int PL, bool NORM, bool DIV>
 __global__ void __launch_bounds__(256)
 resample_to_map_kernel(const T *__restrict__ x, const void *__restrict__ plan_blob, T *__restrict__ out, int n_dst,
-                       int n_src, int planes, SrcValue<T> sv) {
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;
-  if (p >= n_dst) return;
+                       int n_src, int planes, int chunk, SrcValue<T, DIV> sv) {
+  extern __shared__ unsigned char walk_smem[];
   bool ok;
   const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok);
-  const int p0 = blockIdx.y * PPT;
-  const int np = min(PPT, planes - p0);
+  const int p0 = blockIdx.y * PL;
+  const int np = min(PL, planes - p0);
   const T *xp = x + (size_t)p0 * n_src;
-  T acc[PPT];
-#pragma unroll
-  for (int j = 0; j < PPT; j++) acc[j] = T(0);
-  const int e0 = ok ? __ldg(plan.offsets + p) : 0, e1 = ok ? __ldg(plan.offsets + p + 1) : 0;
-  T wsum = T(0);
-  for (int e = e0; e < e1; e++) {
-    const int s = __ldg(plan.src + e);
-    const T w = __ldg(plan.w + e);
-    if (NORM) wsum += w;
-#pragma unroll
-    for (int j = 0; j < PPT; j++)
-      if (j < np) acc[j] += w * sv(xp + (size_t)j * n_src, s);
-  }
-#pragma unroll
-  for (int j = 0; j < PPT; j++)
-    if (j < np) out[(size_t)(p0 + j) * n_dst + p] = NORM ? acc[j] / (wsum + T(1e-12)) : acc[j];
-}
-
-// Same operator, four consecutive destination pixels per thread (n_dst a multiple of 4) in a grid-stride loop:
-// the five segment offsets of the next group are requested before the current group is processed, and every
-// plane is written with one 16-byte (float) / two 16-byte (double) stores.  Most of this kernel's traffic is the
-// output it writes; the point is to keep enough bytes in flight per thread.
-template <typename T, int PPT, bool NORM>
-__global__ void __launch_bounds__(256)
-resample_to_map4_kernel(const T *__restrict__ x, const void *__restrict__ plan_blob, T *__restrict__ out, int n_dst,
-                        int n_src, int planes, SrcValue<T> sv) {
-  bool ok;
-  const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok);
-  const int p0 = blockIdx.y * PPT;
-  const int np = min(PPT, planes - p0);
-  const T *xp = x + (size_t)p0 * n_src;
-  const int stride = gridDim.x * blockDim.x * 4;
-  int p = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-  int nxt[5];
-#pragma unroll
-  for (int q = 0; q < 5; q++) nxt[q] = (ok && p < n_dst) ? __ldg(plan.offsets + p + q) : 0;
-  for (; p < n_dst; p += stride) {
-    int off[5];
-#pragma unroll
-    for (int q = 0; q < 5; q++) off[q] = nxt[q];
-    const int pn = p + stride;
-#pragma unroll
-    for (int q = 0; q < 5; q++) nxt[q] = (ok && pn < n_dst) ? __ldg(plan.offsets + pn + q) : 0;
-    T acc[4][PPT], wsum[4];
-#pragma unroll
-    for (int q = 0; q < 4; q++) {
-      wsum[q] = T(0);
-#pragma unroll
-      for (int j = 0; j < PPT; j++) acc[q][j] = T(0);
-    }
-#pragma unroll
-    for (int q = 0; q < 4; q++) {
-      for (int e = off[q]; e < off[q + 1]; e++) {
-        const int s = __ldg(plan.src + e);
-        const T w = __ldg(plan.w + e);
-        if (NORM) wsum[q] += w;
-#pragma unroll
-        for (int j = 0; j < PPT; j++)
-          if (j < np) acc[q][j] += w * sv(xp + (size_t)j * n_src, s);
-      }
-      if (NORM) {
-#pragma unroll
-        for (int j = 0; j < PPT; j++) acc[q][j] = acc[q][j] / (wsum[q] + T(1e-12));
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < PPT; j++)
-      if (j < np) {
-        T *o = out + (size_t)(p0 + j) * n_dst + p;
-        if (sizeof(T) == 4) {
-          *(float4 *)o = make_float4((float)acc[0][j], (float)acc[1][j], (float)acc[2][j], (float)acc[3][j]);
-        } else {
-          *(double2 *)o = make_double2((double)acc[0][j], (double)acc[1][j]);
-          *(double2 *)(o + 2) = make_double2((double)acc[2][j], (double)acc[3][j]);
-        }
-      }
-  }
+  const int q_begin = blockIdx.x * chunk, q_end = min(q_begin + chunk, n_dst);
+  plan_walk<T, PL, NORM>(plan, ok, n_dst, q_begin, q_end, (T *)walk_smem,
+                         [&](int s) { return xp + sv.index(s); },
+                         [&](const T *src, T w, int j) { return w * sv.value(__ldg(src + (size_t)j * n_src)); },
+                         out + (size_t)p0 * n_dst, np);
 }
 
 // Planes walked per thread: 8 amortises the tap decode best; small problems use 2 so that enough threads are
@@ -196,30 +122,38 @@ static int from_map(const void *x, const void *map, const void *iw, void *y, int
 }
 
 // n_src: elements per source plane; src_div: see SrcValue.
-template <typename T, bool NORM>
+template <typename T, int PL, bool NORM, bool DIV>
+static void to_map_launch(const void *x, const void *plan, void *out, int64_t planes, int64_t n_src, int64_t n_dst, int src_div,
+                          cudaStream_t st) {
+  const int groups = cdiv(planes, PL);
+  // CTAs of 8 warps; enough CTAs for a few waves of the SMs, each warp walking several 32-pixel blocks so that the
+  // segment bounds of the next block are in flight while the current one is summed
+  int64_t chunks = ((int64_t)148 * 16 + groups - 1) / groups;
+  const int64_t max_chunks = (n_dst + 255) / 256;
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks < 1) chunks = 1;
+  const int chunk = (int)(((n_dst + chunks - 1) / chunks + 255) / 256 * 256);
+  const size_t smem = 8 * (size_t)walk_smem_per_warp<T, PL, NORM>();
+  resample_to_map_kernel<T, PL, NORM, DIV><<<dim3(cdiv(n_dst, chunk), groups), 256, smem, st>>>(
+      (const T *)x, plan, (T *)out, (int)n_dst, (int)n_src, (int)planes, chunk, SrcValue<T, DIV>{src_div, FastDiv::make((unsigned)src_div)});
+}
+
+template <typename T, bool NORM, bool DIV>
 static int to_map_n(const void *x, const void *plan, void *out, int64_t planes, int64_t n_src, int64_t n_dst, int src_div,
                     cudaStream_t st) {
-  const SrcValue<T> sv{src_div};
-  if (n_dst % 4 == 0 && ((uintptr_t)out & 31) == 0 && n_dst * ((planes + 3) / 4) >= (int64_t)148 * 2048 * 4) {
-    const int gx = (int)std::min<int64_t>(cdiv(n_dst / 4, 256), 64);  // each thread walks several groups of four pixels
-    resample_to_map4_kernel<T, 4, NORM><<<dim3(gx, cdiv(planes, 4)), 256, 0, st>>>((const T *)x, plan, (T *)out, (int)n_dst,
-                                                                                   (int)n_src, (int)planes, sv);
-    return launch_status();
-  }
-  if (planes_per_thread(n_dst, planes) == 8)
-    resample_to_map_kernel<T, 8, NORM><<<dim3(cdiv(n_dst, 256), cdiv(planes, 8)), 256, 0, st>>>((const T *)x, plan, (T *)out,
-                                                                                               (int)n_dst, (int)n_src, (int)planes, sv);
-  else
-    resample_to_map_kernel<T, 2, NORM><<<dim3(cdiv(n_dst, 256), cdiv(planes, 2)), 256, 0, st>>>((const T *)x, plan, (T *)out,
-                                                                                               (int)n_dst, (int)n_src, (int)planes, sv);
+  // planes per CTA: more planes amortise the plan reads and put more stores in flight per warp
+  if (sizeof(T) == 4 && planes >= 128) to_map_launch<T, 16, NORM, DIV>(x, plan, out, planes, n_src, n_dst, src_div, st);
+  else if (planes >= 8) to_map_launch<T, 8, NORM, DIV>(x, plan, out, planes, n_src, n_dst, src_div, st);
+  else to_map_launch<T, 4, NORM, DIV>(x, plan, out, planes, n_src, n_dst, src_div, st);
   return launch_status();
 }
 
 template <typename T>
 static int to_map(const void *x, const void *plan, void *out, int64_t planes, int64_t n_src, int64_t n_dst, cudaStream_t st,
                   int src_div = 1, bool normalize = false) {
-  return normalize ? to_map_n<T, true>(x, plan, out, planes, n_src, n_dst, src_div, st)
-                   : to_map_n<T, false>(x, plan, out, planes, n_src, n_dst, src_div, st);
+  if (src_div > 1) return to_map_n<T, false, true>(x, plan, out, planes, n_src, n_dst, src_div, st);  // never normalised
+  return normalize ? to_map_n<T, true, false>(x, plan, out, planes, n_src, n_dst, 1, st)
+                   : to_map_n<T, false, false>(x, plan, out, planes, n_src, n_dst, 1, st);
 }
 
 // Voting resample of integer labels through a nearest-neighbour plan: destination pixel o takes the label that most

@@ -87,13 +87,20 @@ def test_device_map_builders_match_the_reference_python_builders(golden_dir):
         assert m64.shape == c["f64"].shape and m32.dtype == torch.float32
         ok = ~torch.isnan(c["f64"])   # even kernels: the reference's zero differential is 0/0; here it is the pixel itself
         assert torch.isfinite(m64).all()
+        # A sample whose own latitude is a pole has no defined longitude: its x comes out of a division by, or the sign
+        # of, cos(+-pi/2) (+6e-17 in float64, -4e-8 in float32), i.e. of round-off.  Those samples are compared in y
+        # only; on the two pole rows the same holds for every tangent-plane sample of the float32 maps.
+        y = c["f64"][..., 1:2]
+        defined = ok & (y > 1e-6) & (y < c["H"] - 1 - 1e-6)
         # longitudes within round-off of the +-pi seam may wrap to either end of the row: compare x modulo W
         d = (m64 - c["f64"]).abs()
         d[..., 0] = torch.minimum(d[..., 0], (d[..., 0] - c["W"]).abs())
-        assert d[ok].max() <= 1e-9, (c["kind"], d[ok].max())
+        assert d[defined].max() <= 1e-9 and d[..., 1][ok[..., 1]].max() <= 1e-9, (c["kind"], d[defined].max())
         d32 = (m32.double() - c["f32"].double()).abs()
         d32[..., 0] = torch.minimum(d32[..., 0], (d32[..., 0] - c["W"]).abs())
-        assert d32[ok].max() <= 2e-3, (c["kind"], d32[ok].max())
+        rows = torch.arange(0, c["H"], c["stride"])
+        defined32 = defined & ((rows != 0) & (rows != c["H"] - 1)).view(-1, 1, 1, 1)
+        assert d32[defined32].max() <= 2e-3 and d32[..., 1][ok[..., 1]].max() <= 2e-3, (c["kind"], d32[defined32].max())
         n += 1
     assert n == 12
     # a map built on the device drives a layer exactly like the same map built on the host
