@@ -73,10 +73,20 @@ unsigned long long sph_launch_count(void);
  *       (nanoseconds, at most 1e9), on a barrier nothing arrives at; it must
  *       write 1 to *status (DEVICE pointer), set the sticky word, free its
  *       tensor memory and return.
+ * Checked build.  Compiled with -DSPH_BOUNDS_CHECK (build.py --checked ->
+ * libsphmap_checked.so, same ABI) every data-dependent index a kernel is
+ * about to use - tap offsets, plan entries, positions while a plan is
+ * written - is range-checked first; a violation skips the access and sets
+ * bit 1 (value 2) of the status word.  It is the stand-in for a memory
+ * checker where none may run; sph_build_is_checked() tells which build is
+ * loaded.  In every build a plan that was made for tensors of another size
+ * is recognised by its header and the operator writes zeros instead of
+ * following it.
  * The reference has no counterpart: its CUDA_CHECK ends the process
  * (ext_modules/include/cuda_helper.h:5-10).
  * ---------------------------------------------------------------------- */
 int sph_device_status(int *status, int reset);
+int sph_build_is_checked(void);
 int sph_debug_bounded_wait(unsigned long long limit_ns, int *status, void *stream);
 
 /* ------------------------------------------------------------------------

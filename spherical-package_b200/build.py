@@ -2,6 +2,7 @@
 
     python build.py            # libsphmap.so (nvcc, sm_100a) + the PyTorch host extension (_C)
     python build.py --lib-only # only the C-ABI library (no torch headers needed)
+    python build.py --checked  # also libsphmap_checked.so: same ABI, every data-dependent index range-checked
 
 Outputs go next to the Python modules in ``_spherical_distortion_ext/``:
 ``libsphmap.so`` (the C ABI of include/sphmap.h; depends only on the CUDA
@@ -48,22 +49,26 @@ def _run(cmd):
     return r.stdout + r.stderr
 
 
-def build_lib(verbose=False, ptxas_info=False):
-    os.makedirs(OBJ, exist_ok=True)
+def build_lib(verbose=False, ptxas_info=False, checked=False):
+    """libsphmap.so, or with checked=True libsphmap_checked.so: the same sources compiled with -DSPH_BOUNDS_CHECK
+    (every data-dependent index is range-checked on the device; see include/sphmap.h)."""
+    obj_dir = OBJ + ("_checked" if checked else "")
+    os.makedirs(obj_dir, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))] + \
               [os.path.join(INCLUDE, "sphmap.h")]
     logs = []
 
     def one(src):
-        s, o = os.path.join(CSRC, src), os.path.join(OBJ, src[:-3] + ".o")
+        s, o = os.path.join(CSRC, src), os.path.join(obj_dir, src[:-3] + ".o")
         if _newer(o, [s] + headers):
             return o
-        logs.append(_run([_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-c", s, "-o", o]))
+        flags = NVCC_FLAGS + (["-DSPH_BOUNDS_CHECK"] if checked else []) + (["-Xptxas", "-v"] if ptxas_info else [])
+        logs.append(_run([_nvcc()] + flags + ["-c", s, "-o", o]))
         return o
 
     with ThreadPoolExecutor(len(CU_SOURCES)) as ex:
         objs = list(ex.map(one, CU_SOURCES))
-    lib = os.path.join(OUT, "libsphmap.so")
+    lib = os.path.join(OUT, "libsphmap_checked.so" if checked else "libsphmap.so")
     if not _newer(lib, objs):
         _run([_nvcc(), "-shared", "-o", lib] + objs + ["-lcudart"])
     if verbose:
@@ -99,6 +104,7 @@ def build_ext(verbose=False):
 
 def build_all(verbose=False):
     build_lib(verbose)
+    build_lib(verbose, checked=True)
     build_ext(verbose)
 
 
@@ -106,8 +112,11 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--lib-only", action="store_true")
     ap.add_argument("--ptxas-info", action="store_true", help="print registers / spills / shared memory per kernel")
+    ap.add_argument("--checked", action="store_true", help="also build libsphmap_checked.so (-DSPH_BOUNDS_CHECK)")
     a = ap.parse_args()
     lib, log = build_lib(True, a.ptxas_info)
+    if a.checked:
+        build_lib(True, False, checked=True)
     if a.ptxas_info:
         print(log)
     if not a.lib_only:

@@ -30,11 +30,39 @@ template <> struct RN<double> {
   static __device__ __forceinline__ int floor_int(double v) { return (int)floor(v); }
 };
 
+// ---- checked build (-DSPH_BOUNDS_CHECK) ----------------------------------------------------------------------
+// The stand-in for a memory checker on machines where none may run: every data-dependent index a kernel is about to
+// use (tap offsets, plan entries, plan positions while a plan is being written) is compared with its range first.
+// A violation is recorded in a sticky per-device word, which sph_device_status() reports as bit 2, and the access is
+// skipped - nothing traps.  In the normal build index_ok() is the constant true and costs nothing.
+#ifdef SPH_BOUNDS_CHECK
+static __device__ int g_bad_index;  // one copy per translation unit, collected by sph_device_status()
+__device__ __forceinline__ bool index_ok(long long i, long long n) {
+  if (i >= 0 && i < n) return true;
+  g_bad_index = 1;
+  return false;
+}
+#define SPH_TU_STATUS(name)                                                                       \
+  extern "C" int sph_tu_status_##name(int reset) {                                                \
+    int v = 0;                                                                                    \
+    if (cudaMemcpyFromSymbol(&v, sph::g_bad_index, sizeof(int)) != cudaSuccess) return -1;        \
+    if (reset && v) {                                                                             \
+      const int zero = 0;                                                                         \
+      if (cudaMemcpyToSymbol(sph::g_bad_index, &zero, sizeof(int)) != cudaSuccess) return -1;     \
+    }                                                                                             \
+    return v;                                                                                     \
+  }
+#else
+__device__ __forceinline__ constexpr bool index_ok(long long, long long) { return true; }
+#define SPH_TU_STATUS(name)
+#endif
+
 // Up to four taps of one map coordinate: element offset inside a plane
-// (negative = outside, contributes zero) and interpolation weight.
+// (negative = outside, contributes zero) and interpolation weight; limit = elements of a plane.
 template <typename T> struct Taps {
   int off[4];
   T w[4];
+  int limit;
 };
 
 template <int INTERP> struct TapCount { static constexpr int value = (INTERP == SPH_NEAREST) ? 1 : 4; };
@@ -47,6 +75,7 @@ template <int INTERP> struct TapCount { static constexpr int value = (INTERP == 
 template <typename T, int INTERP>
 __device__ __forceinline__ void decode(T x, T y, int H, int W, Taps<T> &t) {
   const bool sane = (fabs((double)x) < 1e9) && (fabs((double)y) < 1e9);
+  t.limit = H * W;
   if (INTERP == SPH_NEAREST) {
     const int xi = RN<T>::round_away(x), yi = RN<T>::round_away(y);
     const bool ok = sane && xi >= 0 && xi <= W - 1 && yi >= 0 && yi <= H - 1;
@@ -89,7 +118,8 @@ __device__ __forceinline__ void decode(T x, T y, int H, int W, Taps<T> &t) {
 template <typename T, int INTERP>
 __device__ __forceinline__ void gather_load(const T *__restrict__ plane, const Taps<T> &t, T (&v)[TapCount<INTERP>::value]) {
 #pragma unroll
-  for (int i = 0; i < TapCount<INTERP>::value; i++) v[i] = t.off[i] >= 0 ? __ldg(plane + t.off[i]) : T(0);
+  for (int i = 0; i < TapCount<INTERP>::value; i++)
+    v[i] = (t.off[i] >= 0 && index_ok(t.off[i], t.limit)) ? __ldg(plane + t.off[i]) : T(0);
 }
 template <typename T, int INTERP>
 __device__ __forceinline__ T gather_combine(const Taps<T> &t, const T (&v)[TapCount<INTERP>::value]) {
@@ -130,6 +160,7 @@ template <typename T> struct PlanView {
   const int *offsets;  // n_keys + 1
   const int *src;      // source position of each entry
   const T *w;          // weight of each entry
+  int n_src;           // source positions the plan was built over (entries' src are below it)
 };
 
 // First 256 bytes of a plan blob, written on the device by sph_plan_build.
@@ -140,6 +171,7 @@ struct PlanHeader {
   int n_keys, K, dtype, e_max;
   unsigned long long off_offsets, off_src, off_w;
   int max_seg;  // longest segment (entries of one key), written by the sort pass
+  int n_src;    // map positions the plan was built over
 };
 constexpr unsigned kPlanMagic = 0x53504c4eu;  // "SPLN"
 
@@ -175,13 +207,15 @@ inline bool plan_layout(int64_t n_src, int64_t K, int64_t P, int interp, int64_t
 }
 
 // Resolve the arrays of a plan on the device; `ok` is false when the blob was
-// not built for n_keys keys of type T (the caller then writes zeros).
+// not built for n_keys keys of type T, or (n_src >= 0) not over n_src map positions: the caller then writes zeros
+// instead of following entries that were made for tensors of another size.
 template <typename T>
-__device__ __forceinline__ PlanView<T> plan_view(const void *plan, int n_keys, bool &ok) {
+__device__ __forceinline__ PlanView<T> plan_view(const void *plan, int n_keys, bool &ok, int n_src = -1) {
   const PlanHeader *h = (const PlanHeader *)plan;
   const char *p = (const char *)plan;
-  ok = h->magic == kPlanMagic && h->n_keys == n_keys && h->dtype == (sizeof(T) == 8 ? SPH_F64 : SPH_F32);
-  return PlanView<T>{(const int *)(p + h->off_offsets), (const int *)(p + h->off_src), (const T *)(p + h->off_w)};
+  ok = h->magic == kPlanMagic && h->n_keys == n_keys && h->dtype == (sizeof(T) == 8 ? SPH_F64 : SPH_F32) &&
+       (n_src < 0 || h->n_src == n_src);
+  return PlanView<T>{(const int *)(p + h->off_offsets), (const int *)(p + h->off_src), (const T *)(p + h->off_w), h->n_src};
 }
 
 // Kernel launches issued by this library in this process (tracing aid, see sph_launch_count()).

@@ -38,7 +38,10 @@ __device__ __forceinline__ T col_value(const ColSrc<T> &s, const PlanView<T> &pv
     const int key = pix * s.K + k;
     const int e0 = __ldg(pv.offsets + key), e1 = __ldg(pv.offsets + key + 1);
     T acc = T(0);
-    for (int e = e0; e < e1; e++) acc += __ldg(pv.w + e) * __ldg(plane + __ldg(pv.src + e));
+    for (int e = e0; e < e1; e++) {
+      const int sp = __ldg(pv.src + e);
+      if (index_ok(sp, pv.n_src)) acc += __ldg(pv.w + e) * __ldg(plane + sp);
+    }
     return acc;
   } else {
     const int PP = WEIGHTED ? s.P : 1;
@@ -329,3 +332,5 @@ template int simt_dw<double>(const void *, const void *, const void *, const voi
                              void *, void *, size_t, cudaStream_t);
 
 }  // namespace sph
+
+SPH_TU_STATUS(conv_simt)

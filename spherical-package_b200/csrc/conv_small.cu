@@ -305,7 +305,9 @@ small_plan_gather_kernel(const T *__restrict__ tbuf, const void *__restrict__ pl
         const int e0 = e1;
         e1 = __ldg(pv.offsets + p * K + k + 1);
         for (int e = e0; e < e1; e++) {
-          const T *row = tb + (size_t)__ldg(pv.src + e) * Rp + k * Mq + m0;
+          const int sp = __ldg(pv.src + e);
+          if (!index_ok(sp, pv.n_src)) continue;
+          const T *row = tb + (size_t)sp * Rp + k * Mq + m0;
           const T w = __ldg(pv.w + e);
           SmallVec<T, VM> v[kGatherImages];
 #pragma unroll
@@ -588,3 +590,5 @@ SPH_INSTANTIATE_SMALL(float)
 SPH_INSTANTIATE_SMALL(double)
 
 }  // namespace sph
+
+SPH_TU_STATUS(conv_small)

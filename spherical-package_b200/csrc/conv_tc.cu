@@ -248,7 +248,10 @@ __device__ __forceinline__ void gather_pair(const char *__restrict__ imgc, const
 // Plan entries [e0, e1) that did not fit the tap table, straight from the plan.
 __device__ __forceinline__ void gather_plan_rest(Acc8 &acc, const char *__restrict__ imgc, const PlanView<float> &pv, int e0,
                                                  int e1, int pitch) {
-  for (int e = e0; e < e1; e++) acc_fma(acc, tap_weight(__ldg(pv.w + e)), ldg16(imgc + (size_t)__ldg(pv.src + e) * pitch));
+  for (int e = e0; e < e1; e++) {
+    const int sp = __ldg(pv.src + e);
+    if (index_ok(sp, pv.n_src)) acc_fma(acc, tap_weight(__ldg(pv.w + e)), ldg16(imgc + (size_t)sp * pitch));
+  }
 }
 
 constexpr int kPlanTaps = 4;  // plan entries per (pixel, slot) kept in the shared tap table; the rest is read from the plan
@@ -399,7 +402,9 @@ __device__ __forceinline__ void produce_chunk_pair(const Gather &g, const Tap *t
       const int2 rr = rest[row];
       for (int e = rr.x; e < rr.y; e++) {
         uint4 xa, xb;
-        ldg32(imgc + (size_t)__ldg(pv.src + e) * (g.Cp * 2), xa, xb);
+        const int sp = __ldg(pv.src + e);
+        if (!index_ok(sp, pv.n_src)) continue;
+        ldg32(imgc + (size_t)sp * (g.Cp * 2), xa, xb);
         const uint32_t we = tap_weight(__ldg(pv.w + e));
         acc_fma(a0, we, xa);
         acc_fma(a1, we, xb);
@@ -482,7 +487,9 @@ __device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem 
       const int2 rr = sm.rest[slot * kTileM + pl];
       for (int e = rr.x; e < rr.y; e++) {
         uint4 xa, xb;
-        ldg32(imgc + (size_t)__ldg(pv.src + e) * (g.Cp * 2), xa, xb);
+        const int sp = __ldg(pv.src + e);
+        if (!index_ok(sp, pv.n_src)) continue;
+        ldg32(imgc + (size_t)sp * (g.Cp * 2), xa, xb);
         const uint32_t we = tap_weight(__ldg(pv.w + e));
         acc_fma(a0, we, xa);
         acc_fma(a1, we, xb);
@@ -720,7 +727,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
 #pragma unroll
           for (int i = 0; i < kPlanTaps; i++) {
             const bool in = e0 + i < e1;
-            t[i].off = in ? __ldg(pv.src + e0 + i) * pitch : zero_off;
+            const int sp = in ? __ldg(pv.src + e0 + i) : 0;
+            t[i].off = (in && index_ok(sp, pv.n_src)) ? sp * pitch : zero_off;
             t[i].w = tap_weight(in ? __ldg(pv.w + e0 + i) : 0.0f);
           }
           static_assert(kPlanTaps == 4, "two 16-byte stores per entry");
@@ -1351,7 +1359,9 @@ plan_gather_rows_kernel(const __nv_bfloat16 *__restrict__ T, const void *__restr
         e1 = __ldg(pv.offsets + p * K + k + 1);
         for (int e = e0; e < e1; e++) {
           const float w = __ldg(pv.w + e);
-          const __nv_bfloat16 *row = tb + (size_t)__ldg(pv.src + e) * pitch + k * Mp + m0;
+          const int sp = __ldg(pv.src + e);
+          if (!index_ok(sp, pv.n_src)) continue;
+          const __nv_bfloat16 *row = tb + (size_t)sp * pitch + k * Mp + m0;
 #pragma unroll
           for (int v = 0; v < 8; v++) {
             if (m0 + v * 8 < Mp) {
@@ -1782,14 +1792,46 @@ __global__ void __launch_bounds__(128) bounded_wait_check_kernel(unsigned long l
 }  // namespace
 }  // namespace sph
 
+SPH_TU_STATUS(conv_tc)
+#ifdef SPH_BOUNDS_CHECK
+extern "C" {
+int sph_tu_status_resample(int);
+int sph_tu_status_plan(int);
+int sph_tu_status_pool(int);
+int sph_tu_status_conv_simt(int);
+int sph_tu_status_conv_small(int);
+}
+#endif
+
 extern "C" int sph_device_status(int *status, int reset) {
   if (!status) return SPH_ERR_INVALID_ARGUMENT;
-  if (cudaMemcpyFromSymbol(status, sph::g_wait_status, sizeof(int)) != cudaSuccess) return SPH_ERR_CUDA;
-  if (reset) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, sph::g_wait_status, sizeof(int)) != cudaSuccess) return SPH_ERR_CUDA;
+  if (reset && v) {
     const int zero = 0;
     if (cudaMemcpyToSymbol(sph::g_wait_status, &zero, sizeof(int)) != cudaSuccess) return SPH_ERR_CUDA;
   }
+  v = v ? 1 : 0;
+#ifdef SPH_BOUNDS_CHECK
+  // checked build: bit 1 = some kernel met an index outside its range (and skipped the access)
+  int (*const parts[])(int) = {sph_tu_status_resample, sph_tu_status_plan, sph_tu_status_pool, sph_tu_status_conv_simt,
+                               sph_tu_status_conv_small, sph_tu_status_conv_tc};
+  for (auto f : parts) {
+    const int r = f(reset);
+    if (r < 0) return SPH_ERR_CUDA;
+    if (r) v |= 2;
+  }
+#endif
+  *status = v;
   return SPH_OK;
+}
+
+extern "C" int sph_build_is_checked(void) {
+#ifdef SPH_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
 }
 
 extern "C" int sph_debug_bounded_wait(unsigned long long limit_ns, int *status, void *stream) {

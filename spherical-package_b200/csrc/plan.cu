@@ -35,16 +35,22 @@ __global__ void plan_count_kernel(const T *map, const T *iw, int n_slots, int K,
                                   int NT, int *cnt) {
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= n_slots) return;
-  for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, quad, NT, [&](int key, int, T) { atomicAdd(cnt + key, 1); });
+  const int n_keys = NT * H * W * K;
+  for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, quad, NT, [&](int key, int, T) {
+    if (index_ok(key, n_keys)) atomicAdd(cnt + key, 1);
+  });
 }
 
 template <typename T, int INTERP, bool WEIGHTED>
 __global__ void plan_fill_kernel(const T *map, const T *iw, int n_slots, int K, int PP, int H, int W, const int64_t *quad,
-                                 int NT, const int *offsets, int *cursor, int *ids, T *w) {
+                                 int NT, const int *offsets, int *cursor, int *ids, T *w, int e_max) {
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= n_slots) return;
+  const int n_keys = NT * H * W * K;
   for_each_tap<T, INTERP, WEIGHTED>(map, iw, s, K, PP, H, W, quad, NT, [&](int key, int id, T wt) {
+    if (!index_ok(key, n_keys)) return;
     const int pos = offsets[key] + atomicAdd(cursor + key, 1);
+    if (!index_ok(pos, e_max)) return;
     ids[pos] = id;
     w[pos] = wt;
   });
@@ -175,9 +181,9 @@ static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int6
   if (cudaMemsetAsync(cursor, 0, sizeof(int) * (size_t)nk, st) != cudaSuccess) return SPH_ERR_CUDA;
   SPH_DISPATCH_INTERP(interp, {
     if (P > 0)
-      plan_fill_kernel<T, INTERP, true><<<gb, 256, 0, st>>>((const T *)map, (const T *)iw, n_slots, (int)K, PP, (int)H, (int)W, quad, NT, offsets, cursor, src, w);
+      plan_fill_kernel<T, INTERP, true><<<gb, 256, 0, st>>>((const T *)map, (const T *)iw, n_slots, (int)K, PP, (int)H, (int)W, quad, NT, offsets, cursor, src, w, (int)L.e_max);
     else
-      plan_fill_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, quad, NT, offsets, cursor, src, w);
+      plan_fill_kernel<T, INTERP, false><<<gb, 256, 0, st>>>((const T *)map, nullptr, n_slots, (int)K, PP, (int)H, (int)W, quad, NT, offsets, cursor, src, w, (int)L.e_max);
   });
   PlanHeader h;
   h.magic = kPlanMagic;
@@ -189,6 +195,7 @@ static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int6
   h.off_src = L.off_src;
   h.off_w = L.off_w;
   h.max_seg = 1;
+  h.n_src = (int)n_src;  // map positions (each with K slots)
   plan_header_kernel<<<1, 1, 0, st>>>((PlanHeader *)plan, h);
   plan_sort_kernel<T><<<cdiv(nk, 256), 256, 0, st>>>(offsets, src, w, nk, (int)(4 * PP * K), &((PlanHeader *)plan)->max_seg);
   return launch_status(7);
@@ -197,6 +204,8 @@ static int build(const void *map, const void *iw, int64_t n_src, int64_t K, int6
 }  // namespace sph
 
 using namespace sph;
+
+SPH_TU_STATUS(plan)
 
 extern "C" size_t sph_plan_bytes(int64_t n_src, int64_t K, int64_t P, int interp, int64_t dstH, int64_t dstW,
                                  int dtype) {

@@ -74,8 +74,9 @@ __device__ __forceinline__ void plan_walk(const PlanView<T> &plan, bool ok, int 
       for (int u = 0; u < kWalkUnroll; u++) {
         if (u < nu) {
           const int e = t + u * 32 + lane;
-          const bool valid = e < b;
+          bool valid = e < b;
           const int s = valid ? __ldg(plan.src + e) : 0;
+          valid = valid && index_ok(s, plan.n_src);
           const T w = valid ? __ldg(plan.w + e) : T(0);
           const auto pre = prepare(s);
 #pragma unroll

@@ -175,7 +175,7 @@ max_unpool_plan_kernel(const T *__restrict__ g, const int64_t *__restrict__ idx,
     __syncthreads();
   }
   bool ok;
-  const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok);
+  const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok, n * K);
   const int q_begin = blockIdx.x * chunk, q_end = min(q_begin + chunk, n_dst);
   const T *gp = g + (size_t)p0 * n;
   const int64_t *ip = idx + (size_t)p0 * n;
@@ -290,6 +290,8 @@ static int check(const void *a, const void *b, const void *c, const void *d, con
 }  // namespace sph
 
 using namespace sph;
+
+SPH_TU_STATUS(pool)
 
 extern "C" int sph_mapped_max_pool(const void *x, const void *map, const void *iw, void *out, int64_t *idx, int64_t B,
                                    int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,

@@ -82,7 +82,7 @@ resample_to_map_kernel(const T *__restrict__ x, const void *__restrict__ plan_bl
                        int n_src, int planes, int chunk, SrcValue<T, DIV> sv) {
   extern __shared__ unsigned char walk_smem[];
   bool ok;
-  const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok);
+  const PlanView<T> plan = plan_view<T>(plan_blob, n_dst, ok, DIV ? n_src * sv.div : n_src);
   const int p0 = blockIdx.y * PL;
   const int np = min(PL, planes - p0);
   const T *xp = x + (size_t)p0 * n_src;
@@ -167,7 +167,7 @@ voting_resample_kernel(const int64_t *__restrict__ x, const void *__restrict__ p
   const int o = blockIdx.x * blockDim.x + threadIdx.x, p = blockIdx.y;
   if (o >= n_dst) return;
   const PlanHeader *h = (const PlanHeader *)plan_blob;
-  const bool ok = h->magic == kPlanMagic && h->n_keys == n_dst && h->dtype == dtype;
+  const bool ok = h->magic == kPlanMagic && h->n_keys == n_dst && h->dtype == dtype && h->n_src == n_src;
   const int *offsets = (const int *)((const char *)plan_blob + h->off_offsets);
   const int *src = (const int *)((const char *)plan_blob + h->off_src);
   const int64_t *xp = x + (size_t)p * n_src;
@@ -195,6 +195,8 @@ voting_resample_kernel(const int64_t *__restrict__ x, const void *__restrict__ p
 }  // namespace sph
 
 using namespace sph;
+
+SPH_TU_STATUS(resample)
 
 extern "C" int sph_resample_from_map(const void *x, const void *map, const void *iw, void *y, int64_t B, int64_t C,
                                      int64_t H, int64_t W, int64_t MH, int64_t MW, int64_t P, int dtype, int interp,

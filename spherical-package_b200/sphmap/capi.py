@@ -11,7 +11,9 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "_spherical_distortion_ext", "libsphmap.so")
+# SPHMAP_LIBRARY=checked loads the bounds-checked build of the same ABI (libsphmap_checked.so, build.py --checked)
+_LIB_NAME = "libsphmap_checked.so" if os.environ.get("SPHMAP_LIBRARY", "") == "checked" else "libsphmap.so"
+LIB_PATH = os.path.join(os.path.dirname(_HERE), "_spherical_distortion_ext", _LIB_NAME)
 
 F32, F64 = 0, 1
 NEAREST, BILINEAR, BISPHERICAL = 0, 1, 2
@@ -27,7 +29,7 @@ SYMBOLS = [
     "sph_mapped_conv_relu_forward", "sph_mapped_conv_relu_backward_input", "sph_mapped_conv_relu_backward_weight",
     "sph_device_status", "sph_debug_bounded_wait", "sph_mapped_max_unpool_planned", "sph_mapped_avg_pool",
     "sph_mapped_avg_unpool", "sph_resample_to_map_normalized", "sph_resample_from_uv_maps", "sph_plan_build_uv",
-    "sph_voting_resample_to_map", "sph_build_kernel_map",
+    "sph_voting_resample_to_map", "sph_build_kernel_map", "sph_build_is_checked",
 ]
 ERR_UNSUPPORTED = 2
 
