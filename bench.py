@@ -174,7 +174,7 @@ def run_encoder(args, rank, local, world):
     flops_step = 3 * wl.encoder_flops(B, args.height, 2 * args.height)
 
     # --- device-resident arm: straight through the C ABI, every conv launch bracketed by CUDA events ---
-    phases = [(li, ph) for li in range(4) for ph in ("fwd", "dw", "dx")]
+    phases = [(li, ph) for li in range(4) for ph in ("fwd", "dw", "dx", "bwd")]   # "bwd": dInput + dW in one combined call
 
     def new_timers():
         return {k: [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)] for k in phases}
@@ -197,7 +197,8 @@ def run_encoder(args, rank, local, world):
     sampler = ClockSampler(local) if rank == 0 else None
     ms, clocks = timed_loop(step_timed, args.steps, 0, world, dev, sampler)
     # per-launch durations of the timed region itself (events were recorded on the launching stream)
-    per_launch = {k: sum(t[k][0].elapsed_time(t[k][1]) for t in per_step_timers) / len(per_step_timers) for k in phases}
+    ran = sorted(stack.timed_keys)
+    per_launch = {k: sum(t[k][0].elapsed_time(t[k][1]) for t in per_step_timers) / len(per_step_timers) for k in ran}
     value = flops_step * args.steps / (ms * 1e-3) / 1e12
 
     # --- end-to-end arm: public nn.Module API, pinned host input copied in and loss read back per step ---
@@ -282,17 +283,17 @@ def run_encoder(args, rank, local, world):
         ci = cfg["layers"][li][0]
         if ci * 9 <= 32:
             return "small_%s (SIMT, thin contraction)" % ph
-        return "tc_dw_kernel" if ph == "dw" else "tc_gemm_kernel"
+        return {"dw": "tc_dw_kernel", "bwd": "tc_gemm_kernel + tc_dw_kernel (combined backward call)"}.get(ph, "tc_gemm_kernel")
 
-    def launch_flops(li):
+    def launch_flops(li, ph):
         ci, co, _, (oh, ow), _ = cfg["layers"][li]
-        return 2 * (hi - lo) * co * ci * 9 * oh * ow
+        return (2 if ph == "bwd" else 1) * 2 * (hi - lo) * co * ci * 9 * oh * ow
 
     groups = {}
     for (li, ph), t in per_launch.items():
         gk = groups.setdefault(kernel_of(li, ph), [0.0, 0.0, 0])
         gk[0] += t
-        gk[1] += launch_flops(li)
+        gk[1] += launch_flops(li, ph)
         gk[2] += 1
     dom_kernel = max(groups, key=lambda k: groups[k][0])
     dom_ms, dom_flops_total, dom_n = groups[dom_kernel]

@@ -285,7 +285,8 @@ enum sph_conv_op {
   SPH_CONV_BACKWARD_WEIGHT = 2,
   SPH_TCONV_FORWARD = 3,
   SPH_TCONV_BACKWARD_INPUT = 4,
-  SPH_TCONV_BACKWARD_WEIGHT = 5
+  SPH_TCONV_BACKWARD_WEIGHT = 5,
+  SPH_CONV_BACKWARD = 6 /* sph_mapped_conv_backward_cl: input, weight and bias gradients in one call */
 };
 size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
                                 int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
@@ -330,6 +331,46 @@ int sph_mapped_conv_relu_backward_weight(const void *gout, const void *act_out, 
                                          int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
                                          int dtype, int interp, int precision, void *ws, size_t ws_bytes,
                                          void *stream);
+
+/* ------------------------------------------------------------------------
+ * Channels-last companions and the combined backward (bf16 tensor-core path;
+ * no counterpart in the reference).  The tensor-core kernels gather from a
+ * bf16 copy of the gathered tensor laid out (B, H*W + 1, Cp): channels last,
+ * Cp = C padded to a multiple of 8 that divides 64 or to a multiple of 64,
+ * one extra all-zero pixel behind every image.  The plain entry points make
+ * that copy in their workspace on every call.  A caller that runs a stack of
+ * layers can keep the copies ("companions") next to its float32 activations:
+ *   sph_conv_companion_bytes  size of the companion of a (B,C,H,W) tensor.
+ *       The owner zero-fills it once (cudaMemsetAsync); the kernels only ever
+ *       write real channels of real pixels.
+ *   sph_mapped_conv_forward_cl  the forward operator (with the fused ReLU if
+ *       relu != 0).  x_cl: companion of x, or NULL (then converted as usual).
+ *       out_cl: if not NULL the kernel epilogue also writes the output as a
+ *       companion, for the next layer.  Returns SPH_ERR_UNSUPPORTED, before
+ *       launching anything, when out_cl cannot be honoured (float64, Cout not
+ *       a multiple of 8, shapes that run on the generic SIMT kernels): call
+ *       again with out_cl = NULL.
+ *   sph_mapped_conv_backward_cl  input, weight and bias gradients in one
+ *       call, as the reference's mapped_conv_backward computes them
+ *       (ext_modules/include/layers/mapped_convolution_layer.h:89-134):
+ *       grad_output is read once and converted for both consumers; act_out
+ *       (or NULL) is the fused ReLU's output whose sign masks it; x_cl (or
+ *       NULL) the companion of x.  Workspace: op SPH_CONV_BACKWARD.  Returns
+ *       SPH_ERR_UNSUPPORTED before launching anything for shapes that do not
+ *       run on the two tensor-core kernels (exact precision, thin layers):
+ *       use the separate entry points there.
+ * Results are bit-identical to the separate entry points.
+ * ---------------------------------------------------------------------- */
+size_t sph_conv_companion_bytes(int64_t B, int64_t C, int64_t H, int64_t W);
+int sph_mapped_conv_forward_cl(const void *x, const void *x_cl, const void *map, const void *iw, const void *weight,
+                               const void *bias, void *out, void *out_cl, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
+                               int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                               int precision, int relu, void *ws, size_t ws_bytes, void *stream);
+int sph_mapped_conv_backward_cl(const void *gout, const void *act_out, const void *x, const void *x_cl, const void *plan,
+                                const void *map, const void *iw, const void *weight, void *gx, void *gw, void *gb,
+                                int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
+                                int64_t K, int64_t P, int dtype, int interp, int precision, void *ws, size_t ws_bytes,
+                                void *stream);
 
 /* ------------------------------------------------------------------------
  * Mapped transposed convolution.  weight (Cin,Cout,K), bias (Cout),

@@ -61,8 +61,11 @@ extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64
     case SPH_TCONV_FORWARD: if (small_ok(Cout, K, Cin, ts)) return small_premul_workspace(B, Cout, K, IH * IW, ts); break;
     case SPH_TCONV_BACKWARD_INPUT: if (small_ok(Cout, K, Cin, ts)) return 0; break;
     case SPH_TCONV_BACKWARD_WEIGHT: if (small_ok(Cout, K, Cin, ts)) return small_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, ts); break;
+    case SPH_CONV_BACKWARD: if (small_ok(Cin, K, Cout, ts)) return 0; break;  // thin layers: use the separate entry points
     default: break;
   }
+  if (op == SPH_CONV_BACKWARD)
+    return precision == SPH_PRECISION_BF16 ? tc_conv_backward_workspace(B, Cin, Cout, IH, IW, OH, OW, K, P, interp) : 0;
   if (precision == SPH_PRECISION_BF16) return tc_workspace_bytes(op, B, Cin, Cout, IH, IW, OH, OW, K, P, interp);
   switch (op) {
     case SPH_CONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts);
@@ -86,10 +89,10 @@ int conv_forward(const void *x, const void *map, const void *iw, const void *wei
   cudaStream_t st = (cudaStream_t)stream;
   if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
     return SPH_BY_DTYPE(small_fwd, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, st,
-                        fz.relu_out);
+                        fz.relu_out, fz.out_cl);
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
-  if (fz.active()) return SPH_ERR_UNSUPPORTED;
+  if (fz.active() || fz.out_cl != nullptr) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_gemm, false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1,
                       bias, out, Cout, B, st);
 }
@@ -192,6 +195,43 @@ extern "C" int sph_mapped_conv_relu_backward_weight(const void *gout, const void
   if (!act_out) return SPH_ERR_INVALID_ARGUMENT;
   return conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws,
                               ws_bytes, stream, Fusion{false, act_out});
+}
+
+// ---- channels-last companions and the combined backward (no counterpart in the reference; see sphmap.h) ------
+extern "C" size_t sph_conv_companion_bytes(int64_t B, int64_t C, int64_t H, int64_t W) {
+  if (B < 0 || C <= 0 || H <= 0 || W <= 0 || H * W >= ((int64_t)1 << 31)) return 0;
+  return align_up((size_t)(B * (H * W + 1)) * (size_t)padded_channels(C) * 2, 256);
+}
+
+extern "C" int sph_mapped_conv_forward_cl(const void *x, const void *x_cl, const void *map, const void *iw, const void *weight,
+                                          const void *bias, void *out, void *out_cl, int64_t B, int64_t Cin, int64_t Cout,
+                                          int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
+                                          int interp, int precision, int relu, void *ws, size_t ws_bytes, void *stream) {
+  Fusion fz;
+  fz.relu_out = relu != 0;
+  fz.src_cl = x_cl;
+  fz.out_cl = out_cl;
+  if (x_cl != nullptr && (precision != SPH_PRECISION_BF16 || small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)))
+    fz.src_cl = nullptr;  // the kernels that run this shape gather from the float32 tensor
+  return conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws, ws_bytes,
+                      stream, fz);
+}
+
+extern "C" int sph_mapped_conv_backward_cl(const void *gout, const void *act_out, const void *x, const void *x_cl,
+                                           const void *plan, const void *map, const void *iw, const void *weight, void *gx,
+                                           void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                                           int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp, int precision,
+                                           void *ws, size_t ws_bytes, void *stream) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
+  const int rc = check_dims(d, dtype, interp, precision);
+  if (rc != SPH_OK) return rc;
+  if (!gout || !x || !plan || !map || !weight || !gx || !gw || !gb || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
+  if (precision != SPH_PRECISION_BF16 || B == 0 || small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)) return SPH_ERR_UNSUPPORTED;
+  Fusion fz;
+  fz.mask = act_out;
+  fz.src_cl = x_cl;
+  return tc_conv_backward(gout, x, plan, map, iw, weight, gx, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes,
+                          (cudaStream_t)stream, fz);
 }
 
 extern "C" int sph_mapped_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias,

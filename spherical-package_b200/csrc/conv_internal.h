@@ -11,9 +11,19 @@ namespace sph {
 // forward outputs at zero in the epilogue; mask (the saved activation output, same shape as grad_output) makes
 // every kernel that reads grad_output see grad_output * (mask > 0).  Code paths that cannot honour it return
 // SPH_ERR_UNSUPPORTED before launching anything.
+//
+// Channels-last copies: the tensor-core kernels gather from a bf16 copy of the source laid out (B, H*W + 1, Cp)
+// (Cp = channels padded as padded_channels() says; pixel H*W of every image and the padding channels are zero).  A
+// caller that keeps such copies next to its float32 activations passes them here and the conversion pre-passes
+// disappear: src_cl is the copy of the gathered tensor, out_cl (forward only) is where the epilogue also writes the
+// output in that layout (real channels and pixels only: the buffer is zero-filled once by its owner).
+// gt_ready (weight gradient): the gradient tile images and bias partial sums already sit in the workspace.
 struct Fusion {
   bool relu_out = false;
   const void *mask = nullptr;
+  const void *src_cl = nullptr;
+  void *out_cl = nullptr;
+  bool gt_ready = false;
   bool active() const { return relu_out || mask != nullptr; }
 };
 
@@ -42,7 +52,7 @@ size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_
 template <typename T>
 int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K, int64_t P,
               int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out,
-              int64_t M, int64_t B, cudaStream_t st, bool relu_out = false);
+              int64_t M, int64_t B, cudaStream_t st, bool relu_out = false, void *out_cl = nullptr);
 template <typename T>
 int small_adjoint(const void *src, const void *plan, int64_t CH, int64_t n_src, int64_t K, int64_t n_dst, const void *wgt,
                   int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out, int64_t M, int64_t B, void *ws,
@@ -64,6 +74,13 @@ int tc_conv_backward_input(const void *gout, const void *plan, const void *weigh
 int tc_conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb,
                             int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
                             int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz = Fusion{});
+// dInput + dW + dBias of one convolution with grad_output converted once (it feeds both): see conv_tc.cu.
+int tc_conv_backward(const void *gout, const void *x, const void *plan, const void *map, const void *iw, const void *weight,
+                     void *gx, void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
+                     int64_t OW, int64_t K, int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz);
+size_t tc_conv_backward_workspace(int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
+                                  int64_t K, int64_t P, int interp);
+int padded_channels(int64_t CH);
 int tc_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out, int64_t B,
                      int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
                      size_t ws_bytes, cudaStream_t st);

@@ -10,6 +10,8 @@
 //                      src/cpp/mapped_convolution_layer.cpp:69-86): T[b,(m,k),o] = sum_ch Wgt[m,ch,k] * Src[b,ch,o],
 //                      then Out[b,m,p] = sum_k sum_{e in plan(p,k)} w_e * T[b,(m,k),o_e]   (+ bias), m*K <= 32
 //   small_dw_kernel    dW[m,j] = sum_{b,pix} A[b,m,pix] * Col[b,j,pix], split over pixel ranges
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "conv_internal.h"
 
@@ -92,13 +94,20 @@ __device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
 
+__device__ __forceinline__ unsigned pack_bf16x2(float lo, float hi) {
+  unsigned r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
 constexpr int kTilePix = 256, kTileOut = 64;
 
 template <int INTERP, bool WEIGHTED>
 __global__ void __launch_bounds__(256, 2)
 small_fwd_tile_kernel(const float *__restrict__ src, const float *__restrict__ map, const float *__restrict__ iw,
                       const float *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk, const float *__restrict__ bias,
-                      float *__restrict__ out, int CH, int K, int P, int SH, int SW, int npix, int M, int relu) {
+                      float *__restrict__ out, int CH, int K, int P, int SH, int SW, int npix, int M, int relu,
+                      __nv_bfloat16 *__restrict__ out_cl, int cl_pitch) {
   __shared__ __align__(16) float Cs[kSmallJ][kTilePix];
   __shared__ __align__(16) float Ws[kSmallJ][kTileOut];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, b = blockIdx.y, J = CH * K;
@@ -201,6 +210,29 @@ small_fwd_tile_kernel(const float *__restrict__ src, const float *__restrict__ m
           for (int q = 0; q < 4; q++)
             if (px + q < npix) o[q] = v[4 * h + q];
         }
+      }
+    }
+    // channels-last bf16 copy of the same outputs: this warp's 8 channels of each of the thread's 8 pixels, 16 bytes
+    // per pixel (channels beyond M carry zero weights and bias, so they come out as the zeros the layout wants)
+    if (out_cl != nullptr && mw + 8 <= cl_pitch) {
+#pragma unroll
+      for (int t = 0; t < 8; t++) {
+        const int px = p0 + (t >> 2) * 128 + lane * 4 + (t & 3);
+        if (px >= npix) continue;
+        float c[8];
+#pragma unroll
+        for (int m = 0; m < 8; m++) {
+          float lo, hi;
+          unpack2(acc[m][t >> 1], lo, hi);
+          c[m] = (t & 1) ? hi : lo;
+          if (relu) c[m] = c[m] > 0.0f ? c[m] : 0.0f;
+        }
+        uint4 o;
+        o.x = pack_bf16x2(c[0], c[1]);
+        o.y = pack_bf16x2(c[2], c[3]);
+        o.z = pack_bf16x2(c[4], c[5]);
+        o.w = pack_bf16x2(c[6], c[7]);
+        *(uint4 *)(out_cl + ((size_t)b * (npix + 1) + px) * cl_pitch + mw) = o;
       }
     }
   }
@@ -480,14 +512,16 @@ size_t small_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_
 template <typename T>
 int small_fwd(const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K, int64_t P,
               int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc, int64_t sk, const void *bias, void *out,
-              int64_t M, int64_t B, cudaStream_t st, bool relu_out) {
+              int64_t M, int64_t B, cudaStream_t st, bool relu_out, void *out_cl) {
+  if (out_cl != nullptr && (sizeof(T) != 4 || M % 8 != 0)) return SPH_ERR_UNSUPPORTED;
   if constexpr (sizeof(T) == 4) {  // float32: tiled product
+    const int cl_pitch = out_cl ? padded_channels(M) : 0;
     const dim3 tgrid(cdiv(npix, kTilePix), (unsigned)B);
 #define SPH_FWD_TILE(W)                                                                                                \
   small_fwd_tile_kernel<INTERP, W><<<tgrid, 256, 0, st>>>((const float *)src, (const float *)map, (const float *)iw,     \
                                                           (const float *)wgt, sm, sc, sk, (const float *)bias,          \
                                                           (float *)out, (int)CH, (int)K, (int)P, (int)SH, (int)SW,       \
-                                                          (int)npix, (int)M, relu_out ? 1 : 0)
+                                                          (int)npix, (int)M, relu_out ? 1 : 0, (__nv_bfloat16 *)out_cl, cl_pitch)
     SPH_DISPATCH_INTERP(interp, {
       if (P > 0) SPH_FWD_TILE(true);
       else SPH_FWD_TILE(false);
@@ -580,7 +614,7 @@ int small_dw(const void *A, const void *src, const void *map, const void *iw, in
 #define SPH_INSTANTIATE_SMALL(T)                                                                                          \
   template int small_fwd<T>(const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, \
                             int, const void *, int64_t, int64_t, int64_t, const void *, void *, int64_t, int64_t,          \
-                            cudaStream_t, bool);                                                                           \
+                            cudaStream_t, bool, void *);                                                                           \
   template int small_adjoint<T>(const void *, const void *, int64_t, int64_t, int64_t, int64_t, const void *, int64_t,     \
                                 int64_t, int64_t, const void *, void *, int64_t, int64_t, void *, size_t, cudaStream_t);   \
   template int small_dw<T>(const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t,     \

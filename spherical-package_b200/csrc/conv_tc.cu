@@ -28,6 +28,15 @@
 #include "tc_common.cuh"
 
 namespace sph {
+
+// Channels of the channels-last bf16 copies: padded to a multiple of 8 that divides 64, or to a multiple of 64.
+int padded_channels(int64_t CH) {
+  int cp = (int)align_up((size_t)CH, 8);
+  if (cp > 64) return (int)align_up((size_t)CH, 64);
+  while (64 % cp) cp += 8;  // a 16-byte vector never straddles two slots and whole slots tile a chunk
+  return cp;
+}
+
 namespace {
 
 using namespace tc;
@@ -280,6 +289,8 @@ struct TcParams {
   int B, Nout, Npb, nblk, nchunks, tiles_x, tiles_y, stages;
   int use_out_map;          // outputs leave through the tensor map passed beside these parameters
   int relu;                 // clamp the outputs at zero (fused activation)
+  __nv_bfloat16 *out_cl;    // if set: the outputs are also written as a channels-last bf16 copy (B, GH*GW + 1, cl_pitch)
+  int cl_pitch;
 };
 
 struct Smem {
@@ -293,7 +304,8 @@ struct Smem {
 };
 
 constexpr int kOutStageCh = 16;
-constexpr int kOutStageBytes = kEpilogueWarps * kOutStageCh * 32 * 4;
+constexpr int kClStageBytes = kEpilogueWarps * 32 * kOutStageCh * 2;  // channels-last copy: [warp][2 rows][16 px][16 ch] bf16
+constexpr int kOutStageBytes = kEpilogueWarps * kOutStageCh * 32 * 4 + kClStageBytes;
 
 inline size_t gemm_smem_bytes(int stages, int Npb, int K, int nt, bool direct) {
   size_t s = 1024;  // alignment slack
@@ -513,7 +525,8 @@ __device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem 
 }
 
 template <int MODE, int NT>
-__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, const __grid_constant__ CUtensorMap out_map) {
+__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, const __grid_constant__ CUtensorMap out_map,
+                                                               const __grid_constant__ CUtensorMap cl_map) {
   extern __shared__ uint8_t smem_raw[];
   const Smem sm = carve(smem_raw, p, MODE == MODE_DIRECT);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -567,6 +580,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
         // clips whatever lies outside the image or beyond the last channel.
         const uint32_t st_s = smem_u32(sm.ostage) + warp * (kOutStageCh * 32 * 4);
         const uint32_t st_lane = st_s + lane * 4;
+        // channels-last copy: this lane's pixel is row lane >> 4, column lane & 15 of the warp's 2 x 16 pixels; its 16
+        // channels of a pass are 32 consecutive bytes of the [row][pixel][channel] staging block
+        const uint32_t cl_s = smem_u32(sm.ostage) + kEpilogueWarps * (kOutStageCh * 32 * 4) + warp * (32 * kOutStageCh * 2);
+        const uint32_t cl_lane = cl_s + lane * (kOutStageCh * 2);
         for (int n0 = 0; n0 < p.Npb; n0 += kOutStageCh) {
           uint32_t h[16];
           tmem_ld_32x16(taddr + n0, h);
@@ -579,16 +596,26 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
           tmem_ld_wait();
           if (lane == 0) bulk_wait_read();  // the previous pass has left the staging rows
           __syncwarp();
+          float ov[16];
 #pragma unroll
           for (int j = 0; j < 16; j++) {
             float o = __uint_as_float(h[j]) + bv[j];
             if (p.relu) o = fmaxf(o, 0.0f);
+            ov[j] = o;
             sts32(st_lane + j * 128, __float_as_uint(o));
+          }
+          if (p.out_cl != nullptr) {
+            // the same 16 channels as bf16 (columns beyond Nout are exact zeros); they leave through a second tensor map
+            // over the (B, rows, pixels, channels) view of the copy, which clips pixels outside the image and
+            // channels beyond the copy's pitch
+            sts128(cl_lane, make_uint4(pack_bf16(ov[0], ov[1]), pack_bf16(ov[2], ov[3]), pack_bf16(ov[4], ov[5]), pack_bf16(ov[6], ov[7])));
+            sts128(cl_lane + 16, make_uint4(pack_bf16(ov[8], ov[9]), pack_bf16(ov[10], ov[11]), pack_bf16(ov[12], ov[13]), pack_bf16(ov[14], ov[15])));
           }
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) {
             tensor_store_4d(&out_map, st_s, tx * kTW, ty * kTH + 2 * warp, nb * p.Npb + n0, b);
+            if (p.out_cl != nullptr) tensor_store_4d(&cl_map, cl_s, nb * p.Npb + n0, tx * kTW, ty * kTH + 2 * warp, b);
             bulk_commit();
           }
         }
@@ -621,14 +648,25 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
                                                 pack_bf16(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
                                                 pack_bf16(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
         } else if (pix >= 0) {
+          float ov[32];
 #pragma unroll
           for (int j = 0; j < 32; j++) {
             const int n = nb * p.Npb + n0 + j;
+            ov[j] = 0.0f;
             if (n < p.Nout && n0 + j < p.Npb) {
               float o = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + n) : 0.0f);
               if (p.relu) o = fmaxf(o, 0.0f);
+              ov[j] = o;
               orow[(size_t)n * npix] = o;
             }
+          }
+          if (p.out_cl != nullptr) {
+            __nv_bfloat16 *crow = p.out_cl + ((size_t)b * (npix + 1) + pix) * p.cl_pitch + nb * p.Npb + n0;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8)
+              if (n0 + j < p.Npb && nb * p.Npb + n0 + j + 8 <= p.cl_pitch)
+                *(uint4 *)(crow + j) = make_uint4(pack_bf16(ov[j], ov[j + 1]), pack_bf16(ov[j + 2], ov[j + 3]),
+                                                  pack_bf16(ov[j + 4], ov[j + 5]), pack_bf16(ov[j + 6], ov[j + 7]));
           }
         }
       }
@@ -1254,9 +1292,15 @@ __global__ void weight_image_kernel(const float *__restrict__ w, __nv_bfloat16 *
 // are a 4x16 block of the (GH, GW) grid; 16-byte vector v (8 pixels) of row r sits at position v ^ (r & 7).
 // With `row_part` the kernel also writes the sum of every row over the tile's pixels to
 // row_part[(b * tiles + tile) * mbs_total * 128 + row] (first stage of the bias gradient).
+// With `cl` the same (masked) values are also written as the channels-last bf16 copy (B, GH*GW + 1, cl_pitch) that the
+// input-gradient kernel gathers from, so the gradient is read from memory once for both of its consumers; the extra
+// zero pixel of every image is not written here.
+constexpr int kClStride = 128 + 8;  // bf16 per staged pixel row: 16-byte aligned rows, shifted banks
 __global__ void __launch_bounds__(256) grad_image_kernel(const float *__restrict__ gsrc, __nv_bfloat16 *__restrict__ gt, int N,
                                                           int GH, int GW, int tiles_x, int tiles_y, int mbs_total,
-                                                          float *__restrict__ row_part, const float *__restrict__ mask) {
+                                                          float *__restrict__ row_part, const float *__restrict__ mask,
+                                                          __nv_bfloat16 *__restrict__ cl, int cl_pitch) {
+  __shared__ __align__(16) __nv_bfloat16 cls[64 * kClStride];  // [pixel of the 4x16 tile][channel of this 128-row block]
   const int t2 = blockIdx.x, mb = blockIdx.y, b = blockIdx.z;
   const int ty = t2 / tiles_x, tx = t2 % tiles_x;
   const size_t npix = (size_t)GH * GW;
@@ -1292,12 +1336,26 @@ __global__ void __launch_bounds__(256) grad_image_kernel(const float *__restrict
     o.z = pack_bf16(f[4], f[5]);
     o.w = pack_bf16(f[6], f[7]);
     *(uint4 *)(dst + r * 64 + ((v ^ (r & 7)) << 3)) = o;
+    if (cl != nullptr) {
+#pragma unroll
+      for (int e = 0; e < 8; e++) cls[(v * 8 + e) * kClStride + r] = __float2bfloat16(f[e]);
+    }
     if (row_part) {
       float sum = ((f[0] + f[1]) + (f[2] + f[3])) + ((f[4] + f[5]) + (f[6] + f[7]));
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
       sum += __shfl_xor_sync(0xffffffffu, sum, 4);
       if (v == 0) row_part[(((size_t)b * tiles_x * tiles_y + t2) * mbs_total + mb) * 128 + r] = sum;
+    }
+  }
+  if (cl != nullptr) {
+    __syncthreads();
+    // pixel v * 8 + e of the tile is (row v >> 1, column (v & 1) * 8 + e); 16 threads write one pixel's 128 channels
+    for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+      const int pl = i >> 4, vec = i & 15, v = pl >> 3, e = pl & 7;
+      const int y = ty * kDwTH + (v >> 1), x = tx * kTW + (v & 1) * 8 + e, c = mb * 128 + vec * 8;
+      if (y < GH && x < GW && c + 8 <= cl_pitch)
+        *(uint4 *)(cl + ((size_t)b * (npix + 1) + (size_t)y * GW + x) * cl_pitch + c) = *(const uint4 *)(cls + pl * kClStride + vec * 8);
     }
   }
 }
@@ -1402,21 +1460,34 @@ __global__ void tc_dw_reduce_kernel(const float *__restrict__ partial, int split
 // =================================================================================================
 // host side
 // =================================================================================================
-int padded_channels(int64_t CH) {
-  int cp = (int)align_up((size_t)CH, 8);
-  if (cp > 64) return (int)align_up((size_t)CH, 64);
-  while (64 % cp) cp += 8;  // a 16-byte vector never straddles two slots and whole slots tile a chunk
-  return cp;
+
+constexpr int kMaxDevices = 64;
+
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
 }
 
+// SM count of the current device (one process may drive several devices).
 int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  static int n[kMaxDevices] = {0};
+  const int dev = current_device();
+  int v = __atomic_load_n(&n[dev], __ATOMIC_RELAXED);
+  if (v == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    __atomic_store_n(&n[dev], v, __ATOMIC_RELAXED);
   }
-  return n;
+  return v;
+}
+
+// Opt a kernel in to `smem` bytes of dynamic shared memory, once per device and kernel (the largest request so far).
+template <typename Kernel>
+void ensure_dynamic_smem(Kernel kernel, int *granted /* [kMaxDevices], zero-initialised, one array per kernel */, size_t smem) {
+  const int dev = current_device();
+  if (__atomic_load_n(&granted[dev], __ATOMIC_RELAXED) >= (int)smem) return;
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  __atomic_store_n(&granted[dev], (int)smem, __ATOMIC_RELAXED);
 }
 
 struct Geometry {
@@ -1468,6 +1539,33 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// The last few encoded maps are kept (a training loop stores to the same activation buffers every step).
+struct OutMapSlot {
+  float *out;
+  int64_t B, Nout, GH, GW;
+  CUtensorMap map;
+};
+constexpr int kOutMapSlots = 16;
+thread_local OutMapSlot g_out_maps[kOutMapSlots];
+thread_local int g_out_map_next = 0;
+
+bool make_out_map(CUtensorMap *m, float *out, int64_t B, int64_t Nout, int64_t GH, int64_t GW);
+
+bool cached_out_map(CUtensorMap *m, float *out, int64_t B, int64_t Nout, int64_t GH, int64_t GW) {
+  for (int i = 0; i < kOutMapSlots; i++) {
+    const OutMapSlot &s = g_out_maps[i];
+    if (s.out == out && out != nullptr && s.B == B && s.Nout == Nout && s.GH == GH && s.GW == GW) {
+      *m = s.map;
+      return true;
+    }
+  }
+  if (!make_out_map(m, out, B, Nout, GH, GW)) return false;
+  OutMapSlot &s = g_out_maps[g_out_map_next];
+  g_out_map_next = (g_out_map_next + 1) % kOutMapSlots;
+  s.out = out; s.B = B; s.Nout = Nout; s.GH = GH; s.GW = GW; s.map = *m;
+  return true;
+}
+
 bool make_out_map(CUtensorMap *m, float *out, int64_t B, int64_t Nout, int64_t GH, int64_t GW) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn || out == nullptr || (GW & 3) != 0 || ((uintptr_t)out & 15) != 0) return false;
@@ -1478,13 +1576,29 @@ bool make_out_map(CUtensorMap *m, float *out, int64_t B, int64_t Nout, int64_t G
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor map of a channels-last bf16 copy (B, GH*GW + 1, pitch) seen as (B, GH, GW, pitch) with the image stride of
+// GH*GW + 1 pixels; box = 16 channels x 16 pixels x 2 rows.
+bool make_cl_map(CUtensorMap *m, __nv_bfloat16 *cl, int64_t B, int64_t pitch, int64_t GH, int64_t GW) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || cl == nullptr || (pitch & 7) != 0 || ((uintptr_t)cl & 15) != 0) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)pitch, (cuuint64_t)GW, (cuuint64_t)GH, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)pitch * 2, (cuuint64_t)GW * pitch * 2, (cuuint64_t)(GH * GW + 1) * pitch * 2};
+  const cuuint32_t box[4] = {(cuuint32_t)kOutStageCh, (cuuint32_t)kTW, 2, 1}, estr[4] = {1, 1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, cl, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int MODE, int NT>
 void launch_gemm(TcParams p, int grid, size_t smem, cudaStream_t st) {
-  CUtensorMap out_map;
+  CUtensorMap out_map, cl_map;
   memset(&out_map, 0, sizeof(out_map));
-  p.use_out_map = (p.out_h == nullptr && make_out_map(&out_map, p.out, p.B, p.Nout, p.g.GH, p.g.GW)) ? 1 : 0;
-  cudaFuncSetAttribute(tc_gemm_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  tc_gemm_kernel<MODE, NT><<<grid, kThreads, smem, st>>>(p, out_map);
+  memset(&cl_map, 0, sizeof(cl_map));
+  p.use_out_map = (p.out_h == nullptr && cached_out_map(&out_map, p.out, p.B, p.Nout, p.g.GH, p.g.GW)) ? 1 : 0;
+  // the copy leaves through its own tensor map when the float32 output does; otherwise with plain stores
+  if (p.use_out_map && p.out_cl != nullptr && !make_cl_map(&cl_map, p.out_cl, p.B, p.cl_pitch, p.g.GH, p.g.GW)) p.use_out_map = 0;
+  static int granted[kMaxDevices];
+  ensure_dynamic_smem(tc_gemm_kernel<MODE, NT>, granted, smem);
+  tc_gemm_kernel<MODE, NT><<<grid, kThreads, smem, st>>>(p, out_map, cl_map);
 }
 
 // ---- multiply-first adjoint -------------------------------------------------------------------------
@@ -1520,12 +1634,14 @@ int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
   __nv_bfloat16 *T = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes + g.wp_bytes);
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
-  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, fz.mask);  // adjoint: src is grad_output
+  if (fz.src_cl != nullptr) xh = (__nv_bfloat16 *)fz.src_cl;  // already converted (and masked) by the caller
+  else to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, fz.mask);   // adjoint: src is grad_output
   const int64_t wtotal = (int64_t)g.nblk * g.nchunks * g.Npb * kChunk;
   premul_weight_image_kernel<<<cdiv(wtotal, 256), 256, 0, st>>>((const float *)wgt, wp, (int)M, q.Mp, (int)K, (int)CH, g.Npb, g.nblk,
                                                                 g.nchunks, sm_, sc, sk);
   TcParams p{};
   p.g = Gather{xh, nullptr, nullptr, nullptr, g.Cp, (int)SH, (int)SW, 1, 0, (int)SH, (int)SW, SPH_NEAREST, 1};
+  p.out_cl = nullptr; p.cl_pitch = 0;
   p.wp = wp; p.bias = nullptr; p.out = nullptr; p.out_h = T; p.out_pitch = (int)(K * q.Mp); p.status = status;
   p.B = (int)B; p.Nout = (int)(K * q.Mp); p.Npb = g.Npb; p.nblk = g.nblk; p.nchunks = g.nchunks;
   p.tiles_x = cdiv(SW, kTW); p.tiles_y = cdiv(SH, kTH); p.stages = g.stages;
@@ -1546,7 +1662,8 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
     if (q.use) return tc_adjoint_premul(q, src, plan, CH, SH, SW, K, GH, GW, wgt, sn, sc, sk, bias, out, Nout, B, ws, ws_bytes, st, fz);
   }
   const Geometry g = geometry(B, CH, SH * SW, K, P, interp, Nout, !use_plan);
-  if (!g.ok && fz.active()) return SPH_ERR_UNSUPPORTED;
+  if (!g.ok && (fz.active() || fz.out_cl != nullptr)) return SPH_ERR_UNSUPPORTED;
+  if (fz.out_cl != nullptr && (use_plan || Nout % 8 != 0)) return SPH_ERR_UNSUPPORTED;
   if (!g.ok)  // shapes the tile kernel does not cover run on the exact SIMT kernels instead
     return simt_gemm<float>(use_plan, src, map, iw, plan, CH, SH, SW, K, P, GH * GW, interp, wgt, sn, sc, sk, bias, out, Nout, B, st);
   if (!ws || ws_bytes < 256 + g.xh_bytes + g.wp_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
@@ -1555,7 +1672,8 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
   __nv_bfloat16 *xh = (__nv_bfloat16 *)((char *)ws + 256);
   __nv_bfloat16 *wp = (__nv_bfloat16 *)((char *)ws + 256 + g.xh_bytes);
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
-  to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, use_plan ? fz.mask : nullptr);
+  if (fz.src_cl != nullptr) xh = (__nv_bfloat16 *)fz.src_cl;  // the caller keeps a channels-last copy of src
+  else to_nhwc(src, xh, B, CH, g.Cp, SH * SW, st, use_plan ? fz.mask : nullptr);
   const int64_t wtotal = (int64_t)g.nblk * g.nchunks * g.Npb * kChunk;
   weight_image_kernel<<<cdiv(wtotal, 256), 256, 0, st>>>((const float *)wgt, wp, (int)Nout, (int)CH, g.Cp, (int)K, g.Npb, g.nblk,
                                                          g.nchunks, sn, sc, sk);
@@ -1563,6 +1681,8 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
   p.g = Gather{xh, (const float *)map, (const float *)iw, plan, g.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, g.nt};
   p.wp = wp; p.bias = (const float *)bias; p.out = (float *)out; p.status = status;
   p.relu = (!use_plan && fz.relu_out) ? 1 : 0;
+  p.out_cl = (__nv_bfloat16 *)fz.out_cl;
+  p.cl_pitch = fz.out_cl ? padded_channels(Nout) : 0;
   p.B = (int)B; p.Nout = (int)Nout; p.Npb = g.Npb; p.nblk = g.nblk; p.nchunks = g.nchunks;
   p.tiles_x = cdiv(GW, kTW); p.tiles_y = cdiv(GH, kTH); p.stages = g.stages;
   const int64_t tiles = (int64_t)B * p.tiles_x * p.tiles_y * g.nblk;
@@ -1571,7 +1691,7 @@ int tc_gemm(bool use_plan, const void *src, const void *map, const void *iw, con
   else if (g.nt == 4) launch_gemm<MODE_DIRECT, 4>(p, grid, g.smem, st);
   else if (g.nt == 1) launch_gemm<MODE_DIRECT, 1>(p, grid, g.smem, st);
   else launch_gemm<MODE_DIRECT, 0>(p, grid, g.smem, st);
-  return launch_status(3);
+  return launch_status(fz.src_cl ? 2 : 3);
 }
 
 // n_dst > 0: plan mode with that many destination pixels (may select the multiply-first adjoint)
@@ -1629,7 +1749,8 @@ DwGeometry dw_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P,
 
 template <int NT, int GRP, bool WT>
 void launch_dw_g(const DwParams &p, dim3 grid, size_t smem, cudaStream_t st) {
-  cudaFuncSetAttribute(tc_dw_kernel<NT, GRP, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static int granted[kMaxDevices];
+  ensure_dynamic_smem(tc_dw_kernel<NT, GRP, WT>, granted, smem);
   tc_dw_kernel<NT, GRP, WT><<<grid, kThreads, smem, st>>>(p);
 }
 template <int NT>
@@ -1659,16 +1780,18 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
   float *partial = (float *)(w8 + 256 + d.xh_bytes + d.gt_bytes);
   void *bias_ws = w8 + 256 + d.xh_bytes + d.gt_bytes + d.partial_bytes;
   if (cudaMemsetAsync(status, 0, 4, st) != cudaSuccess) return SPH_ERR_CUDA;
-  to_nhwc(src, xh, B, CH, d.Cp, SH * SW, st);
+  if (fz.src_cl != nullptr) xh = (__nv_bfloat16 *)fz.src_cl;  // the caller keeps a channels-last copy of src
+  else to_nhwc(src, xh, B, CH, d.Cp, SH * SW, st);
   // When the operand being imaged is also the tensor whose channel sums give the bias gradient (conv dW:
   // both are grad_output), the sums ride along with the imaging pass instead of re-reading the tensor.
   const bool fuse_bias = gbias_src == A && Cbias == Nout && nbias == GH * GW;
   const int64_t nblocks = B * d.tiles_x * d.tiles_y;
   float *row_part = (float *)((char *)bias_ws + simt_bias_workspace(Cbias, 4));
   float *part2 = (float *)((char *)row_part + align_up((size_t)nblocks * d.mbs_total * 128 * 4, 256));
-  grad_image_kernel<<<dim3(d.tiles_x * d.tiles_y, d.mbs_total, (unsigned)B), 256, 0, st>>>(
-      (const float *)A, gt, (int)Nout, (int)GH, (int)GW, d.tiles_x, d.tiles_y, d.mbs_total, fuse_bias ? row_part : nullptr,
-      (const float *)fz.mask);
+  if (!fz.gt_ready)  // (else the caller's combined pre-pass has filled gt and row_part already)
+    grad_image_kernel<<<dim3(d.tiles_x * d.tiles_y, d.mbs_total, (unsigned)B), 256, 0, st>>>(
+        (const float *)A, gt, (int)Nout, (int)GH, (int)GW, d.tiles_x, d.tiles_y, d.mbs_total, fuse_bias ? row_part : nullptr,
+        (const float *)fz.mask, nullptr, 0);
   DwParams p{};
   p.g = Gather{xh, (const float *)map, (const float *)iw, nullptr, d.Cp, (int)SH, (int)SW, (int)K, (int)P, (int)GH, (int)GW, interp, d.nt};
   p.gt = gt; p.partial = partial; p.status = status;
@@ -1731,6 +1854,57 @@ int tc_conv_backward_weight(const void *gout, const void *x, const void *map, co
                             int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz) {
   return tc_dw(gout, x, map, iw, Cin, IH, IW, K, P, OH, OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout, OH * OW, gb, ws,
                ws_bytes, st, fz);
+}
+
+// Combined backward of one convolution.  grad_output feeds two kernels in two layouts - channels-last bf16 for the
+// input-gradient gather, 128-row tile images for the weight-gradient MMA - and, with a fused ReLU, has to be masked
+// for both.  One pre-pass reads it (and the mask) once and writes both, where the separate entry points read it
+// twice; the reference likewise computes all three gradients in one call
+// (ext_modules/include/layers/mapped_convolution_layer.h:89-134).  Workspace: the input-gradient part first, then
+// the weight-gradient part, each laid out as its own operator expects.
+size_t tc_conv_backward_workspace(int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
+                                  int64_t K, int64_t P, int interp) {
+  const size_t a = gemm_ws(B, Cout, OH * OW, K, 0, 0, Cin, false, IH * IW);
+  const DwGeometry d = dw_geometry(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
+  if (a == 0 || !d.ok) return 0;
+  return align_up(a, 256) + dw_ws(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
+}
+
+int tc_conv_backward(const void *gout, const void *x, const void *plan, const void *map, const void *iw, const void *weight,
+                     void *gx, void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
+                     int64_t OW, int64_t K, int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz) {
+  const size_t dx_bytes = gemm_ws(B, Cout, OH * OW, K, 0, 0, Cin, false, IH * IW);
+  const DwGeometry d = dw_geometry(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
+  if (dx_bytes == 0 || !d.ok) return SPH_ERR_UNSUPPORTED;  // one of the two runs on other kernels: use the separate entry points
+  const size_t dw_bytes = dw_ws(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
+  if (!ws || ws_bytes < align_up(dx_bytes, 256) + dw_bytes) return SPH_ERR_WORKSPACE_TOO_SMALL;
+  if ((uintptr_t)ws & 255) return SPH_ERR_INVALID_ARGUMENT;
+  char *ws_dx = (char *)ws, *ws_dw = (char *)ws + align_up(dx_bytes, 256);
+  // where the two operators expect their operands (see tc_gemm / tc_adjoint_premul and tc_dw)
+  const int cp_go = padded_channels(Cout);
+  __nv_bfloat16 *go_cl = (__nv_bfloat16 *)(ws_dx + 256);
+  __nv_bfloat16 *gt = (__nv_bfloat16 *)(ws_dw + 256 + d.xh_bytes);
+  char *bias_ws = ws_dw + 256 + d.xh_bytes + d.gt_bytes + d.partial_bytes;
+  float *row_part = (float *)(bias_ws + simt_bias_workspace(Cout, 4));
+  const size_t npix = (size_t)(OH * OW);
+  // the zero pixel behind every image of the channels-last copy (unused taps point there)
+  if (cudaMemset2DAsync((char *)go_cl + npix * cp_go * 2, (npix + 1) * cp_go * 2, 0, (size_t)cp_go * 2, (size_t)B, st) != cudaSuccess)
+    return SPH_ERR_CUDA;
+  grad_image_kernel<<<dim3(d.tiles_x * d.tiles_y, d.mbs_total, (unsigned)B), 256, 0, st>>>(
+      (const float *)gout, gt, (int)Cout, (int)OH, (int)OW, d.tiles_x, d.tiles_y, d.mbs_total, row_part, (const float *)fz.mask,
+      go_cl, cp_go);
+  note_launches(1);
+  // channels between mbs_total * 128 and cp_go do not exist (cp_go <= mbs_total * 128), so the copy is complete
+  Fusion fx;
+  fx.src_cl = go_cl;  // already masked
+  int rc = tc_gemm(true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH, IW, 0, weight, K, Cin * K, 1, nullptr, gx, Cin, B,
+                   ws_dx, dx_bytes, st, fx);
+  if (rc != SPH_OK) return rc;
+  Fusion fw;
+  fw.src_cl = fz.src_cl;  // channels-last copy of x, if the caller keeps one
+  fw.gt_ready = true;
+  return tc_dw(gout, x, map, iw, Cin, IH, IW, K, P, OH, OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout, OH * OW, gb, ws_dw,
+               dw_bytes, st, fw);
 }
 
 int tc_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out, int64_t B,

@@ -56,25 +56,58 @@ __global__ void plan_fill_kernel(const T *map, const T *iw, int n_slots, int K, 
   });
 }
 
-// One thread per key: order the segment by entry id (the fill order above is
-// not reproducible), then turn ids into source positions.
+// One thread per key: order the segment by entry id (the fill order above is not reproducible), then turn ids into
+// source positions.  Short segments (the usual case: a handful of samples per pixel) by insertion, longer ones by an
+// in-place heap sort, so that a map that sends very many samples to one pixel costs n log n, not n^2.
+template <typename T>
+__device__ __forceinline__ void sift_down(int *ids, T *w, int root, int n) {
+  for (;;) {
+    int child = 2 * root + 1;
+    if (child >= n) return;
+    if (child + 1 < n && ids[child + 1] > ids[child]) child++;
+    if (ids[root] >= ids[child]) return;
+    const int ti = ids[root];
+    ids[root] = ids[child];
+    ids[child] = ti;
+    const T tw = w[root];
+    w[root] = w[child];
+    w[child] = tw;
+    root = child;
+  }
+}
+
 template <typename T>
 __global__ void plan_sort_kernel(const int *offsets, int *ids, T *w, int n_keys, int id_div, int *max_seg) {
   const int key = blockIdx.x * blockDim.x + threadIdx.x;
   if (key >= n_keys) return;
-  const int e0 = offsets[key], e1 = offsets[key + 1];
-  if (e1 - e0 > 1) atomicMax(max_seg, e1 - e0);
-  for (int i = e0 + 1; i < e1; i++) {
-    const int id = ids[i];
-    const T wi = w[i];
-    int j = i - 1;
-    while (j >= e0 && ids[j] > id) {
-      ids[j + 1] = ids[j];
-      w[j + 1] = w[j];
-      j--;
+  const int e0 = offsets[key], e1 = offsets[key + 1], n = e1 - e0;
+  if (n > 1) atomicMax(max_seg, n);
+  if (n <= 16) {
+    for (int i = e0 + 1; i < e1; i++) {
+      const int id = ids[i];
+      const T wi = w[i];
+      int j = i - 1;
+      while (j >= e0 && ids[j] > id) {
+        ids[j + 1] = ids[j];
+        w[j + 1] = w[j];
+        j--;
+      }
+      ids[j + 1] = id;
+      w[j + 1] = wi;
     }
-    ids[j + 1] = id;
-    w[j + 1] = wi;
+  } else {
+    int *a = ids + e0;
+    T *aw = w + e0;
+    for (int r = n / 2 - 1; r >= 0; r--) sift_down(a, aw, r, n);
+    for (int end = n - 1; end > 0; end--) {
+      const int ti = a[0];
+      a[0] = a[end];
+      a[end] = ti;
+      const T tw = aw[0];
+      aw[0] = aw[end];
+      aw[end] = tw;
+      sift_down(a, aw, 0, end);
+    }
   }
   for (int i = e0; i < e1; i++) ids[i] = ids[i] / id_div;
 }

@@ -8,10 +8,12 @@
 #include <torch/extension.h>
 
 #include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAEvent.h>
 #include <c10/cuda/CUDAGuard.h>
 
 #include <cstdlib>
 #include <list>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -111,7 +113,12 @@ struct PlanKey {
   int64_t n_src, K, P, dstH, dstW;
   int interp, dtype, device;
   torch::Tensor blob;
+  std::shared_ptr<at::cuda::CUDAEvent> built;  // recorded after the build kernels, on the stream that ran them
+  cudaStream_t build_stream;
 };
+
+// Version counter of a tensor; inference tensors have none (and cannot be modified in place): 0.
+uint32_t version_of(const torch::Tensor &t) { return t.is_inference() ? 0u : (uint32_t)t._version(); }
 std::list<PlanKey> g_plans;
 std::mutex g_plan_mu;
 constexpr size_t kMaxPlans = 64;
@@ -128,15 +135,18 @@ torch::Tensor get_plan(const torch::Tensor &map, const torch::Tensor *iw, int64_
       it = g_plans.erase(it);
       continue;
     }
-    const bool hit = it->map_p == map.data_ptr() && it->map_off == map.storage_offset() && it->map_v == map._version() &&
+    const bool hit = it->map_p == map.data_ptr() && it->map_off == map.storage_offset() && it->map_v == version_of(map) &&
                      it->map_s.lock().get() == map.storage().unsafeGetStorageImpl() &&
-                     (iw ? (it->iw_p == iw->data_ptr() && it->iw_v == iw->_version() &&
+                     (iw ? (it->iw_p == iw->data_ptr() && it->iw_v == version_of(*iw) &&
                             it->iw_s.lock().get() == iw->storage().unsafeGetStorageImpl())
                          : it->iw_p == nullptr) &&
                      it->n_src == n_src && it->K == K && it->P == P && it->dstH == dstH && it->dstW == dstW &&
                      it->interp == interp && it->dtype == dtype && it->device == device;
     if (hit) {
       g_plans.splice(g_plans.begin(), g_plans, it);
+      // a caller on another stream than the one that built the plan waits for the build first
+      const cudaStream_t cur = at::cuda::getCurrentCUDAStream().stream();
+      if (cur != g_plans.front().build_stream) g_plans.front().built->block(at::cuda::getCurrentCUDAStream());
       return g_plans.front().blob;
     }
     ++it;
@@ -156,7 +166,9 @@ torch::Tensor get_plan(const torch::Tensor &map, const torch::Tensor *iw, int64_
             iw ? c10::weak_intrusive_ptr<c10::StorageImpl>(iw->storage().getWeakStorageImpl())
                : c10::weak_intrusive_ptr<c10::StorageImpl>(map.storage().getWeakStorageImpl()),
             map.data_ptr(), iw ? iw->data_ptr() : nullptr, map.storage_offset(), iw ? iw->storage_offset() : 0,
-            map._version(), iw ? iw->_version() : 0u, n_src, K, P, dstH, dstW, interp, dtype, device, blob};
+            version_of(map), iw ? version_of(*iw) : 0u, n_src, K, P, dstH, dstW, interp, dtype, device, blob,
+            std::make_shared<at::cuda::CUDAEvent>(), at::cuda::getCurrentCUDAStream().stream()};
+  k.built->record(at::cuda::getCurrentCUDAStream());
   g_plans.push_front(std::move(k));
   if (g_plans.size() > kMaxPlans) g_plans.pop_back();
   return blob;

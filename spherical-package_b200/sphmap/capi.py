@@ -19,6 +19,7 @@ F32, F64 = 0, 1
 NEAREST, BILINEAR, BISPHERICAL = 0, 1, 2
 EXACT, BF16 = 0, 1
 CONV_FORWARD, CONV_BACKWARD_INPUT, CONV_BACKWARD_WEIGHT = 0, 1, 2
+CONV_BACKWARD = 6
 TCONV_FORWARD, TCONV_BACKWARD_INPUT, TCONV_BACKWARD_WEIGHT = 3, 4, 5
 
 SYMBOLS = [
@@ -29,7 +30,8 @@ SYMBOLS = [
     "sph_mapped_conv_relu_forward", "sph_mapped_conv_relu_backward_input", "sph_mapped_conv_relu_backward_weight",
     "sph_device_status", "sph_debug_bounded_wait", "sph_mapped_max_unpool_planned", "sph_mapped_avg_pool",
     "sph_mapped_avg_unpool", "sph_resample_to_map_normalized", "sph_resample_from_uv_maps", "sph_plan_build_uv",
-    "sph_voting_resample_to_map", "sph_build_kernel_map", "sph_build_is_checked",
+    "sph_voting_resample_to_map", "sph_build_kernel_map", "sph_build_is_checked", "sph_conv_companion_bytes",
+    "sph_mapped_conv_forward_cl", "sph_mapped_conv_backward_cl",
 ]
 ERR_UNSUPPORTED = 2
 
@@ -41,6 +43,7 @@ lib.sph_status_string.argtypes = [ctypes.c_int]
 lib.sph_plan_bytes.restype = ctypes.c_size_t
 lib.sph_launch_count.restype = ctypes.c_ulonglong
 lib.sph_conv_workspace_bytes.restype = ctypes.c_size_t
+lib.sph_conv_companion_bytes.restype = ctypes.c_size_t
 
 _vp, _i64, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
 
@@ -369,6 +372,53 @@ def conv_relu_backward_weight(go, act_out, x, smap, K, interp, iw=None, precisio
         return conv_backward_weight(torch.ops.aten.threshold_backward(go, act_out, 0), x, smap, K, interp, iw, precision, ws)
     _ok(rc, "sph_mapped_conv_relu_backward_weight")
     return gw, gb
+
+
+def companion(B, C, H, W, device):
+    """Zero-filled channels-last bf16 companion buffer of a (B, C, H, W) float32 activation (see include/sphmap.h)."""
+    n = lib.sph_conv_companion_bytes(*_ints(B, C, H, W))
+    if n == 0:
+        raise SphError("sph_conv_companion_bytes: bad shape")
+    return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def conv_forward_cl(x, x_cl, smap, weight, bias, K, interp, iw=None, precision=BF16, relu=False, out=None, out_cl=None, ws=None):
+    """Forward with channels-last companions: x_cl (or None) is the companion of x, out_cl (or None) receives the
+    companion of the output.  Raises Unsupported when out_cl cannot be written for this shape."""
+    B, Cin, IH, IW = x.shape
+    OH, OW = smap.shape[:2]
+    Cout = weight.shape[0]
+    if out is None:
+        out = torch.empty(B, Cout, OH, OW, dtype=x.dtype, device=x.device)
+    if ws is None:
+        ws = conv_workspace(CONV_FORWARD, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
+    rc = lib.sph_mapped_conv_forward_cl(_ptr(x), _ptr(x_cl), _ptr(smap), _ptr(iw), _ptr(weight), _ptr(bias), _ptr(out), _ptr(out_cl),
+                                        *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)), _int(_dt(x)), _int(int(interp)),
+                                        _int(precision), _int(1 if relu else 0), _ptr(ws[0]), _sz(ws[1]), _stream())
+    if rc == ERR_UNSUPPORTED:
+        raise Unsupported("sph_mapped_conv_forward_cl")
+    _ok(rc, "sph_mapped_conv_forward_cl")
+    return out
+
+
+def conv_backward_cl(go, act_out, x, x_cl, plan, smap, weight, K, interp, iw=None, precision=BF16, gx=None, ws=None):
+    """(grad_input, grad_weight, grad_bias) in one call; act_out (or None) masks grad_output (fused ReLU), x_cl (or
+    None) is the companion of x.  Raises Unsupported for shapes that use the separate entry points."""
+    B, Cin, IH, IW = x.shape
+    _, Cout, OH, OW = go.shape
+    if gx is None:
+        gx = torch.empty_like(x)
+    gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
+    gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
+    if ws is None:
+        ws = conv_workspace(CONV_BACKWARD, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
+    rc = lib.sph_mapped_conv_backward_cl(_ptr(go), _ptr(act_out), _ptr(x), _ptr(x_cl), _ptr(plan), _ptr(smap), _ptr(iw),
+                                         _ptr(weight), _ptr(gx), _ptr(gw), _ptr(gb), *_ints(B, Cin, Cout, IH, IW, OH, OW, K, _P(iw)),
+                                         _int(_dt(x)), _int(int(interp)), _int(precision), _ptr(ws[0]), _sz(ws[1]), _stream())
+    if rc == ERR_UNSUPPORTED:
+        raise Unsupported("sph_mapped_conv_backward_cl")
+    _ok(rc, "sph_mapped_conv_backward_cl")
+    return gx, gw, gb
 
 
 def tconv_forward(x, plan, weight, bias, oh, ow, K, precision=EXACT):

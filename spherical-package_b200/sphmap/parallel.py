@@ -49,7 +49,7 @@ class EncoderStack:
     convolution kernels (sph_mapped_conv_relu_*); without it as separate passes over the activations, the way the
     reference's operators compose."""
 
-    def __init__(self, cfg, device, precision, local_batch, reducer=None, timers=None, fuse_relu=True):
+    def __init__(self, cfg, device, precision, local_batch, reducer=None, timers=None, fuse_relu=True, companions=None):
         from . import capi
         self.c = capi
         self.prec = precision
@@ -63,13 +63,22 @@ class EncoderStack:
         self.reducer = reducer
         self.fuse_relu = fuse_relu
         self.fused_bwd = [fuse_relu] * 4   # per layer: backward kernels mask the gradient themselves (else one masking pass)
+        # Channels-last bf16 companions of the activations between the layers (tensor-core precision with the fused
+        # ReLU only): layer i's epilogue writes the companion of its output, layer i+1 gathers from it in forward and
+        # in its weight gradient, and each layer's backward is one combined call that converts grad_output once.
+        self.companions = (precision == capi.BF16 and fuse_relu) if companions is None else bool(companions)
+        self.out_cl = [None] * 4
+        self.combined = [self.companions] * 4
         self.timers = timers          # optional {(layer, phase): [start_event, end_event]} to time single launches
+        self.timed_keys = set()       # the (layer, phase) pairs that actually ran (phase "bwd" = combined backward)
         self.plans, self.acts, self.ws = [], [], {}
         f32 = dict(dtype=torch.float32, device=device)
         for li, (ci, co, (ih, iw), (oh, ow), s) in enumerate(self.layers):
             self.plans.append(capi.plan_build(self.maps[li], None, oh * ow, self.K, self.interp, ih, iw))
             self.acts.append(torch.empty(local_batch, co, oh, ow, **f32))
-            for op in (capi.CONV_FORWARD, capi.CONV_BACKWARD_INPUT, capi.CONV_BACKWARD_WEIGHT):
+            if self.companions and li < 3 and co % 8 == 0:
+                self.out_cl[li] = capi.companion(local_batch, co, oh, ow, device)
+            for op in (capi.CONV_FORWARD, capi.CONV_BACKWARD_INPUT, capi.CONV_BACKWARD_WEIGHT, capi.CONV_BACKWARD):
                 self.ws[(li, op)] = capi.conv_workspace(op, local_batch, ci, co, ih, iw, oh, ow, self.K, 0, capi.F32,
                                                         self.interp, precision, self.w[li])
         self.gx = [torch.empty(local_batch, ci, ih, iw, **f32) for ci, co, (ih, iw), _, _ in self.layers]
@@ -77,6 +86,7 @@ class EncoderStack:
 
     def _timed(self, key, fn):
         if self.timers is not None and key in self.timers:
+            self.timed_keys.add(key)
             s, e = self.timers[key]
             s.record()
             r = fn()
@@ -90,6 +100,19 @@ class EncoderStack:
         h = x
         for li in range(4):
             self.inputs.append(h)
+            if self.companions:
+                x_cl = self.out_cl[li - 1] if li > 0 else None
+                try:
+                    out = self._timed((li, "fwd"), lambda: c.conv_forward_cl(
+                        h, x_cl, self.maps[li], self.w[li], self.b[li], self.K, self.interp, None, self.prec, True,
+                        out=self.acts[li], out_cl=self.out_cl[li], ws=self.ws[(li, c.CONV_FORWARD)]))
+                except c.Unsupported:      # this layer cannot write a companion: the next one converts its input itself
+                    self.out_cl[li] = None
+                    out = self._timed((li, "fwd"), lambda: c.conv_forward_cl(
+                        h, x_cl, self.maps[li], self.w[li], self.b[li], self.K, self.interp, None, self.prec, True,
+                        out=self.acts[li], out_cl=None, ws=self.ws[(li, c.CONV_FORWARD)]))
+                h = out
+                continue
             fwd = c.conv_relu_forward if self.fuse_relu else c.conv_forward
             out = self._timed((li, "fwd"), lambda: fwd(h, self.maps[li], self.w[li], self.b[li], self.K, self.interp, None,
                                                        self.prec, out=self.acts[li], ws=self.ws[(li, c.CONV_FORWARD)]))
@@ -102,6 +125,19 @@ class EncoderStack:
         for li in reversed(range(4)):
             ci, co, (ih, iw), (oh, ow), s = self.layers[li]
             gw = None
+            if self.combined[li]:     # one call: grad_output converted once for the input and the weight gradient
+                try:
+                    x_cl = self.out_cl[li - 1] if li > 0 else None
+                    gx, gw, gb = self._timed((li, "bwd"), lambda: c.conv_backward_cl(
+                        g, self.acts[li], self.inputs[li], x_cl, self.plans[li], self.maps[li], self.w[li], self.K, self.interp,
+                        None, self.prec, gx=self.gx[li], ws=self.ws[(li, c.CONV_BACKWARD)]))
+                    self.gw[li], self.gb[li] = gw, gb
+                    if self.reducer is not None:
+                        self.reducer.submit(gw, gb)
+                    g = gx
+                    continue
+                except c.Unsupported:
+                    self.combined[li] = False
             if self.fused_bwd[li]:   # the kernels read g * (activation > 0) wherever they read g
                 try:
                     gw, gb = self._timed((li, "dw"), lambda: c.conv_relu_backward_weight(

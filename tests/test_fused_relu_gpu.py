@@ -153,3 +153,71 @@ def test_encoder_stack_fused_equals_unfused():
     assert torch.equal(res[0][0], res[1][0])
     for a, b in zip(res[0][1] + res[0][2] + [res[0][3]], res[1][1] + res[1][2] + [res[1][3]]):
         assert torch.equal(a, b)
+
+
+def test_companions_and_combined_backward_are_bit_identical_to_the_separate_calls():
+    """Channels-last companions (written by a layer's epilogue, gathered from by the next layer) and the combined
+    backward call (grad_output converted once for dInput and dW) change where the bf16 copies come from, not their
+    contents: every result equals the plain entry points' bit for bit."""
+    from sphmap import capi, workloads as wl
+    g = torch.Generator().manual_seed(91)
+    B, C0, C1, C2, H, W, K = 2, 3, 64, 128, 32, 64, 9
+    x = torch.rand(B, C0, H, W, generator=g).cuda()
+    m1, m2 = wl.gnomonic_map(H, W, 2).cuda(), wl.gnomonic_map(H // 2, W // 2, 1).cuda()
+    w1, b1 = (torch.randn(C1, C0, K, generator=g) / 5).cuda(), (torch.randn(C1, generator=g) * 0.1).cuda()
+    w2, b2 = (torch.randn(C2, C1, K, generator=g) / 24).cuda(), (torch.randn(C2, generator=g) * 0.1).cuda()
+    go = torch.randn(B, C2, H // 2, W // 2, generator=g).cuda()
+    # plain path
+    a1 = capi.conv_relu_forward(x, m1, w1, b1, K, 1, None, capi.BF16)
+    a2 = capi.conv_relu_forward(a1, m2, w2, b2, K, 1, None, capi.BF16)
+    plan2 = capi.plan_build(m2, None, (H // 2) * (W // 2), K, 1, H // 2, W // 2)
+    gx_ref = capi.conv_relu_backward_input(go, a2, plan2, w2, H // 2, W // 2, K, capi.BF16)
+    gw_ref, gb_ref = capi.conv_relu_backward_weight(go, a2, a1, m2, K, 1, None, capi.BF16)
+    # companions: layer 1 (thin kernels) writes the companion of its output, layer 2 (tensor cores) gathers from it
+    cl1 = capi.companion(B, C1, H // 2, W // 2, "cuda")
+    cl2 = capi.companion(B, C2, H // 2, W // 2, "cuda")
+    c1 = capi.conv_forward_cl(x, None, m1, w1, b1, K, 1, None, capi.BF16, True, out_cl=cl1)
+    c2 = capi.conv_forward_cl(c1, cl1, m2, w2, b2, K, 1, None, capi.BF16, True, out_cl=cl2)
+    assert torch.equal(c1, a1) and torch.equal(c2, a2)
+    # the companion holds bf16(activation), channels last, with a zero pixel behind every image
+    n1 = (H // 2) * (W // 2)
+    v = cl1[:B * (n1 + 1) * C1 * 2].view(torch.bfloat16).view(B, n1 + 1, C1)
+    assert torch.equal(v[:, :n1].float(), a1.to(torch.bfloat16).float().flatten(2).transpose(1, 2)) and (v[:, n1] == 0).all()
+    gx, gw, gb = capi.conv_backward_cl(go, c2, c1, cl1, plan2, m2, w2, K, 1, None, capi.BF16)
+    assert torch.equal(gx, gx_ref) and torch.equal(gw, gw_ref) and torch.equal(gb, gb_ref)
+    gx, gw, gb = capi.conv_backward_cl(go, c2, c1, None, plan2, m2, w2, K, 1, None, capi.BF16)      # without the companion of x
+    assert torch.equal(gx, gx_ref) and torch.equal(gw, gw_ref) and torch.equal(gb, gb_ref)
+    gx, gw, gb = capi.conv_backward_cl(go * (c2 > 0), None, c1, cl1, plan2, m2, w2, K, 1, None, capi.BF16)   # unfused mask
+    assert torch.equal(gx, gx_ref) and torch.equal(gw, gw_ref) and torch.equal(gb, gb_ref)
+    # thin layers and exact precision decline the combined call before launching anything
+    plan1 = capi.plan_build(m1, None, n1, K, 1, H, W)
+    with pytest.raises(capi.Unsupported):
+        capi.conv_backward_cl(gx_ref, a1, x, None, plan1, m1, w1, K, 1, None, capi.BF16)
+    # ragged sizes (tiles with tail pixels, width not a multiple of 4 -> plain-store epilogue) and a down-sampling map
+    xr = torch.randn(1, 72, 13, 22, generator=g).cuda()
+    mr = (torch.rand(13, 22, 5, 2, generator=g) * torch.tensor([23.0, 14.0]) - 0.5).cuda()
+    wr, br = (torch.randn(40, 72, 5, generator=g) / 19).cuda(), torch.zeros(40).cuda()
+    clr = capi.companion(1, 40, 13, 22, "cuda")
+    yr = capi.conv_forward_cl(xr, None, mr, wr, br, 5, 1, None, capi.BF16, True, out_cl=clr)
+    assert torch.equal(yr, capi.conv_relu_forward(xr, mr, wr, br, 5, 1, None, capi.BF16))
+    cp = 64   # 40 channels pad to 64
+    vr = clr[:(13 * 22 + 1) * cp * 2].view(torch.bfloat16).view(13 * 22 + 1, cp)
+    assert torch.equal(vr[:13 * 22, :40].float(), yr.to(torch.bfloat16).float().flatten(2)[0].t()) and (vr[:, 40:] == 0).all()
+
+
+def test_encoder_stack_with_companions_equals_without():
+    from sphmap import capi, workloads as wl
+    from sphmap.parallel import EncoderStack
+    cfg = wl.config4(B=2, H=64, W=128)
+    dev = torch.device("cuda")
+    x, go = cfg["x"].to(dev), cfg["grad_output"].to(dev)
+    res = []
+    for comp in (False, True):
+        st = EncoderStack(cfg, dev, capi.BF16, 2, companions=comp)
+        for _ in range(2):      # twice: the companions are reused across steps
+            loss = st.step(x, go)
+        res.append((loss.clone(), [t.clone() for t in st.gw], [t.clone() for t in st.gb], st.gx[0].clone()))
+        assert any(st.combined) == comp
+    assert torch.equal(res[0][0], res[1][0])
+    for a, b in zip(res[0][1] + res[0][2] + [res[0][3]], res[1][1] + res[1][2] + [res[1][3]]):
+        assert torch.equal(a, b)

@@ -264,3 +264,46 @@ def test_standard_convolution_wrappers_match_torch():
     got = torch.randn_like(yt)
     for a, b in zip(torch.autograd.grad(yt, (x, tconv.weight, tconv.bias), got), torch.autograd.grad(reft, (x, tconv.weight, tconv.bias), got)):
         torch.testing.assert_close(a, b)
+
+
+def test_plan_with_very_long_segments():
+    """A map that sends thousands of samples to a handful of pixels: the plan's per-pixel ordering takes the heap-sort
+    path; the scatter still sums every pixel in map order (compared with a float64 sum taken in that order)."""
+    from sphmap import capi
+    g = torch.Generator().manual_seed(71)
+    MH, MW, OH, OW = 64, 96, 8, 8
+    m = torch.zeros(MH, MW, 2)
+    m[..., 0] = torch.randint(2, 5, (MH, MW), generator=g).float()      # x in {2, 3, 4}
+    m[..., 1] = 3.0
+    x = torch.randn(2, 2, MH, MW, generator=g)
+    plan = capi.plan_build(m.cuda(), None, MH * MW, 1, 0, OH, OW)
+    out = capi.resample_to_map(x.cuda(), plan, OH, OW)
+    assert torch.equal(out, capi.resample_to_map(x.cuda(), plan, OH, OW))
+    want = port.resample_to_map(x, m, OH, OW, 0)
+    torch.testing.assert_close(out.cpu(), want, rtol=1e-4, atol=1e-4 * want.abs().max().item())
+    # in-order float32 sum of one pixel, reproduced on the host
+    sel = (m[..., 0] == 3.0).flatten()
+    acc = torch.zeros((), dtype=torch.float32)
+    for v in x[0, 0].flatten()[sel]:
+        acc = acc + v
+    assert out[0, 0, 3, 3].item() == acc.item()
+
+
+def test_plan_cache_under_inference_mode_and_across_streams():
+    import _spherical_distortion_ext as ext
+    from spherical_distortion import functional as F
+    from spherical_distortion.nn import InterpolationType
+    ext.clear_plan_cache()
+    g = torch.Generator().manual_seed(81)
+    with torch.inference_mode():
+        x = torch.randn(2, 3, 16, 24, generator=g).cuda()
+        m = (torch.rand(16, 24, 2, generator=g) * torch.tensor([31.0, 19.0])).cuda()
+        a = F.resample(x, m, (20, 32), InterpolationType.BILINEAR)           # builds and caches a plan
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            b = F.resample(x, m, (20, 32), InterpolationType.BILINEAR)       # cache hit from another stream
+        torch.cuda.current_stream().wait_stream(side)
+        assert ext.plan_cache_size() == 1
+        assert torch.equal(a, b)
+        torch.testing.assert_close(a.cpu(), port.resample_to_map(x.cpu(), m.cpu(), 20, 32, 1), rtol=1e-5, atol=1e-5)
