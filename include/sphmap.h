@@ -362,6 +362,7 @@ int sph_mapped_conv_relu_backward_weight(const void *gout, const void *act_out, 
  * Results are bit-identical to the separate entry points.
  * ---------------------------------------------------------------------- */
 size_t sph_conv_companion_bytes(int64_t B, int64_t C, int64_t H, int64_t W);
+int64_t sph_conv_companion_channels(int64_t C); /* Cp, the companion's channel pitch */
 int sph_mapped_conv_forward_cl(const void *x, const void *x_cl, const void *map, const void *iw, const void *weight,
                                const void *bias, void *out, void *out_cl, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
                                int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,

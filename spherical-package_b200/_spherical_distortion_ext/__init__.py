@@ -22,3 +22,5 @@ get_precision = _C.get_precision
 clear_plan_cache = _C.clear_plan_cache
 plan_cache_size = _C.plan_cache_size
 device_status = _C.device_status
+set_companions = _C.set_companions
+clear_companions = _C.clear_companions

@@ -203,6 +203,8 @@ extern "C" size_t sph_conv_companion_bytes(int64_t B, int64_t C, int64_t H, int6
   return align_up((size_t)(B * (H * W + 1)) * (size_t)padded_channels(C) * 2, 256);
 }
 
+extern "C" int64_t sph_conv_companion_channels(int64_t C) { return C > 0 ? padded_channels(C) : 0; }
+
 extern "C" int sph_mapped_conv_forward_cl(const void *x, const void *x_cl, const void *map, const void *iw, const void *weight,
                                           const void *bias, void *out, void *out_cl, int64_t B, int64_t Cin, int64_t Cout,
                                           int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,

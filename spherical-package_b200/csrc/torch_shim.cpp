@@ -184,6 +184,66 @@ int64_t plan_cache_size() {
   return (int64_t)g_plans.size();
 }
 
+// ---- channels-last companions of activations (bf16 precision) -------------------
+// The tensor-core kernels gather from a channels-last bf16 copy of their input.  A layer with the fused ReLU writes
+// that copy of its output from its own epilogue; it is remembered here under the identity of the output tensor, so
+// that the next layer (whose input that tensor is) finds it in forward and in backward and skips its conversion
+// pass.  An entry dies with the tensor's storage, on an in-place modification (version counter) or by eviction.
+struct CompanionEntry {
+  c10::weak_intrusive_ptr<c10::StorageImpl> storage;
+  const void *ptr;
+  uint32_t version;
+  std::vector<int64_t> sizes;
+  torch::Tensor companion;
+};
+std::list<CompanionEntry> g_companions;
+std::mutex g_companion_mu;
+constexpr size_t kMaxCompanions = 8;
+bool g_use_companions = true;
+
+const void *find_companion(const torch::Tensor &t) {
+  if (!g_use_companions) return nullptr;
+  std::lock_guard<std::mutex> lock(g_companion_mu);
+  for (auto it = g_companions.begin(); it != g_companions.end();) {
+    if (it->storage.expired()) {
+      it = g_companions.erase(it);
+      continue;
+    }
+    if (it->ptr == t.data_ptr() && it->version == version_of(t) && it->sizes == t.sizes().vec() &&
+        it->storage.lock().get() == t.storage().unsafeGetStorageImpl())
+      return it->companion.data_ptr();
+    ++it;
+  }
+  return nullptr;
+}
+
+// Fresh companion buffer for a (B, C, H, W) activation: only the zero pixel behind every image (and, if the channel
+// count is padded, the padding) has to be cleared; the kernel writes the rest.
+torch::Tensor new_companion(const torch::Tensor &like, int64_t B, int64_t C, int64_t H, int64_t W) {
+  const size_t bytes = sph_conv_companion_bytes(B, C, H, W);
+  TORCH_CHECK(bytes > 0, "activation too large for a channels-last companion");
+  const int64_t cp = sph_conv_companion_channels(C);
+  if (cp != C) return torch::zeros({(int64_t)bytes}, like.options().dtype(torch::kUInt8));
+  torch::Tensor c = torch::empty({(int64_t)bytes}, like.options().dtype(torch::kUInt8));
+  const size_t px = (size_t)cp * 2, img = (size_t)(H * W + 1) * px;
+  TORCH_CHECK(cudaMemset2DAsync((char *)c.data_ptr() + (size_t)(H * W) * px, img, 0, px, (size_t)B,
+                                at::cuda::getCurrentCUDAStream().stream()) == cudaSuccess,
+              "clearing the companion's zero pixels failed");
+  return c;
+}
+
+void register_companion(const torch::Tensor &t, torch::Tensor companion) {
+  std::lock_guard<std::mutex> lock(g_companion_mu);
+  g_companions.push_front(CompanionEntry{c10::weak_intrusive_ptr<c10::StorageImpl>(t.storage().getWeakStorageImpl()), t.data_ptr(),
+                                         version_of(t), t.sizes().vec(), std::move(companion)});
+  while (g_companions.size() > kMaxCompanions) g_companions.pop_back();
+}
+
+void clear_companions() {
+  std::lock_guard<std::mutex> lock(g_companion_mu);
+  g_companions.clear();
+}
+
 torch::Tensor workspace(size_t bytes, const torch::Tensor &like) {
   return torch::empty({(int64_t)(bytes ? bytes : 1)}, like.options().dtype(torch::kUInt8));
 }
@@ -497,6 +557,33 @@ torch::Tensor conv_forward_impl(torch::Tensor x, torch::Tensor map, const torch:
   const size_t wb = sph_conv_workspace_bytes(SPH_CONV_FORWARD, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
                                              a.interp, a.prec);
   torch::Tensor ws = workspace(wb, x);
+  if (a.prec == SPH_PRECISION_BF16 && g_use_companions) {
+    // channels-last companions: gather from the input's copy if a previous layer left one; with the fused ReLU also
+    // write the copy of the output for the next layer
+    const void *x_cl = find_companion(x);
+    torch::Tensor out_cl;
+    if (relu && a.Cout % 8 == 0) out_cl = new_companion(x, a.B, a.Cout, a.OH, a.OW);
+    if (x_cl != nullptr || out_cl.defined()) {
+      int rc = sph_mapped_conv_forward_cl(x.data_ptr(), x_cl, map.data_ptr(), iw ? iw->data_ptr() : nullptr, weight.data_ptr(),
+                                          bias.data_ptr(), out.data_ptr(), out_cl.defined() ? out_cl.data_ptr() : nullptr, a.B,
+                                          a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp, a.prec, relu ? 1 : 0,
+                                          ws.data_ptr(), wb, stream());
+      if (rc == SPH_ERR_UNSUPPORTED && out_cl.defined()) {   // this shape cannot write the copy (or cannot fuse): without it
+        out_cl = torch::Tensor();
+        rc = x_cl == nullptr ? SPH_ERR_UNSUPPORTED
+                             : sph_mapped_conv_forward_cl(x.data_ptr(), x_cl, map.data_ptr(), iw ? iw->data_ptr() : nullptr,
+                                                          weight.data_ptr(), bias.data_ptr(), out.data_ptr(), nullptr, a.B, a.Cin,
+                                                          a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp, a.prec,
+                                                          relu ? 1 : 0, ws.data_ptr(), wb, stream());
+      }
+      if (rc != SPH_ERR_UNSUPPORTED) {
+        ok(rc, "sph_mapped_conv_forward_cl");
+        if (out_cl.defined()) register_companion(out, out_cl);
+        maybe_check_device("mapped convolution");
+        return out;
+      }
+    }
+  }
   if (relu) {
     const int rc = sph_mapped_conv_relu_forward(x.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr, weight.data_ptr(),
                                                 bias.data_ptr(), out.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K,
@@ -536,6 +623,29 @@ std::vector<torch::Tensor> conv_backward_impl(torch::Tensor go, torch::Tensor ma
                    dtype_of(x) == SPH_F32 ? precision() : SPH_PRECISION_EXACT};
   torch::Tensor gx = torch::empty_like(x), gw = torch::empty_like(weight), gb = torch::empty({a.Cout}, x.options());
   torch::Tensor plan = get_plan(map, iw, a.OH * a.OW, a.K, a.P, a.interp, a.IH, a.IW);
+  if (act_out)
+    TORCH_CHECK(act_out->is_contiguous() && act_out->sizes() == go.sizes() && act_out->dtype() == go.dtype() &&
+                    act_out->device() == go.device(),
+                "activation output must be a contiguous tensor like grad_output");
+  if (a.prec == SPH_PRECISION_BF16) {
+    // all three gradients in one call: grad_output is converted (and masked) once for both of its consumers, and the
+    // input's channels-last copy is used if a previous layer left one
+    const size_t wbc = sph_conv_workspace_bytes(SPH_CONV_BACKWARD, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype,
+                                                a.interp, a.prec);
+    if (wbc > 0) {
+      torch::Tensor wsc = workspace(wbc, x);
+      const int rc = sph_mapped_conv_backward_cl(go.data_ptr(), act_out ? act_out->data_ptr() : nullptr, x.data_ptr(),
+                                                 find_companion(x), plan.data_ptr(), map.data_ptr(), iw ? iw->data_ptr() : nullptr,
+                                                 weight.data_ptr(), gx.data_ptr(), gw.data_ptr(), gb.data_ptr(), a.B, a.Cin, a.Cout,
+                                                 a.IH, a.IW, a.OH, a.OW, a.K, a.P, a.dtype, a.interp, a.prec, wsc.data_ptr(), wbc,
+                                                 stream());
+      if (rc != SPH_ERR_UNSUPPORTED) {
+        ok(rc, "sph_mapped_conv_backward_cl");
+        maybe_check_device("mapped convolution");
+        return {gx, gw, gb};
+      }
+    }
+  }
   size_t wb = sph_conv_workspace_bytes(SPH_CONV_BACKWARD_INPUT, a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.P,
                                        a.dtype, a.interp, a.prec);
   torch::Tensor ws = workspace(wb, x);
@@ -543,9 +653,6 @@ std::vector<torch::Tensor> conv_backward_impl(torch::Tensor go, torch::Tensor ma
                                         a.interp, a.prec);
   torch::Tensor ws2 = workspace(wb2, x);
   if (act_out) {  // gradient of the fused ReLU: the kernels read grad_output * (act_out > 0)
-    TORCH_CHECK(act_out->is_contiguous() && act_out->sizes() == go.sizes() && act_out->dtype() == go.dtype() &&
-                    act_out->device() == go.device(),
-                "activation output must be a contiguous tensor like grad_output");
     const int rc = sph_mapped_conv_relu_backward_input(go.data_ptr(), act_out->data_ptr(), plan.data_ptr(), weight.data_ptr(),
                                                        gx.data_ptr(), a.B, a.Cin, a.Cout, a.IH, a.IW, a.OH, a.OW, a.K, a.dtype,
                                                        a.prec, ws.data_ptr(), wb, stream());
@@ -737,6 +844,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("conv_backward", &conv_backward);
   m.def("transposed_conv_forward", &transposed_conv_forward);
   m.def("transposed_conv_backward", &transposed_conv_backward);
+  m.def("set_companions", [](bool on) { g_use_companions = on; if (!on) clear_companions(); },
+        "true (default): with bf16 precision, layers with a fused activation leave a channels-last bf16 copy of their output "
+        "for the next layer, which then skips its conversion pass; false: every call converts its own input");
+  m.def("clear_companions", &clear_companions);
   m.def("set_deterministic_unpool", [](bool on) { g_deterministic_unpool = on; },
         "true (default): argmax backward sums through a scatter plan in a fixed order; false: float atomics as the reference");
   m.def("mapped_conv_forward", &mapped_conv_forward);

@@ -31,7 +31,7 @@ SYMBOLS = [
     "sph_device_status", "sph_debug_bounded_wait", "sph_mapped_max_unpool_planned", "sph_mapped_avg_pool",
     "sph_mapped_avg_unpool", "sph_resample_to_map_normalized", "sph_resample_from_uv_maps", "sph_plan_build_uv",
     "sph_voting_resample_to_map", "sph_build_kernel_map", "sph_build_is_checked", "sph_conv_companion_bytes",
-    "sph_mapped_conv_forward_cl", "sph_mapped_conv_backward_cl",
+    "sph_conv_companion_channels", "sph_mapped_conv_forward_cl", "sph_mapped_conv_backward_cl",
 ]
 ERR_UNSUPPORTED = 2
 

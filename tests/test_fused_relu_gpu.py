@@ -221,3 +221,43 @@ def test_encoder_stack_with_companions_equals_without():
     assert torch.equal(res[0][0], res[1][0])
     for a, b in zip(res[0][1] + res[0][2] + [res[0][3]], res[1][1] + res[1][2] + [res[1][3]]):
         assert torch.equal(a, b)
+
+
+def test_layer_stack_with_and_without_companion_cache():
+    """Two stacked layers with the fused activation through the module API in bf16: with the companion cache on, the
+    second layer gathers from the channels-last copy the first one left; results and gradients equal the run with the
+    cache off bit for bit, also when the intermediate tensor was modified in place (the stale copy must not be used)."""
+    import _spherical_distortion_ext as ext
+    from spherical_distortion.nn import InterpolationType, MappedConvolution
+    from sphmap import workloads as wl
+    old = ext.get_precision()
+    ext.set_precision("bf16")
+    try:
+        g = torch.Generator().manual_seed(77)
+        x = torch.rand(2, 3, 32, 64, generator=g).cuda().requires_grad_(True)
+        m1, m2 = wl.gnomonic_map(32, 64, 2).cuda(), wl.gnomonic_map(16, 32, 1).cuda()
+        l1 = MappedConvolution(3, 64, 9, InterpolationType.BILINEAR, activation="relu").cuda()
+        l2 = MappedConvolution(64, 96, 9, InterpolationType.BILINEAR, activation="relu").cuda()
+        go = torch.randn(2, 96, 16, 32, generator=g).cuda()
+        runs = []
+        for on in (False, True):
+            ext.set_companions(on)
+            for p in list(l1.parameters()) + list(l2.parameters()) + [x]:
+                p.grad = None
+            y = l2(l1(x, m1), m2)
+            y.backward(go)
+            runs.append([y.detach().clone(), x.grad.clone()] + [p.grad.clone() for p in list(l1.parameters()) + list(l2.parameters())])
+        for a, b in zip(runs[0], runs[1]):
+            assert torch.equal(a, b)
+        # a tensor modified in place after the layer produced it no longer matches its cached copy (version counter):
+        # the next layer converts the tensor itself instead of gathering from the stale copy
+        ext.set_companions(True)
+        with torch.no_grad():
+            h = l1(x, m1)
+            h.add_(0.25)
+            y_inplace = l2(h, m2)
+            y_fresh = l2(h.clone(), m2)
+        assert torch.equal(y_inplace, y_fresh)
+    finally:
+        ext.set_companions(True)
+        ext.set_precision(old)
