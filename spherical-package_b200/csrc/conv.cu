@@ -106,7 +106,8 @@ int conv_backward_input(const void *gout, const void *plan, const void *weight, 
   if (!gout || !plan || !weight || !gx) return SPH_ERR_INVALID_ARGUMENT;
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  // the thin kernels stream grad_output once per operator; masking it in both would cost more than one masking pass
+  // The thin kernels are issue-bound, not memory-bound: reading the mask inside them was measured slower (layer-1 dInput
+  // of the encoder 2.1 -> 4.4 ms, dW 2.6 -> 2.9 ms) than one separate masking pass (0.9 ms), so they decline the mask.
   if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4) && fz.mask) return SPH_ERR_UNSUPPORTED;
   if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
     return SPH_BY_DTYPE(small_adjoint, gout, plan, Cout, OH * OW, K, IH * IW, weight, K, Cin * K, 1, nullptr, gx, Cin, B, ws,
