@@ -177,7 +177,13 @@ def run_encoder(args, rank, local, world):
     phases = [(li, ph) for li in range(4) for ph in ("fwd", "dw", "dx", "bwd")]   # "bwd": dInput + dW in one combined call
 
     def new_timers():
-        return {k: [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)] for k in phases}
+        t = {k: [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)] for k in phases}
+        for li in range(4):   # events the combined backward call records at its internal phase boundaries
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            for e in ev:
+                e.record()    # creates the handle the library records on later
+            t[(li, "bwd.phases")] = ev
+        return t
 
     stack = EncoderStack(cfg, dev, prec, hi - lo, GradReducer(), None)
     per_step_timers = []
@@ -198,7 +204,13 @@ def run_encoder(args, rank, local, world):
     ms, clocks = timed_loop(step_timed, args.steps, 0, world, dev, sampler)
     # per-launch durations of the timed region itself (events were recorded on the launching stream)
     ran = sorted(stack.timed_keys)
-    per_launch = {k: sum(t[k][0].elapsed_time(t[k][1]) for t in per_step_timers) / len(per_step_timers) for k in ran}
+    per_launch = {}
+    for k in ran:
+        if k[1] == "bwd.phases":   # split the combined backward call into its three parts
+            for name, i in (("bwd.prepass", 0), ("dx", 1), ("dw", 2)):
+                per_launch[(k[0], name)] = sum(t[k][i].elapsed_time(t[k][i + 1]) for t in per_step_timers) / len(per_step_timers)
+        elif not (k[1] == "bwd" and (k[0], "bwd.phases") in stack.timed_keys):
+            per_launch[k] = sum(t[k][0].elapsed_time(t[k][1]) for t in per_step_timers) / len(per_step_timers)
     value = flops_step * args.steps / (ms * 1e-3) / 1e12
 
     # --- end-to-end arm: public nn.Module API, pinned host input copied in and loss read back per step ---
@@ -283,11 +295,12 @@ def run_encoder(args, rank, local, world):
         ci = cfg["layers"][li][0]
         if ci * 9 <= 32:
             return "small_%s (SIMT, thin contraction)" % ph
-        return {"dw": "tc_dw_kernel", "bwd": "tc_gemm_kernel + tc_dw_kernel (combined backward call)"}.get(ph, "tc_gemm_kernel")
+        return {"dw": "tc_dw_kernel", "bwd": "tc_gemm_kernel + tc_dw_kernel (combined backward call)",
+                "bwd.prepass": "grad_image_kernel (layout pre-pass of the backward call)"}.get(ph, "tc_gemm_kernel")
 
     def launch_flops(li, ph):
         ci, co, _, (oh, ow), _ = cfg["layers"][li]
-        return (2 if ph == "bwd" else 1) * 2 * (hi - lo) * co * ci * 9 * oh * ow
+        return {"bwd": 2, "bwd.prepass": 0}.get(ph, 1) * 2 * (hi - lo) * co * ci * 9 * oh * ow
 
     groups = {}
     for (li, ph), t in per_launch.items():

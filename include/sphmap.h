@@ -373,6 +373,14 @@ int sph_mapped_conv_backward_cl(const void *gout, const void *act_out, const voi
                                 int64_t K, int64_t P, int dtype, int interp, int precision, void *ws, size_t ws_bytes,
                                 void *stream);
 
+/* Tracing aid for sph_mapped_conv_backward_cl: the NEXT such call made by the
+ * calling thread records the given CUDA events (cudaEvent_t passed as
+ * void*, up to 4) on its stream at its phase boundaries - [0] entry, [1]
+ * grad_output converted, [2] input gradient done, [3] weight and bias
+ * gradients done - so that a benchmark can time the kernels inside the one
+ * call.  The list is used once.  No counterpart in the reference. */
+int sph_trace_phases(void **events, int n_events);
+
 /* ------------------------------------------------------------------------
  * Mapped transposed convolution.  weight (Cin,Cout,K), bias (Cout),
  * x (B,Cin,IH,IW), out / gout (B,Cout,OH,OW); the map has the INPUT's size,

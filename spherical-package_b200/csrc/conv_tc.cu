@@ -263,6 +263,13 @@ __device__ __forceinline__ void gather_plan_rest(Acc8 &acc, const char *__restri
   }
 }
 
+// 32 bytes (two neighbouring 16-byte vectors) with one load; the address is 32-byte aligned.
+__device__ __forceinline__ void ldg32(const char *p, uint4 &a, uint4 &b) {
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
+               : "l"(p));
+}
+
 constexpr int kPlanTaps = 4;  // plan entries per (pixel, slot) kept in the shared tap table; the rest is read from the plan
 
 // Pixel of local index l inside tile (ty, tx) of a (GH, GW) grid tiled TH x kTW; -1 if outside.
@@ -369,13 +376,6 @@ __device__ __forceinline__ void produce_chunk(const Gather &g, const Tap *taps, 
     *(uint4 *)(dst + r * kRowStep * 128) = acc_pack(a0);
     *(uint4 *)(dst + (r + 1) * kRowStep * 128) = acc_pack(a1);
   }
-}
-
-// 32 bytes (two neighbouring 16-byte vectors) with one load; the address is 32-byte aligned.
-__device__ __forceinline__ void ldg32(const char *p, uint4 &a, uint4 &b) {
-  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w), "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w)
-               : "l"(p));
 }
 
 // The same share cut the other way, for Cp >= 16: thread = (pixel pt >> 2, vector pair pt & 3), i.e. one pixel and
@@ -1509,8 +1509,17 @@ Geometry geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int 
   if ((SHW + 1) * g.Cp * 2 >= ((int64_t)1 << 31)) g.ok = false;
   g.wp_bytes = align_up((size_t)g.nblk * g.nchunks * g.Npb * kChunk * 2, 256);
   g.ok = g.ok && (size_t)K * kTileM * g.nt * sizeof(Tap) <= (size_t)kMaxTapBytes;
+  // Pipeline depth.  Shared memory and L1 share one 256 KB array whose split moves in steps; a CTA that asks for more
+  // than 196 KB leaves 28 KB of L1 for the gather instead of 60 KB, which costs more than a pipeline stage gains
+  // (layer-4 input gradient of the encoder: 3 stages at 207 KB 3.97 ms, 2 stages at 158 KB 3.77 ms).  So: as many stages
+  // as fit 196 KB, and only if two do not fit, as many as fit the whole array.
+  constexpr size_t kSoftLimit = 196 * 1024;
   g.stages = 4;
-  while (g.stages > 2 && gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct) > (size_t)kSmemLimit) g.stages--;
+  while (g.stages > 2 && gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct) > kSoftLimit) g.stages--;
+  if (gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct) > kSoftLimit) {
+    g.stages = 4;
+    while (g.stages > 2 && gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct) > (size_t)kSmemLimit) g.stages--;
+  }
   g.smem = gemm_smem_bytes(g.stages, g.Npb, (int)K, g.nt, direct);
   if (g.smem > (size_t)kSmemLimit) g.ok = false;
   return g;
@@ -1870,6 +1879,14 @@ size_t tc_conv_backward_workspace(int64_t B, int64_t Cin, int64_t Cout, int64_t 
   return align_up(a, 256) + dw_ws(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
 }
 
+// Tracing aid (sph_trace_phases): events the next combined backward call on this thread records at its phase boundaries.
+thread_local cudaEvent_t g_phase_events[4];
+thread_local int g_phase_count = 0;
+
+static void mark_phase(int i, cudaStream_t st) {
+  if (i < g_phase_count && g_phase_events[i] != nullptr) cudaEventRecord(g_phase_events[i], st);
+}
+
 int tc_conv_backward(const void *gout, const void *x, const void *plan, const void *map, const void *iw, const void *weight,
                      void *gx, void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
                      int64_t OW, int64_t K, int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz) {
@@ -1887,6 +1904,10 @@ int tc_conv_backward(const void *gout, const void *x, const void *plan, const vo
   char *bias_ws = ws_dw + 256 + d.xh_bytes + d.gt_bytes + d.partial_bytes;
   float *row_part = (float *)(bias_ws + simt_bias_workspace(Cout, 4));
   const size_t npix = (size_t)(OH * OW);
+  struct PhaseScope {  // the event list is consumed by this call, whatever its outcome
+    ~PhaseScope() { g_phase_count = 0; }
+  } phase_scope;
+  mark_phase(0, st);
   // the zero pixel behind every image of the channels-last copy (unused taps point there)
   if (cudaMemset2DAsync((char *)go_cl + npix * cp_go * 2, (npix + 1) * cp_go * 2, 0, (size_t)cp_go * 2, (size_t)B, st) != cudaSuccess)
     return SPH_ERR_CUDA;
@@ -1894,17 +1915,21 @@ int tc_conv_backward(const void *gout, const void *x, const void *plan, const vo
       (const float *)gout, gt, (int)Cout, (int)OH, (int)OW, d.tiles_x, d.tiles_y, d.mbs_total, row_part, (const float *)fz.mask,
       go_cl, cp_go);
   note_launches(1);
+  mark_phase(1, st);
   // channels between mbs_total * 128 and cp_go do not exist (cp_go <= mbs_total * 128), so the copy is complete
   Fusion fx;
   fx.src_cl = go_cl;  // already masked
   int rc = tc_gemm(true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH, IW, 0, weight, K, Cin * K, 1, nullptr, gx, Cin, B,
                    ws_dx, dx_bytes, st, fx);
   if (rc != SPH_OK) return rc;
+  mark_phase(2, st);
   Fusion fw;
   fw.src_cl = fz.src_cl;  // channels-last copy of x, if the caller keeps one
   fw.gt_ready = true;
-  return tc_dw(gout, x, map, iw, Cin, IH, IW, K, P, OH, OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout, OH * OW, gb, ws_dw,
-               dw_bytes, st, fw);
+  rc = tc_dw(gout, x, map, iw, Cin, IH, IW, K, P, OH, OW, interp, Cout, B, gw, Cin * K, K, 1, gout, Cout, OH * OW, gb, ws_dw,
+             dw_bytes, st, fw);
+  mark_phase(3, st);
+  return rc;
 }
 
 int tc_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out, int64_t B,
@@ -2006,6 +2031,13 @@ extern "C" int sph_build_is_checked(void) {
 #else
   return 0;
 #endif
+}
+
+extern "C" int sph_trace_phases(void **events, int n_events) {
+  if (n_events < 0 || n_events > 4 || (n_events > 0 && !events)) return SPH_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < n_events; i++) sph::g_phase_events[i] = (cudaEvent_t)events[i];
+  sph::g_phase_count = n_events;
+  return SPH_OK;
 }
 
 extern "C" int sph_debug_bounded_wait(unsigned long long limit_ns, int *status, void *stream) {

@@ -31,7 +31,7 @@ SYMBOLS = [
     "sph_device_status", "sph_debug_bounded_wait", "sph_mapped_max_unpool_planned", "sph_mapped_avg_pool",
     "sph_mapped_avg_unpool", "sph_resample_to_map_normalized", "sph_resample_from_uv_maps", "sph_plan_build_uv",
     "sph_voting_resample_to_map", "sph_build_kernel_map", "sph_build_is_checked", "sph_conv_companion_bytes",
-    "sph_conv_companion_channels", "sph_mapped_conv_forward_cl", "sph_mapped_conv_backward_cl",
+    "sph_conv_companion_channels", "sph_trace_phases", "sph_mapped_conv_forward_cl", "sph_mapped_conv_backward_cl",
 ]
 ERR_UNSUPPORTED = 2
 
@@ -399,6 +399,14 @@ def conv_forward_cl(x, x_cl, smap, weight, bias, K, interp, iw=None, precision=B
         raise Unsupported("sph_mapped_conv_forward_cl")
     _ok(rc, "sph_mapped_conv_forward_cl")
     return out
+
+
+def trace_phases(events):
+    """The next conv_backward_cl call of this thread records these torch.cuda.Event objects (up to 4, created with
+    enable_timing=True and recorded once before so that their handles exist) at its phase boundaries: entry,
+    grad_output converted, input gradient done, weight gradient done."""
+    arr = (ctypes.c_void_p * len(events))(*[ctypes.c_void_p(e.cuda_event) for e in events])
+    _ok(lib.sph_trace_phases(arr, _int(len(events))), "sph_trace_phases")
 
 
 def conv_backward_cl(go, act_out, x, x_cl, plan, smap, weight, K, interp, iw=None, precision=BF16, gx=None, ws=None):

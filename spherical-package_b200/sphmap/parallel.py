@@ -128,6 +128,9 @@ class EncoderStack:
             if self.combined[li]:     # one call: grad_output converted once for the input and the weight gradient
                 try:
                     x_cl = self.out_cl[li - 1] if li > 0 else None
+                    if self.timers is not None and (li, "bwd.phases") in self.timers:
+                        c.trace_phases(self.timers[(li, "bwd.phases")])   # entry / converted / dInput done / dW done
+                        self.timed_keys.add((li, "bwd.phases"))
                     gx, gw, gb = self._timed((li, "bwd"), lambda: c.conv_backward_cl(
                         g, self.acts[li], self.inputs[li], x_cl, self.plans[li], self.maps[li], self.w[li], self.K, self.interp,
                         None, self.prec, gx=self.gx[li], ws=self.ws[(li, c.CONV_BACKWARD)]))
