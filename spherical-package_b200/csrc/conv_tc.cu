@@ -1737,8 +1737,15 @@ DwGeometry dw_geometry(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P,
   const int mbs_cta = 8 / d.grp;
   const int mbs = d.mbs_total >= mbs_cta ? mbs_cta : 1;
   d.ok = (size_t)d.tap_rows * kDwPix * d.nt * sizeof(Tap) <= (size_t)kDwMaxTapBytes;
+  // pipeline depth: as for the forward-type kernel, stay within 196 KB of shared memory if two stages fit there
+  // (layer-4 dW of the encoder: 3 stages at 209 KB 3.62 ms, 2 stages at 145 KB 3.32 ms)
+  constexpr size_t kSoftLimit = 196 * 1024;
   d.stages = 4;
-  while (d.stages > 2 && dw_smem_bytes(d.stages, d.grp, mbs, d.tap_rows, d.nt) > (size_t)kSmemLimit) d.stages--;
+  while (d.stages > 2 && dw_smem_bytes(d.stages, d.grp, mbs, d.tap_rows, d.nt) > kSoftLimit) d.stages--;
+  if (dw_smem_bytes(d.stages, d.grp, mbs, d.tap_rows, d.nt) > kSoftLimit) {
+    d.stages = 4;
+    while (d.stages > 2 && dw_smem_bytes(d.stages, d.grp, mbs, d.tap_rows, d.nt) > (size_t)kSmemLimit) d.stages--;
+  }
   d.smem = dw_smem_bytes(d.stages, d.grp, mbs, d.tap_rows, d.nt);
   if (d.smem > (size_t)kSmemLimit) d.ok = false;
   const int64_t steps = B * d.tiles_x * d.tiles_y;
