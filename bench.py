@@ -258,7 +258,7 @@ def run_encoder(args, rank, local, world):
             h = xb
             for m, sm in zip(mods, maps):
                 h = m(h, sm) if fused else torch.relu(m(h, sm))
-            loss = (h * go).sum()
+            loss = torch.dot(h.reshape(-1), go.reshape(-1))   # sum(h * go) in one pass
             for p in params:
                 p.grad = None
             loss.backward()

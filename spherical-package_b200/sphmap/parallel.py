@@ -170,6 +170,6 @@ class EncoderStack:
 
     def step(self, x, go):
         out = self.forward(x)
-        loss = (out * go).sum()
+        loss = torch.dot(out.reshape(-1), go.reshape(-1))   # sum(out * go) in one pass, without the product tensor
         self.backward(go)
         return loss
