@@ -427,8 +427,9 @@ def run_pool(args, rank, local, world):
     out, idx = capi.mapped_max_pool(x, m, 9, 0)
     gin = torch.empty_like(x)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    ef = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-    tf, tb = [], []
+    ef = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+    tf, tb, td = [], [], []
+    plans = {}
 
     def step():
         flush.zero_()
@@ -437,15 +438,22 @@ def run_pool(args, rank, local, world):
         ef[1].record()
         flush.zero_()
         ef[2].record()
-        capi.mapped_max_unpool(go, idx, m, x.shape[2], x.shape[3], 9, 0, None, gin)
+        capi.mapped_max_unpool(go, idx, m, x.shape[2], x.shape[3], 9, 0, None, gin)      # float atomics, as the reference
         ef[3].record()
+        if id(m) not in plans:
+            plans[id(m)] = capi.slot_plan_build(m, None, 9, 0, x.shape[2], x.shape[3])
+        flush.zero_()
+        ef[4].record()
+        capi.mapped_max_unpool_planned(go, idx, plans[id(m)], x.shape[2], x.shape[3], 9, 0, gin)   # deterministic (plan walk)
+        ef[5].record()
         torch.cuda.synchronize()
         tf.append(ef[0].elapsed_time(ef[1]))
         tb.append(ef[2].elapsed_time(ef[3]))
+        td.append(ef[4].elapsed_time(ef[5]))
 
     for _ in range(args.warmup):
         step()
-    tf.clear(), tb.clear()
+    tf.clear(), tb.clear(), td.clear()
     sampler = ClockSampler(local) if rank == 0 else None
     barrier_sync(world)
     if sampler:
@@ -456,8 +464,8 @@ def run_pool(args, rank, local, world):
     # the same kernels on a map with locality (3x3 gnomonic, stride 2: what a pooling layer of a spherical network
     # uses), same tensor sizes: shows the kernels' bandwidth when the taps are not uniformly random
     ml = wl.gnomonic_map(x.shape[2], x.shape[3], 2).to(dev)
-    tf_r, tb_r = list(tf), list(tb)
-    tf.clear(), tb.clear()
+    tf_r, tb_r, det_ms = list(tf), list(tb), sum(td) / len(td)
+    tf.clear(), tb.clear(), td.clear()
     m_random, m = m, ml
     for _ in range(2 + max(3, args.steps // 2)):
         step()
@@ -492,6 +500,9 @@ def run_pool(args, rank, local, world):
                          # DRAM read+write of the forward launch from an ncu capture at B=8, scaled by the local batch
                          "traffic": int(450.7e6 * n / 8), "traffic_of": "constant from an ncu capture, not measured in this run", "fwd_ms": round(f_ms, 4), "bwd_ms": round(b_ms, 4),
                          "bwd_achieved": round(fwd_bytes / (b_ms * 1e-3) / 1e9, 1),
+                         "bwd_note": "value and bwd_ms use the atomic argmax backward (the reference's scheme); the "
+                                     "deterministic plan-walk backward the layers use by default takes bwd_deterministic_ms",
+                         "bwd_deterministic_ms": round(det_ms, 4),
                          "local_map": {"map": "3x3 gnomonic, stride 2", "fwd_ms": round(lf_ms, 4), "bwd_ms": round(lb_ms, 4),
                                        "fwd_gbs": round(fwd_bytes / (lf_ms * 1e-3) / 1e9, 1),
                                        "fwd_frac": round(fwd_bytes / (lf_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
