@@ -54,14 +54,27 @@ extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64
   if (check_dims(d, dtype, interp, precision) != SPH_OK) return 0;
   const size_t ts = dtype == SPH_F64 ? 8 : 4;
   // thin contractions (few channels on the gathered / produced side) have their own kernels in both precisions
+  const bool thin_tc = precision == SPH_PRECISION_BF16 && tc_thin_backward_ok(Cin, K, Cout, OH * OW);  // conv backward only
   switch (op) {
-    case SPH_CONV_FORWARD: if (small_ok(Cin, K, Cout, ts)) return 0; break;
-    case SPH_CONV_BACKWARD_INPUT: if (small_ok(Cin, K, Cout, ts)) return small_premul_workspace(B, Cin, K, OH * OW, ts); break;
-    case SPH_CONV_BACKWARD_WEIGHT: if (small_ok(Cin, K, Cout, ts)) return small_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts); break;
+    case SPH_CONV_FORWARD:
+      if (small_ok(Cin, K, Cout, ts))
+        return (precision == SPH_PRECISION_BF16 && tc_thin_forward_ok(Cin, K, Cout, OW)) ? tc_thin_forward_workspace(Cout) : 0;
+      break;
+    case SPH_CONV_BACKWARD_INPUT:
+      if (small_ok(Cin, K, Cout, ts))
+        return thin_tc ? tc_thin_backward_workspace(B, Cin, K, OH * OW, true) : small_premul_workspace(B, Cin, K, OH * OW, ts);
+      break;
+    case SPH_CONV_BACKWARD_WEIGHT:
+      if (small_ok(Cin, K, Cout, ts))
+        return thin_tc ? tc_thin_backward_workspace(B, Cin, K, OH * OW, false) : small_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts);
+      break;
     case SPH_TCONV_FORWARD: if (small_ok(Cout, K, Cin, ts)) return small_premul_workspace(B, Cout, K, IH * IW, ts); break;
     case SPH_TCONV_BACKWARD_INPUT: if (small_ok(Cout, K, Cin, ts)) return 0; break;
     case SPH_TCONV_BACKWARD_WEIGHT: if (small_ok(Cout, K, Cin, ts)) return small_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, ts); break;
-    case SPH_CONV_BACKWARD: if (small_ok(Cin, K, Cout, ts)) return 0; break;  // thin layers: use the separate entry points
+    case SPH_CONV_BACKWARD:  // thin layers: their own combined kernel in bf16 precision, else the separate entry points
+      if (small_ok(Cin, K, Cout, ts))
+        return thin_tc ? tc_thin_backward_workspace(B, Cin, K, OH * OW, true) : 0;
+      break;
     default: break;
   }
   if (op == SPH_CONV_BACKWARD)
@@ -87,9 +100,16 @@ int conv_forward(const void *x, const void *map, const void *iw, const void *wei
   if (!x || !map || !weight || !bias || !out || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)) {
+    // bf16 precision: one 64-column operand block per tile on the tensor cores, if the output can leave through a
+    // tensor map; else (and in the exact precision) the register-tiled kernels
+    if (precision == SPH_PRECISION_BF16 && tc_thin_forward_ok(Cin, K, Cout, OW)) {
+      const int rt = tc_thin_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
+      if (rt != SPH_ERR_UNSUPPORTED) return rt;
+    }
     return SPH_BY_DTYPE(small_fwd, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, st,
                         fz.relu_out, fz.out_cl);
+  }
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
   if (fz.active() || fz.out_cl != nullptr) return SPH_ERR_UNSUPPORTED;
@@ -108,6 +128,11 @@ int conv_backward_input(const void *gout, const void *plan, const void *weight, 
   cudaStream_t st = (cudaStream_t)stream;
   // The thin kernels are issue-bound, not memory-bound: reading the mask inside them was measured slower (layer-1 dInput
   // of the encoder 2.1 -> 4.4 ms, dW 2.6 -> 2.9 ms) than one separate masking pass (0.9 ms), so they decline the mask.
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4) && precision == SPH_PRECISION_BF16 && tc_thin_backward_ok(Cin, K, Cout, OH * OW)) {
+    const int rt = tc_thin_conv_backward(gout, fz.mask, nullptr, plan, nullptr, nullptr, weight, gx, nullptr, nullptr, B, Cin, Cout, IH, IW,
+                                         OH, OW, K, 0, 0, ws, ws_bytes, st);
+    if (rt != SPH_ERR_UNSUPPORTED) return rt;
+  }
   if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4) && fz.mask) return SPH_ERR_UNSUPPORTED;
   if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
     return SPH_BY_DTYPE(small_adjoint, gout, plan, Cout, OH * OW, K, IH * IW, weight, K, Cin * K, 1, nullptr, gx, Cin, B, ws,
@@ -131,6 +156,11 @@ int conv_backward_weight(const void *gout, const void *x, const void *map, const
   if (B == 0) {
     if (cudaMemsetAsync(gw, 0, ts * (size_t)(Cout * Cin * K), st) != cudaSuccess) return SPH_ERR_CUDA;
     return cudaMemsetAsync(gb, 0, ts * (size_t)Cout, st) == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
+  }
+  if (small_ok(Cin, K, Cout, ts) && precision == SPH_PRECISION_BF16 && tc_thin_backward_ok(Cin, K, Cout, OH * OW)) {
+    const int rt = tc_thin_conv_backward(gout, fz.mask, x, nullptr, map, iw, nullptr, nullptr, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P,
+                                         interp, ws, ws_bytes, st);
+    if (rt != SPH_ERR_UNSUPPORTED) return rt;
   }
   if (small_ok(Cin, K, Cout, ts) && fz.mask) return SPH_ERR_UNSUPPORTED;  // see conv_backward_input
   if (small_ok(Cin, K, Cout, ts))
@@ -229,7 +259,12 @@ extern "C" int sph_mapped_conv_backward_cl(const void *gout, const void *act_out
   const int rc = check_dims(d, dtype, interp, precision);
   if (rc != SPH_OK) return rc;
   if (!gout || !x || !plan || !map || !weight || !gx || !gw || !gb || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
-  if (precision != SPH_PRECISION_BF16 || B == 0 || small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)) return SPH_ERR_UNSUPPORTED;
+  if (precision != SPH_PRECISION_BF16 || B == 0) return SPH_ERR_UNSUPPORTED;
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)) {
+    if (!tc_thin_backward_ok(Cin, K, Cout, OH * OW)) return SPH_ERR_UNSUPPORTED;
+    return tc_thin_conv_backward(gout, act_out, x, plan, map, iw, weight, gx, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes,
+                                 (cudaStream_t)stream);
+  }
   Fusion fz;
   fz.mask = act_out;
   fz.src_cl = x_cl;

@@ -81,6 +81,18 @@ int tc_conv_backward(const void *gout, const void *x, const void *plan, const vo
 size_t tc_conv_backward_workspace(int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
                                   int64_t K, int64_t P, int interp);
 int padded_channels(int64_t CH);
+// Thin gathered side (channels x K <= 63) on the tensor cores, bf16 precision: see conv_tc_thin.cuh.
+bool tc_thin_backward_ok(int64_t CH, int64_t K, int64_t N, int64_t npix);
+size_t tc_thin_backward_workspace(int64_t B, int64_t CH, int64_t K, int64_t npix, bool with_dx);  // with_dx: gx is wanted
+// (a null gx, or null gw and gb, leaves that gradient out)
+int tc_thin_conv_backward(const void *gout, const void *act, const void *x, const void *plan, const void *map, const void *iw,
+                          const void *weight, void *gx, void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                          int64_t OH, int64_t OW, int64_t K, int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st);
+bool tc_thin_forward_ok(int64_t CH, int64_t K, int64_t Nout, int64_t GW);
+size_t tc_thin_forward_workspace(int64_t Nout);
+int tc_thin_conv_forward(const void *x, const void *map, const void *iw, const void *weight, const void *bias, void *out, int64_t B,
+                         int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int interp,
+                         void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz);
 int tc_tconv_forward(const void *x, const void *plan, const void *weight, const void *bias, void *out, int64_t B,
                      int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, void *ws,
                      size_t ws_bytes, cudaStream_t st);

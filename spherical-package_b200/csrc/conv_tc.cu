@@ -1838,6 +1838,36 @@ size_t dw_ws(int64_t B, int64_t CH, int64_t SHW, int64_t K, int64_t P, int inter
 
 }  // namespace
 
+// Tracing aid (sph_trace_phases): events the next combined backward call on this thread records at its phase boundaries.
+thread_local cudaEvent_t g_phase_events[4];
+thread_local int g_phase_count = 0;
+
+static void mark_phase(int i, cudaStream_t st) {
+  if (i < g_phase_count && g_phase_events[i] != nullptr) cudaEventRecord(g_phase_events[i], st);
+}
+
+namespace {
+#include "conv_tc_thin.cuh"
+}  // namespace
+
+bool tc_thin_backward_ok(int64_t CH, int64_t K, int64_t N, int64_t npix) { return thin_bwd_ok(CH, K, N, npix); }
+size_t tc_thin_backward_workspace(int64_t B, int64_t CH, int64_t K, int64_t npix, bool with_dx) {
+  return thin_bwd_layout(B, CH, K, npix, with_dx).total;
+}
+int tc_thin_conv_backward(const void *gout, const void *act, const void *x, const void *plan, const void *map, const void *iw,
+                          const void *weight, void *gx, void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                          int64_t OH, int64_t OW, int64_t K, int64_t P, int interp, void *ws, size_t ws_bytes, cudaStream_t st) {
+  return tc_thin_backward(gout, act, x, plan, map, iw, weight, gx, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
+}
+
+bool tc_thin_forward_ok(int64_t CH, int64_t K, int64_t Nout, int64_t GW) { return thin_fwd_ok(CH, K, Nout, GW); }
+size_t tc_thin_forward_workspace(int64_t Nout) { return thin_fwd_workspace(Nout); }
+int tc_thin_conv_forward(const void *x, const void *map, const void *iw, const void *weight, const void *bias, void *out, int64_t B,
+                         int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int interp,
+                         void *ws, size_t ws_bytes, cudaStream_t st, const Fusion &fz) {
+  return tc_thin_forward(x, map, iw, Cin, IH, IW, K, P, OH, OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, ws, ws_bytes, st, fz);
+}
+
 size_t tc_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
                           int64_t K, int64_t P, int interp) {
   switch (op) {
@@ -1884,14 +1914,6 @@ size_t tc_conv_backward_workspace(int64_t B, int64_t Cin, int64_t Cout, int64_t 
   const DwGeometry d = dw_geometry(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
   if (a == 0 || !d.ok) return 0;
   return align_up(a, 256) + dw_ws(B, Cin, IH * IW, K, P, interp, Cout, OH, OW, Cout);
-}
-
-// Tracing aid (sph_trace_phases): events the next combined backward call on this thread records at its phase boundaries.
-thread_local cudaEvent_t g_phase_events[4];
-thread_local int g_phase_count = 0;
-
-static void mark_phase(int i, cudaStream_t st) {
-  if (i < g_phase_count && g_phase_events[i] != nullptr) cudaEventRecord(g_phase_events[i], st);
 }
 
 int tc_conv_backward(const void *gout, const void *x, const void *plan, const void *map, const void *iw, const void *weight,

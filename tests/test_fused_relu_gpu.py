@@ -189,10 +189,15 @@ def test_companions_and_combined_backward_are_bit_identical_to_the_separate_call
     assert torch.equal(gx, gx_ref) and torch.equal(gw, gw_ref) and torch.equal(gb, gb_ref)
     gx, gw, gb = capi.conv_backward_cl(go * (c2 > 0), None, c1, cl1, plan2, m2, w2, K, 1, None, capi.BF16)   # unfused mask
     assert torch.equal(gx, gx_ref) and torch.equal(gw, gw_ref) and torch.equal(gb, gb_ref)
-    # thin layers and exact precision decline the combined call before launching anything
+    # a thin layer (3 input channels) has its own combined kernel in bf16 precision: same results as its separate
+    # entry points; the exact precision declines the combined call before launching anything
     plan1 = capi.plan_build(m1, None, n1, K, 1, H, W)
+    tx, tw, tb = capi.conv_backward_cl(gx_ref, a1, x, None, plan1, m1, w1, K, 1, None, capi.BF16)
+    assert torch.equal(tx, capi.conv_relu_backward_input(gx_ref, a1, plan1, w1, H, W, K, capi.BF16))
+    sw, sb = capi.conv_relu_backward_weight(gx_ref, a1, x, m1, K, 1, None, capi.BF16)
+    assert torch.equal(tw, sw) and torch.equal(tb, sb)
     with pytest.raises(capi.Unsupported):
-        capi.conv_backward_cl(gx_ref, a1, x, None, plan1, m1, w1, K, 1, None, capi.BF16)
+        capi.conv_backward_cl(gx_ref, a1, x, None, plan1, m1, w1, K, 1, None, capi.EXACT)
     # ragged sizes (tiles with tail pixels, width not a multiple of 4 -> plain-store epilogue) and a down-sampling map
     xr = torch.randn(1, 72, 13, 22, generator=g).cuda()
     mr = (torch.rand(13, 22, 5, 2, generator=g) * torch.tensor([23.0, 14.0]) - 0.5).cuda()

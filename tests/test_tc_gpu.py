@@ -97,3 +97,58 @@ def test_bf16_path_is_deterministic():
     c = tc.mapped_conv_backward(go, m, x, w, b, 9, 1, None)
     for u, v in zip(a, c):
         assert torch.equal(u, v)
+
+
+# Thin gathered side (channels x K <= 63): one 64-column operand block per tile (forward) and the combined
+# dW / dBias / multiply-first dInput kernel (backward).  Shapes outside their cover fall back to the exact kernels.
+THIN_CASES = [
+    # seed, B, Cin, Cout, IH, IW, OH, OW, K, interp, P, gnomonic
+    (21, 3, 3, 64, 64, 128, 32, 64, 9, 1, 0, True),      # RGB first layer, stride-2 gnomonic map
+    (22, 2, 1, 16, 20, 24, 10, 12, 4, 0, 0, False),      # one channel, nearest, 120 pixels: a partial last step
+    (23, 2, 4, 32, 18, 40, 9, 16, 9, 2, 0, False),       # bispherical
+    (24, 1, 2, 48, 16, 32, 16, 32, 5, 1, 2, False),      # weighted bilinear, two points per slot
+    (25, 2, 3, 64, 30, 50, 15, 25, 9, 1, 0, False),      # width not a multiple of 4, 375 pixels: the exact kernels
+    (26, 2, 3, 128, 32, 64, 16, 32, 9, 1, 0, True),      # forward thin (N = 128), backward on the exact kernels
+    (27, 5, 3, 64, 16, 32, 8, 16, 7, 1, 0, False),       # five images (a partial image group in the plan gather)
+]
+
+
+@pytest.mark.parametrize("case", THIN_CASES, ids=lambda c: "s%d" % c[0])
+def test_thin_layer_bf16(case):
+    from sphmap import capi
+    seed, B, Cin, Cout, IH, IW, OH, OW, K, interp, P, gn = case
+    x, w, b, m, iw, go = _case(seed, B, Cin, Cout, IH, IW, OH, OW, K, interp, P, gn)
+    ref = port.mapped_conv_forward(x, m, w, b, K, interp, iw)
+    rgx, rgw, rgb = port.mapped_conv_backward(go * (ref > 0), m, x, w, b, K, interp, iw)
+    d = lambda t: None if t is None else t.cuda()
+    xd, wd, bd, md, iwd, god = d(x), d(w), d(b), d(m), d(iw), d(go)
+    # forward with the fused ReLU and the channels-last copy of the output
+    cl = capi.companion(B, Cout, OH, OW, "cuda") if Cout % 8 == 0 else None
+    try:
+        out = capi.conv_forward_cl(xd, None, md, wd, bd, K, interp, iwd, capi.BF16, True, out_cl=cl)
+    except capi.Unsupported:
+        cl = None
+        out = capi.conv_forward_cl(xd, None, md, wd, bd, K, interp, iwd, capi.BF16, True, out_cl=None)
+    _close(out.cpu(), ref.clamp(min=0), "forward + relu")
+    if cl is not None:
+        import ctypes
+        cp = int(capi.lib.sph_conv_companion_channels(ctypes.c_int64(Cout)))
+        v = cl[:B * (OH * OW + 1) * cp * 2].view(torch.bfloat16).view(B, OH * OW + 1, cp)
+        assert torch.equal(v[:, :OH * OW, :Cout].float(), out.to(torch.bfloat16).float().flatten(2).transpose(1, 2))
+        assert (v[:, OH * OW] == 0).all() and (v[:, :, Cout:] == 0).all()
+    # backward: the combined call where it applies, and the separate entry points (same kernels, same results)
+    act = (ref > 0).float().cuda()     # the oracle's activation pattern, so that the masks agree
+    plan = capi.plan_build(md, iwd, OH * OW, K, interp, IH, IW)
+    gx = capi.conv_relu_backward_input(god, act, plan, wd, IH, IW, K, capi.BF16)
+    gw, gb = capi.conv_relu_backward_weight(god, act, xd, md, K, interp, iwd, capi.BF16)
+    _close(gx.cpu(), rgx, "grad_input")
+    _close(gw.cpu(), rgw, "grad_weight")
+    _close(gb.cpu(), rgb, "grad_bias")
+    try:
+        cx, cw, cb = capi.conv_backward_cl(god, act, xd, None, plan, md, wd, K, interp, iwd, capi.BF16)
+    except capi.Unsupported:
+        assert Cout > 64 or (OH * OW) % 8 != 0
+    else:
+        assert torch.equal(cx, gx) and torch.equal(cw, gw) and torch.equal(cb, gb)
+        cx2, cw2, cb2 = capi.conv_backward_cl(god, act, xd, None, plan, md, wd, K, interp, iwd, capi.BF16)
+        assert torch.equal(cx, cx2) and torch.equal(cw, cw2) and torch.equal(cb, cb2)   # run-to-run identical
