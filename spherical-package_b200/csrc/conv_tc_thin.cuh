@@ -55,6 +55,83 @@ __device__ __forceinline__ void thin_gather_row(const ThinFwdParams &p, const fl
   }
 }
 
+// The common case spelled out: bilinear, one point per slot, CHT (1..4) channels.  Slots are taken two at a time so
+// that their 2 * CHT values leave as aligned bf16 pairs; the interpolation uses fused multiply-adds (the value is
+// rounded to bf16 anyway) and 32-bit offsets; the map coordinates of the next slot pair are loaded a pair ahead.
+__device__ __forceinline__ void thin_store_pair(uint32_t row_s, int l, int j, float a, float b) {
+  const uint32_t addr = row_s + ((((uint32_t)j >> 3) ^ ((uint32_t)l & 7u)) << 4) + (((uint32_t)j & 7u) << 1);
+  sts32(addr, pack_bf16(a, b));
+}
+__device__ __forceinline__ void thin_store_one(uint32_t row_s, int l, int j, float a) {
+  const uint32_t addr = row_s + ((((uint32_t)j >> 3) ^ ((uint32_t)l & 7u)) << 4) + (((uint32_t)j & 7u) << 1);
+  asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(__bfloat16_as_ushort(__float2bfloat16(a))) : "memory");
+}
+template <int CHT>
+__device__ __forceinline__ void thin_bilinear_slot(const float *__restrict__ img, int plane, int SH, int SW, float2 xy, float (&v)[CHT]) {
+  const float xf = floorf(xy.x), yf = floorf(xy.y);
+  const int x1 = (int)xf, y1 = (int)yf;
+  const float C = xy.x - xf, D = xy.y - yf, B = (xf + 1.0f) - xy.x, A = (yf + 1.0f) - xy.y;
+  const bool sane = fabsf(xy.x) < 1e9f && fabsf(xy.y) < 1e9f;
+  const bool vx1 = sane && (unsigned)x1 < (unsigned)SW, vx2 = sane && (unsigned)(x1 + 1) < (unsigned)SW;
+  const bool vy1 = (unsigned)y1 < (unsigned)SH, vy2 = (unsigned)(y1 + 1) < (unsigned)SH;
+  const int o00 = y1 * SW + x1;
+  const bool p0 = vx1 && vy1, p1 = vx2 && vy1, p2 = vx1 && vy2, p3 = vx2 && vy2;
+  const float w0 = A * B, w1 = A * C, w2 = D * B, w3 = D * C;
+#pragma unroll
+  for (int c = 0; c < CHT; c++) {
+    const float *pc = img + c * plane;
+    const float a0 = (p0 && index_ok(o00, plane)) ? __ldg(pc + o00) : 0.0f;
+    const float a1 = (p1 && index_ok(o00 + 1, plane)) ? __ldg(pc + o00 + 1) : 0.0f;
+    const float a2 = (p2 && index_ok(o00 + SW, plane)) ? __ldg(pc + o00 + SW) : 0.0f;
+    const float a3 = (p3 && index_ok(o00 + SW + 1, plane)) ? __ldg(pc + o00 + SW + 1) : 0.0f;
+    v[c] = fmaf(w3, a3, fmaf(w2, a2, fmaf(w1, a1, w0 * a0)));
+  }
+}
+template <int CHT>
+__device__ __forceinline__ void thin_gather_row_bilinear(const ThinFwdParams &p, const float *__restrict__ img, int pix, uint32_t row_s,
+                                                         int l) {
+  const int plane = p.SH * p.SW;
+  const float2 *m = (const float2 *)p.map + (size_t)pix * p.K;
+  int k = 0;
+  float2 c0 = __ldg(m), c1 = p.K > 1 ? __ldg(m + 1) : make_float2(0.0f, 0.0f);
+  for (; k + 1 < p.K; k += 2) {
+    const float2 n0 = k + 2 < p.K ? __ldg(m + k + 2) : make_float2(0.0f, 0.0f);
+    const float2 n1 = k + 3 < p.K ? __ldg(m + k + 3) : make_float2(0.0f, 0.0f);
+    float v[2 * CHT];
+    thin_bilinear_slot<CHT>(img, plane, p.SH, p.SW, c0, *(float(*)[CHT])(v));
+    thin_bilinear_slot<CHT>(img, plane, p.SH, p.SW, c1, *(float(*)[CHT])(v + CHT));
+#pragma unroll
+    for (int i = 0; i < CHT; i++) thin_store_pair(row_s, l, k * CHT + 2 * i, v[2 * i], v[2 * i + 1]);
+    c0 = n0;
+    c1 = n1;
+  }
+  if (k < p.K) {  // odd K: the last slot alone
+    float v[CHT];
+    thin_bilinear_slot<CHT>(img, plane, p.SH, p.SW, c0, v);
+    const int j0 = k * CHT;  // even when k is even
+#pragma unroll
+    for (int i = 0; i + 1 < CHT; i += 2) thin_store_pair(row_s, l, j0 + i, v[i], v[i + 1]);
+    if (CHT & 1) thin_store_one(row_s, l, j0 + CHT - 1, v[CHT - 1]);
+  }
+}
+
+// Row of one pixel, by the fastest form that covers the call.
+template <int INTERP>
+__device__ __forceinline__ void thin_row(const ThinFwdParams &p, const float *__restrict__ img, int pix, uint32_t row_s, int l) {
+  if constexpr (INTERP == SPH_BILINEAR) {
+    if (p.P == 0 && p.SH * p.SW < (1 << 30)) {
+      switch (p.CH) {
+        case 1: thin_gather_row_bilinear<1>(p, img, pix, row_s, l); return;
+        case 2: thin_gather_row_bilinear<2>(p, img, pix, row_s, l); return;
+        case 3: thin_gather_row_bilinear<3>(p, img, pix, row_s, l); return;
+        case 4: thin_gather_row_bilinear<4>(p, img, pix, row_s, l); return;
+        default: break;
+      }
+    }
+  }
+  thin_gather_row<INTERP>(p, img, pix, row_s, l);
+}
+
 template <int INTERP>
 __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_fwd_kernel(const ThinFwdParams p, const __grid_constant__ CUtensorMap out_map,
                                                                        const __grid_constant__ CUtensorMap cl_map) {
@@ -172,7 +249,7 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_fwd_kernel(const Thin
       const int pix = tile_pixel(l, t2 / p.tiles_x, t2 % p.tiles_x, kTH, p.GH, p.GW);
       const bool ok = mbar_wait(empty + grp, (n & 1) ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, ok)) break;  // the whole warp leaves together
-      if (pix >= 0) thin_gather_row<INTERP>(p, p.src + (size_t)b * p.CH * p.SH * p.SW, pix, row_s, l);
+      if (pix >= 0) thin_row<INTERP>(p, p.src + (size_t)b * p.CH * p.SH * p.SW, pix, row_s, l);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(full + grp);
@@ -454,7 +531,7 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_bwd_kernel(const Thin
       } else if (valid) {
         ThinFwdParams f{};
         f.map = p.map; f.iw = p.iw; f.CH = p.CH; f.SH = p.SH; f.SW = p.SW; f.K = p.K; f.P = p.P;
-        thin_gather_row<INTERP>(f, p.src + (size_t)b * p.CH * p.SH * p.SW, pix, row_s, lt);
+        thin_row<INTERP>(f, p.src + (size_t)b * p.CH * p.SH * p.SW, pix, row_s, lt);
       } else {
         for (int c = 0; c < 8; c++) sts128(row_s + (c << 4), make_uint4(0, 0, 0, 0));
       }
