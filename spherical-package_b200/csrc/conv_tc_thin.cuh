@@ -344,7 +344,8 @@ struct ThinBwdParams {
   const float *src;          // (B, CH, SH, SW) input of the convolution
   const float *map, *iw;
   const __nv_bfloat16 *wt;   // [128 rows j][64 columns o] bf16, 128B-swizzled: W[o, c, k] at row j = k*CH + c
-  __nv_bfloat16 *t2;         // (B, CH*K, npix) bf16 out
+  __nv_bfloat16 *t2;         // (B, npix, t2_pitch bytes) out: per pixel K slots of four bf16 (channels 0..CH-1, then zeros)
+  int t2_pitch;
   float *partial;            // [grid][64 rows o][64 columns j] fp32 out
   int *status;
   int B, N, CH, SH, SW, K, P, npix, steps_per_image;
@@ -352,7 +353,7 @@ struct ThinBwdParams {
   long long total_steps;
 };
 
-inline size_t thin_bwd_smem() { return 1024 + (size_t)kThinBwdTeams * kThinBwdStage + 128 * 128 + 8 * 16 + 16; }
+inline size_t thin_bwd_smem() { return 1024 + (size_t)kThinBwdTeams * kThinBwdStage + 128 * 128 + 64 * 33 * 4 + 8 * 16 + 16; }
 
 template <int INTERP>
 __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_bwd_kernel(const ThinBwdParams p) {
@@ -360,7 +361,8 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_bwd_kernel(const Thin
   uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *stages = base;
   uint8_t *Wt = stages + kThinBwdTeams * kThinBwdStage;
-  uint64_t *full = (uint64_t *)(Wt + 128 * 128);
+  uint32_t *tr = (uint32_t *)(Wt + 128 * 128);  // [64 rows][33 words]: D2 rows on their way to the pixel-major T2
+  uint64_t *full = (uint64_t *)(tr + 64 * 33);  // 8448 bytes on: still 8-byte aligned
   uint64_t *empty = full + kThinBwdTeams, *t2full = empty + kThinBwdTeams, *t2empty = t2full + 2, *d1full = t2empty + 2;
   uint32_t *tmem_ptr = (uint32_t *)(d1full + 1);
   volatile int *abort_flag = (volatile int *)(tmem_ptr + 1);
@@ -400,6 +402,11 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_bwd_kernel(const Thin
     // ---------------- epilogue: D2 of every step -> T2; D1 at the end -> partial sums ----------------
     if (p.do_dx && warp < t2_warps) {
       const int j = warp * 32 + lane;
+      const uint32_t tr_s = smem_u32(tr);
+      auto epi_sync = [&]() {
+        if (t2_warps == 1) __syncwarp();
+        else asm volatile("bar.sync 2, 64;" ::: "memory");
+      };
       for (int i = 0; i < nsteps; i++) {
         const int u = i & 1;
         if (!mbar_wait(t2full + u, (i >> 1) & 1, abort_flag)) break;
@@ -430,11 +437,31 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_bwd_kernel(const Thin
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(t2empty + u);  // the accumulator is in registers: the next product may overwrite it
-        if (j < ncols) {
-          __nv_bfloat16 *row = p.t2 + ((size_t)b * ncols + j) * p.npix + px0;
+        // Row j of D2 holds one column for 64 pixels; T2 wants, per pixel, the CH values of every slot side by side
+        // (one 8-byte vector per slot).  The rows go through shared memory ([j][33 words]: conflict-free both ways) and
+        // come back pixel by pixel.
+        epi_sync();  // the previous step's rows have been read
 #pragma unroll
-          for (int c = 0; c < 8; c++)
-            if (px0 + 8 * c < p.npix) *(uint4 *)(row + 8 * c) = q[c];
+        for (int c = 0; c < 8; c++) {
+          const uint32_t a = tr_s + (uint32_t)(j * 33 + 4 * c) * 4;
+          sts32(a, q[c].x); sts32(a + 4, q[c].y); sts32(a + 8, q[c].z); sts32(a + 12, q[c].w);
+        }
+        epi_sync();
+        for (int px = warp * 32 + lane; px < kThinBwdPix; px += 32 * t2_warps) {
+          if (px0 + px >= p.npix) continue;
+          char *row = (char *)p.t2 + ((size_t)b * p.npix + px0 + px) * p.t2_pitch;
+          const uint32_t col_s = tr_s + (uint32_t)(px >> 1) * 4 + (px & 1) * 2;
+          for (int k = 0; k < p.K; k++) {
+            uint32_t h[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+              if (c < p.CH) {
+                unsigned short t;
+                asm volatile("ld.shared.u16 %0, [%1];" : "=h"(t) : "r"(col_s + (uint32_t)((k * p.CH + c) * 33) * 4));
+                h[c] = t;
+              }
+            *(uint2 *)(row + k * 8) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+          }
         }
       }
     }
@@ -578,23 +605,24 @@ __global__ void thin_dw_reduce_kernel(const float *__restrict__ partial, int npa
   else gw[o * so + (j % CH) * sc + (j / CH) * sk] = s;
 }
 
-// gx[b, c, q] = sum over the plan entries (p, k, w) of destination pixel q of w * T2[b][k*CH + c][p], in plan order.
-// Thread = destination pixel x IMG images; neighbouring pixels read neighbouring elements of the same T2 planes.
-template <int CHT, int IMG>
-__global__ void __launch_bounds__(256) thin_plan_gather_kernel(const __nv_bfloat16 *__restrict__ t2, const void *__restrict__ plan_blob,
-                                                               float *__restrict__ gx, int B, int CH, int K, int n_src, int n_dst) {
+// gx[b, c, q] = sum over the plan entries (p, k, w) of destination pixel q of w * T2[b][p][k][c], in plan order.
+// Thread = destination pixel x IMG images: per entry one 8-byte load per image fetches all channels of the slot.
+template <int IMG>
+__global__ void __launch_bounds__(256) thin_plan_gather_kernel(const __nv_bfloat16 *__restrict__ t2, int t2_pitch,
+                                                               const void *__restrict__ plan_blob, float *__restrict__ gx, int B, int CH,
+                                                               int K, int n_src, int n_dst) {
   const int q = blockIdx.x * blockDim.x + threadIdx.x, b0 = blockIdx.y * IMG;
   if (q >= n_dst) return;
   bool ok;
   const PlanView<float> pv = plan_view<float>(plan_blob, n_dst * K, ok);
-  const int ch = CHT > 0 ? CHT : CH;
   const int nimg = min(IMG, B - b0);
-  const size_t img_stride = (size_t)ch * K * n_src;
-  float acc[IMG][CHT > 0 ? CHT : 4];
+  const size_t img_stride = (size_t)n_src * t2_pitch;
+  const char *base = (const char *)t2 + (size_t)b0 * img_stride;
+  float acc[IMG][4];
 #pragma unroll
   for (int bi = 0; bi < IMG; bi++)
 #pragma unroll
-    for (int c = 0; c < (CHT > 0 ? CHT : 4); c++) acc[bi][c] = 0.0f;
+    for (int c = 0; c < 4; c++) acc[bi][c] = 0.0f;
   if (ok) {
     int e1 = __ldg(pv.offsets + (size_t)q * K);
     for (int k = 0; k < K; k++) {
@@ -604,15 +632,16 @@ __global__ void __launch_bounds__(256) thin_plan_gather_kernel(const __nv_bfloat
         const int sp = __ldg(pv.src + e);
         if (!index_ok(sp, pv.n_src)) continue;
         const float w = __ldg(pv.w + e);
-        const unsigned short *base = (const unsigned short *)t2 + (size_t)b0 * img_stride + (size_t)(k * ch) * n_src + sp;
+        const char *pe = base + (size_t)sp * t2_pitch + k * 8;
+        uint2 v[IMG];
+#pragma unroll
+        for (int bi = 0; bi < IMG; bi++) v[bi] = bi < nimg ? __ldg((const uint2 *)(pe + bi * img_stride)) : make_uint2(0, 0);
 #pragma unroll
         for (int bi = 0; bi < IMG; bi++) {
-          if (bi < nimg) {
-#pragma unroll
-            for (int c = 0; c < (CHT > 0 ? CHT : 4); c++)
-              if (c < ch)
-                acc[bi][c] = fmaf(w, __uint_as_float((uint32_t)__ldg(base + bi * img_stride + (size_t)c * n_src) << 16), acc[bi][c]);
-          }
+          acc[bi][0] = fmaf(w, bf16_lo(v[bi].x), acc[bi][0]);
+          acc[bi][1] = fmaf(w, bf16_hi(v[bi].x), acc[bi][1]);
+          acc[bi][2] = fmaf(w, bf16_lo(v[bi].y), acc[bi][2]);
+          acc[bi][3] = fmaf(w, bf16_hi(v[bi].y), acc[bi][3]);
         }
       }
     }
@@ -621,14 +650,15 @@ __global__ void __launch_bounds__(256) thin_plan_gather_kernel(const __nv_bfloat
   for (int bi = 0; bi < IMG; bi++)
     if (bi < nimg)
 #pragma unroll
-      for (int c = 0; c < (CHT > 0 ? CHT : 4); c++)
-        if (c < ch) gx[((size_t)(b0 + bi) * ch + c) * n_dst + q] = acc[bi][c];
+      for (int c = 0; c < 4; c++)
+        if (c < CH) gx[((size_t)(b0 + bi) * CH + c) * n_dst + q] = acc[bi][c];
 }
 
 // Shapes the thin tensor-core backward covers.
 inline bool thin_bwd_ok(int64_t CH, int64_t K, int64_t N, int64_t npix) {
   return CH * K <= kThinMaxCols && CH <= 4 && N % 8 == 0 && N <= 64 && npix % 8 == 0;
 }
+inline size_t thin_t2_pitch(int64_t K) { return align_up((size_t)K * 8, 16); }  // bytes of T2 per pixel
 struct ThinBwdLayout {
   size_t off_wt, off_partial, off_t2, total;
   int grid;
@@ -640,7 +670,7 @@ inline ThinBwdLayout thin_bwd_layout(int64_t B, int64_t CH, int64_t K, int64_t n
   size_t o = 256;
   L.off_wt = o;      o = align_up(o + 128 * kChunk * 2, 256);
   L.off_partial = o; o = align_up(o + (size_t)L.grid * 64 * 64 * 4, 256);
-  L.off_t2 = o;      o = align_up(o + (with_t2 ? (size_t)(B * CH * K * npix) * 2 : 0), 256);
+  L.off_t2 = o;      o = align_up(o + (with_t2 ? (size_t)(B * npix) * thin_t2_pitch(K) : 0), 256);
   L.total = o;
   return L;
 }
@@ -676,6 +706,7 @@ int tc_thin_backward(const void *gout, const void *act, const void *x, const voi
   p.steps_per_image = (int)((npix + kThinBwdPix - 1) / kThinBwdPix);
   p.total_steps = (long long)B * p.steps_per_image;
   p.do_dw = do_dw ? 1 : 0; p.do_dx = do_dx ? 1 : 0;
+  p.t2_pitch = (int)thin_t2_pitch(K);
   struct PhaseScope {  // the event list is consumed by this call, whatever its outcome
     ~PhaseScope() { g_phase_count = 0; }
   } phase_scope;
@@ -689,13 +720,10 @@ int tc_thin_backward(const void *gout, const void *act, const void *x, const voi
     thin_dw_reduce_kernel<<<cdiv(N * (CH * K + 1), 128), 128, 0, st>>>(p.partial, L.grid, (int)N, (int)CH, (int)K, CH * K, K, 1, (float *)gw,
                                                                       (float *)gb);
   mark_phase(2, st);
-  constexpr int kImg = 4;
+  constexpr int kImg = 8;
   const dim3 grid(cdiv(SH * SW, 256), (unsigned)cdiv(B, kImg));
-  if (!do_dx) {
-  } else if (CH == 3)
-    thin_plan_gather_kernel<3, kImg><<<grid, 256, 0, st>>>(p.t2, plan, (float *)gx, (int)B, (int)CH, (int)K, (int)npix, (int)(SH * SW));
-  else
-    thin_plan_gather_kernel<0, kImg><<<grid, 256, 0, st>>>(p.t2, plan, (float *)gx, (int)B, (int)CH, (int)K, (int)npix, (int)(SH * SW));
+  if (do_dx)
+    thin_plan_gather_kernel<kImg><<<grid, 256, 0, st>>>(p.t2, p.t2_pitch, plan, (float *)gx, (int)B, (int)CH, (int)K, (int)npix, (int)(SH * SW));
   mark_phase(3, st);
   return launch_status(4);
 }
