@@ -23,7 +23,7 @@ struct ThinFwdParams {
 };
 
 inline size_t thin_fwd_smem(int Npb) {
-  return 1024 + 2 * (size_t)kAStageBytes + (size_t)Npb * 128 + kOutStageBytes + 8 * 8 + 16;
+  return 1024 + 2 * (size_t)kAStageBytes + (size_t)Npb * 128 + (((size_t)Npb * 4 + 127) & ~(size_t)127) + kOutStageBytes + 8 * 8 + 16;
 }
 
 // One producer thread's pixel: columns j = slot * CH + c, interpolated in float32 from the planes and stored as bf16
@@ -139,7 +139,8 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_fwd_kernel(const Thin
   uint8_t *base = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *A = base;                                   // two operand stages, one per producer group
   uint8_t *Bw = A + 2 * kAStageBytes;                  // weight block, resident
-  float *ostage = (float *)(Bw + (size_t)p.Npb * 128); // epilogue staging (128-byte aligned)
+  float *bias_s = (float *)(Bw + (size_t)p.Npb * 128);  // bias (zeros if there is none), padded to 128 bytes
+  float *ostage = (float *)((uint8_t *)bias_s + (((size_t)p.Npb * 4 + 127) & ~(size_t)127));  // epilogue staging (128-byte aligned)
   uint64_t *full = (uint64_t *)((uint8_t *)ostage + kOutStageBytes);
   uint64_t *empty = full + 2, *tfull = empty + 2, *tempty = tfull + 2;
   uint32_t *tmem_ptr = (uint32_t *)(tempty + 2);
@@ -159,6 +160,7 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_fwd_kernel(const Thin
   // operand stages start as zeros (the padding columns are never written again); the weight block is copied once
   for (int i = tid; i < 2 * kAStageBytes / 16; i += kThinThreads) ((uint4 *)A)[i] = make_uint4(0, 0, 0, 0);
   for (int i = tid; i < p.Npb * 8; i += kThinThreads) ((uint4 *)Bw)[i] = __ldg((const uint4 *)p.wp + i);
+  for (int i = tid; i < p.Npb; i += kThinThreads) bias_s[i] = (p.bias && i < p.Nout) ? __ldg(p.bias + i) : 0.0f;
   fence_proxy_async();
   if (warp == kEpilogueWarps) {
     tmem_alloc(tmem_ptr, (uint32_t)p.tmem_cols);
@@ -191,7 +193,10 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_fwd_kernel(const Thin
         tmem_ld_32x16(taddr + n0, h);
         float bv[16];
 #pragma unroll
-        for (int j = 0; j < 16; j++) bv[j] = (p.bias && n0 + j < p.Nout) ? __ldg(p.bias + n0 + j) : 0.0f;
+        for (int j = 0; j < 16; j += 4) {
+          const float4 t = *(const float4 *)(bias_s + n0 + j);
+          bv[j] = t.x; bv[j + 1] = t.y; bv[j + 2] = t.z; bv[j + 3] = t.w;
+        }
         tmem_ld_wait();
         if (lane == 0) bulk_wait_read();  // the previous pass has left the staging rows
         __syncwarp();
@@ -354,6 +359,17 @@ struct ThinBwdParams {
 };
 
 inline size_t thin_bwd_smem() { return 1024 + (size_t)kThinBwdTeams * kThinBwdStage + 128 * 128 + 64 * 33 * 4 + 8 * 16 + 16; }
+
+// 16 bytes that are read once: kept out of L1, which the gather needs
+__device__ __forceinline__ float4 ldg_stream(const float *p) {
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 thin_mask_pack(const float4 &g0, const float4 &g1, const float4 &a0, const float4 &a1) {
+  return make_uint4(pack_bf16(a0.x > 0.0f ? g0.x : 0.0f, a0.y > 0.0f ? g0.y : 0.0f), pack_bf16(a0.z > 0.0f ? g0.z : 0.0f, a0.w > 0.0f ? g0.w : 0.0f),
+                    pack_bf16(a1.x > 0.0f ? g1.x : 0.0f, a1.y > 0.0f ? g1.y : 0.0f), pack_bf16(a1.z > 0.0f ? g1.z : 0.0f, a1.w > 0.0f ? g1.w : 0.0f));
+}
 
 template <int INTERP>
 __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_bwd_kernel(const ThinBwdParams p) {
@@ -532,23 +548,22 @@ __global__ void __launch_bounds__(kThinThreads, 2) tc_thin_bwd_kernel(const Thin
       // G: chunk q = (channel o = q >> 3, pixels 8 * (q & 7) ...), consecutive threads on consecutive chunks
       const float *gb_ = p.gout + (size_t)b * p.N * p.npix + px0;
       const float *ab_ = p.act ? p.act + (size_t)b * p.N * p.npix + px0 : nullptr;
-      for (int q = lt; q < nchunks; q += 64) {
-        const int o = q >> 3, c = q & 7;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (px0 + 8 * c < p.npix) {  // npix is a multiple of 8: a chunk is inside or outside as a whole
-          const float4 g0 = __ldg((const float4 *)(gb_ + (size_t)o * p.npix + 8 * c));
-          const float4 g1 = __ldg((const float4 *)(gb_ + (size_t)o * p.npix + 8 * c + 4));
-          float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-          if (ab_) {
-            const float4 a0 = __ldg((const float4 *)(ab_ + (size_t)o * p.npix + 8 * c));
-            const float4 a1 = __ldg((const float4 *)(ab_ + (size_t)o * p.npix + 8 * c + 4));
-            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
-            for (int e = 0; e < 8; e++) g[e] = a[e] > 0.0f ? g[e] : 0.0f;
-          }
-          v = make_uint4(pack_bf16(g[0], g[1]), pack_bf16(g[2], g[3]), pack_bf16(g[4], g[5]), pack_bf16(g[6], g[7]));
+      const float4 one = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+      for (int q = lt; q < nchunks; q += 128) {  // two chunks' loads in flight
+        const int q2 = q + 64;
+        const int o = q >> 3, c = q & 7, o2 = q2 >> 3;  // (q2 & 7 == c)
+        const bool in = px0 + 8 * c < p.npix, in2 = in && q2 < nchunks;  // npix is a multiple of 8: whole chunks
+        float4 g0 = make_float4(0, 0, 0, 0), g1 = g0, h0 = g0, h1 = g0, a0 = one, a1 = one, e0 = one, e1 = one;
+        if (in) {
+          g0 = ldg_stream(gb_ + (size_t)o * p.npix + 8 * c); g1 = ldg_stream(gb_ + (size_t)o * p.npix + 8 * c + 4);
+          if (ab_) { a0 = ldg_stream(ab_ + (size_t)o * p.npix + 8 * c); a1 = ldg_stream(ab_ + (size_t)o * p.npix + 8 * c + 4); }
         }
-        sts128(g_s + o * 128 + ((c ^ (o & 7)) << 4), v);
+        if (in2) {
+          h0 = ldg_stream(gb_ + (size_t)o2 * p.npix + 8 * c); h1 = ldg_stream(gb_ + (size_t)o2 * p.npix + 8 * c + 4);
+          if (ab_) { e0 = ldg_stream(ab_ + (size_t)o2 * p.npix + 8 * c); e1 = ldg_stream(ab_ + (size_t)o2 * p.npix + 8 * c + 4); }
+        }
+        sts128(g_s + o * 128 + ((c ^ (o & 7)) << 4), thin_mask_pack(g0, g1, a0, a1));
+        if (q2 < nchunks) sts128(g_s + o2 * 128 + ((c ^ (o2 & 7)) << 4), thin_mask_pack(h0, h1, e0, e1));
       }
       // Col: this thread's pixel, then the ones column
       const int pix = px0 + lt;
