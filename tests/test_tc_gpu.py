@@ -51,6 +51,8 @@ CASES = [
     (7, 1, 72, 272, 8, 16, 8, 16, 2, 0, 0, False),       # Cout > 256 (two N blocks), Cin padded to 128
     (8, 2, 32, 64, 32, 64, 16, 32, 9, 1, 0, True),       # stride-2 map: the adjoints multiply first on the small grid
     (9, 1, 40, 48, 20, 36, 7, 11, 5, 1, 0, False),       # down-sampling random map, ragged sizes, multiply-first adjoint
+    (10, 3, 64, 64, 32, 64, 16, 32, 9, 1, 0, True),      # multiply-first adjoint with 64 input channels (lane-split row gather)
+    (11, 1, 128, 32, 21, 37, 7, 11, 5, 1, 0, False),     # the same with two channel groups and ragged destination tiles
 ]
 
 
