@@ -207,7 +207,8 @@ def run_encoder(args, rank, local, world):
     per_launch = {}
     for k in ran:
         if k[1] == "bwd.phases":   # split the combined backward call into its three parts
-            for name, i in (("bwd.prepass", 0), ("dx", 1), ("dw", 2)):
+            thin = cfg["layers"][k[0]][0] * 9 <= 32   # thin layers: weight image | dW + dBias + column buffer | plan gather of dInput
+            for name, i in ((("bwd.prepass", 0), ("bwd.main", 1), ("bwd.gather", 2)) if thin else (("bwd.prepass", 0), ("dx", 1), ("dw", 2))):
                 per_launch[(k[0], name)] = sum(t[k][i].elapsed_time(t[k][i + 1]) for t in per_step_timers) / len(per_step_timers)
         elif not (k[1] == "bwd" and (k[0], "bwd.phases") in stack.timed_keys):
             per_launch[k] = sum(t[k][0].elapsed_time(t[k][1]) for t in per_step_timers) / len(per_step_timers)
@@ -289,18 +290,22 @@ def run_encoder(args, rank, local, world):
         return None
     peaks = measured_peaks()
     # Dominant kernel = the kernel (not the single launch) with the largest share of the step.  Layers whose
-    # gathered side has <= 32 (channel, slot) columns run the thin-contraction SIMT kernels, the others the two
-    # tcgen05 kernels (forward-type gather-GEMM for forward and dInput, weight-gradient kernel for dW).
+    # gathered side has <= 32 (channel, slot) columns run the thin-contraction kernels (one operand block per tile on the
+    # tensor cores in bf16 precision), the others the two general tcgen05 kernels (forward-type gather-GEMM for forward
+    # and dInput, weight-gradient kernel for dW).
     def kernel_of(li, ph):
         ci = cfg["layers"][li][0]
         if ci * 9 <= 32:
-            return "small_%s (SIMT, thin contraction)" % ph
+            return {"fwd": "tc_thin_fwd_kernel", "bwd.main": "tc_thin_bwd_kernel (dW, dBias, column buffer of dInput)",
+                    "bwd.gather": "thin_plan_gather_kernel (dInput)", "bwd.prepass": "thin_wt_image_kernel",
+                    "bwd": "tc_thin_bwd_kernel + thin_plan_gather_kernel (combined backward call)"}.get(
+                        ph, "small_%s (SIMT, thin contraction)" % ph)
         return {"dw": "tc_dw_kernel", "bwd": "tc_gemm_kernel + tc_dw_kernel (combined backward call)",
                 "bwd.prepass": "grad_image_kernel (layout pre-pass of the backward call)"}.get(ph, "tc_gemm_kernel")
 
     def launch_flops(li, ph):
         ci, co, _, (oh, ow), _ = cfg["layers"][li]
-        return {"bwd": 2, "bwd.prepass": 0}.get(ph, 1) * 2 * (hi - lo) * co * ci * 9 * oh * ow
+        return {"bwd": 2, "bwd.main": 2, "bwd.prepass": 0, "bwd.gather": 0}.get(ph, 1) * 2 * (hi - lo) * co * ci * 9 * oh * ow
 
     groups = {}
     for (li, ph), t in per_launch.items():
