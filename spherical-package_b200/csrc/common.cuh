@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <stdint.h>
 
 #include "sphmap.h"
@@ -217,6 +218,16 @@ __device__ __forceinline__ PlanView<T> plan_view(const void *plan, int n_keys, b
        (n_src < 0 || h->n_src == n_src);
   return PlanView<T>{(const int *)(p + h->off_offsets), (const int *)(p + h->off_src), (const T *)(p + h->off_w), h->n_src};
 }
+
+// NVTX range over one C entry point (header-only NVTX 3: a no-op unless a profiler that injects itself is attached),
+// so that a timeline shows which operator the kernels below it belong to.
+struct NvtxRange {
+  explicit NvtxRange(const char *name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange &) = delete;
+  NvtxRange &operator=(const NvtxRange &) = delete;
+};
+#define SPH_RANGE(name) ::sph::NvtxRange sph_nvtx_range_(name)
 
 // Kernel launches issued by this library in this process (tracing aid, see sph_launch_count()).
 extern unsigned long long g_launch_count;

@@ -179,6 +179,7 @@ extern "C" int sph_mapped_conv_forward(const void *x, const void *map, const voi
                                        const void *bias, void *out, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
                                        int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
                                        int precision, void *ws, size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_conv_forward");
   return conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws, ws_bytes,
                       stream, Fusion{});
 }
@@ -187,6 +188,7 @@ extern "C" int sph_mapped_conv_backward_input(const void *gout, const void *plan
                                               int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
                                               int64_t OW, int64_t K, int dtype, int precision, void *ws,
                                               size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_conv_backward_input");
   return conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, dtype, precision, ws, ws_bytes, stream,
                              Fusion{});
 }
@@ -195,6 +197,7 @@ extern "C" int sph_mapped_conv_backward_weight(const void *gout, const void *x, 
                                                void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
                                                int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
                                                int interp, int precision, void *ws, size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_conv_backward_weight");
   return conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws,
                               ws_bytes, stream, Fusion{});
 }
@@ -205,6 +208,7 @@ extern "C" int sph_mapped_conv_relu_forward(const void *x, const void *map, cons
                                             int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
                                             int dtype, int interp, int precision, void *ws, size_t ws_bytes,
                                             void *stream) {
+  SPH_RANGE("sph_mapped_conv_relu_forward");
   return conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws, ws_bytes,
                       stream, Fusion{true, nullptr});
 }
@@ -213,6 +217,7 @@ extern "C" int sph_mapped_conv_relu_backward_input(const void *gout, const void 
                                                    const void *weight, void *gx, int64_t B, int64_t Cin, int64_t Cout,
                                                    int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int dtype,
                                                    int precision, void *ws, size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_conv_relu_backward_input");
   if (!act_out) return SPH_ERR_INVALID_ARGUMENT;
   return conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, dtype, precision, ws, ws_bytes, stream,
                              Fusion{false, act_out});
@@ -223,6 +228,7 @@ extern "C" int sph_mapped_conv_relu_backward_weight(const void *gout, const void
                                                     int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH,
                                                     int64_t OW, int64_t K, int64_t P, int dtype, int interp,
                                                     int precision, void *ws, size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_conv_relu_backward_weight");
   if (!act_out) return SPH_ERR_INVALID_ARGUMENT;
   return conv_backward_weight(gout, x, map, iw, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws,
                               ws_bytes, stream, Fusion{false, act_out});
@@ -240,6 +246,7 @@ extern "C" int sph_mapped_conv_forward_cl(const void *x, const void *x_cl, const
                                           const void *bias, void *out, void *out_cl, int64_t B, int64_t Cin, int64_t Cout,
                                           int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
                                           int interp, int precision, int relu, void *ws, size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_conv_forward_cl");
   Fusion fz;
   fz.relu_out = relu != 0;
   fz.src_cl = x_cl;
@@ -255,6 +262,7 @@ extern "C" int sph_mapped_conv_backward_cl(const void *gout, const void *act_out
                                            void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
                                            int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp, int precision,
                                            void *ws, size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_conv_backward_cl");
   const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
   const int rc = check_dims(d, dtype, interp, precision);
   if (rc != SPH_OK) return rc;
@@ -276,6 +284,7 @@ extern "C" int sph_mapped_tconv_forward(const void *x, const void *plan, const v
                                         void *out, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
                                         int64_t OH, int64_t OW, int64_t K, int dtype, int precision, void *ws,
                                         size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_tconv_forward");
   const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, 0};
   const int rc = check_dims(d, dtype, 0, precision);
   if (rc != SPH_OK) return rc;
@@ -295,6 +304,7 @@ extern "C" int sph_mapped_tconv_backward_input(const void *gout, const void *map
                                                void *gx, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
                                                int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
                                                int precision, void *ws, size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_tconv_backward_input");
   const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
   const int rc = check_dims(d, dtype, interp, precision);
   if (rc != SPH_OK) return rc;
@@ -314,6 +324,7 @@ extern "C" int sph_mapped_tconv_backward_weight(const void *gout, const void *x,
                                                 void *gw, void *gb, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
                                                 int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,
                                                 int interp, int precision, void *ws, size_t ws_bytes, void *stream) {
+  SPH_RANGE("sph_mapped_tconv_backward_weight");
   const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
   const int rc = check_dims(d, dtype, interp, precision);
   if (rc != SPH_OK) return rc;

@@ -607,15 +607,20 @@ __global__ void thin_wt_image_kernel(const float *__restrict__ w, __nv_bfloat16 
   wt[(size_t)j * kChunk + (((o >> 3) ^ (j & 7)) << 3) + (o & 7)] = __float2bfloat16(v);
 }
 
-// gw[o, c, k] and gb[o] from the per-CTA partial sums, added in CTA order.
-__global__ void thin_dw_reduce_kernel(const float *__restrict__ partial, int nparts, int N, int CH, int K, int64_t so, int64_t sc,
-                                      int64_t sk, float *__restrict__ gw, float *__restrict__ gb) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+// gw[o, c, k] and gb[o] from the per-CTA partial sums.  One warp per output element: lane l adds the parts l, l + 32,
+// ... in order, then the 32 lane sums are combined by a fixed shuffle tree - the same order on every run.
+__global__ void __launch_bounds__(256) thin_dw_reduce_kernel(const float *__restrict__ partial, int nparts, int N, int CH, int K,
+                                                             int64_t so, int64_t sc, int64_t sk, float *__restrict__ gw,
+                                                             float *__restrict__ gb) {
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int ncols = CH * K;
-  if (i >= N * (ncols + 1)) return;
+  if (i >= N * (ncols + 1)) return;  // whole warps leave together
   const int j = i % (ncols + 1), o = i / (ncols + 1);
   float s = 0.0f;
-  for (int z = 0; z < nparts; z++) s += partial[((size_t)z * 64 + o) * 64 + j];
+  for (int z = lane; z < nparts; z += 32) s += partial[((size_t)z * 64 + o) * 64 + j];
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+  if (lane != 0) return;
   if (j == ncols) gb[o] = s;
   else gw[o * so + (j % CH) * sc + (j / CH) * sk] = s;
 }
@@ -732,7 +737,7 @@ int tc_thin_backward(const void *gout, const void *act, const void *x, const voi
   mark_phase(1, st);
   SPH_DISPATCH_INTERP(interp, launch_thin_bwd<INTERP>(p, L.grid, st));
   if (do_dw)
-    thin_dw_reduce_kernel<<<cdiv(N * (CH * K + 1), 128), 128, 0, st>>>(p.partial, L.grid, (int)N, (int)CH, (int)K, CH * K, K, 1, (float *)gw,
+    thin_dw_reduce_kernel<<<cdiv(N * (CH * K + 1) * 32, 256), 256, 0, st>>>(p.partial, L.grid, (int)N, (int)CH, (int)K, CH * K, K, 1, (float *)gw,
                                                                       (float *)gb);
   mark_phase(2, st);
   constexpr int kImg = 8;

@@ -62,6 +62,7 @@ using namespace sph;
 
 extern "C" int sph_build_kernel_map(void *map, int64_t H, int64_t W, int64_t kh, int64_t kw, int64_t stride, int64_t dilation,
                                     int kind, int dtype, void *stream) {
+  SPH_RANGE("sph_build_kernel_map");
   if (!map || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || stride <= 0 || dilation <= 0 || kind < 0 || kind > 2)
     return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;

@@ -249,6 +249,7 @@ extern "C" size_t sph_plan_bytes(int64_t n_src, int64_t K, int64_t P, int interp
 
 extern "C" int sph_plan_build(const void *map, const void *iw, int64_t n_src, int64_t K, int64_t P, int interp,
                               int64_t dstH, int64_t dstW, int dtype, void *plan, size_t plan_bytes, void *stream) {
+  SPH_RANGE("sph_plan_build");
   if (!map || !plan || P < 0 || (P > 0 && !iw) || interp < 0 || interp > 2) return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
   PlanLayout L;
@@ -264,6 +265,7 @@ extern "C" int sph_plan_build(const void *map, const void *iw, int64_t n_src, in
 // (NT*TH) x TW image; interpolation and its zero padding act inside the texture quad_idx names.
 extern "C" int sph_plan_build_uv(const void *tex_uv, const int64_t *quad_idx, int64_t n_src, int64_t NT, int64_t TH,
                                  int64_t TW, int interp, int dtype, void *plan, size_t plan_bytes, void *stream) {
+  SPH_RANGE("sph_plan_build_uv");
   if (!tex_uv || !quad_idx || !plan || NT <= 0 || interp < 0 || interp > 2) return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
   PlanLayout L;

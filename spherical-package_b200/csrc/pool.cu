@@ -296,6 +296,7 @@ SPH_TU_STATUS(pool)
 extern "C" int sph_mapped_max_pool(const void *x, const void *map, const void *iw, void *out, int64_t *idx, int64_t B,
                                    int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
                                    int dtype, int interp, void *stream) {
+  SPH_RANGE("sph_mapped_max_pool");
   const int rc = check(x, map, out, idx, iw, B, C, IH, IW, OH, OW, K, P, dtype, interp);
   if (rc != SPH_OK) return rc;
   if (B * C == 0 || OH * OW == 0) return SPH_OK;
@@ -307,6 +308,7 @@ extern "C" int sph_mapped_max_pool(const void *x, const void *map, const void *i
 extern "C" int sph_mapped_max_unpool(const void *g, const int64_t *idx, const void *map, const void *iw, void *grad_in,
                                      int64_t B, int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
                                      int64_t P, int dtype, int interp, void *stream) {
+  SPH_RANGE("sph_mapped_max_unpool");
   const int rc = check(g, map, grad_in, idx, iw, B, C, IH, IW, OH, OW, K, P, dtype, interp);
   if (rc != SPH_OK) return rc;
   if (B * C == 0) return SPH_OK;
@@ -321,6 +323,7 @@ extern "C" int sph_mapped_max_unpool(const void *g, const int64_t *idx, const vo
 extern "C" int sph_mapped_max_unpool_planned(const void *g, const int64_t *idx, const void *plan, void *grad_in, int64_t B,
                                              int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P,
                                              int dtype, void *stream) {
+  SPH_RANGE("sph_mapped_max_unpool_planned");
   const int rc = check(g, plan, grad_in, idx, nullptr, B, C, IH, IW, OH, OW, K, 0, dtype, 0);
   if (rc != SPH_OK) return rc;
   if (P < 0 || OH * OW * K >= ((int64_t)1 << 31) / (2 * (P > 0 ? P : 1))) return P < 0 ? SPH_ERR_INVALID_ARGUMENT : SPH_ERR_TOO_LARGE;
@@ -336,6 +339,7 @@ extern "C" int sph_mapped_max_unpool_planned(const void *g, const int64_t *idx, 
 extern "C" int sph_mapped_avg_pool(const void *x, const void *map, const void *iw, void *out, int64_t B, int64_t C, int64_t IH,
                                    int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
                                    void *stream) {
+  SPH_RANGE("sph_mapped_avg_pool");
   const int rc = check(x, map, out, out, iw, B, C, IH, IW, OH, OW, K, P, dtype, interp);
   if (rc != SPH_OK) return rc;
   if (B * C == 0 || OH * OW == 0) return SPH_OK;

@@ -201,6 +201,7 @@ SPH_TU_STATUS(resample)
 extern "C" int sph_resample_from_map(const void *x, const void *map, const void *iw, void *y, int64_t B, int64_t C,
                                      int64_t H, int64_t W, int64_t MH, int64_t MW, int64_t P, int dtype, int interp,
                                      void *stream) {
+  SPH_RANGE("sph_resample_from_map");
   if (!x || !map || !y || B < 0 || C < 0 || H <= 0 || W <= 0 || MH < 0 || MW < 0 || P < 0 || (P > 0 && !iw))
     return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
@@ -215,6 +216,7 @@ extern "C" int sph_resample_from_map(const void *x, const void *map, const void 
 
 extern "C" int sph_resample_to_map(const void *x, const void *plan, void *out, int64_t B, int64_t C, int64_t MH,
                                    int64_t MW, int64_t OH, int64_t OW, int dtype, void *stream) {
+  SPH_RANGE("sph_resample_to_map");
   if (!x || !plan || !out || B < 0 || C < 0 || MH <= 0 || MW <= 0 || OH <= 0 || OW <= 0) return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
   const int64_t planes = B * C, lim = (int64_t)1 << 31;
@@ -227,6 +229,7 @@ extern "C" int sph_resample_to_map(const void *x, const void *plan, void *out, i
 
 extern "C" int sph_resample_to_map_normalized(const void *x, const void *plan, void *out, int64_t B, int64_t C, int64_t MH,
                                               int64_t MW, int64_t OH, int64_t OW, int dtype, void *stream) {
+  SPH_RANGE("sph_resample_to_map_normalized");
   if (!x || !plan || !out || B < 0 || C < 0 || MH <= 0 || MW <= 0 || OH <= 0 || OW <= 0) return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
   const int64_t planes = B * C, lim = (int64_t)1 << 31;
@@ -239,6 +242,7 @@ extern "C" int sph_resample_to_map_normalized(const void *x, const void *plan, v
 
 extern "C" int sph_mapped_avg_unpool(const void *g, const void *plan, void *grad_in, int64_t B, int64_t C, int64_t IH,
                                      int64_t IW, int64_t OH, int64_t OW, int64_t K, int dtype, void *stream) {
+  SPH_RANGE("sph_mapped_avg_unpool");
   if (!g || !plan || !grad_in || B < 0 || C < 0 || IH <= 0 || IW <= 0 || OH <= 0 || OW <= 0 || K <= 0)
     return SPH_ERR_INVALID_ARGUMENT;
   if (dtype != SPH_F32 && dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
@@ -253,6 +257,7 @@ extern "C" int sph_mapped_avg_unpool(const void *g, const void *plan, void *grad
 extern "C" int sph_resample_from_uv_maps(const void *tex, const int64_t *quad_idx, const void *tex_uv, void *out, int64_t B,
                                          int64_t C, int64_t NT, int64_t TH, int64_t TW, int64_t IH, int64_t IW, int dtype,
                                          int interp, void *stream) {
+  SPH_RANGE("sph_resample_from_uv_maps");
   if (!tex || !quad_idx || !tex_uv || !out || B < 0 || C < 0 || NT <= 0 || TH <= 0 || TW <= 0 || IH < 0 || IW < 0 ||
       interp < 0 || interp > 2)
     return SPH_ERR_INVALID_ARGUMENT;
@@ -268,6 +273,7 @@ extern "C" int sph_resample_from_uv_maps(const void *tex, const int64_t *quad_id
 extern "C" int sph_voting_resample_to_map(const int64_t *labels, const void *plan, int plan_dtype, int64_t *out, int64_t B,
                                           int64_t C, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t num_candidates,
                                           void *stream) {
+  SPH_RANGE("sph_voting_resample_to_map");
   if (!labels || !plan || !out || B < 0 || C < 0 || IH <= 0 || IW <= 0 || OH <= 0 || OW <= 0 || num_candidates <= 0)
     return SPH_ERR_INVALID_ARGUMENT;
   if (plan_dtype != SPH_F32 && plan_dtype != SPH_F64) return SPH_ERR_UNSUPPORTED;
