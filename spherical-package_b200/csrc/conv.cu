@@ -47,34 +47,20 @@ unsigned long long g_launch_count = 0;
 }  // namespace sph
 extern "C" unsigned long long sph_launch_count(void) { return __atomic_load_n(&sph::g_launch_count, __ATOMIC_RELAXED); }
 
-extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
-                                           int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
-                                           int precision) {
-  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
-  if (check_dims(d, dtype, interp, precision) != SPH_OK) return 0;
+namespace {
+// Scratch of the kernels an operator falls back on when a thin layer's tensor-core form does not apply.
+size_t base_workspace(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K,
+                      int64_t P, int dtype, int interp, int precision) {
   const size_t ts = dtype == SPH_F64 ? 8 : 4;
   // thin contractions (few channels on the gathered / produced side) have their own kernels in both precisions
-  const bool thin_tc = precision == SPH_PRECISION_BF16 && tc_thin_backward_ok(Cin, K, Cout, OH * OW);  // conv backward only
   switch (op) {
-    case SPH_CONV_FORWARD:
-      if (small_ok(Cin, K, Cout, ts))
-        return (precision == SPH_PRECISION_BF16 && tc_thin_forward_ok(Cin, K, Cout, OW)) ? tc_thin_forward_workspace(Cout) : 0;
-      break;
-    case SPH_CONV_BACKWARD_INPUT:
-      if (small_ok(Cin, K, Cout, ts))
-        return thin_tc ? tc_thin_backward_workspace(B, Cin, K, OH * OW, true) : small_premul_workspace(B, Cin, K, OH * OW, ts);
-      break;
-    case SPH_CONV_BACKWARD_WEIGHT:
-      if (small_ok(Cin, K, Cout, ts))
-        return thin_tc ? tc_thin_backward_workspace(B, Cin, K, OH * OW, false) : small_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts);
-      break;
+    case SPH_CONV_FORWARD: if (small_ok(Cin, K, Cout, ts)) return 0; break;
+    case SPH_CONV_BACKWARD_INPUT: if (small_ok(Cin, K, Cout, ts)) return small_premul_workspace(B, Cin, K, OH * OW, ts); break;
+    case SPH_CONV_BACKWARD_WEIGHT: if (small_ok(Cin, K, Cout, ts)) return small_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts); break;
     case SPH_TCONV_FORWARD: if (small_ok(Cout, K, Cin, ts)) return small_premul_workspace(B, Cout, K, IH * IW, ts); break;
     case SPH_TCONV_BACKWARD_INPUT: if (small_ok(Cout, K, Cin, ts)) return 0; break;
     case SPH_TCONV_BACKWARD_WEIGHT: if (small_ok(Cout, K, Cin, ts)) return small_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, ts); break;
-    case SPH_CONV_BACKWARD:  // thin layers: their own combined kernel in bf16 precision, else the separate entry points
-      if (small_ok(Cin, K, Cout, ts))
-        return thin_tc ? tc_thin_backward_workspace(B, Cin, K, OH * OW, true) : 0;
-      break;
+    case SPH_CONV_BACKWARD: if (small_ok(Cin, K, Cout, ts)) return 0; break;  // thin layers: the separate entry points
     default: break;
   }
   if (op == SPH_CONV_BACKWARD)
@@ -85,6 +71,27 @@ extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64
     case SPH_TCONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, ts);
     default: return 0;
   }
+}
+}  // namespace
+
+extern "C" size_t sph_conv_workspace_bytes(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW,
+                                           int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,
+                                           int precision) {
+  const Dims d{B, Cin, Cout, IH, IW, OH, OW, K, P};
+  if (check_dims(d, dtype, interp, precision) != SPH_OK) return 0;
+  const size_t base = base_workspace(op, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision);
+  if (precision != SPH_PRECISION_BF16 || dtype != SPH_F32) return base;
+  // bf16 precision: a convolution whose gathered side has at most 63 columns runs its own tensor-core kernels; they may
+  // still decline at call time (an unaligned pointer), so the scratch covers the fallback as well
+  size_t thin = 0;
+  switch (op) {
+    case SPH_CONV_FORWARD: if (tc_thin_forward_ok(Cin, K, Cout, OW)) thin = tc_thin_forward_workspace(Cout); break;
+    case SPH_CONV_BACKWARD_INPUT:
+    case SPH_CONV_BACKWARD: if (tc_thin_backward_ok(Cin, K, Cout, OH * OW)) thin = tc_thin_backward_workspace(B, Cin, K, OH * OW, true); break;
+    case SPH_CONV_BACKWARD_WEIGHT: if (tc_thin_backward_ok(Cin, K, Cout, OH * OW)) thin = tc_thin_backward_workspace(B, Cin, K, OH * OW, false); break;
+    default: break;
+  }
+  return thin > base ? thin : base;
 }
 
 #define SPH_BY_DTYPE(fn, ...) (dtype == SPH_F32 ? fn<float>(__VA_ARGS__) : fn<double>(__VA_ARGS__))
@@ -100,16 +107,15 @@ int conv_forward(const void *x, const void *map, const void *iw, const void *wei
   if (!x || !map || !weight || !bias || !out || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
   if (B == 0) return SPH_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)) {
-    // bf16 precision: one 64-column operand block per tile on the tensor cores, if the output can leave through a
-    // tensor map; else (and in the exact precision) the register-tiled kernels
-    if (precision == SPH_PRECISION_BF16 && tc_thin_forward_ok(Cin, K, Cout, OW)) {
-      const int rt = tc_thin_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
-      if (rt != SPH_ERR_UNSUPPORTED) return rt;
-    }
+  // bf16 precision, at most 63 gathered columns: one 64-column operand block per tile on the tensor cores, if the output
+  // can leave through a tensor map; else (and in the exact precision) thin layers run the register-tiled kernels
+  if (precision == SPH_PRECISION_BF16 && tc_thin_forward_ok(Cin, K, Cout, OW)) {
+    const int rt = tc_thin_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
+    if (rt != SPH_ERR_UNSUPPORTED) return rt;
+  }
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4))
     return SPH_BY_DTYPE(small_fwd, x, map, iw, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1, bias, out, Cout, B, st,
                         fz.relu_out, fz.out_cl);
-  }
   if (precision == SPH_PRECISION_BF16)
     return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
   if (fz.active() || fz.out_cl != nullptr) return SPH_ERR_UNSUPPORTED;
@@ -128,7 +134,7 @@ int conv_backward_input(const void *gout, const void *plan, const void *weight, 
   cudaStream_t st = (cudaStream_t)stream;
   // The thin kernels are issue-bound, not memory-bound: reading the mask inside them was measured slower (layer-1 dInput
   // of the encoder 2.1 -> 4.4 ms, dW 2.6 -> 2.9 ms) than one separate masking pass (0.9 ms), so they decline the mask.
-  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4) && precision == SPH_PRECISION_BF16 && tc_thin_backward_ok(Cin, K, Cout, OH * OW)) {
+  if (precision == SPH_PRECISION_BF16 && tc_thin_backward_ok(Cin, K, Cout, OH * OW)) {
     const int rt = tc_thin_conv_backward(gout, fz.mask, nullptr, plan, nullptr, nullptr, weight, gx, nullptr, nullptr, B, Cin, Cout, IH, IW,
                                          OH, OW, K, 0, 0, ws, ws_bytes, st);
     if (rt != SPH_ERR_UNSUPPORTED) return rt;
@@ -157,7 +163,7 @@ int conv_backward_weight(const void *gout, const void *x, const void *map, const
     if (cudaMemsetAsync(gw, 0, ts * (size_t)(Cout * Cin * K), st) != cudaSuccess) return SPH_ERR_CUDA;
     return cudaMemsetAsync(gb, 0, ts * (size_t)Cout, st) == cudaSuccess ? SPH_OK : SPH_ERR_CUDA;
   }
-  if (small_ok(Cin, K, Cout, ts) && precision == SPH_PRECISION_BF16 && tc_thin_backward_ok(Cin, K, Cout, OH * OW)) {
+  if (precision == SPH_PRECISION_BF16 && tc_thin_backward_ok(Cin, K, Cout, OH * OW)) {
     const int rt = tc_thin_conv_backward(gout, fz.mask, x, nullptr, map, iw, nullptr, nullptr, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P,
                                          interp, ws, ws_bytes, st);
     if (rt != SPH_ERR_UNSUPPORTED) return rt;
@@ -251,7 +257,8 @@ extern "C" int sph_mapped_conv_forward_cl(const void *x, const void *x_cl, const
   fz.relu_out = relu != 0;
   fz.src_cl = x_cl;
   fz.out_cl = out_cl;
-  if (x_cl != nullptr && (precision != SPH_PRECISION_BF16 || small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)))
+  if (x_cl != nullptr && (precision != SPH_PRECISION_BF16 || small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4) ||
+                          tc_thin_forward_ok(Cin, K, Cout, OW)))
     fz.src_cl = nullptr;  // the kernels that run this shape gather from the float32 tensor
   return conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, dtype, interp, precision, ws, ws_bytes,
                       stream, fz);
@@ -268,11 +275,12 @@ extern "C" int sph_mapped_conv_backward_cl(const void *gout, const void *act_out
   if (rc != SPH_OK) return rc;
   if (!gout || !x || !plan || !map || !weight || !gx || !gw || !gb || (P > 0 && !iw)) return SPH_ERR_INVALID_ARGUMENT;
   if (precision != SPH_PRECISION_BF16 || B == 0) return SPH_ERR_UNSUPPORTED;
-  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)) {
-    if (!tc_thin_backward_ok(Cin, K, Cout, OH * OW)) return SPH_ERR_UNSUPPORTED;
-    return tc_thin_conv_backward(gout, act_out, x, plan, map, iw, weight, gx, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes,
-                                 (cudaStream_t)stream);
+  if (tc_thin_backward_ok(Cin, K, Cout, OH * OW)) {
+    const int rt = tc_thin_conv_backward(gout, act_out, x, plan, map, iw, weight, gx, gw, gb, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws,
+                                         ws_bytes, (cudaStream_t)stream);
+    if (rt != SPH_ERR_UNSUPPORTED) return rt;
   }
+  if (small_ok(Cin, K, Cout, dtype == SPH_F64 ? 8 : 4)) return SPH_ERR_UNSUPPORTED;
   Fusion fz;
   fz.mask = act_out;
   fz.src_cl = x_cl;

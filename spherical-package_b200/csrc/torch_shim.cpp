@@ -119,7 +119,13 @@ struct PlanKey {
 
 // Version counter of a tensor; inference tensors have none (and cannot be modified in place): 0.
 uint32_t version_of(const torch::Tensor &t) { return t.is_inference() ? 0u : (uint32_t)t._version(); }
-std::list<PlanKey> g_plans;
+// (The caches are never destroyed: at interpreter shutdown the CUDA runtime may already be gone when static destructors
+// run, and releasing an event or a tensor then throws.  The process exit reclaims them.)
+std::list<PlanKey> &plan_cache() {
+  static auto *cache = new std::list<PlanKey>();
+  return *cache;
+}
+#define g_plans plan_cache()
 std::mutex g_plan_mu;
 constexpr size_t kMaxPlans = 64;
 
@@ -196,7 +202,11 @@ struct CompanionEntry {
   std::vector<int64_t> sizes;
   torch::Tensor companion;
 };
-std::list<CompanionEntry> g_companions;
+std::list<CompanionEntry> &companion_cache() {  // never destroyed, like the plan cache
+  static auto *cache = new std::list<CompanionEntry>();
+  return *cache;
+}
+#define g_companions companion_cache()
 std::mutex g_companion_mu;
 constexpr size_t kMaxCompanions = 8;
 bool g_use_companions = true;

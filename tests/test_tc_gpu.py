@@ -112,6 +112,9 @@ THIN_CASES = [
     (25, 2, 3, 64, 30, 50, 15, 25, 9, 1, 0, False),      # width not a multiple of 4, 375 pixels: the exact kernels
     (26, 2, 3, 128, 32, 64, 16, 32, 9, 1, 0, True),      # forward thin (N = 128), backward on the exact kernels
     (27, 5, 3, 64, 16, 32, 8, 16, 7, 1, 0, False),       # five images (a partial image group in the plan gather)
+    (28, 1, 1, 16, 12, 16, 6, 8, 63, 1, 0, False),       # 63 columns: the ones column of the backward is the last one
+    (29, 2, 7, 32, 12, 16, 6, 8, 9, 0, 0, False),        # seven channels: forward thin (general gather), backward exact
+    (30, 9, 2, 64, 16, 16, 16, 16, 3, 1, 0, False),      # nine images: two image groups of the plan gather, K odd
 ]
 
 
@@ -149,7 +152,7 @@ def test_thin_layer_bf16(case):
     try:
         cx, cw, cb = capi.conv_backward_cl(god, act, xd, None, plan, md, wd, K, interp, iwd, capi.BF16)
     except capi.Unsupported:
-        assert Cout > 64 or (OH * OW) % 8 != 0
+        assert Cout > 64 or (OH * OW) % 8 != 0 or Cin > 4
     else:
         assert torch.equal(cx, gx) and torch.equal(cw, gw) and torch.equal(cb, gb)
         cx2, cw2, cb2 = capi.conv_backward_cl(god, act, xd, None, plan, md, wd, K, interp, iwd, capi.BF16)
