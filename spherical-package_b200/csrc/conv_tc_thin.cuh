@@ -76,7 +76,8 @@ __device__ __forceinline__ void thin_bilinear_slot(const float *__restrict__ img
   const bool vy1 = (unsigned)y1 < (unsigned)SH, vy2 = (unsigned)(y1 + 1) < (unsigned)SH;
   const int o00 = y1 * SW + x1;
   const bool p0 = vx1 && vy1, p1 = vx2 && vy1, p2 = vx1 && vy2, p3 = vx2 && vy2;
-  const float w0 = A * B, w1 = A * C, w2 = D * B, w3 = D * C;
+  // (a NaN, infinite or astronomically large coordinate has no tap: zero weights, or NaN * 0 would reach the sum)
+  const float w0 = sane ? A * B : 0.0f, w1 = sane ? A * C : 0.0f, w2 = sane ? D * B : 0.0f, w3 = sane ? D * C : 0.0f;
 #pragma unroll
   for (int c = 0; c < CHT; c++) {
     const float *pc = img + c * plane;

@@ -87,6 +87,12 @@ for dtype in (torch.float32, torch.float64):
                 outs.append(capi.conv_forward(x64, md, w64, b64, K, interp, None, capi.BF16))
                 outs.append(capi.conv_backward_input(g64, plan, w64, IH, IW, K, capi.BF16))
                 outs += list(capi.conv_backward_weight(g64, x64, md, K, interp, None, capi.BF16))
+            if dtype == torch.float32:                 # the thin layer's own tensor-core kernels (3 channels, bf16 precision)
+                w16 = (torch.randn(16, C, K, generator=g) / 3).cuda(); b16 = torch.zeros(16).cuda()
+                g16 = torch.randn(B, 16, OH, OW, generator=g).cuda()
+                outs.append(capi.conv_forward(xd, md, w16, b16, K, interp, iwd, capi.BF16))
+                outs.append(capi.conv_backward_input(g16, plan, w16, IH, IW, K, capi.BF16))
+                outs += list(capi.conv_backward_weight(g16, xd, md, K, interp, iwd, capi.BF16))
             for t in outs:
                 assert torch.isfinite(t).all(), (dtype, interp, P)
             # NaN, infinite and astronomically large coordinates have no tap in this library (the reference converts
