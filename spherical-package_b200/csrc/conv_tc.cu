@@ -524,7 +524,9 @@ __device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem 
   return true;
 }
 
-template <int MODE, int NT>
+// ROWS: the outputs leave as bf16 rows (p.out_h, the column buffer of the multiply-first adjoint) and nothing else; the
+// other instantiations carry no code for it.
+template <int MODE, int NT, bool ROWS = false>
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, const __grid_constant__ CUtensorMap out_map,
                                                                const __grid_constant__ CUtensorMap cl_map) {
   extern __shared__ uint8_t smem_raw[];
@@ -573,7 +575,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * 256;
       const int ty = t2 / p.tiles_x, tx = t2 % p.tiles_x;
-      if (p.use_out_map) {
+      if (!ROWS && p.use_out_map) {
         // This warp's 32 pixels are two rows of 16.  Sixteen channels at a time go through shared memory as
         // [channel][row][x] and leave as one tiled tensor store (box 16 x 2 x 16 channels) issued by lane 0, so the
         // outputs cost this warp shared-memory stores only; the copy engine writes the 64-byte row segments and
@@ -637,16 +639,30 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
           for (int j = 0; j < 16; j++) { r[j] = h[j]; r[j + 16] = 0; }
         }
         tmem_ld_wait();
-        if (pix >= 0 && p.out_h) {
-          // 32 consecutive columns of this pixel's row, as bf16 (out_pitch and Npb are multiples of 8)
-          __nv_bfloat16 *hrow = p.out_h + ((size_t)b * npix + pix) * p.out_pitch + nb * p.Npb + n0;
+        if constexpr (ROWS) {
+          // 32 consecutive columns of every pixel's row, as bf16 (out_pitch and Npb are multiples of 8).  A thread holds
+          // its own pixel's 64 bytes; stored directly, one instruction would touch 32 rows with 16 bytes each.  The warp's
+          // 32 x 64 bytes go through shared memory (16-byte chunks XOR-swizzled, conflict-free both ways) and leave with
+          // eight pixels of 64 contiguous bytes per instruction.
+          const uint32_t hs = smem_u32(sm.ostage) + warp * (kOutStageCh * 32 * 4);
+          __syncwarp();  // the previous pass has been read
 #pragma unroll
-          for (int j = 0; j < 32; j += 8)
-            if (n0 + j < p.Npb && nb * p.Npb + n0 + j < p.out_pitch)
-              *(uint4 *)(hrow + j) = make_uint4(pack_bf16(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
-                                                pack_bf16(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
-                                                pack_bf16(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
-                                                pack_bf16(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
+          for (int j = 0; j < 4; j++)
+            sts128(hs + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4),
+                   make_uint4(pack_bf16(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
+                              pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3])),
+                              pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5])),
+                              pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]))));
+          __syncwarp();
+          const int c = lane & 3, col = nb * p.Npb + n0 + c * 8;
+#pragma unroll
+          for (int it = 0; it < 4; it++) {
+            const int pl = it * 8 + (lane >> 2);
+            const int ppix = tile_pixel(warp * 32 + pl, ty, tx, kTH, g.GH, g.GW);
+            const uint4 v = lds128(hs + pl * 64 + ((c ^ ((pl >> 1) & 3)) << 4));
+            if (ppix >= 0 && n0 + c * 8 < p.Npb && col < p.out_pitch)
+              *(uint4 *)(p.out_h + ((size_t)b * npix + ppix) * p.out_pitch + col) = v;
+          }
         } else if (pix >= 0) {
           float ov[32];
 #pragma unroll
@@ -1601,7 +1617,7 @@ bool make_cl_map(CUtensorMap *m, __nv_bfloat16 *cl, int64_t B, int64_t pitch, in
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MODE, int NT>
+template <int MODE, int NT, bool ROWS = false>
 void launch_gemm(TcParams p, int grid, size_t smem, cudaStream_t st) {
   CUtensorMap out_map, cl_map;
   memset(&out_map, 0, sizeof(out_map));
@@ -1610,8 +1626,8 @@ void launch_gemm(TcParams p, int grid, size_t smem, cudaStream_t st) {
   // the copy leaves through its own tensor map when the float32 output does; otherwise with plain stores
   if (p.use_out_map && p.out_cl != nullptr && !make_cl_map(&cl_map, p.out_cl, p.B, p.cl_pitch, p.g.GH, p.g.GW)) p.use_out_map = 0;
   static int granted[kMaxDevices];
-  ensure_dynamic_smem(tc_gemm_kernel<MODE, NT>, granted, smem);
-  tc_gemm_kernel<MODE, NT><<<grid, kThreads, smem, st>>>(p, out_map, cl_map);
+  ensure_dynamic_smem(tc_gemm_kernel<MODE, NT, ROWS>, granted, smem);
+  tc_gemm_kernel<MODE, NT, ROWS><<<grid, kThreads, smem, st>>>(p, out_map, cl_map);
 }
 
 // ---- multiply-first adjoint -------------------------------------------------------------------------
@@ -1659,7 +1675,7 @@ int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan
   p.B = (int)B; p.Nout = (int)(K * q.Mp); p.Npb = g.Npb; p.nblk = g.nblk; p.nchunks = g.nchunks;
   p.tiles_x = cdiv(SW, kTW); p.tiles_y = cdiv(SH, kTH); p.stages = g.stages;
   const int64_t tiles = (int64_t)B * p.tiles_x * p.tiles_y * g.nblk;
-  launch_gemm<MODE_DIRECT, 1>(p, (int)(tiles < sm_count() ? tiles : sm_count()), g.smem, st);
+  launch_gemm<MODE_DIRECT, 1, true>(p, (int)(tiles < sm_count() ? tiles : sm_count()), g.smem, st);
   plan_gather_rows_kernel<<<dim3(cdiv(GH * GW, 128), (unsigned)B), 128, 0, st>>>(T, plan, (const float *)bias, (float *)out, (int)K,
                                                                                 (int)M, q.Mp, (int)(SH * SW), (int)(GH * GW));
   return launch_status(4);
