@@ -526,7 +526,9 @@ __device__ __forceinline__ bool produce_tile_lean(const TcParams &p, const Smem 
 
 // ROWS: the outputs leave as bf16 rows (p.out_h, the column buffer of the multiply-first adjoint) and nothing else; the
 // other instantiations carry no code for it.
-template <int MODE, int NT, bool ROWS = false>
+// LEAN: channel copies of at least 64 padded channels with a static tap count - the producers run the lean per-chunk
+// loop and the instantiation carries no code for the general one (and the other way round).
+template <int MODE, int NT, bool ROWS = false, bool LEAN = false>
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, const __grid_constant__ CUtensorMap out_map,
                                                                const __grid_constant__ CUtensorMap cl_map) {
   extern __shared__ uint8_t smem_raw[];
@@ -794,7 +796,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
       producer_bar();
       if (pt == 0) { TC_TOC(t_fill, 0); TC_COUNT(7); }
       TC_TIC(t_loop);
-      if (g.Cp >= 64 && (MODE == MODE_PLAN || NT > 0)) {  // the common shape: lean per-chunk loop
+      if constexpr (LEAN) {  // the common shape: lean per-chunk loop
         if (MODE == MODE_PLAN) {
           if (plan_nti >= 3) alive = produce_tile_lean<kPlanTaps, 4, true>(p, sm, pv, img, nb, pt, lane, ring);
           else if (plan_nti == 2) alive = produce_tile_lean<kPlanTaps, 2, true>(p, sm, pv, img, nb, pt, lane, ring);
@@ -805,6 +807,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const TcParams p, 
         if (pt == 0) { TC_TOC(t_loop, 1); }
         continue;
       }
+      if constexpr (LEAN) continue;  // (not reached; keeps the general loop out of this instantiation)
       int cslot = 0, cblock = 0;  // Cp >= 64: chunk = cblock * K + cslot, kept incrementally (no division)
       // (pixel, vector pair) threads when a pair lies inside one slot and the tap count is static; else
       // (two pixels, one vector)
@@ -1617,8 +1620,8 @@ bool make_cl_map(CUtensorMap *m, __nv_bfloat16 *cl, int64_t B, int64_t pitch, in
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MODE, int NT, bool ROWS = false>
-void launch_gemm(TcParams p, int grid, size_t smem, cudaStream_t st) {
+template <int MODE, int NT, bool ROWS, bool LEAN>
+void launch_gemm_l(TcParams p, int grid, size_t smem, cudaStream_t st) {
   CUtensorMap out_map, cl_map;
   memset(&out_map, 0, sizeof(out_map));
   memset(&cl_map, 0, sizeof(cl_map));
@@ -1626,8 +1629,16 @@ void launch_gemm(TcParams p, int grid, size_t smem, cudaStream_t st) {
   // the copy leaves through its own tensor map when the float32 output does; otherwise with plain stores
   if (p.use_out_map && p.out_cl != nullptr && !make_cl_map(&cl_map, p.out_cl, p.B, p.cl_pitch, p.g.GH, p.g.GW)) p.use_out_map = 0;
   static int granted[kMaxDevices];
-  ensure_dynamic_smem(tc_gemm_kernel<MODE, NT, ROWS>, granted, smem);
-  tc_gemm_kernel<MODE, NT, ROWS><<<grid, kThreads, smem, st>>>(p, out_map, cl_map);
+  ensure_dynamic_smem(tc_gemm_kernel<MODE, NT, ROWS, LEAN>, granted, smem);
+  tc_gemm_kernel<MODE, NT, ROWS, LEAN><<<grid, kThreads, smem, st>>>(p, out_map, cl_map);
+}
+template <int MODE, int NT, bool ROWS = false>
+void launch_gemm(const TcParams &p, int grid, size_t smem, cudaStream_t st) {
+  if (p.g.Cp >= 64 && (MODE == MODE_PLAN || NT > 0)) {
+    if constexpr (MODE == MODE_PLAN || NT > 0) launch_gemm_l<MODE, NT, ROWS, true>(p, grid, smem, st);
+  } else {
+    launch_gemm_l<MODE, NT, ROWS, false>(p, grid, smem, st);
+  }
 }
 
 // ---- multiply-first adjoint -------------------------------------------------------------------------
