@@ -4,7 +4,7 @@ random cases evaluated with the reference's compiled CPU modules.
 
 Bars: gathers (resample_from_map, pooled values) and argmax indices bit exact;
 everything else within rtol 1e-5 (float32) / 1e-12 (float64), the tolerance
-BASELINE.json states for the exact path."""
+of the exact path."""
 import os
 
 import pytest

@@ -1,6 +1,6 @@
 """bf16 tensor-core path (tcgen05) of the mapped convolution family against the CPU oracle.
 
-Tolerance of the tensor-core path (bf16 operands, fp32 accumulation), stated per BASELINE.json:
+Tolerance of the tensor-core path (bf16 operands, fp32 accumulation):
     max |got - ref| <= 2e-2 * max |ref|      and      rms(got - ref) <= 5e-3 * rms(ref)
 where ref is the float32 oracle on the unrounded inputs."""
 import math
