@@ -66,6 +66,11 @@ template <typename T> struct Taps {
   int limit;
 };
 
+// |v| < 1e9, false for NaN.  1e9 is exactly representable in float32, so the float32 comparison decides exactly as the
+// float64 one would (and stays off the double-precision pipe).
+__device__ __forceinline__ bool coord_in_range(float v) { return fabsf(v) < 1e9f; }
+__device__ __forceinline__ bool coord_in_range(double v) { return fabs(v) < 1e9; }
+
 template <int INTERP> struct TapCount { static constexpr int value = (INTERP == SPH_NEAREST) ? 1 : 4; };
 
 // Decode a coordinate exactly as ext_modules/include/core/interpolation.h
@@ -75,7 +80,7 @@ template <int INTERP> struct TapCount { static constexpr int value = (INTERP == 
 // (191-218).  Coordinates that are NaN or beyond +-1e9 have no valid tap.
 template <typename T, int INTERP>
 __device__ __forceinline__ void decode(T x, T y, int H, int W, Taps<T> &t) {
-  const bool sane = (fabs((double)x) < 1e9) && (fabs((double)y) < 1e9);
+  const bool sane = coord_in_range(x) && coord_in_range(y);
   t.limit = H * W;
   if (INTERP == SPH_NEAREST) {
     const int xi = RN<T>::round_away(x), yi = RN<T>::round_away(y);

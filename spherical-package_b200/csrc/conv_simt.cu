@@ -111,6 +111,157 @@ conv_gemm_kernel(ColSrc<T> cs, const T *__restrict__ wgt, int64_t sm, int64_t sc
   }
 }
 
+// The same operator for float32 with at least ~100 output rows: 128 x 128 output tile, 8 x 8 accumulators per thread
+// read through 16-byte shared-memory loads, the next step's operands fetched into registers while the current step is
+// multiplied, and the columns ordered slot-major (kk = k * CH + ch) so that a thread decodes a map entry once for all
+// the channels it gathers with it.
+constexpr int GM = 128, GN = 128, GK = 16;
+__device__ __forceinline__ void gffma2(unsigned long long &d, unsigned long long a, unsigned long long b) {
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
+}
+__device__ __forceinline__ unsigned long long gpack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void gunpack2(unsigned long long v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+template <int MODE, bool WEIGHTED>
+__global__ void __launch_bounds__(256, 2)
+conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk,
+                    const float *__restrict__ bias, float *__restrict__ out, int M) {
+  __shared__ __align__(16) float Ws[GK][GM];
+  __shared__ __align__(16) float Cs[GK][GN];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int b = blockIdx.z, m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
+  const int CHK = cs.CH * cs.K;
+  const size_t shw = (size_t)cs.SH * cs.SW;
+  PlanView<float> pv{};
+  bool ok = true;
+  if (MODE == COL_PLAN) pv = plan_view<float>(cs.plan, cs.npix * cs.K, ok);
+  const float *img = cs.src + (size_t)b * cs.CH * shw;
+  // operand fetch: weights (kl = tid >> 7 + 2 i, row tid & 127), columns (pixel tid & 127, kl = 8 * (tid >> 7) + j)
+  const int nl = tid & 127, half = tid >> 7, pix = n0 + nl;
+  const bool pix_ok = ok && pix < cs.npix;
+  float wreg[8], creg[8];
+  auto fetch = [&](int kk0) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int kk = kk0 + half + 2 * i, m = m0 + nl;
+      float v = 0.0f;
+      if (kk < CHK && m < M) {
+        const int k = kk / cs.CH, ch = kk - k * cs.CH;
+        v = __ldg(wgt + m * sm + ch * sc + k * sk);
+      }
+      wreg[i] = v;
+    }
+    if constexpr (MODE == COL_PLAN) {
+      // the eight columns are consecutive channels; when they share their slot, the slot's plan entries are read once
+      const int kk_first = kk0 + half * 8, k = kk_first / cs.CH, ch0 = kk_first - k * cs.CH;
+      if (pix_ok && kk_first + 8 <= CHK && ch0 + 8 <= cs.CH) {
+#pragma unroll
+        for (int j = 0; j < 8; j++) creg[j] = 0.0f;
+        const int key = pix * cs.K + k;
+        const int e0 = __ldg(pv.offsets + key), e1 = __ldg(pv.offsets + key + 1);
+        const float *plane0 = img + (size_t)ch0 * shw;
+        for (int e = e0; e < e1; e++) {
+          const int sp = __ldg(pv.src + e);
+          if (!index_ok(sp, pv.n_src)) continue;
+          const float w = __ldg(pv.w + e);
+#pragma unroll
+          for (int j = 0; j < 8; j++) creg[j] += w * __ldg(plane0 + (size_t)j * shw + sp);
+        }
+        return;
+      }
+    }
+    int cur_k = -1;
+    Taps<float> t;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      const int kk = kk0 + half * 8 + j;
+      float v = 0.0f;
+      if (pix_ok && kk < CHK) {
+        const int k = kk / cs.CH, ch = kk - k * cs.CH;
+        const float *plane = img + (size_t)ch * shw;
+        if constexpr (MODE != COL_PLAN && !WEIGHTED) {
+          if (k != cur_k) {
+            const float *mp = cs.map + 2 * ((size_t)pix * cs.K + k);
+            decode<float, MODE == COL_PLAN ? 0 : MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t);
+            cur_k = k;
+          }
+          v = gather<float, MODE == COL_PLAN ? 0 : MODE>(plane, t);
+        } else {
+          v = col_value<float, MODE, WEIGHTED>(cs, pv, plane, k, pix);
+        }
+      }
+      creg[j] = v;
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int i = 0; i < 8; i++) Ws[half + 2 * i][nl] = wreg[i];
+#pragma unroll
+    for (int j = 0; j < 8; j++) Cs[half * 8 + j][nl] = creg[j];
+  };
+  unsigned long long acc2[8][4];  // 8 rows x 4 pixel pairs, multiplied with packed float32 pair FMAs
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc2[i][j] = 0ull;
+
+  fetch(0);
+  stash();
+  __syncthreads();
+  for (int kk0 = 0; kk0 < CHK; kk0 += GK) {
+    const bool more = kk0 + GK < CHK;
+    if (more) fetch(kk0 + GK);  // in flight while this step is multiplied
+#pragma unroll
+    for (int kl = 0; kl < GK; kl++) {
+      const float4 a0 = *(const float4 *)&Ws[kl][ty * 8], a1 = *(const float4 *)&Ws[kl][ty * 8 + 4];
+      const float4 c0 = *(const float4 *)&Cs[kl][tx * 4], c1 = *(const float4 *)&Cs[kl][64 + tx * 4];
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const unsigned long long c2[4] = {gpack2(c0.x, c0.y), gpack2(c0.z, c0.w), gpack2(c1.x, c1.y), gpack2(c1.z, c1.w)};
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const unsigned long long aa = gpack2(a[i], a[i]);
+#pragma unroll
+        for (int j = 0; j < 4; j++) gffma2(acc2[i][j], aa, c2[j]);
+      }
+    }
+    __syncthreads();
+    if (more) {
+      stash();
+      __syncthreads();
+    }
+  }
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) gunpack2(acc2[i][j], acc[i][2 * j], acc[i][2 * j + 1]);
+  const bool vec = (cs.npix & 3) == 0 && (((uintptr_t)out) & 15) == 0;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int m = m0 + ty * 8 + i;
+    if (m >= M) continue;
+    const float bv = bias ? __ldg(bias + m) : 0.0f;
+    float *row = out + ((size_t)b * M + m) * cs.npix;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const int p0 = n0 + h * 64 + tx * 4;
+      if (vec && p0 + 4 <= cs.npix) {
+        *(float4 *)(row + p0) = make_float4(acc[i][4 * h] + bv, acc[i][4 * h + 1] + bv, acc[i][4 * h + 2] + bv, acc[i][4 * h + 3] + bv);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          if (p0 + j < cs.npix) row[p0 + j] = acc[i][4 * h + j] + bv;
+      }
+    }
+  }
+}
+
 constexpr int kDwChunk = 256;  // pixels per split-K work unit
 
 template <typename T, int MODE, bool WEIGHTED>
@@ -275,6 +426,13 @@ size_t simt_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t
 template <typename T, int MODE, bool WEIGHTED>
 static void launch_gemm(const ColSrc<T> &cs, const T *wgt, int64_t sm, int64_t sc, int64_t sk, const T *bias, T *out, int M,
                         int B, cudaStream_t st) {
+  if constexpr (sizeof(T) == 4) {
+    if (M >= 48) {  // (a half-empty tile still beats several passes of the small one over the same gathered columns)
+      dim3 grid128(cdiv(cs.npix, GN), cdiv(M, GM), B);
+      conv_gemm128_kernel<MODE, WEIGHTED><<<grid128, 256, 0, st>>>(cs, wgt, sm, sc, sk, bias, out, M);
+      return;
+    }
+  }
   dim3 grid(cdiv(cs.npix, TN), cdiv(M, TM), B);
   conv_gemm_kernel<T, MODE, WEIGHTED><<<grid, 256, 0, st>>>(cs, wgt, sm, sc, sk, bias, out, M);
 }
