@@ -67,6 +67,10 @@ size_t base_workspace(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, 
     return precision == SPH_PRECISION_BF16 ? tc_conv_backward_workspace(B, Cin, Cout, IH, IW, OH, OW, K, P, interp) : 0;
   if (precision == SPH_PRECISION_BF16) return tc_workspace_bytes(op, B, Cin, Cout, IH, IW, OH, OW, K, P, interp);
   switch (op) {
+    case SPH_CONV_FORWARD: return simt_gemm_workspace(Cout, Cin, K, ts);
+    case SPH_CONV_BACKWARD_INPUT: return simt_gemm_workspace(Cin, Cout, K, ts);
+    case SPH_TCONV_FORWARD: return simt_gemm_workspace(Cout, Cin, K, ts);
+    case SPH_TCONV_BACKWARD_INPUT: return simt_gemm_workspace(Cin, Cout, K, ts);
     case SPH_CONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts);
     case SPH_TCONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, ts);
     default: return 0;
@@ -120,7 +124,7 @@ int conv_forward(const void *x, const void *map, const void *iw, const void *wei
     return tc_conv_forward(x, map, iw, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st, fz);
   if (fz.active() || fz.out_cl != nullptr) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_gemm, false, x, map, iw, nullptr, Cin, IH, IW, K, P, OH * OW, interp, weight, Cin * K, K, 1,
-                      bias, out, Cout, B, st);
+                      bias, out, Cout, B, st, ws, ws_bytes);
 }
 
 int conv_backward_input(const void *gout, const void *plan, const void *weight, void *gx, int64_t B, int64_t Cin, int64_t Cout,
@@ -147,7 +151,7 @@ int conv_backward_input(const void *gout, const void *plan, const void *weight, 
     return tc_conv_backward_input(gout, plan, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st, fz);
   if (fz.active()) return SPH_ERR_UNSUPPORTED;
   return SPH_BY_DTYPE(simt_gemm, true, gout, nullptr, nullptr, plan, Cout, OH, OW, K, 0, IH * IW, 0, weight, K, Cin * K, 1,
-                      nullptr, gx, Cin, B, st);
+                      nullptr, gx, Cin, B, st, ws, ws_bytes);
 }
 
 int conv_backward_weight(const void *gout, const void *x, const void *map, const void *iw, void *gw, void *gb, int64_t B,
@@ -305,7 +309,7 @@ extern "C" int sph_mapped_tconv_forward(const void *x, const void *plan, const v
   if (precision == SPH_PRECISION_BF16)
     return tc_tconv_forward(x, plan, weight, bias, out, B, Cin, Cout, IH, IW, OH, OW, K, ws, ws_bytes, st);
   return SPH_BY_DTYPE(simt_gemm, true, x, nullptr, nullptr, plan, Cin, IH, IW, K, 0, OH * OW, 0, weight, K, Cout * K, 1,
-                      bias, out, Cout, B, st);
+                      bias, out, Cout, B, st, ws, ws_bytes);
 }
 
 extern "C" int sph_mapped_tconv_backward_input(const void *gout, const void *map, const void *iw, const void *weight,
@@ -325,7 +329,7 @@ extern "C" int sph_mapped_tconv_backward_input(const void *gout, const void *map
   if (precision == SPH_PRECISION_BF16)
     return tc_tconv_backward_input(gout, map, iw, weight, gx, B, Cin, Cout, IH, IW, OH, OW, K, P, interp, ws, ws_bytes, st);
   return SPH_BY_DTYPE(simt_gemm, false, gout, map, iw, nullptr, Cout, OH, OW, K, P, IH * IW, interp, weight, Cout * K, K, 1,
-                      nullptr, gx, Cin, B, st);
+                      nullptr, gx, Cin, B, st, ws, ws_bytes);
 }
 
 extern "C" int sph_mapped_tconv_backward_weight(const void *gout, const void *x, const void *map, const void *iw,

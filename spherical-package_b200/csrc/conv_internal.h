@@ -31,7 +31,10 @@ struct Fusion {
 template <typename T>
 int simt_gemm(bool use_plan, const void *src, const void *map, const void *iw, const void *plan, int64_t CH, int64_t SH,
               int64_t SW, int64_t K, int64_t P, int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc,
-              int64_t sk, const void *bias, void *out, int64_t M, int64_t B, cudaStream_t st);
+              int64_t sk, const void *bias, void *out, int64_t M, int64_t B, cudaStream_t st, void *ws = nullptr,
+              size_t ws_bytes = 0);
+// scratch simt_gemm can use (optional: a transposed copy of the weights for coalesced reads)
+size_t simt_gemm_workspace(int64_t M, int64_t CH, int64_t K, size_t ts);
 template <typename T>
 int simt_dw(const void *A, const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K,
             int64_t P, int64_t npix, int interp, int64_t M, int64_t B, void *gw, int64_t sm, int64_t sc, int64_t sk,

@@ -131,7 +131,7 @@ __device__ __forceinline__ void gunpack2(unsigned long long v, float &lo, float 
 template <int MODE, bool WEIGHTED>
 __global__ void __launch_bounds__(256, 2)
 conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk,
-                    const float *__restrict__ bias, float *__restrict__ out, int M) {
+                    const float *__restrict__ bias, float *__restrict__ out, int M, const float *__restrict__ wt) {
   __shared__ __align__(16) float Ws[GK][GM];
   __shared__ __align__(16) float Cs[GK][GN];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -152,8 +152,12 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
       const int kk = kk0 + half + 2 * i, m = m0 + nl;
       float v = 0.0f;
       if (kk < CHK && m < M) {
-        const int k = kk / cs.CH, ch = kk - k * cs.CH;
-        v = __ldg(wgt + m * sm + ch * sc + k * sk);
+        if (wt != nullptr) {  // transposed copy [kk][m]: neighbouring threads read neighbouring words
+          v = __ldg(wt + (size_t)kk * M + m);
+        } else {
+          const int k = kk / cs.CH, ch = kk - k * cs.CH;
+          v = __ldg(wgt + m * sm + ch * sc + k * sk);
+        }
       }
       wreg[i] = v;
     }
@@ -323,13 +327,159 @@ conv_dw_kernel(ColSrc<T> cs, const T *__restrict__ A, int M, int B, T *__restric
   }
 }
 
+// Weight gradient for float32 with at least 64 gathered channels: 128 rows x 128 columns per block, 8 x 8 accumulators
+// per thread (packed pair multiply-adds), columns slot-major (kk = k * CH + ch).  A block's 128 columns lie in at most
+// three slots, so the taps of a 16-pixel step are decoded once per (slot, pixel) into shared memory and every thread
+// gathers its column's eight pixels with them; the next step's operands are fetched while the current one is
+// multiplied.  partial[split][m][kk] in the same slot-major order (dw_reduce_kernel is told).
+constexpr int kDwSlots = 3;
+template <int MODE>
+__global__ void __launch_bounds__(256, 2)
+conv_dw128_kernel(ColSrc<float> cs, const float *__restrict__ A, int M, int B, float *__restrict__ partial) {
+  __shared__ __align__(16) float As[GK][GM];
+  __shared__ __align__(16) float Cs[GK][GN + 4];  // (padded: a thread stores eight columns of one pixel row)
+  __shared__ int t_off[2][kDwSlots][GK][4];
+  __shared__ float t_w[2][kDwSlots][GK][4];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int kk0 = blockIdx.x * GN, m0 = blockIdx.y * GM, splits = gridDim.z;
+  const int CHK = cs.CH * cs.K;
+  const size_t shw = (size_t)cs.SH * cs.SW;
+  const int chunks = (cs.npix + kDwChunk - 1) / kDwChunk;
+  const int k_first = kk0 / cs.CH;                       // first slot of the block's columns
+  // operand rows: gradient row cl, pixels half * 8 ..; columns: pixel gp of the step, the eight columns 8 * gc .. (a warp
+  // reads 16 neighbouring pixels of two channels per load instruction, not 32 channels of one pixel)
+  const int cl = tid & 127, half = tid >> 7;
+  const int gp = tid & 15, gc = tid >> 4, kk_first = kk0 + gc * 8;
+  const int ks0 = kk_first / cs.CH, ch_first = kk_first - ks0 * cs.CH;
+  const bool cols_uniform = kk_first + 8 <= CHK && ch_first + 8 <= cs.CH;  // all eight exist and share their slot
+  const bool a_ok = m0 + cl < M;
+  const bool vec = (cs.npix & 3) == 0 && (((uintptr_t)A) & 15) == 0;
+  unsigned long long acc2[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc2[i][j] = 0ull;
+  float areg[8], creg[8];
+  constexpr int TAPS = TapCount<MODE>::value;
+
+  // taps of the 16 pixels [p0, p0 + 16) for the block's slots into table `buf` (threads 0 .. 16 * kDwSlots - 1)
+  auto decode_step = [&](int buf, int p0, int pend) {
+    if (tid < GK * kDwSlots) {
+      const int pl = tid % GK, sl = tid / GK, pix = p0 + pl, k = k_first + sl;
+      Taps<float> t;
+#pragma unroll
+      for (int i = 0; i < 4; i++) { t.off[i] = -1; t.w[i] = 0.0f; }
+      if (pix < pend && k < cs.K) {
+        const float *mp = cs.map + 2 * ((size_t)pix * cs.K + k);
+        decode<float, MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        t_off[buf][sl][pl][i] = (i < TAPS && t.off[i] >= 0 && index_ok(t.off[i], (long long)shw)) ? t.off[i] : -1;
+        t_w[buf][sl][pl][i] = t.w[i];
+      }
+    }
+  };
+  // operands of the step whose taps are in table `buf`: A rows (row cl, pixels half * 8 ..) and this column's values
+  auto fetch = [&](int buf, int b, int p0, int pend) {
+    const float *arow = A + ((size_t)b * M + m0 + cl) * cs.npix + p0 + half * 8;
+    if (a_ok && vec && p0 + half * 8 + 8 <= pend) {
+      const float4 u = __ldg((const float4 *)arow), v = __ldg((const float4 *)arow + 1);
+      areg[0] = u.x; areg[1] = u.y; areg[2] = u.z; areg[3] = u.w; areg[4] = v.x; areg[5] = v.y; areg[6] = v.z; areg[7] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++) areg[j] = (a_ok && p0 + half * 8 + j < pend) ? __ldg(arow + j) : 0.0f;
+    }
+    auto value = [&](const float *plane, const int4 &o, const float4 &w) {
+      const float v0 = o.x >= 0 ? __ldg(plane + o.x) : 0.0f;
+      if constexpr (TAPS == 1) {
+        return v0;
+      } else {
+        const float v1 = o.y >= 0 ? __ldg(plane + o.y) : 0.0f, v2 = o.z >= 0 ? __ldg(plane + o.z) : 0.0f;
+        const float v3 = o.w >= 0 ? __ldg(plane + o.w) : 0.0f;
+        // ((w0 v0 + w1 v1) + w2 v2) + w3 v3 with separate roundings, as the forward operator
+        return __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(w.x, v0), __fmul_rn(w.y, v1)), __fmul_rn(w.z, v2)), __fmul_rn(w.w, v3));
+      }
+    };
+    const float *img = cs.src + (size_t)b * cs.CH * shw;
+    if (cols_uniform) {
+      const int4 o = *(const int4 *)t_off[buf][ks0 - k_first][gp];
+      const float4 w = *(const float4 *)t_w[buf][ks0 - k_first][gp];
+#pragma unroll
+      for (int j = 0; j < 8; j++) creg[j] = value(img + (size_t)(ch_first + j) * shw, o, w);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int kk = kk_first + j;
+        float v = 0.0f;
+        if (kk < CHK) {
+          const int k = kk / cs.CH, ch = kk - k * cs.CH;
+          v = value(img + (size_t)ch * shw, *(const int4 *)t_off[buf][k - k_first][gp], *(const float4 *)t_w[buf][k - k_first][gp]);
+        }
+        creg[j] = v;
+      }
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int j = 0; j < 8; j++) As[half * 8 + j][cl] = areg[j];
+    *(float4 *)&Cs[gp][gc * 8] = make_float4(creg[0], creg[1], creg[2], creg[3]);
+    *(float4 *)&Cs[gp][gc * 8 + 4] = make_float4(creg[4], creg[5], creg[6], creg[7]);
+  };
+
+  for (int unit = blockIdx.z; unit < B * chunks; unit += splits) {
+    const int b = unit / chunks, pbase = (unit % chunks) * kDwChunk, pend = min(cs.npix, pbase + kDwChunk);
+    int buf = 0;
+    decode_step(0, pbase, pend);
+    __syncthreads();
+    fetch(0, b, pbase, pend);
+    for (int p0 = pbase; p0 < pend; p0 += GK) {
+      const bool more = p0 + GK < pend;
+      __syncthreads();  // the previous step's tiles have been read
+      stash();
+      if (more) decode_step(buf ^ 1, p0 + GK, pend);
+      __syncthreads();
+      if (more) fetch(buf ^ 1, b, p0 + GK, pend);  // in flight while this step is multiplied
+#pragma unroll
+      for (int kl = 0; kl < GK; kl++) {
+        const float4 a0 = *(const float4 *)&As[kl][ty * 8], a1 = *(const float4 *)&As[kl][ty * 8 + 4];
+        const float4 c0 = *(const float4 *)&Cs[kl][tx * 4], c1 = *(const float4 *)&Cs[kl][64 + tx * 4];
+        const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const unsigned long long c2[4] = {gpack2(c0.x, c0.y), gpack2(c0.z, c0.w), gpack2(c1.x, c1.y), gpack2(c1.z, c1.w)};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const unsigned long long aa = gpack2(a[i], a[i]);
+#pragma unroll
+          for (int j = 0; j < 4; j++) gffma2(acc2[i][j], aa, c2[j]);
+        }
+      }
+      buf ^= 1;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const int m = m0 + ty * 8 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      float lo, hi;
+      gunpack2(acc2[i][j], lo, hi);
+      const int c = kk0 + (j >> 1) * 64 + tx * 4 + (j & 1) * 2;
+      float *dst = partial + ((size_t)blockIdx.z * M + m) * CHK + c;
+      if (c < CHK) dst[0] = lo;
+      if (c + 1 < CHK) dst[1] = hi;
+    }
+  }
+}
+
 // gw[m,ch,k] = sum over splits, in a fixed order (deterministic): 32 outputs per block, sixteen threads per
 // output each summing every sixteenth split, then the sixteen sums in order.
 constexpr int kReduceLanes = 16;
 template <typename T>
 __global__ void __launch_bounds__(32 * kReduceLanes) dw_reduce_kernel(const T *__restrict__ partial, int splits, int M, int CHK,
                                                                       int K, int64_t sm, int64_t sc, int64_t sk,
-                                                                      T *__restrict__ gw) {
+                                                                      T *__restrict__ gw, int slot_major = 0) {
   __shared__ T red[kReduceLanes][32];
   const int i = blockIdx.x * 32 + threadIdx.x, zl = threadIdx.y;
   const size_t n = (size_t)M * CHK;
@@ -350,8 +500,9 @@ __global__ void __launch_bounds__(32 * kReduceLanes) dw_reduce_kernel(const T *_
     T s = red[0][threadIdx.x];
 #pragma unroll
     for (int j = 1; j < kReduceLanes; j++) s += red[j][threadIdx.x];
-    const int m = i / CHK, kk = i % CHK;
-    gw[m * sm + (kk / K) * sc + (kk % K) * sk] = s;
+    const int m = i / CHK, kk = i % CHK, CH = CHK / K;
+    const int ch = slot_major ? kk % CH : kk / K, k = slot_major ? kk / CH : kk % K;
+    gw[m * sm + ch * sc + k * sk] = s;
   }
 }
 
@@ -408,10 +559,13 @@ int simt_bias_grad(const void *g, int64_t B, int64_t C, int64_t n, void *gb, voi
 template int simt_bias_grad<float>(const void *, int64_t, int64_t, int64_t, void *, void *, cudaStream_t);
 template int simt_bias_grad<double>(const void *, int64_t, int64_t, int64_t, void *, void *, cudaStream_t);
 
-static int dw_splits(int64_t B, int64_t npix, int64_t M, int64_t CHK) {
+// big: the shape the 128 x 128 float32 kernel takes (fewer, larger tiles: more splits to fill the device)
+static bool dw_big(int64_t M, int64_t CH, size_t ts) { return ts == 4 && M >= 48 && CH >= 64; }
+static int dw_splits(int64_t B, int64_t npix, int64_t M, int64_t CHK, bool big) {
   const int64_t units = B * ((npix + kDwChunk - 1) / kDwChunk);
-  const int64_t tiles = ((CHK + TN - 1) / TN) * ((M + TM - 1) / TM);
-  int64_t s = (4 * 148 + tiles - 1) / tiles;
+  const int64_t tn = big ? GN : TN, tm = big ? GM : TM;
+  const int64_t tiles = ((CHK + tn - 1) / tn) * ((M + tm - 1) / tm);
+  int64_t s = big ? (4 * 148) / tiles : (4 * 148 + tiles - 1) / tiles;  // (large tile: two blocks per SM, two full waves)
   if (s > 64) s = 64;
   if (s > units) s = units;
   if (s < 1) s = 1;
@@ -420,16 +574,36 @@ static int dw_splits(int64_t B, int64_t npix, int64_t M, int64_t CHK) {
 
 size_t simt_dw_workspace(int64_t B, int64_t npix, int64_t M, int64_t CH, int64_t K, int64_t Cbias, size_t ts) {
   const int64_t CHK = CH * K;
-  return align_up(ts * (size_t)(dw_splits(B, npix, M, CHK) * M * CHK), 256) + align_up(ts * (size_t)(Cbias * kBiasSplits), 256);
+  return align_up(ts * (size_t)(dw_splits(B, npix, M, CHK, dw_big(M, CH, ts)) * M * CHK), 256) +
+         align_up(ts * (size_t)(Cbias * kBiasSplits), 256);
+}
+
+// wt[kk][m] = w[m*sm + ch*sc + k*sk] with kk = k * CH + ch (the slot-major column order of conv_gemm128_kernel)
+__global__ void weight_transpose_kernel(const float *__restrict__ w, float *__restrict__ wt, int M, int CH, int K, int64_t sm,
+                                        int64_t sc, int64_t sk) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * CH * K) return;
+  const int m = i % M, kk = i / M, k = kk / CH, ch = kk - k * CH;
+  wt[i] = w[m * sm + ch * sc + k * sk];
+}
+
+size_t simt_gemm_workspace(int64_t M, int64_t CH, int64_t K, size_t ts) {
+  return (ts == 4 && M >= 48) ? align_up((size_t)(M * CH * K) * 4, 256) : 0;
 }
 
 template <typename T, int MODE, bool WEIGHTED>
 static void launch_gemm(const ColSrc<T> &cs, const T *wgt, int64_t sm, int64_t sc, int64_t sk, const T *bias, T *out, int M,
-                        int B, cudaStream_t st) {
+                        int B, cudaStream_t st, void *ws, size_t ws_bytes) {
   if constexpr (sizeof(T) == 4) {
     if (M >= 48) {  // (a half-empty tile still beats several passes of the small one over the same gathered columns)
+      const float *wt = nullptr;
+      if (ws != nullptr && ws_bytes >= simt_gemm_workspace(M, cs.CH, cs.K, 4) && (((uintptr_t)ws) & 3) == 0) {
+        weight_transpose_kernel<<<cdiv((int64_t)M * cs.CH * cs.K, 256), 256, 0, st>>>(wgt, (float *)ws, M, cs.CH, cs.K, sm, sc, sk);
+        note_launches(1);
+        wt = (const float *)ws;
+      }
       dim3 grid128(cdiv(cs.npix, GN), cdiv(M, GM), B);
-      conv_gemm128_kernel<MODE, WEIGHTED><<<grid128, 256, 0, st>>>(cs, wgt, sm, sc, sk, bias, out, M);
+      conv_gemm128_kernel<MODE, WEIGHTED><<<grid128, 256, 0, st>>>(cs, wgt, sm, sc, sk, bias, out, M, wt);
       return;
     }
   }
@@ -441,14 +615,14 @@ static void launch_gemm(const ColSrc<T> &cs, const T *wgt, int64_t sm, int64_t s
 template <typename T>
 int simt_gemm(bool use_plan, const void *src, const void *map, const void *iw, const void *plan, int64_t CH, int64_t SH,
               int64_t SW, int64_t K, int64_t P, int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc,
-              int64_t sk, const void *bias, void *out, int64_t M, int64_t B, cudaStream_t st) {
+              int64_t sk, const void *bias, void *out, int64_t M, int64_t B, cudaStream_t st, void *ws, size_t ws_bytes) {
   ColSrc<T> cs{(const T *)src, (const T *)map, (const T *)iw, plan, (int)CH, (int)SH, (int)SW, (int)K, (int)P, (int)npix};
   if (use_plan) {
-    launch_gemm<T, COL_PLAN, false>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st);
+    launch_gemm<T, COL_PLAN, false>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st, ws, ws_bytes);
   } else {
     SPH_DISPATCH_INTERP(interp, {
-      if (P > 0) launch_gemm<T, INTERP, true>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st);
-      else launch_gemm<T, INTERP, false>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st);
+      if (P > 0) launch_gemm<T, INTERP, true>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st, ws, ws_bytes);
+      else launch_gemm<T, INTERP, false>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st, ws, ws_bytes);
     });
   }
   return launch_status();
@@ -460,17 +634,30 @@ int simt_dw(const void *A, const void *src, const void *map, const void *iw, int
             int64_t P, int64_t npix, int interp, int64_t M, int64_t B, void *gw, int64_t sm, int64_t sc, int64_t sk,
             const void *gbias_src, int64_t Cbias, int64_t nbias, void *gb, void *ws, size_t ws_bytes, cudaStream_t st) {
   const int64_t CHK = CH * K;
-  const int splits = dw_splits(B, npix, M, CHK);
+  const int splits = dw_splits(B, npix, M, CHK, dw_big(M, CH, sizeof(T)));
   if (ws_bytes < simt_dw_workspace(B, npix, M, CH, K, Cbias, sizeof(T)) || !ws) return SPH_ERR_WORKSPACE_TOO_SMALL;
   T *partial = (T *)ws;
   T *bpart = (T *)((char *)ws + align_up(sizeof(T) * (size_t)(splits * M * CHK), 256));
   ColSrc<T> cs{(const T *)src, (const T *)map, (const T *)iw, nullptr, (int)CH, (int)SH, (int)SW, (int)K, (int)P, (int)npix};
-  dim3 grid(cdiv(CHK, TN), cdiv(M, TM), splits);
-  SPH_DISPATCH_INTERP(interp, {
-    if (P > 0) conv_dw_kernel<T, INTERP, true><<<grid, 256, 0, st>>>(cs, (const T *)A, (int)M, (int)B, partial);
-    else conv_dw_kernel<T, INTERP, false><<<grid, 256, 0, st>>>(cs, (const T *)A, (int)M, (int)B, partial);
-  });
-  dw_reduce_kernel<T><<<cdiv(M * CHK, 32), dim3(32, kReduceLanes), 0, st>>>(partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw);
+  int slot_major = 0;
+  if constexpr (sizeof(T) == 4) {
+    // the large tile: unweighted maps, enough rows to fill it, and so many channels that a block's columns lie in at
+    // most kDwSlots slots
+    if (P == 0 && dw_big(M, CH, sizeof(T))) {
+      slot_major = 1;
+      dim3 grid128(cdiv(CHK, GN), cdiv(M, GM), splits);
+      SPH_DISPATCH_INTERP(interp, (conv_dw128_kernel<INTERP><<<grid128, 256, 0, st>>>(cs, (const float *)A, (int)M, (int)B, (float *)partial)));
+    }
+  }
+  if (!slot_major) {
+    dim3 grid(cdiv(CHK, TN), cdiv(M, TM), splits);
+    SPH_DISPATCH_INTERP(interp, {
+      if (P > 0) conv_dw_kernel<T, INTERP, true><<<grid, 256, 0, st>>>(cs, (const T *)A, (int)M, (int)B, partial);
+      else conv_dw_kernel<T, INTERP, false><<<grid, 256, 0, st>>>(cs, (const T *)A, (int)M, (int)B, partial);
+    });
+  }
+  dw_reduce_kernel<T><<<cdiv(M * CHK, 32), dim3(32, kReduceLanes), 0, st>>>(partial, splits, (int)M, (int)CHK, (int)K, sm, sc, sk, (T *)gw,
+                                                                           slot_major);
   bias_partial_kernel<T><<<dim3((unsigned)Cbias, kBiasSplits), 256, 0, st>>>((const T *)gbias_src, (int)B, (int)Cbias, (int)nbias, bpart);
   bias_final_kernel<T><<<cdiv(Cbias, 128), 128, 0, st>>>(bpart, (int)Cbias, (T *)gb);
   return launch_status(4);
@@ -478,10 +665,10 @@ int simt_dw(const void *A, const void *src, const void *map, const void *iw, int
 
 template int simt_gemm<float>(bool, const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t,
                               int64_t, int64_t, int, const void *, int64_t, int64_t, int64_t, const void *, void *, int64_t,
-                              int64_t, cudaStream_t);
+                              int64_t, cudaStream_t, void *, size_t);
 template int simt_gemm<double>(bool, const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t,
                                int64_t, int64_t, int, const void *, int64_t, int64_t, int64_t, const void *, void *, int64_t,
-                               int64_t, cudaStream_t);
+                               int64_t, cudaStream_t, void *, size_t);
 template int simt_dw<float>(const void *, const void *, const void *, const void *, int64_t, int64_t, int64_t, int64_t, int64_t,
                             int64_t, int, int64_t, int64_t, void *, int64_t, int64_t, int64_t, const void *, int64_t, int64_t,
                             void *, void *, size_t, cudaStream_t);
