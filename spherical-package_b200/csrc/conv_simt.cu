@@ -180,6 +180,19 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
         return;
       }
     }
+    if constexpr (MODE != COL_PLAN && !WEIGHTED) {
+      // likewise through the map: one division and one decoded map entry for the eight channels
+      const int kk_first = kk0 + half * 8, k = kk_first / cs.CH, ch0 = kk_first - k * cs.CH;
+      if (pix_ok && kk_first + 8 <= CHK && ch0 + 8 <= cs.CH) {
+        Taps<float> t8;
+        const float *mp = cs.map + 2 * ((size_t)pix * cs.K + k);
+        decode<float, MODE == COL_PLAN ? 0 : MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t8);
+        const float *plane0 = img + (size_t)ch0 * shw;
+#pragma unroll
+        for (int j = 0; j < 8; j++) creg[j] = gather<float, MODE == COL_PLAN ? 0 : MODE>(plane0 + (size_t)j * shw, t8);
+        return;
+      }
+    }
     int cur_k = -1;
     Taps<float> t;
 #pragma unroll
