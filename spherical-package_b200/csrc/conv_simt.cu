@@ -193,6 +193,26 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
         return;
       }
     }
+    if constexpr (MODE != COL_PLAN && WEIGHTED) {
+      // weighted maps: the slot's P points are decoded once for the eight channels; per channel the sum runs over the
+      // points in order, acc += w_q * interp_q with separate roundings (as gather_slot)
+      const int kk_first = kk0 + half * 8, k = kk_first / cs.CH, ch0 = kk_first - k * cs.CH;
+      if (pix_ok && kk_first + 8 <= CHK && ch0 + 8 <= cs.CH) {
+        const size_t e = ((size_t)pix * cs.K + k) * cs.P;
+        const float *plane0 = img + (size_t)ch0 * shw;
+#pragma unroll
+        for (int j = 0; j < 8; j++) creg[j] = 0.0f;
+        for (int q = 0; q < cs.P; q++) {
+          Taps<float> tq;
+          decode<float, MODE == COL_PLAN ? 0 : MODE>(__ldg(cs.map + 2 * (e + q)), __ldg(cs.map + 2 * (e + q) + 1), cs.SH, cs.SW, tq);
+          const float wq = __ldg(cs.iw + e + q);
+#pragma unroll
+          for (int j = 0; j < 8; j++)
+            creg[j] = __fadd_rn(creg[j], __fmul_rn(wq, gather<float, MODE == COL_PLAN ? 0 : MODE>(plane0 + (size_t)j * shw, tq)));
+        }
+        return;
+      }
+    }
     int cur_k = -1;
     Taps<float> t;
 #pragma unroll
@@ -345,8 +365,10 @@ conv_dw_kernel(ColSrc<T> cs, const T *__restrict__ A, int M, int B, T *__restric
 // three slots, so the taps of a 16-pixel step are decoded once per (slot, pixel) into shared memory and every thread
 // gathers its column's eight pixels with them; the next step's operands are fetched while the current one is
 // multiplied.  partial[split][m][kk] in the same slot-major order (dw_reduce_kernel is told).
+// WN: weighted nearest map with at most four points per slot - its value sum_q w_q x[tap_q], added in order, is the
+// four-tap combine with the points in the taps' places.
 constexpr int kDwSlots = 3;
-template <int MODE>
+template <int MODE, bool WN = false>
 __global__ void __launch_bounds__(256, 2)
 conv_dw128_kernel(ColSrc<float> cs, const float *__restrict__ A, int M, int B, float *__restrict__ partial) {
   __shared__ __align__(16) float As[GK][GM];
@@ -373,7 +395,7 @@ conv_dw128_kernel(ColSrc<float> cs, const float *__restrict__ A, int M, int B, f
 #pragma unroll
     for (int j = 0; j < 4; j++) acc2[i][j] = 0ull;
   float areg[8], creg[8];
-  constexpr int TAPS = TapCount<MODE>::value;
+  constexpr int TAPS = WN ? 4 : TapCount<MODE>::value;
 
   // taps of the 16 pixels [p0, p0 + 16) for the block's slots into table `buf` (threads 0 .. 16 * kDwSlots - 1)
   auto decode_step = [&](int buf, int p0, int pend) {
@@ -383,8 +405,18 @@ conv_dw128_kernel(ColSrc<float> cs, const float *__restrict__ A, int M, int B, f
 #pragma unroll
       for (int i = 0; i < 4; i++) { t.off[i] = -1; t.w[i] = 0.0f; }
       if (pix < pend && k < cs.K) {
-        const float *mp = cs.map + 2 * ((size_t)pix * cs.K + k);
-        decode<float, MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t);
+        if constexpr (WN) {
+          const size_t e = ((size_t)pix * cs.K + k) * cs.P;
+          for (int q = 0; q < cs.P && q < 4; q++) {
+            Taps<float> tq;
+            decode<float, SPH_NEAREST>(__ldg(cs.map + 2 * (e + q)), __ldg(cs.map + 2 * (e + q) + 1), cs.SH, cs.SW, tq);
+            t.off[q] = tq.off[0];
+            t.w[q] = __ldg(cs.iw + e + q);
+          }
+        } else {
+          const float *mp = cs.map + 2 * ((size_t)pix * cs.K + k);
+          decode<float, MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t);
+        }
       }
 #pragma unroll
       for (int i = 0; i < 4; i++) {
@@ -656,10 +688,14 @@ int simt_dw(const void *A, const void *src, const void *map, const void *iw, int
   if constexpr (sizeof(T) == 4) {
     // the large tile: unweighted maps, enough rows to fill it, and so many channels that a block's columns lie in at
     // most kDwSlots slots
-    if (P == 0 && dw_big(M, CH, sizeof(T))) {
+    const bool weighted_nearest = P > 0 && P <= 4 && interp == SPH_NEAREST;
+    if ((P == 0 || weighted_nearest) && dw_big(M, CH, sizeof(T))) {
       slot_major = 1;
       dim3 grid128(cdiv(CHK, GN), cdiv(M, GM), splits);
-      SPH_DISPATCH_INTERP(interp, (conv_dw128_kernel<INTERP><<<grid128, 256, 0, st>>>(cs, (const float *)A, (int)M, (int)B, (float *)partial)));
+      if (weighted_nearest)
+        conv_dw128_kernel<SPH_NEAREST, true><<<grid128, 256, 0, st>>>(cs, (const float *)A, (int)M, (int)B, (float *)partial);
+      else
+        SPH_DISPATCH_INTERP(interp, (conv_dw128_kernel<INTERP><<<grid128, 256, 0, st>>>(cs, (const float *)A, (int)M, (int)B, (float *)partial)));
     }
   }
   if (!slot_major) {
