@@ -128,28 +128,31 @@ __device__ __forceinline__ void gunpack2(unsigned long long v, float &lo, float 
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
 
-template <int MODE, bool WEIGHTED>
+// RM = output rows per thread: 8 (128-row tile) or 4 (64-row tile, for operators with about 64 output rows).
+template <int MODE, bool WEIGHTED, int RM>
 __global__ void __launch_bounds__(256, 2)
 conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm, int64_t sc, int64_t sk,
                     const float *__restrict__ bias, float *__restrict__ out, int M, const float *__restrict__ wt) {
-  __shared__ __align__(16) float Ws[GK][GM];
+  constexpr int GMt = 16 * RM, kWPass = 256 / GMt, kWN = GK / kWPass;  // tile rows; weight rows per pass; passes
+  __shared__ __align__(16) float Ws[GK][GMt];
   __shared__ __align__(16) float Cs[GK][GN];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  const int b = blockIdx.z, m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
+  const int b = blockIdx.z, m0 = blockIdx.y * GMt, n0 = blockIdx.x * GN;
   const int CHK = cs.CH * cs.K;
   const size_t shw = (size_t)cs.SH * cs.SW;
   PlanView<float> pv{};
   bool ok = true;
   if (MODE == COL_PLAN) pv = plan_view<float>(cs.plan, cs.npix * cs.K, ok);
   const float *img = cs.src + (size_t)b * cs.CH * shw;
-  // operand fetch: weights (kl = tid >> 7 + 2 i, row tid & 127), columns (pixel tid & 127, kl = 8 * (tid >> 7) + j)
+  // operand fetch: weights (row wl, kl = wr + kWPass * i), columns (pixel tid & 127, kl = 8 * (tid >> 7) + j)
   const int nl = tid & 127, half = tid >> 7, pix = n0 + nl;
+  const int wl = tid % GMt, wr = tid / GMt;
   const bool pix_ok = ok && pix < cs.npix;
-  float wreg[8], creg[8];
+  float wreg[kWN], creg[8];
   auto fetch = [&](int kk0) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const int kk = kk0 + half + 2 * i, m = m0 + nl;
+    for (int i = 0; i < kWN; i++) {
+      const int kk = kk0 + wr + kWPass * i, m = m0 + wl;
       float v = 0.0f;
       if (kk < CHK && m < M) {
         if (wt != nullptr) {  // transposed copy [kk][m]: neighbouring threads read neighbouring words
@@ -238,13 +241,13 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
   };
   auto stash = [&]() {
 #pragma unroll
-    for (int i = 0; i < 8; i++) Ws[half + 2 * i][nl] = wreg[i];
+    for (int i = 0; i < kWN; i++) Ws[wr + kWPass * i][wl] = wreg[i];
 #pragma unroll
     for (int j = 0; j < 8; j++) Cs[half * 8 + j][nl] = creg[j];
   };
-  unsigned long long acc2[8][4];  // 8 rows x 4 pixel pairs, multiplied with packed float32 pair FMAs
+  unsigned long long acc2[RM][4];  // RM rows x 4 pixel pairs, multiplied with packed float32 pair FMAs
 #pragma unroll
-  for (int i = 0; i < 8; i++)
+  for (int i = 0; i < RM; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc2[i][j] = 0ull;
 
@@ -256,12 +259,16 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
     if (more) fetch(kk0 + GK);  // in flight while this step is multiplied
 #pragma unroll
     for (int kl = 0; kl < GK; kl++) {
-      const float4 a0 = *(const float4 *)&Ws[kl][ty * 8], a1 = *(const float4 *)&Ws[kl][ty * 8 + 4];
+      float a[RM];
+#pragma unroll
+      for (int i = 0; i < RM; i += 4) {
+        const float4 av = *(const float4 *)&Ws[kl][ty * RM + i];
+        a[i] = av.x; a[i + 1] = av.y; a[i + 2] = av.z; a[i + 3] = av.w;
+      }
       const float4 c0 = *(const float4 *)&Cs[kl][tx * 4], c1 = *(const float4 *)&Cs[kl][64 + tx * 4];
-      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const unsigned long long c2[4] = {gpack2(c0.x, c0.y), gpack2(c0.z, c0.w), gpack2(c1.x, c1.y), gpack2(c1.z, c1.w)};
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
+      for (int i = 0; i < RM; i++) {
         const unsigned long long aa = gpack2(a[i], a[i]);
 #pragma unroll
         for (int j = 0; j < 4; j++) gffma2(acc2[i][j], aa, c2[j]);
@@ -273,15 +280,15 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
       __syncthreads();
     }
   }
-  float acc[8][8];
+  float acc[RM][8];
 #pragma unroll
-  for (int i = 0; i < 8; i++)
+  for (int i = 0; i < RM; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) gunpack2(acc2[i][j], acc[i][2 * j], acc[i][2 * j + 1]);
   const bool vec = (cs.npix & 3) == 0 && (((uintptr_t)out) & 15) == 0;
 #pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const int m = m0 + ty * 8 + i;
+  for (int i = 0; i < RM; i++) {
+    const int m = m0 + ty * RM + i;
     if (m >= M) continue;
     const float bv = bias ? __ldg(bias + m) : 0.0f;
     float *row = out + ((size_t)b * M + m) * cs.npix;
@@ -647,8 +654,13 @@ static void launch_gemm(const ColSrc<T> &cs, const T *wgt, int64_t sm, int64_t s
         note_launches(1);
         wt = (const float *)ws;
       }
-      dim3 grid128(cdiv(cs.npix, GN), cdiv(M, GM), B);
-      conv_gemm128_kernel<MODE, WEIGHTED><<<grid128, 256, 0, st>>>(cs, wgt, sm, sc, sk, bias, out, M, wt);
+      if (M % 128 > 0 && M % 128 <= 64) {  // (the last row block would be at most half full: 64-row tiles)
+        dim3 grid64(cdiv(cs.npix, GN), cdiv(M, 64), B);
+        conv_gemm128_kernel<MODE, WEIGHTED, 4><<<grid64, 256, 0, st>>>(cs, wgt, sm, sc, sk, bias, out, M, wt);
+      } else {
+        dim3 grid128(cdiv(cs.npix, GN), cdiv(M, GM), B);
+        conv_gemm128_kernel<MODE, WEIGHTED, 8><<<grid128, 256, 0, st>>>(cs, wgt, sm, sc, sk, bias, out, M, wt);
+      }
       return;
     }
   }
