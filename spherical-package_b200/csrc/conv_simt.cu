@@ -173,7 +173,24 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
         const int key = pix * cs.K + k;
         const int e0 = __ldg(pv.offsets + key), e1 = __ldg(pv.offsets + key + 1);
         const float *plane0 = img + (size_t)ch0 * shw;
-        for (int e = e0; e < e1; e++) {
+        // the first four entries' sources and weights are read together, then their 32 values (a dependent load per
+        // entry, one after the other, would leave the chain of latencies exposed); longer segments continue one by one
+        int sp4[4];
+        float w4[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const bool in = e0 + i < e1;
+          sp4[i] = in ? __ldg(pv.src + e0 + i) : -1;
+          w4[i] = in ? __ldg(pv.w + e0 + i) : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          if (sp4[i] >= 0 && index_ok(sp4[i], pv.n_src)) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) creg[j] += w4[i] * __ldg(plane0 + (size_t)j * shw + sp4[i]);
+          }
+        }
+        for (int e = e0 + 4; e < e1; e++) {
           const int sp = __ldg(pv.src + e);
           if (!index_ok(sp, pv.n_src)) continue;
           const float w = __ldg(pv.w + e);
