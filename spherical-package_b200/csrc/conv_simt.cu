@@ -421,25 +421,55 @@ conv_dw128_kernel(ColSrc<float> cs, const float *__restrict__ A, int M, int B, f
   float areg[8], creg[8];
   constexpr int TAPS = WN ? 4 : TapCount<MODE>::value;
 
-  // taps of the 16 pixels [p0, p0 + 16) for the block's slots into table `buf` (threads 0 .. 16 * kDwSlots - 1)
-  auto decode_step = [&](int buf, int p0, int pend) {
+  // Taps of the 16 pixels [p0, p0 + 16) for the block's slots (threads 0 .. 16 * kDwSlots - 1), in two parts: the map
+  // coordinates (and point weights) are loaded a step early, so that between the two barriers of a step only the
+  // arithmetic and the table stores remain.
+  constexpr int NPT = WN ? 4 : 1;  // points per slot held in registers
+  float cx[NPT], cy[NPT], cw[NPT];
+  bool c_have = false;
+  auto coords_load = [&](int p0, int pend) {
+    c_have = false;
     if (tid < GK * kDwSlots) {
       const int pl = tid % GK, sl = tid / GK, pix = p0 + pl, k = k_first + sl;
-      Taps<float> t;
-#pragma unroll
-      for (int i = 0; i < 4; i++) { t.off[i] = -1; t.w[i] = 0.0f; }
       if (pix < pend && k < cs.K) {
+        c_have = true;
         if constexpr (WN) {
           const size_t e = ((size_t)pix * cs.K + k) * cs.P;
-          for (int q = 0; q < cs.P && q < 4; q++) {
-            Taps<float> tq;
-            decode<float, SPH_NEAREST>(__ldg(cs.map + 2 * (e + q)), __ldg(cs.map + 2 * (e + q) + 1), cs.SH, cs.SW, tq);
-            t.off[q] = tq.off[0];
-            t.w[q] = __ldg(cs.iw + e + q);
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const bool in = q < cs.P;
+            cx[q] = in ? __ldg(cs.map + 2 * (e + q)) : 0.0f;
+            cy[q] = in ? __ldg(cs.map + 2 * (e + q) + 1) : 0.0f;
+            cw[q] = in ? __ldg(cs.iw + e + q) : 0.0f;
           }
         } else {
           const float *mp = cs.map + 2 * ((size_t)pix * cs.K + k);
-          decode<float, MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t);
+          cx[0] = __ldg(mp);
+          cy[0] = __ldg(mp + 1);
+          cw[0] = 1.0f;
+        }
+      }
+    }
+  };
+  auto decode_store = [&](int buf) {
+    if (tid < GK * kDwSlots) {
+      const int pl = tid % GK, sl = tid / GK;
+      Taps<float> t;
+#pragma unroll
+      for (int i = 0; i < 4; i++) { t.off[i] = -1; t.w[i] = 0.0f; }
+      if (c_have) {
+        if constexpr (WN) {
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            if (q < cs.P) {
+              Taps<float> tq;
+              decode<float, SPH_NEAREST>(cx[q], cy[q], cs.SH, cs.SW, tq);
+              t.off[q] = tq.off[0];
+              t.w[q] = cw[q];
+            }
+          }
+        } else {
+          decode<float, MODE>(cx[0], cy[0], cs.SH, cs.SW, t);
         }
       }
 #pragma unroll
@@ -499,16 +529,21 @@ conv_dw128_kernel(ColSrc<float> cs, const float *__restrict__ A, int M, int B, f
   for (int unit = blockIdx.z; unit < B * chunks; unit += splits) {
     const int b = unit / chunks, pbase = (unit % chunks) * kDwChunk, pend = min(cs.npix, pbase + kDwChunk);
     int buf = 0;
-    decode_step(0, pbase, pend);
+    coords_load(pbase, pend);
+    decode_store(0);
     __syncthreads();
     fetch(0, b, pbase, pend);
+    if (pbase + GK < pend) coords_load(pbase + GK, pend);
     for (int p0 = pbase; p0 < pend; p0 += GK) {
       const bool more = p0 + GK < pend;
       __syncthreads();  // the previous step's tiles have been read
       stash();
-      if (more) decode_step(buf ^ 1, p0 + GK, pend);
+      if (more) decode_store(buf ^ 1);  // (coordinates of step p0 + GK: loaded during the previous step)
       __syncthreads();
-      if (more) fetch(buf ^ 1, b, p0 + GK, pend);  // in flight while this step is multiplied
+      if (more) {
+        fetch(buf ^ 1, b, p0 + GK, pend);  // in flight while this step is multiplied
+        if (p0 + 2 * GK < pend) coords_load(p0 + 2 * GK, pend);
+      }
 #pragma unroll
       for (int kl = 0; kl < GK; kl++) {
         const float4 a0 = *(const float4 *)&As[kl][ty * 8], a1 = *(const float4 *)&As[kl][ty * 8 + 4];
