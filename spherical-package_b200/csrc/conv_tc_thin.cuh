@@ -337,8 +337,9 @@ int tc_thin_forward(const void *src, const void *map, const void *iw, int64_t CH
 // blocks: G[o][px] = grad_output (masked by the saved activation) as bf16, rows = output channel, and Col[px][j] =
 // the gathered columns (plus a column of ones at j = CH*K for the bias gradient), rows = pixel.  G serves twice:
 //   D1[o, j]  += G (K-major A: M = o, K = px) x Col (MN-major B: K = px, N = j)          -> dW and dBias, kept in TMEM
-//   D2[j, px]  = Wt (K-major A: M = j, K = o, resident) x G (MN-major B: K = o, N = px)  -> T2[b][j][px] = sum_o W g
-// T2 (bf16, one plane per column j) is what the plan gather of the input gradient reads, so grad_output and the
+//   D2[j, px]  = Wt (K-major A: M = j, K = o, resident) x G (MN-major B: K = o, N = px)  -> sum_o W[o, j] g[o, px]
+// D2 is drained every step, transposed through shared memory and written as the bf16 column buffer T2[b][px][k][c]
+// (per pixel one 8-byte vector per slot), which the plan gather of the input gradient reads - so grad_output and the
 // activation are read from memory exactly once for all three gradients.
 constexpr int kThinBwdTeams = 4;                 // producer teams of two warps; team t fills stage t
 constexpr int kThinBwdPix = 64;                  // pixels per step
