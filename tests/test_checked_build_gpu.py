@@ -87,6 +87,12 @@ for dtype in (torch.float32, torch.float64):
                 outs.append(capi.conv_forward(x64, md, w64, b64, K, interp, None, capi.BF16))
                 outs.append(capi.conv_backward_input(g64, plan, w64, IH, IW, K, capi.BF16))
                 outs += list(capi.conv_backward_weight(g64, x64, md, K, interp, None, capi.BF16))
+                # and the large-tile exact float32 kernels (64 output rows, 64 gathered channels)
+                e_out = capi.conv_forward(x64, md, w64, b64, K, interp, None)
+                outs += [e_out, capi.conv_backward_input(g64, plan, w64, IH, IW, K)]
+                outs += list(capi.conv_backward_weight(g64, x64, md, K, interp, None))
+                mm64 = m.clone(); mm64.view(-1, 2)[:5] = -100.0
+                close(e_out.cpu(), port.mapped_conv_forward(x64.cpu(), mm64, w64.cpu(), b64.cpu(), K, interp, None), 1e-4)
             if dtype == torch.float32:                 # the thin layer's own tensor-core kernels (3 channels, bf16 precision)
                 w16 = (torch.randn(16, C, K, generator=g) / 3).cuda(); b16 = torch.zeros(16).cuda()
                 g16 = torch.randn(B, 16, OH, OW, generator=g).cuda()
