@@ -357,12 +357,17 @@ int sph_mapped_conv_relu_backward_weight(const void *gout, const void *act_out, 
  *       (or NULL) is the fused ReLU's output whose sign masks it; x_cl (or
  *       NULL) the companion of x.  Workspace: op SPH_CONV_BACKWARD.  Returns
  *       SPH_ERR_UNSUPPORTED before launching anything for shapes that do not
- *       run on the two tensor-core kernels (exact precision, thin layers):
- *       use the separate entry points there.
+ *       run on tensor-core kernels (exact precision; thin layers whose
+ *       tensor-core form does not apply): use the separate entry points
+ *       there.
+ *   sph_conv_companion_fill  writes the companion of an existing float32
+ *       tensor (a host that calls the same layer's forward and backward can
+ *       convert the input once and pass the copy to both).
  * Results are bit-identical to the separate entry points.
  * ---------------------------------------------------------------------- */
 size_t sph_conv_companion_bytes(int64_t B, int64_t C, int64_t H, int64_t W);
 int64_t sph_conv_companion_channels(int64_t C); /* Cp, the companion's channel pitch */
+int sph_conv_companion_fill(const void *x, void *x_cl, int64_t B, int64_t C, int64_t H, int64_t W, void *stream);
 int sph_mapped_conv_forward_cl(const void *x, const void *x_cl, const void *map, const void *iw, const void *weight,
                                const void *bias, void *out, void *out_cl, int64_t B, int64_t Cin, int64_t Cout, int64_t IH,
                                int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype, int interp,

@@ -252,6 +252,14 @@ extern "C" size_t sph_conv_companion_bytes(int64_t B, int64_t C, int64_t H, int6
 
 extern "C" int64_t sph_conv_companion_channels(int64_t C) { return C > 0 ? padded_channels(C) : 0; }
 
+extern "C" int sph_conv_companion_fill(const void *x, void *x_cl, int64_t B, int64_t C, int64_t H, int64_t W, void *stream) {
+  SPH_RANGE("sph_conv_companion_fill");
+  if (!x || !x_cl || ((uintptr_t)x_cl & 15) != 0) return SPH_ERR_INVALID_ARGUMENT;
+  if (sph_conv_companion_bytes(B, C, H, W) == 0) return SPH_ERR_INVALID_ARGUMENT;
+  if (B == 0) return SPH_OK;
+  return tc_fill_companion(x, x_cl, B, C, H * W, (cudaStream_t)stream);
+}
+
 extern "C" int sph_mapped_conv_forward_cl(const void *x, const void *x_cl, const void *map, const void *iw, const void *weight,
                                           const void *bias, void *out, void *out_cl, int64_t B, int64_t Cin, int64_t Cout,
                                           int64_t IH, int64_t IW, int64_t OH, int64_t OW, int64_t K, int64_t P, int dtype,

@@ -84,6 +84,7 @@ int tc_conv_backward(const void *gout, const void *x, const void *plan, const vo
 size_t tc_conv_backward_workspace(int64_t B, int64_t Cin, int64_t Cout, int64_t IH, int64_t IW, int64_t OH, int64_t OW,
                                   int64_t K, int64_t P, int interp);
 int padded_channels(int64_t CH);
+int tc_fill_companion(const void *x, void *x_cl, int64_t B, int64_t C, int64_t HW, cudaStream_t st);
 // Thin gathered side (channels x K <= 63) on the tensor cores, bf16 precision: see conv_tc_thin.cuh.
 bool tc_thin_backward_ok(int64_t CH, int64_t K, int64_t N, int64_t npix);
 size_t tc_thin_backward_workspace(int64_t B, int64_t CH, int64_t K, int64_t npix, bool with_dx);  // with_dx: gx is wanted

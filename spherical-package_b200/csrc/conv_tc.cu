@@ -1881,6 +1881,11 @@ namespace {
 #include "conv_tc_thin.cuh"
 }  // namespace
 
+int tc_fill_companion(const void *x, void *x_cl, int64_t B, int64_t C, int64_t HW, cudaStream_t st) {
+  to_nhwc(x, (__nv_bfloat16 *)x_cl, B, C, padded_channels(C), HW, st);
+  return launch_status();
+}
+
 bool tc_thin_backward_ok(int64_t CH, int64_t K, int64_t N, int64_t npix) { return thin_bwd_ok(CH, K, N, npix); }
 size_t tc_thin_backward_workspace(int64_t B, int64_t CH, int64_t K, int64_t npix, bool with_dx) {
   return thin_bwd_layout(B, CH, K, npix, with_dx).total;

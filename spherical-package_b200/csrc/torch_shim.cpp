@@ -571,6 +571,14 @@ torch::Tensor conv_forward_impl(torch::Tensor x, torch::Tensor map, const torch:
     // channels-last companions: gather from the input's copy if a previous layer left one; with the fused ReLU also
     // write the copy of the output for the next layer
     const void *x_cl = find_companion(x);
+    if (x_cl == nullptr && a.Cin * a.K > 63 && x.numel() > 0) {
+      // no previous layer left a copy of this input (the reference's own composition: convolution, then a separate
+      // activation): convert it once here, for this call and for the weight gradient in backward
+      torch::Tensor cl = torch::empty({(int64_t)sph_conv_companion_bytes(a.B, a.Cin, a.IH, a.IW)}, x.options().dtype(torch::kUInt8));
+      ok(sph_conv_companion_fill(x.data_ptr(), cl.data_ptr(), a.B, a.Cin, a.IH, a.IW, stream()), "sph_conv_companion_fill");
+      register_companion(x, cl);
+      x_cl = cl.data_ptr();
+    }
     torch::Tensor out_cl;
     if (relu && a.Cout % 8 == 0) out_cl = new_companion(x, a.B, a.Cout, a.OH, a.OW);
     if (x_cl != nullptr || out_cl.defined()) {

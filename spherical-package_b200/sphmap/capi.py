@@ -31,7 +31,7 @@ SYMBOLS = [
     "sph_device_status", "sph_debug_bounded_wait", "sph_mapped_max_unpool_planned", "sph_mapped_avg_pool",
     "sph_mapped_avg_unpool", "sph_resample_to_map_normalized", "sph_resample_from_uv_maps", "sph_plan_build_uv",
     "sph_voting_resample_to_map", "sph_build_kernel_map", "sph_build_is_checked", "sph_conv_companion_bytes",
-    "sph_conv_companion_channels", "sph_trace_phases", "sph_mapped_conv_forward_cl", "sph_mapped_conv_backward_cl",
+    "sph_conv_companion_channels", "sph_conv_companion_fill", "sph_trace_phases", "sph_mapped_conv_forward_cl", "sph_mapped_conv_backward_cl",
 ]
 ERR_UNSUPPORTED = 2
 
@@ -380,6 +380,14 @@ def companion(B, C, H, W, device):
     if n == 0:
         raise SphError("sph_conv_companion_bytes: bad shape")
     return torch.zeros(n, dtype=torch.uint8, device=device)
+
+
+def companion_of(x):
+    """Channels-last bf16 companion of an existing float32 activation (B, C, H, W), converted now."""
+    B, C, H, W = x.shape
+    cl = torch.empty(lib.sph_conv_companion_bytes(*_ints(B, C, H, W)), dtype=torch.uint8, device=x.device)
+    _ok(lib.sph_conv_companion_fill(_ptr(x), _ptr(cl), *_ints(B, C, H, W), _stream()), "sph_conv_companion_fill")
+    return cl
 
 
 def conv_forward_cl(x, x_cl, smap, weight, bias, K, interp, iw=None, precision=BF16, relu=False, out=None, out_cl=None, ws=None):

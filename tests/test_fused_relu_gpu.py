@@ -266,3 +266,42 @@ def test_layer_stack_with_and_without_companion_cache():
     finally:
         ext.set_companions(True)
         ext.set_precision(old)
+
+
+def test_unfused_composition_converts_an_input_once():
+    """The reference's own composition (convolution, then a separate torch.relu) in bf16 precision: no layer leaves a
+    channels-last copy for the next one, so the host extension converts a layer's input once in forward and keeps the
+    copy for the weight gradient in backward.  Results and gradients equal the run with the cache off bit for bit, and
+    sph_conv_companion_fill writes what a fused forward would have written."""
+    import _spherical_distortion_ext as ext
+    from spherical_distortion.nn import InterpolationType, MappedConvolution
+    from sphmap import capi, workloads as wl
+    old = ext.get_precision()
+    ext.set_precision("bf16")
+    try:
+        g = torch.Generator().manual_seed(78)
+        x = torch.rand(2, 3, 32, 64, generator=g).cuda().requires_grad_(True)
+        m1, m2 = wl.gnomonic_map(32, 64, 2).cuda(), wl.gnomonic_map(16, 32, 1).cuda()
+        l1 = MappedConvolution(3, 64, 9, InterpolationType.BILINEAR).cuda()
+        l2 = MappedConvolution(64, 96, 9, InterpolationType.BILINEAR).cuda()
+        go = torch.randn(2, 96, 16, 32, generator=g).cuda()
+        runs = []
+        for on in (False, True):
+            ext.set_companions(on)
+            for p in list(l1.parameters()) + list(l2.parameters()) + [x]:
+                p.grad = None
+            y = l2(torch.relu(l1(x, m1)), m2)
+            y.backward(go)
+            runs.append([y.detach().clone(), x.grad.clone()] + [p.grad.clone() for p in list(l1.parameters()) + list(l2.parameters())])
+        for a, b in zip(runs[0], runs[1]):
+            assert torch.equal(a, b)
+    finally:
+        ext.set_companions(True)
+        ext.set_precision(old)
+    # the entry point itself: the same bytes as the copy a fused forward writes beside its output
+    xa = torch.rand(2, 16, 8, 16, generator=torch.Generator().manual_seed(5)).cuda()
+    ma = wl.gnomonic_map(8, 16, 1).cuda()
+    wa, ba = (torch.randn(64, 16, 9) / 12).cuda(), torch.zeros(64).cuda()
+    cl = capi.companion(2, 64, 8, 16, "cuda")
+    out = capi.conv_forward_cl(xa, None, ma, wa, ba, 9, 1, None, capi.BF16, True, out_cl=cl)
+    assert torch.equal(capi.companion_of(out), cl)
