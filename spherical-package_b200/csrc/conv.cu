@@ -68,8 +68,8 @@ size_t base_workspace(int op, int64_t B, int64_t Cin, int64_t Cout, int64_t IH, 
   if (precision == SPH_PRECISION_BF16) return tc_workspace_bytes(op, B, Cin, Cout, IH, IW, OH, OW, K, P, interp);
   switch (op) {
     case SPH_CONV_FORWARD: return simt_gemm_workspace(Cout, Cin, K, ts);
-    case SPH_CONV_BACKWARD_INPUT: return simt_gemm_workspace(Cin, Cout, K, ts);
-    case SPH_TCONV_FORWARD: return simt_gemm_workspace(Cout, Cin, K, ts);
+    case SPH_CONV_BACKWARD_INPUT: return simt_adjoint_workspace(B, Cin, Cout, K, OH * OW, IH * IW, ts);
+    case SPH_TCONV_FORWARD: return simt_adjoint_workspace(B, Cout, Cin, K, IH * IW, OH * OW, ts);
     case SPH_TCONV_BACKWARD_INPUT: return simt_gemm_workspace(Cin, Cout, K, ts);
     case SPH_CONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, OH * OW, Cout, Cin, K, Cout, ts);
     case SPH_TCONV_BACKWARD_WEIGHT: return simt_dw_workspace(B, IH * IW, Cin, Cout, K, Cout, ts);

@@ -35,6 +35,8 @@ int simt_gemm(bool use_plan, const void *src, const void *map, const void *iw, c
               size_t ws_bytes = 0);
 // scratch simt_gemm can use (optional: a transposed copy of the weights for coalesced reads)
 size_t simt_gemm_workspace(int64_t M, int64_t CH, int64_t K, size_t ts);
+// the same for plan-mode (adjoint) calls: n_src source and n_dst destination pixels (may select the multiply-first form)
+size_t simt_adjoint_workspace(int64_t B, int64_t M, int64_t CH, int64_t K, int64_t n_src, int64_t n_dst, size_t ts);
 template <typename T>
 int simt_dw(const void *A, const void *src, const void *map, const void *iw, int64_t CH, int64_t SH, int64_t SW, int64_t K,
             int64_t P, int64_t npix, int interp, int64_t M, int64_t B, void *gw, int64_t sm, int64_t sc, int64_t sk,

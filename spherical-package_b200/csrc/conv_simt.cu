@@ -21,7 +21,8 @@
 
 namespace sph {
 
-constexpr int COL_PLAN = 3;  // column source: scatter plan (modes 0..2 are the interpolation types)
+constexpr int COL_PLAN = 3;   // column source: scatter plan (modes 0..2 are the interpolation types)
+constexpr int COL_IDENT = 4;  // the pixel itself (K = 1): a dense product over the source grid
 
 template <typename T> struct ColSrc {
   const T *src;      // (B, CH, SH*SW) tensor the columns are gathered from
@@ -34,6 +35,7 @@ template <typename T> struct ColSrc {
 template <typename T, int MODE, bool WEIGHTED>
 __device__ __forceinline__ T col_value(const ColSrc<T> &s, const PlanView<T> &pv, const T *__restrict__ plane, int k,
                                        int pix) {
+  if (MODE == COL_IDENT) return __ldg(plane + pix);
   if (MODE == COL_PLAN) {
     const int key = pix * s.K + k;
     const int e0 = __ldg(pv.offsets + key), e1 = __ldg(pv.offsets + key + 1);
@@ -46,7 +48,7 @@ __device__ __forceinline__ T col_value(const ColSrc<T> &s, const PlanView<T> &pv
   } else {
     const int PP = WEIGHTED ? s.P : 1;
     const size_t e = ((size_t)pix * s.K + k) * PP;
-    return gather_slot<T, MODE == COL_PLAN ? 0 : MODE, WEIGHTED>(plane, s.map + 2 * e, s.iw + e, s.P, s.SH, s.SW);
+    return gather_slot<T, MODE >= COL_PLAN ? 0 : MODE, WEIGHTED>(plane, s.map + 2 * e, s.iw + e, s.P, s.SH, s.SW);
   }
 }
 
@@ -164,6 +166,14 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
       }
       wreg[i] = v;
     }
+    if constexpr (MODE == COL_IDENT) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int ch = kk0 + half * 8 + j;
+        creg[j] = (pix_ok && ch < CHK) ? __ldg(img + (size_t)ch * shw + pix) : 0.0f;
+      }
+      return;
+    }
     if constexpr (MODE == COL_PLAN) {
       // the eight columns are consecutive channels; when they share their slot, the slot's plan entries are read once
       const int kk_first = kk0 + half * 8, k = kk_first / cs.CH, ch0 = kk_first - k * cs.CH;
@@ -206,10 +216,10 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
       if (pix_ok && kk_first + 8 <= CHK && ch0 + 8 <= cs.CH) {
         Taps<float> t8;
         const float *mp = cs.map + 2 * ((size_t)pix * cs.K + k);
-        decode<float, MODE == COL_PLAN ? 0 : MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t8);
+        decode<float, MODE >= COL_PLAN ? 0 : MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t8);
         const float *plane0 = img + (size_t)ch0 * shw;
 #pragma unroll
-        for (int j = 0; j < 8; j++) creg[j] = gather<float, MODE == COL_PLAN ? 0 : MODE>(plane0 + (size_t)j * shw, t8);
+        for (int j = 0; j < 8; j++) creg[j] = gather<float, MODE >= COL_PLAN ? 0 : MODE>(plane0 + (size_t)j * shw, t8);
         return;
       }
     }
@@ -224,11 +234,11 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
         for (int j = 0; j < 8; j++) creg[j] = 0.0f;
         for (int q = 0; q < cs.P; q++) {
           Taps<float> tq;
-          decode<float, MODE == COL_PLAN ? 0 : MODE>(__ldg(cs.map + 2 * (e + q)), __ldg(cs.map + 2 * (e + q) + 1), cs.SH, cs.SW, tq);
+          decode<float, MODE >= COL_PLAN ? 0 : MODE>(__ldg(cs.map + 2 * (e + q)), __ldg(cs.map + 2 * (e + q) + 1), cs.SH, cs.SW, tq);
           const float wq = __ldg(cs.iw + e + q);
 #pragma unroll
           for (int j = 0; j < 8; j++)
-            creg[j] = __fadd_rn(creg[j], __fmul_rn(wq, gather<float, MODE == COL_PLAN ? 0 : MODE>(plane0 + (size_t)j * shw, tq)));
+            creg[j] = __fadd_rn(creg[j], __fmul_rn(wq, gather<float, MODE >= COL_PLAN ? 0 : MODE>(plane0 + (size_t)j * shw, tq)));
         }
         return;
       }
@@ -245,10 +255,10 @@ conv_gemm128_kernel(ColSrc<float> cs, const float *__restrict__ wgt, int64_t sm,
         if constexpr (MODE != COL_PLAN && !WEIGHTED) {
           if (k != cur_k) {
             const float *mp = cs.map + 2 * ((size_t)pix * cs.K + k);
-            decode<float, MODE == COL_PLAN ? 0 : MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t);
+            decode<float, MODE >= COL_PLAN ? 0 : MODE>(__ldg(mp), __ldg(mp + 1), cs.SH, cs.SW, t);
             cur_k = k;
           }
-          v = gather<float, MODE == COL_PLAN ? 0 : MODE>(plane, t);
+          v = gather<float, MODE >= COL_PLAN ? 0 : MODE>(plane, t);
         } else {
           v = col_value<float, MODE, WEIGHTED>(cs, pv, plane, k, pix);
         }
@@ -691,6 +701,66 @@ __global__ void weight_transpose_kernel(const float *__restrict__ w, float *__re
   wt[i] = w[m * sm + ch * sc + k * sk];
 }
 
+size_t simt_gemm_workspace(int64_t M, int64_t CH, int64_t K, size_t ts);
+
+// ---- multiply-first adjoint (float32) --------------------------------------------------------------------------
+// When the destination grid of an adjoint is several times larger than its source grid (a down-sampling map), the
+// gather form repeats the channel contraction for every destination pixel, most of whose (pixel, slot) keys are
+// empty.  Contract first on the source grid - T[b][k*M + m][p] = sum_ch W[m, ch, k] src[b, ch, p], a dense product
+// with the large-tile kernel - then gather planes of T through the plan (the reference's own order: GEMM, then
+// mapped_col2im, src/cpp/mapped_convolution_layer.cpp:69-86).
+// wt[ch][k*M + m] = w[m*sm + ch*sc + k*sk]: the transposed weight copy the dense product reads
+__global__ void premul_weight_transpose_kernel(const float *__restrict__ w, float *__restrict__ wt, int M, int CH, int K, int64_t sm,
+                                               int64_t sc, int64_t sk) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= M * CH * K) return;
+  const int mm = i % (K * M), ch = i / (K * M), k = mm / M, m = mm - k * M;
+  wt[i] = w[m * sm + ch * sc + k * sk];
+}
+
+// out[b][m][q] (+bias) = sum over the plan entries (p, k, w) of destination pixel q, in plan order, of w * T[b][k*M + m][p].
+// Thread = destination pixel x 8 output rows: neighbouring pixels read neighbouring words of the same planes.
+__global__ void __launch_bounds__(128) plan_gather_planes_kernel(const float *__restrict__ T, const void *__restrict__ plan_blob,
+                                                                 const float *__restrict__ bias, float *__restrict__ out, int K, int M,
+                                                                 int n_src, int n_dst) {
+  const int q = blockIdx.x * blockDim.x + threadIdx.x, m0 = blockIdx.y * 8, b = blockIdx.z;
+  if (q >= n_dst) return;
+  bool ok;
+  const PlanView<float> pv = plan_view<float>(plan_blob, n_dst * K, ok);
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) acc[j] = 0.0f;
+  if (ok) {
+    int e1 = __ldg(pv.offsets + (size_t)q * K);
+    for (int k = 0; k < K; k++) {
+      const int e0 = e1;
+      e1 = __ldg(pv.offsets + (size_t)q * K + k + 1);
+      const float *tk = T + ((size_t)b * K * M + (size_t)k * M + m0) * n_src;
+      for (int e = e0; e < e1; e++) {
+        const int sp = __ldg(pv.src + e);
+        if (!index_ok(sp, pv.n_src)) continue;
+        const float w = __ldg(pv.w + e);
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+          if (m0 + j < M) acc[j] = fmaf(w, __ldg(tk + (size_t)j * n_src + sp), acc[j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++)
+    if (m0 + j < M) out[((size_t)b * M + m0 + j) * n_dst + q] = acc[j] + (bias ? __ldg(bias + m0 + j) : 0.0f);
+}
+
+static bool premul_applies(int64_t M, int64_t CH, int64_t K, int64_t n_src, int64_t n_dst, int64_t B) {
+  return n_dst >= 3 * n_src && K * M >= 48 && CH >= 16 && (size_t)(B * K * M * n_src) * 4 <= ((size_t)8 << 30);
+}
+
+size_t simt_adjoint_workspace(int64_t B, int64_t M, int64_t CH, int64_t K, int64_t n_src, int64_t n_dst, size_t ts) {
+  if (ts == 4 && premul_applies(M, CH, K, n_src, n_dst, B))
+    return align_up((size_t)(M * CH * K) * 4, 256) + align_up((size_t)(B * K * M * n_src) * 4, 256);
+  return simt_gemm_workspace(M, CH, K, ts);
+}
+
 size_t simt_gemm_workspace(int64_t M, int64_t CH, int64_t K, size_t ts) {
   return (ts == 4 && M >= 48) ? align_up((size_t)(M * CH * K) * 4, 256) : 0;
 }
@@ -726,6 +796,24 @@ int simt_gemm(bool use_plan, const void *src, const void *map, const void *iw, c
               int64_t SW, int64_t K, int64_t P, int64_t npix, int interp, const void *wgt, int64_t sm, int64_t sc,
               int64_t sk, const void *bias, void *out, int64_t M, int64_t B, cudaStream_t st, void *ws, size_t ws_bytes) {
   ColSrc<T> cs{(const T *)src, (const T *)map, (const T *)iw, plan, (int)CH, (int)SH, (int)SW, (int)K, (int)P, (int)npix};
+  if constexpr (sizeof(T) == 4) {
+    const int64_t n_src = SH * SW;
+    if (use_plan && premul_applies(M, CH, K, n_src, npix, B) && ws != nullptr && (((uintptr_t)ws) & 15) == 0 &&
+        ws_bytes >= simt_adjoint_workspace(B, M, CH, K, n_src, npix, 4)) {
+      float *wt = (float *)ws, *Tb = (float *)((char *)ws + align_up((size_t)(M * CH * K) * 4, 256));
+      premul_weight_transpose_kernel<<<cdiv(M * CH * K, 256), 256, 0, st>>>((const float *)wgt, wt, (int)M, (int)CH, (int)K, sm, sc, sk);
+      ColSrc<float> ci{(const float *)src, nullptr, nullptr, nullptr, (int)CH, (int)SH, (int)SW, 1, 0, (int)n_src};
+      const int MM = (int)(K * M);
+      if (MM % 128 > 0 && MM % 128 <= 64) {
+        conv_gemm128_kernel<COL_IDENT, false, 4><<<dim3(cdiv(n_src, GN), cdiv(MM, 64), (unsigned)B), 256, 0, st>>>(ci, nullptr, 0, 0, 0, nullptr, Tb, MM, wt);
+      } else {
+        conv_gemm128_kernel<COL_IDENT, false, 8><<<dim3(cdiv(n_src, GN), cdiv(MM, GM), (unsigned)B), 256, 0, st>>>(ci, nullptr, 0, 0, 0, nullptr, Tb, MM, wt);
+      }
+      plan_gather_planes_kernel<<<dim3(cdiv(npix, 128), cdiv(M, 8), (unsigned)B), 128, 0, st>>>(Tb, plan, (const float *)bias, (float *)out,
+                                                                                              (int)K, (int)M, (int)n_src, (int)npix);
+      return launch_status(3);
+    }
+  }
   if (use_plan) {
     launch_gemm<T, COL_PLAN, false>(cs, (const T *)wgt, sm, sc, sk, (const T *)bias, (T *)out, (int)M, (int)B, st, ws, ws_bytes);
   } else {
