@@ -293,8 +293,14 @@ def run_encoder(args, rank, local, world):
     # gathered side has <= 32 (channel, slot) columns run the thin-contraction kernels (one operand block per tile on the
     # tensor cores in bf16 precision), the others the two general tcgen05 kernels (forward-type gather-GEMM for forward
     # and dInput, weight-gradient kernel for dW).
+    exact = args.precision != "bf16"
+
     def kernel_of(li, ph):
         ci = cfg["layers"][li][0]
+        if exact:   # the exact float32 path: thin register-tiled kernels for layer 1, large-tile SIMT kernels for the rest
+            if ci * 9 <= 32:
+                return "small_%s (SIMT, thin contraction)" % ph
+            return "conv_dw128_kernel" if ph == "dw" else "conv_gemm128_kernel"
         if ci * 9 <= 32:
             return {"fwd": "tc_thin_fwd_kernel", "bwd.main": "tc_thin_bwd_kernel (dW, dBias, column buffer of dInput)",
                     "bwd.gather": "thin_plan_gather_kernel (dInput)", "bwd.prepass": "thin_wt_image_kernel",
@@ -316,6 +322,10 @@ def run_encoder(args, rank, local, world):
     dom_kernel = max(groups, key=lambda k: groups[k][0])
     dom_ms, dom_flops_total, dom_n = groups[dom_kernel]
     tensor_peak = peaks["bf16_tflops_sustained"]
+    peak_source = peaks["source"] + " bf16 sustained (kernel timed inside a long step)"
+    if exact:   # no measured float32 figure exists: nominal FMA rate of the CUDA cores at the maximum SM clock
+        tensor_peak = round(148 * 128 * 2 * 1.965e9 / 1e12, 1)
+        peak_source = "nominal float32 FMA rate, 148 SMs x 128 lanes x 2 x 1.965 GHz (no measured figure)"
     achieved = dom_flops_total / (dom_ms * 1e-3) / 1e12
     out = {
         "metric": "mapped-conv fwd+bwd TFLOP/s", "value": round(value, 3), "unit": "TFLOP/s", "n_gpus": world,
@@ -336,7 +346,7 @@ def run_encoder(args, rank, local, world):
                         "d2h_bytes_per_step": 4 * world, "ms_per_step": round(e2e["e2e_unfused"][0] / args.steps, 3),
                         "api": "spherical_distortion.nn.MappedConvolution + torch.relu + autograd (the reference's API, no fused activation)"},
         "gpu_launches": int(launches_per_step * args.steps),
-        "roofline": {"bound": "tensor", "kernel": dom_kernel, "launches_per_step": dom_n,
+        "roofline": {"bound": "fp32" if exact else "tensor", "kernel": dom_kernel, "launches_per_step": dom_n,
                      "avg_launch_ms": round(dom_ms / dom_n, 3),
                      "algorithmic_gflop_per_launch": round(dom_flops_total / dom_n / 1e9, 1),
                      "share_of_conv_time": round(dom_ms / sum(per_launch.values()), 3),
@@ -344,9 +354,9 @@ def run_encoder(args, rank, local, world):
                      "frac": round(achieved / tensor_peak, 4),
                      # DRAM read+write of this kernel's layer-4 forward launch: 156.8 MB in an ncu capture at batch 4,
                      # scaled by local batch / 4 (activations in, activations out: proportional to the batch)
-                     "traffic": int(156.8e6 * (hi - lo) / 4),
+                     "traffic": None if exact else int(156.8e6 * (hi - lo) / 4),
                      "traffic_of": "layer-4 forward launch; constant from an ncu capture at batch 4 scaled by the batch, not measured in this run",
-                     "peak_source": peaks["source"] + " bf16 sustained (kernel timed inside a long step)",
+                     "peak_source": peak_source,
                      "per_launch_ms": {"L%d.%s" % (k[0] + 1, k[1]): round(v, 3) for k, v in per_launch.items()}},
         "clocks": clocks,
     }
