@@ -303,11 +303,13 @@ def conv_backward_input(go, plan, weight, IH, IW, K, precision=EXACT, out=None, 
     return out
 
 
-def conv_backward_weight(go, x, smap, K, interp, iw=None, precision=EXACT, ws=None):
+def conv_backward_weight(go, x, smap, K, interp, iw=None, precision=EXACT, ws=None, gw=None, gb=None):
     B, Cin, IH, IW = x.shape
     _, Cout, OH, OW = go.shape
-    gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
-    gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
+    if gw is None:
+        gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
+    if gb is None:
+        gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
     if ws is None:
         ws = conv_workspace(CONV_BACKWARD_WEIGHT, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
     _ok(lib.sph_mapped_conv_backward_weight(_ptr(go), _ptr(x), _ptr(smap), _ptr(iw), _ptr(gw), _ptr(gb),
@@ -356,11 +358,14 @@ def conv_relu_backward_input(go, act_out, plan, weight, IH, IW, K, precision=EXA
     return out
 
 
-def conv_relu_backward_weight(go, act_out, x, smap, K, interp, iw=None, precision=EXACT, ws=None, fallback=True):
+def conv_relu_backward_weight(go, act_out, x, smap, K, interp, iw=None, precision=EXACT, ws=None, fallback=True, gw=None,
+                              gb=None):
     B, Cin, IH, IW = x.shape
     _, Cout, OH, OW = go.shape
-    gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
-    gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
+    if gw is None:
+        gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
+    if gb is None:
+        gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
     if ws is None:
         ws = conv_workspace(CONV_BACKWARD_WEIGHT, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
     rc = lib.sph_mapped_conv_relu_backward_weight(_ptr(go), _ptr(act_out), _ptr(x), _ptr(smap), _ptr(iw), _ptr(gw), _ptr(gb),
@@ -369,7 +374,8 @@ def conv_relu_backward_weight(go, act_out, x, smap, K, interp, iw=None, precisio
     if rc == ERR_UNSUPPORTED:
         if not fallback:
             raise Unsupported("sph_mapped_conv_relu_backward_weight")
-        return conv_backward_weight(torch.ops.aten.threshold_backward(go, act_out, 0), x, smap, K, interp, iw, precision, ws)
+        return conv_backward_weight(torch.ops.aten.threshold_backward(go, act_out, 0), x, smap, K, interp, iw, precision, ws,
+                                    gw, gb)
     _ok(rc, "sph_mapped_conv_relu_backward_weight")
     return gw, gb
 
@@ -417,15 +423,18 @@ def trace_phases(events):
     _ok(lib.sph_trace_phases(arr, _int(len(events))), "sph_trace_phases")
 
 
-def conv_backward_cl(go, act_out, x, x_cl, plan, smap, weight, K, interp, iw=None, precision=BF16, gx=None, ws=None):
+def conv_backward_cl(go, act_out, x, x_cl, plan, smap, weight, K, interp, iw=None, precision=BF16, gx=None, ws=None,
+                     gw=None, gb=None):
     """(grad_input, grad_weight, grad_bias) in one call; act_out (or None) masks grad_output (fused ReLU), x_cl (or
     None) is the companion of x.  Raises Unsupported for shapes that use the separate entry points."""
     B, Cin, IH, IW = x.shape
     _, Cout, OH, OW = go.shape
     if gx is None:
         gx = torch.empty_like(x)
-    gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
-    gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
+    if gw is None:
+        gw = torch.empty(Cout, Cin, K, dtype=x.dtype, device=x.device)
+    if gb is None:
+        gb = torch.empty(Cout, dtype=x.dtype, device=x.device)
     if ws is None:
         ws = conv_workspace(CONV_BACKWARD, B, Cin, Cout, IH, IW, OH, OW, K, _P(iw), _dt(x), interp, precision, x)
     rc = lib.sph_mapped_conv_backward_cl(_ptr(go), _ptr(act_out), _ptr(x), _ptr(x_cl), _ptr(plan), _ptr(smap), _ptr(iw),

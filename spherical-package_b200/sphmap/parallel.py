@@ -19,15 +19,33 @@ def shard_batch(B, rank, world):
 
 
 class GradReducer:
-    """Sum-allreduce of per-layer (dW, dBias), flattened into one message per layer, asynchronously."""
+    """Sum-allreduce of per-layer (dW, dBias), one message per layer, asynchronously.
+
+    Gradients allocated with `buffers()` are two views of one flat tensor, which is reduced in place with no
+    packing or unpacking; any other pair is packed into a temporary and copied back in `finish()`."""
 
     def __init__(self, group=None):
         self.group = group
         self.pending = []
+        self.flats = {}
         self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+
+    def buffers(self, w_shape, b_shape, dtype, device):
+        """(gw, gb) of the given shapes, adjacent in one flat allocation that `submit` reduces directly."""
+        nw = int(torch.Size(w_shape).numel())
+        nb = int(torch.Size(b_shape).numel())
+        flat = torch.empty(nw + nb, dtype=dtype, device=device)
+        gw, gb = flat[:nw].view(w_shape), flat[nw:].view(b_shape)
+        self.flats[(gw.data_ptr(), gb.data_ptr())] = flat
+        return gw, gb
 
     def submit(self, gw, gb):
         if not self.enabled:
+            return
+        flat = self.flats.get((gw.data_ptr(), gb.data_ptr()))
+        if flat is not None and flat.numel() == gw.numel() + gb.numel():
+            work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            self.pending.append((work, None, gw, gb))
             return
         flat = torch.cat([gw.reshape(-1), gb.reshape(-1)])
         work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
@@ -36,8 +54,9 @@ class GradReducer:
     def finish(self):
         for work, flat, gw, gb in self.pending:
             work.wait()
-            gw.copy_(flat[:gw.numel()].view_as(gw))
-            gb.copy_(flat[gw.numel():].view_as(gb))
+            if flat is not None:
+                gw.copy_(flat[:gw.numel()].view_as(gw))
+                gb.copy_(flat[gw.numel():].view_as(gb))
         self.pending = []
 
 
@@ -82,7 +101,15 @@ class EncoderStack:
                 self.ws[(li, op)] = capi.conv_workspace(op, local_batch, ci, co, ih, iw, oh, ow, self.K, 0, capi.F32,
                                                         self.interp, precision, self.w[li])
         self.gx = [torch.empty(local_batch, ci, ih, iw, **f32) for ci, co, (ih, iw), _, _ in self.layers]
-        self.gw, self.gb = [None] * 4, [None] * 4
+        # weight and bias gradients live in fixed buffers (one flat allocation per layer when a reducer owns them)
+        self.gw, self.gb = [], []
+        for ci, co, _, _, _ in self.layers:
+            if reducer is not None:
+                gw, gb = reducer.buffers((co, ci, self.K), (co,), torch.float32, device)
+            else:
+                gw, gb = torch.empty(co, ci, self.K, **f32), torch.empty(co, **f32)
+            self.gw.append(gw)
+            self.gb.append(gb)
 
     def _timed(self, key, fn):
         if self.timers is not None and key in self.timers:
@@ -133,8 +160,7 @@ class EncoderStack:
                         self.timed_keys.add((li, "bwd.phases"))
                     gx, gw, gb = self._timed((li, "bwd"), lambda: c.conv_backward_cl(
                         g, self.acts[li], self.inputs[li], x_cl, self.plans[li], self.maps[li], self.w[li], self.K, self.interp,
-                        None, self.prec, gx=self.gx[li], ws=self.ws[(li, c.CONV_BACKWARD)]))
-                    self.gw[li], self.gb[li] = gw, gb
+                        None, self.prec, gx=self.gx[li], ws=self.ws[(li, c.CONV_BACKWARD)], gw=self.gw[li], gb=self.gb[li]))
                     if self.reducer is not None:
                         self.reducer.submit(gw, gb)
                     g = gx
@@ -145,15 +171,14 @@ class EncoderStack:
                 try:
                     gw, gb = self._timed((li, "dw"), lambda: c.conv_relu_backward_weight(
                         g, self.acts[li], self.inputs[li], self.maps[li], self.K, self.interp, None, self.prec,
-                        ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)], fallback=False))
+                        ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)], fallback=False, gw=self.gw[li], gb=self.gb[li]))
                 except c.Unsupported:
                     self.fused_bwd[li] = False
             if not self.fused_bwd[li]:
                 g = torch.ops.aten.threshold_backward(g, self.acts[li], 0)   # ReLU backward on the rectified activations
                 gw, gb = self._timed((li, "dw"), lambda: c.conv_backward_weight(
                     g, self.inputs[li], self.maps[li], self.K, self.interp, None, self.prec,
-                    ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)]))
-            self.gw[li], self.gb[li] = gw, gb
+                    ws=self.ws[(li, c.CONV_BACKWARD_WEIGHT)], gw=self.gw[li], gb=self.gb[li]))
             if self.reducer is not None:
                 self.reducer.submit(gw, gb)
             if self.fused_bwd[li]:

@@ -43,6 +43,15 @@ def _worker(rank, world, port, out):
         layers.append((gw, gb, scale))
     red.finish()
     ok = all(torch.equal(gw, per_image_gw.sum(0) * s) and torch.equal(gb, per_image_gb.sum(0) * s) for gw, gb, s in layers)
+    # the same through the reducer's own buffers: the flat allocation behind (gw, gb) is reduced where it lies
+    gw, gb = red.buffers((3, 2, 2), (3,), torch.float32, "cpu")
+    for scale in (1.0, 3.0):       # the buffers are reused from step to step
+        gw.copy_(per_image_gw[lo:hi].sum(0) * scale)
+        gb.copy_(per_image_gb[lo:hi].sum(0) * scale)
+        red.submit(gw, gb)
+        packed = red.pending[-1][1]
+        red.finish()
+        ok = ok and packed is None and torch.equal(gw, per_image_gw.sum(0) * scale) and torch.equal(gb, per_image_gb.sum(0) * scale)
     out[rank] = bool(ok)
     dist.destroy_process_group()
 
@@ -61,3 +70,9 @@ def test_grad_reducer_is_a_no_op_without_a_process_group():
     red.submit(gw, gb)
     red.finish()
     assert not red.enabled and torch.equal(gw, torch.ones(2, 2))
+
+
+def test_grad_reducer_buffers_are_adjacent_views_of_one_allocation():
+    gw, gb = GradReducer().buffers((4, 3, 9), (4,), torch.float32, "cpu")
+    assert gw.shape == (4, 3, 9) and gb.shape == (4,) and gw.is_contiguous() and gb.is_contiguous()
+    assert gb.data_ptr() == gw.data_ptr() + gw.numel() * 4
