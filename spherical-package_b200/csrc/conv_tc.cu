@@ -1689,7 +1689,7 @@ int tc_adjoint_premul(const PremulGeometry &q, const void *src, const void *plan
   launch_gemm<MODE_DIRECT, 1, true>(p, (int)(tiles < sm_count() ? tiles : sm_count()), g.smem, st);
   plan_gather_rows_kernel<<<dim3(cdiv(GH * GW, 128), (unsigned)B), 128, 0, st>>>(T, plan, (const float *)bias, (float *)out, (int)K,
                                                                                 (int)M, q.Mp, (int)(SH * SW), (int)(GH * GW));
-  return launch_status(4);
+  return launch_status(fz.src_cl ? 3 : 4);
 }
 
 // Out[b,n,pix] (+bias) on the tensor cores.  src is (B,CH,SH,SW) float32; the GEMM pixels are the (GH,GW) grid.
@@ -1851,7 +1851,7 @@ int tc_dw(const void *A, const void *src, const void *map, const void *iw, int64
   else launch_dw<0>(p, d.grp, false, grid, d.smem, st);
   tc_dw_reduce_kernel<<<cdiv(Nout * CH * K, 256), 256, 0, st>>>(partial, d.splits, d.mbs_total * 128, d.nchunks * kChunk, (int)Nout,
                                                                (int)CH, d.Cp, (int)K, sn, sc, sk, (float *)gw);
-  note_launches(4);
+  note_launches(2 + (fz.src_cl ? 0 : 1) + (fz.gt_ready ? 0 : 1));
   if (fuse_bias) {
     row_sum_split_kernel<<<dim3(cdiv(Cbias, 128), kRowSplits), 128, 0, st>>>(row_part, nblocks, d.mbs_total * 128, (int)Cbias, part2);
     row_sum_final_kernel<<<cdiv(Cbias, 128), 128, 0, st>>>(part2, (int)Cbias, (float *)gb);

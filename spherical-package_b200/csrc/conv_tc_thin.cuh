@@ -747,5 +747,5 @@ int tc_thin_backward(const void *gout, const void *act, const void *x, const voi
   if (do_dx)
     thin_plan_gather_kernel<kImg><<<grid, 256, 0, st>>>(p.t2, p.t2_pitch, plan, (float *)gx, (int)B, (int)CH, (int)K, (int)npix, (int)(SH * SW));
   mark_phase(3, st);
-  return launch_status(4);
+  return launch_status(1 + (do_dx ? 2 : 0) + (do_dw ? 1 : 0));
 }
