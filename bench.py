@@ -219,7 +219,7 @@ def run_encoder(args, rank, local, world):
     from spherical_distortion.nn import InterpolationType, MappedConvolution
     ext.set_precision(args.precision)
     maps = [t.to(dev) for t in cfg["maps"]]
-    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+    loss_host = [torch.empty((), dtype=torch.float32).pin_memory() for _ in range(2)]
     copy_stream = torch.cuda.Stream(device=dev)
 
     def make_e2e(fused):
@@ -241,7 +241,10 @@ def run_encoder(args, rank, local, world):
                 p.register_post_accumulate_grad_hook(lambda t: pending.append(dist.all_reduce(t.grad, async_op=True)))
         # The input batch of step i+1 is copied host->device on a side stream while step i computes (what a
         # prefetching data loader does); every step's copy and its loss read-back lie inside the timed region.
+        # The loss of step i is copied to pinned host memory at the end of step i and the host waits for it one step
+        # later (a training loop that logs its loss one step behind), so the device does not drain between steps.
         staged = {"x": None, "ev": None}
+        readback = {"i": 0, "ev": [torch.cuda.Event(), torch.cuda.Event()]}
 
         def stage_next():
             with torch.cuda.stream(copy_stream):
@@ -259,15 +262,20 @@ def run_encoder(args, rank, local, world):
             h = xb
             for m, sm in zip(mods, maps):
                 h = m(h, sm) if fused else torch.relu(m(h, sm))
-            loss = torch.dot(h.reshape(-1), go.reshape(-1))   # sum(h * go) in one pass
+            with torch.no_grad():
+                loss = torch.dot(h.reshape(-1), go.reshape(-1))   # sum(h * go) in one pass
             for p in params:
                 p.grad = None
-            loss.backward()
+            torch.autograd.backward([h], [go])   # d loss / d h is go itself: backward is seeded with it, not with go * 1.0
             for w in pending:
                 w.wait()
             pending.clear()
-            loss_host.copy_(loss.detach(), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            slot = readback["i"] & 1
+            loss_host[slot].copy_(loss, non_blocking=True)
+            readback["ev"][slot].record()
+            if readback["i"] > 0:
+                readback["ev"][slot ^ 1].synchronize()   # the previous step's loss has reached the host
+            readback["i"] += 1
 
         return e2e_step
 
@@ -341,7 +349,8 @@ def run_encoder(args, rank, local, world):
                                        / (ms * 1e-3) / 1e6, 1)},
         "e2e": {"value": round(e2e_value, 3), "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 4 * world,
                 "d2h_bytes_per_step": 4 * world, "ms_per_step": round(e2e_ms / args.steps, 3),
-                "api": "spherical_distortion.nn.MappedConvolution(activation='relu') + autograd"},
+                "api": "spherical_distortion.nn.MappedConvolution(activation='relu') + autograd",
+                "loss_readback": "every step, pinned host memory, waited for one step behind"},
         "e2e_unfused": {"value": round(e2e["e2e_unfused"][1], 3), "unit": "TFLOP/s", "h2d_bytes_per_step": x_host.numel() * 4 * world,
                         "d2h_bytes_per_step": 4 * world, "ms_per_step": round(e2e["e2e_unfused"][0] / args.steps, 3),
                         "api": "spherical_distortion.nn.MappedConvolution + torch.relu + autograd (the reference's API, no fused activation)"},
