@@ -228,6 +228,30 @@ def test_encoder_stack_with_companions_equals_without():
         assert torch.equal(a, b)
 
 
+def test_encoder_stack_writes_gradients_into_the_reducer_buffers():
+    """With a gradient reducer the stack's dW and dBias of a layer are adjacent views of one flat buffer that the
+    kernels write directly (the allreduce then runs on it in place): same values as with separately allocated
+    gradients, in both precisions."""
+    from sphmap import capi, workloads as wl
+    from sphmap.parallel import EncoderStack, GradReducer
+    cfg = wl.config4(B=2, H=64, W=128)
+    dev = torch.device("cuda")
+    x, go = cfg["x"].to(dev), cfg["grad_output"].to(dev)
+    for prec in (capi.BF16, capi.EXACT):
+        res = []
+        for red in (None, GradReducer()):
+            st = EncoderStack(cfg, dev, prec, 2, reducer=red)
+            ptrs = [t.data_ptr() for t in st.gw]
+            for _ in range(2):
+                st.step(x, go)
+            assert [t.data_ptr() for t in st.gw] == ptrs       # fixed buffers, step after step
+            if red is not None:
+                assert all(b.data_ptr() == w.data_ptr() + 4 * w.numel() for w, b in zip(st.gw, st.gb))
+            res.append([t.clone() for t in st.gw + st.gb])
+        for a, b in zip(*res):
+            assert torch.equal(a, b)
+
+
 def test_layer_stack_with_and_without_companion_cache():
     """Two stacked layers with the fused activation through the module API in bf16: with the companion cache on, the
     second layer gathers from the channels-last copy the first one left; results and gradients equal the run with the
