@@ -185,7 +185,7 @@ def run_encoder(args, rank, local, world):
             t[(li, "bwd.phases")] = ev
         return t
 
-    stack = EncoderStack(cfg, dev, prec, hi - lo, GradReducer(), None)
+    stack = EncoderStack(cfg, dev, prec, hi - lo, GradReducer(mode=args.grad_exchange), None)
     per_step_timers = []
 
     def step():
@@ -234,11 +234,20 @@ def run_encoder(args, rank, local, world):
             mods.append(m)
         params = [p for m in mods for p in (m.weight, m.bias)]
         pending = []
-        if world > 1:
+        if world > 1 and args.grad_exchange == "layer":
             # gradient exchange as a training loop does it: each parameter's gradient is sum-allreduced in place as soon
             # as autograd has produced it, overlapping the rest of backward; the step waits for all of them at the end
             for p in params:
                 p.register_post_accumulate_grad_hook(lambda t: pending.append(dist.all_reduce(t.grad, async_op=True)))
+        sizes = [p.numel() for p in params]
+
+        def exchange_bucket():
+            # --grad-exchange step: all gradients as one bucket, one allreduce at the end of backward; the parameters'
+            # .grad become views of the reduced bucket
+            flat = torch.cat([p.grad.reshape(-1) for p in params])
+            dist.all_reduce(flat)
+            for p, chunk in zip(params, flat.split(sizes)):
+                p.grad = chunk.view_as(p)
         # The input batch of step i+1 is copied host->device on a side stream while step i computes (what a
         # prefetching data loader does); every step's copy and its loss read-back lie inside the timed region.
         # The loss of step i is copied to pinned host memory at the end of step i and the host waits for it one step
@@ -270,6 +279,8 @@ def run_encoder(args, rank, local, world):
             for w in pending:
                 w.wait()
             pending.clear()
+            if world > 1 and args.grad_exchange == "step":
+                exchange_bucket()
             slot = readback["i"] & 1
             loss_host[slot].copy_(loss, non_blocking=True)
             readback["ev"][slot].record()
@@ -343,7 +354,8 @@ def run_encoder(args, rank, local, world):
         "config": {"workload": "spherical encoder stack: 4x bilinear mapped conv + ReLU on 3x3 "
                                "gnomonic maps, 3->64->128->256->256, %dx%d -> %dx%d, fwd+bwd+dW allreduce"
                                % (args.height, 2 * args.height, args.height // 4, args.height // 2),
-                   "global_batch": B, "parallelism": "batch-sharded dp%d" % world, "precision": args.precision,
+                   "global_batch": B, "parallelism": "batch-sharded dp%d" % world, "grad_exchange": args.grad_exchange,
+                   "precision": args.precision,
                    "l2": "activations (GBs per layer) exceed the 126 MB L2; no flush needed",
                    "mpix_per_s": round(B * sum(oh * ow for _, _, _, (oh, ow), _ in cfg["layers"]) * args.steps
                                        / (ms * 1e-3) / 1e6, 1)},
@@ -696,6 +708,9 @@ def main():
     ap.add_argument("--height", type=int, default=512, help="input height of the encoder stack (width = 2x)")
     ap.add_argument("--skip-e2e", action="store_true", help="encoder: only the device-resident arm (for profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    ap.add_argument("--grad-exchange", choices=("layer", "step"), default="layer",
+                    help="N > 1: allreduce dW/dBias per layer as soon as they are final (overlapped with the rest of "
+                         "backward), or as one bucket at the end of backward")
     ap.add_argument("--skip-extras", action="store_true", help="encoder: do not also time the pooling / resampling / weighted-conv workloads")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -19,16 +19,42 @@ def shard_batch(B, rank, world):
 
 
 class GradReducer:
-    """Sum-allreduce of per-layer (dW, dBias), one message per layer, asynchronously.
+    """Sum-allreduce of per-layer (dW, dBias), asynchronously.
 
-    Gradients allocated with `buffers()` are two views of one flat tensor, which is reduced in place with no
+    mode "layer": one message per layer, issued as soon as that layer's gradients are final, so that it overlaps
+    the rest of backward.  mode "step": one message for all layers at the end of backward (a single gradient bucket).
+    Gradients allocated with `buffers()` / `arena()` are views of one flat tensor, which is reduced in place with no
     packing or unpacking; any other pair is packed into a temporary and copied back in `finish()`."""
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, mode="layer"):
+        assert mode in ("layer", "step")
         self.group = group
+        self.mode = mode
         self.pending = []
         self.flats = {}
+        self._arena = None
+        self._arena_dirty = False
         self.enabled = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+
+    def arena(self, shapes, dtype, device):
+        """[(gw, gb), ...] for a list of (w_shape, b_shape): every pair adjacent, all pairs in one allocation (each
+        pair starts on a 256-byte boundary; the padding between pairs is zero)."""
+        sizes = [(int(torch.Size(w).numel()), int(torch.Size(b).numel())) for w, b in shapes]
+        esz = torch.empty(0, dtype=dtype).element_size()
+        unit = max(256 // esz, 1)
+        starts, total = [], 0
+        for nw, nb in sizes:
+            starts.append(total)
+            total += -(-(nw + nb) // unit) * unit
+        flat_all = torch.zeros(total, dtype=dtype, device=device)
+        out = []
+        for (w_shape, b_shape), (nw, nb), lo in zip(shapes, sizes, starts):
+            flat = flat_all[lo:lo + nw + nb]
+            gw, gb = flat[:nw].view(w_shape), flat[nw:].view(b_shape)
+            self.flats[(gw.data_ptr(), gb.data_ptr())] = flat
+            out.append((gw, gb))
+        self._arena = flat_all
+        return out
 
     def buffers(self, w_shape, b_shape, dtype, device):
         """(gw, gb) of the given shapes, adjacent in one flat allocation that `submit` reduces directly."""
@@ -39,11 +65,18 @@ class GradReducer:
         self.flats[(gw.data_ptr(), gb.data_ptr())] = flat
         return gw, gb
 
+    def _in_arena(self, flat):
+        a = self._arena
+        return a is not None and a.data_ptr() <= flat.data_ptr() < a.data_ptr() + a.numel() * a.element_size()
+
     def submit(self, gw, gb):
         if not self.enabled:
             return
         flat = self.flats.get((gw.data_ptr(), gb.data_ptr()))
         if flat is not None and flat.numel() == gw.numel() + gb.numel():
+            if self.mode == "step" and self._in_arena(flat):
+                self._arena_dirty = True        # reduced with the whole arena in finish()
+                return
             work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
             self.pending.append((work, None, gw, gb))
             return
@@ -52,6 +85,10 @@ class GradReducer:
         self.pending.append((work, flat, gw, gb))
 
     def finish(self):
+        if self._arena_dirty:
+            self._arena_dirty = False
+            self.pending.append((dist.all_reduce(self._arena, op=dist.ReduceOp.SUM, group=self.group, async_op=True),
+                                 None, None, None))
         for work, flat, gw, gb in self.pending:
             work.wait()
             if flat is not None:
@@ -102,14 +139,11 @@ class EncoderStack:
                                                         self.interp, precision, self.w[li])
         self.gx = [torch.empty(local_batch, ci, ih, iw, **f32) for ci, co, (ih, iw), _, _ in self.layers]
         # weight and bias gradients live in fixed buffers (one flat allocation per layer when a reducer owns them)
-        self.gw, self.gb = [], []
-        for ci, co, _, _, _ in self.layers:
-            if reducer is not None:
-                gw, gb = reducer.buffers((co, ci, self.K), (co,), torch.float32, device)
-            else:
-                gw, gb = torch.empty(co, ci, self.K, **f32), torch.empty(co, **f32)
-            self.gw.append(gw)
-            self.gb.append(gb)
+        if reducer is not None:
+            pairs = reducer.arena([((co, ci, self.K), (co,)) for ci, co, _, _, _ in self.layers], torch.float32, device)
+        else:
+            pairs = [(torch.empty(co, ci, self.K, **f32), torch.empty(co, **f32)) for ci, co, _, _, _ in self.layers]
+        self.gw, self.gb = [p[0] for p in pairs], [p[1] for p in pairs]
 
     def _timed(self, key, fn):
         if self.timers is not None and key in self.timers:

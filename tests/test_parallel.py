@@ -52,6 +52,18 @@ def _worker(rank, world, port, out):
         packed = red.pending[-1][1]
         red.finish()
         ok = ok and packed is None and torch.equal(gw, per_image_gw.sum(0) * scale) and torch.equal(gb, per_image_gb.sum(0) * scale)
+    # several layers in one arena: per layer (mode "layer") or as one message at the end of backward (mode "step")
+    for mode in ("layer", "step"):
+        red2 = GradReducer(mode=mode)
+        pairs = red2.arena([((3, 2, 2), (3,)), ((3, 2, 2), (3,))], torch.float32, "cpu")
+        for (gw, gb), scale in zip(pairs, (1.0, 2.0)):
+            gw.copy_(per_image_gw[lo:hi].sum(0) * scale)
+            gb.copy_(per_image_gb[lo:hi].sum(0) * scale)
+            red2.submit(gw, gb)
+        ok = ok and len(red2.pending) == (2 if mode == "layer" else 0)
+        red2.finish()
+        for (gw, gb), scale in zip(pairs, (1.0, 2.0)):
+            ok = ok and torch.equal(gw, per_image_gw.sum(0) * scale) and torch.equal(gb, per_image_gb.sum(0) * scale)
     out[rank] = bool(ok)
     dist.destroy_process_group()
 
@@ -76,3 +88,7 @@ def test_grad_reducer_buffers_are_adjacent_views_of_one_allocation():
     gw, gb = GradReducer().buffers((4, 3, 9), (4,), torch.float32, "cpu")
     assert gw.shape == (4, 3, 9) and gb.shape == (4,) and gw.is_contiguous() and gb.is_contiguous()
     assert gb.data_ptr() == gw.data_ptr() + gw.numel() * 4
+    pairs = GradReducer().arena([((4, 3, 9), (4,)), ((5, 4, 9), (5,))], torch.float32, "cpu")
+    for (gw, gb), (ws, bs) in zip(pairs, (((4, 3, 9), (4,)), ((5, 4, 9), (5,)))):
+        assert gw.shape == ws and gb.shape == bs and gb.data_ptr() == gw.data_ptr() + gw.numel() * 4
+        assert (gw.data_ptr() - pairs[0][0].data_ptr()) % 256 == 0
