@@ -708,9 +708,9 @@ def main():
     ap.add_argument("--height", type=int, default=512, help="input height of the encoder stack (width = 2x)")
     ap.add_argument("--skip-e2e", action="store_true", help="encoder: only the device-resident arm (for profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
-    ap.add_argument("--grad-exchange", choices=("layer", "step"), default="layer",
-                    help="N > 1: allreduce dW/dBias per layer as soon as they are final (overlapped with the rest of "
-                         "backward), or as one bucket at the end of backward")
+    ap.add_argument("--grad-exchange", choices=("layer", "step"), default="step",
+                    help="N > 1: allreduce dW/dBias as one bucket at the end of backward (default), or per layer as soon "
+                         "as they are final (overlapped with the rest of backward)")
     ap.add_argument("--skip-extras", action="store_true", help="encoder: do not also time the pooling / resampling / weighted-conv workloads")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
