@@ -4,8 +4,9 @@ Every operator of the path is independent per image and the maps, weights and
 biases are small, so the only sharded axis is the batch: each rank (one process
 per GPU) takes a contiguous slice of the batch, runs forward / backward with no
 exchange, and the single collective is the sum-allreduce of the weight and
-bias gradients (NCCL on GPUs, gloo in the CPU tests), issued per layer as soon
-as that layer's gradients are final so that it overlaps the rest of backward.
+bias gradients (NCCL on GPUs, gloo in the CPU tests): either per layer as soon
+as that layer's gradients are final, overlapping the rest of backward, or as
+one bucket at the end of backward (see GradReducer).
 """
 import torch
 import torch.distributed as dist
